@@ -1,0 +1,20 @@
+// Version and error text of the C ABI.
+
+#include "da_common.cuh"
+
+extern "C" int da_version(void) { return 100; /* 0.1.0 */ }
+
+extern "C" const char *da_error_string(int code) {
+    switch (code) {
+    case DA_OK: return "ok";
+    case DA_ERR_NULL: return "a required pointer is null";
+    case DA_ERR_SHAPE: return "a size is zero, negative or inconsistent";
+    case DA_ERR_DTYPE: return "unknown dtype code";
+    case DA_ERR_ALIGN: return "a pointer or stride breaks the required alignment";
+    case DA_ERR_UNSUPPORTED: return "shape outside what the kernels are built for";
+    case DA_ERR_WORKSPACE: return "workspace too small";
+    default: break;
+    }
+    if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
+    return "unknown error code";
+}

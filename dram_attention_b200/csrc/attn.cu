@@ -1,0 +1,444 @@
+// Decode attention of one query token over the whole slot table plus the local
+// window: split-K flash-decode with the append of the new key/value and the final
+// merge in the same launch.
+//
+// Work unit = 16 consecutive tokens (8 KiB for head_dim 128 in 16-bit types).  A
+// unit of the slot table is one contiguous block (token-major, key then value), so
+// one untiled bulk copy (TMA) brings it into shared memory; a unit of the local
+// window is gathered row by row with small bulk copies into the same layout.  Every
+// warp owns a private ring of stages with one mbarrier each, so there is no
+// CTA-wide synchronisation in the main loop.
+//
+// Arithmetic mapping: 8 lanes share a token (each owns D/8 channels, as two
+// chunks that make conflict-free 128-bit shared-memory reads), 4 tokens per warp
+// pass, all `rep` query heads of the KV head at once.  The dot products finish
+// with a 3-step shuffle tree; softmax is online in the log2 domain with float32
+// state; partial (m, l, acc) of the 4 token groups and the 4 warps are merged
+// through shuffles and shared memory, written to the workspace, and the last CTA
+// of a head (atomic ticket) merges the splits and writes the output.
+
+#include "da_common.cuh"
+
+namespace da {
+
+constexpr int kAttnWarps = 4;
+constexpr int kAttnThreads = kAttnWarps * 32;
+constexpr int kUnitTokens = 16;
+constexpr int kCounterBytes = 1024;
+constexpr int kAttnTargetCtas = 296;  // 2 per SM on 148 SMs
+constexpr int kAttnMaxSplits = 148;
+
+__host__ __device__ inline int attn_splits(int n_kv_heads) {
+    int s = kAttnTargetCtas / n_kv_heads;
+    if (s > kAttnMaxSplits) s = kAttnMaxSplits;
+    if (s < 1) s = 1;
+    return s;
+}
+
+struct AttnParams {
+    const unsigned char *q;
+    const unsigned char *prefix;
+    long long prefix_head_stride;  // elements
+    int n_prefix_tokens;
+    unsigned char *local_k, *local_v;
+    long long local_tok_stride, local_head_stride;  // elements
+    int local_capacity;
+    const unsigned char *new_k, *new_v;
+    const int32_t *start_pos_dev;
+    int start_pos_host;
+    int dram_tokens;
+    unsigned char *out;
+    float *lse_out;
+    float *partials;
+    unsigned int *counters;
+    int32_t *status;
+    float scale_log2;
+};
+
+template <typename T, int D, int REP, int STAGES>
+__global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const AttnParams p) {
+    constexpr int E = (int)sizeof(T);
+    constexpr int ROWB = D * E;                 // one key (or value) row
+    constexpr int TOKB = 2 * ROWB;              // one token: key row then value row
+    constexpr int UNITB = kUnitTokens * TOKB;   // one stage
+    constexpr int NPL = D / 8;                  // channels per lane
+    constexpr int CH = NPL / 2;                 // channels per chunk
+    constexpr int CHB = CH * E;                 // bytes per chunk
+    constexpr int PW = D + 2;                   // floats per partial row: acc[D], m, l
+    constexpr float NEG_INF = -INFINITY;
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ __align__(8) uint64_t bars[kAttnWarps][STAGES];
+    __shared__ float red[kAttnWarps][REP][PW];
+    __shared__ int sh_last;
+
+    const int h = blockIdx.y;
+    const int x = blockIdx.x;
+    const int splits = gridDim.x;
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int g = lane >> 3;  // token group inside the warp
+    const int j = lane & 7;   // channel block inside the token
+
+    // ---- position and unit range ------------------------------------------------
+    const int pos = p.start_pos_dev ? *p.start_pos_dev : p.start_pos_host;
+    int t_new = pos - p.dram_tokens;  // index of the new token in the local window
+    bool pos_ok = true;
+    if (t_new < 0 || t_new >= p.local_capacity) {
+        pos_ok = false;
+        if (tid == 0 && x == 0) atomicOr(p.status, DA_STATUS_BAD_POSITION);
+        t_new = t_new < 0 ? 0 : p.local_capacity - 1;
+    }
+    const int n_local = t_new + 1;
+    const int n_prefix = p.n_prefix_tokens;
+    const int units_prefix = (n_prefix + kUnitTokens - 1) / kUnitTokens;
+    const int units_local = (n_local + kUnitTokens - 1) / kUnitTokens;
+    const int units = units_prefix + units_local;
+    const int per_cta = (units + splits - 1) / splits;
+    const int u0 = x * per_cta;
+    const int u1 = min(units, u0 + per_cta);
+
+    unsigned char *my_stages = smem + (size_t)warp * STAGES * UNITB;
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < STAGES; ++s) mbar_init(&bars[warp][s], 1);
+    }
+    mbar_fence_init();
+    __syncthreads();
+
+    // ---- append the new key/value to the local window -----------------------------
+    if (x == 0 && warp == 0 && pos_ok) {
+        const uint4 *sk = reinterpret_cast<const uint4 *>(p.new_k + (size_t)h * ROWB);
+        const uint4 *sv = reinterpret_cast<const uint4 *>(p.new_v + (size_t)h * ROWB);
+        const size_t off = ((size_t)t_new * p.local_tok_stride + (size_t)h * p.local_head_stride) * E;
+        uint4 *dk = reinterpret_cast<uint4 *>(p.local_k + off);
+        uint4 *dv = reinterpret_cast<uint4 *>(p.local_v + off);
+        for (int i = lane; i < ROWB / 16; i += 32) {
+            dk[i] = sk[i];
+            dv[i] = sv[i];
+        }
+    }
+
+    // ---- query rows of this KV head, pre-scaled by log2(e) / sqrt(D) ----------------
+    float qr[REP][NPL];
+#pragma unroll
+    for (int r = 0; r < REP; ++r) {
+        const unsigned char *qrow = p.q + ((size_t)(h * REP + r)) * ROWB;
+        load_elems<T, CH>(qrow + j * CHB, &qr[r][0]);
+        load_elems<T, CH>(qrow + ROWB / 2 + j * CHB, &qr[r][CH]);
+#pragma unroll
+        for (int i = 0; i < NPL; ++i) qr[r][i] *= p.scale_log2;
+    }
+
+    float m[REP], l[REP], acc[REP][NPL];
+#pragma unroll
+    for (int r = 0; r < REP; ++r) {
+        m[r] = NEG_INF;
+        l[r] = 0.f;
+#pragma unroll
+        for (int i = 0; i < NPL; ++i) acc[r][i] = 0.f;
+    }
+
+    // tokens of unit u
+    auto unit_tokens = [&](int u) -> int {
+        if (u < units_prefix) return min(kUnitTokens, n_prefix - u * kUnitTokens);
+        return min(kUnitTokens, n_local - (u - units_prefix) * kUnitTokens);
+    };
+
+    // start the copies of unit u into stage s of this warp
+    auto issue = [&](int u, int s) {
+        uint64_t *bar = &bars[warp][s];
+        unsigned char *dst = my_stages + (size_t)s * UNITB;
+        const int ntok = unit_tokens(u);
+        if (u < units_prefix) {
+            if (lane == 0) {
+                const uint32_t bytes = (uint32_t)ntok * TOKB;
+                mbar_arrive_expect_tx(bar, bytes);
+                const unsigned char *src =
+                    p.prefix + ((size_t)h * p.prefix_head_stride + (size_t)u * kUnitTokens * 2 * D) * E;
+                bulk_copy_g2s(dst, src, bytes, bar);
+            }
+        } else {
+            const int t0 = (u - units_prefix) * kUnitTokens;
+            if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)ntok * TOKB);
+            __syncwarp();
+            const int tl = lane & 15;
+            const int is_v = lane >> 4;
+            if (tl < ntok) {
+                const int t = t0 + tl;
+                const unsigned char *src;
+                if (t == t_new) {
+                    src = (is_v ? p.new_v : p.new_k) + (size_t)h * ROWB;
+                } else {
+                    src = (is_v ? p.local_v : p.local_k) +
+                          ((size_t)t * p.local_tok_stride + (size_t)h * p.local_head_stride) * E;
+                }
+                bulk_copy_g2s(dst + tl * TOKB + is_v * ROWB, src, ROWB, bar);
+            }
+        }
+    };
+
+    const int span = u1 - u0 - warp;
+    const int n_my = span > 0 ? (span + kAttnWarps - 1) / kAttnWarps : 0;
+    for (int it = 0; it < STAGES && it < n_my; ++it) issue(u0 + warp + it * kAttnWarps, it);
+
+    for (int it = 0; it < n_my; ++it) {
+        const int s = it % STAGES;
+        const bool arrived = mbar_wait_bounded(&bars[warp][s], (uint32_t)((it / STAGES) & 1));
+        if (!__all_sync(DA_FULL_MASK, arrived)) {
+            if (lane == 0) atomicOr(p.status, DA_STATUS_WAIT_TIMEOUT);
+            break;
+        }
+        const int u = u0 + warp + it * kAttnWarps;
+        const int ntok = unit_tokens(u);
+        const unsigned char *sb = my_stages + (size_t)s * UNITB;
+
+        // logits (log2 domain) of 4 tokens x REP heads
+        float sc[4][REP];
+#pragma unroll
+        for (int tt = 0; tt < 4; ++tt) {
+            const unsigned char *kp = sb + (g + 4 * tt) * TOKB;
+            float kf[NPL];
+            load_elems<T, CH>(kp + j * CHB, &kf[0]);
+            load_elems<T, CH>(kp + ROWB / 2 + j * CHB, &kf[CH]);
+#pragma unroll
+            for (int r = 0; r < REP; ++r) {
+                float a = 0.f;
+#pragma unroll
+                for (int i = 0; i < NPL; ++i) a = fmaf(qr[r][i], kf[i], a);
+                sc[tt][r] = a;
+            }
+        }
+#pragma unroll
+        for (int off = 1; off <= 4; off <<= 1)
+#pragma unroll
+            for (int tt = 0; tt < 4; ++tt)
+#pragma unroll
+                for (int r = 0; r < REP; ++r) sc[tt][r] += __shfl_xor_sync(DA_FULL_MASK, sc[tt][r], off);
+#pragma unroll
+        for (int tt = 0; tt < 4; ++tt)
+            if (g + 4 * tt >= ntok) {
+#pragma unroll
+                for (int r = 0; r < REP; ++r) sc[tt][r] = NEG_INF;
+            }
+
+        // online softmax update
+#pragma unroll
+        for (int r = 0; r < REP; ++r) {
+            const float mx = fmaxf(fmaxf(sc[0][r], sc[1][r]), fmaxf(sc[2][r], sc[3][r]));
+            const float mnew = fmaxf(m[r], mx);
+            const float msafe = (mnew == NEG_INF) ? 0.f : mnew;
+            const float alpha = fast_exp2(m[r] - msafe);
+            float psum = 0.f;
+#pragma unroll
+            for (int tt = 0; tt < 4; ++tt) {
+                sc[tt][r] = fast_exp2(sc[tt][r] - msafe);
+                psum += sc[tt][r];
+            }
+            l[r] = l[r] * alpha + psum;
+            m[r] = mnew;
+#pragma unroll
+            for (int i = 0; i < NPL; ++i) acc[r][i] *= alpha;
+        }
+
+        // values
+#pragma unroll
+        for (int tt = 0; tt < 4; ++tt) {
+            if (g + 4 * tt < ntok) {
+                const unsigned char *vp = sb + (g + 4 * tt) * TOKB + ROWB;
+                float vf[NPL];
+                load_elems<T, CH>(vp + j * CHB, &vf[0]);
+                load_elems<T, CH>(vp + ROWB / 2 + j * CHB, &vf[CH]);
+#pragma unroll
+                for (int r = 0; r < REP; ++r)
+#pragma unroll
+                    for (int i = 0; i < NPL; ++i) acc[r][i] = fmaf(sc[tt][r], vf[i], acc[r][i]);
+            }
+        }
+
+        __syncwarp();
+        if (it + STAGES < n_my) issue(u0 + warp + (it + STAGES) * kAttnWarps, s);
+    }
+
+    // ---- merge the 4 token groups of the warp ---------------------------------------
+#pragma unroll
+    for (int off = 8; off <= 16; off <<= 1) {
+#pragma unroll
+        for (int r = 0; r < REP; ++r) {
+            const float mo = __shfl_xor_sync(DA_FULL_MASK, m[r], off);
+            const float lo = __shfl_xor_sync(DA_FULL_MASK, l[r], off);
+            const float mn = fmaxf(m[r], mo);
+            const float ms = (mn == NEG_INF) ? 0.f : mn;
+            const float a = fast_exp2(m[r] - ms);
+            const float b = fast_exp2(mo - ms);
+            l[r] = l[r] * a + lo * b;
+            m[r] = mn;
+#pragma unroll
+            for (int i = 0; i < NPL; ++i) {
+                const float ao = __shfl_xor_sync(DA_FULL_MASK, acc[r][i], off);
+                acc[r][i] = acc[r][i] * a + ao * b;
+            }
+        }
+    }
+    if (g == 0) {
+#pragma unroll
+        for (int r = 0; r < REP; ++r) {
+#pragma unroll
+            for (int i = 0; i < CH; ++i) {
+                red[warp][r][j * CH + i] = acc[r][i];
+                red[warp][r][D / 2 + j * CH + i] = acc[r][CH + i];
+            }
+            if (j == 0) {
+                red[warp][r][D] = m[r];
+                red[warp][r][D + 1] = l[r];
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---- merge the warps, write this CTA's partial ------------------------------------
+    float *part = p.partials + ((size_t)(h * splits + x) * REP) * PW;
+    for (int e = tid; e < REP * PW; e += kAttnThreads) {
+        const int r = e / PW;
+        const int c = e % PW;
+        float mn = NEG_INF;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) mn = fmaxf(mn, red[w][r][D]);
+        float outv;
+        if (c == D) {
+            outv = mn;
+        } else {
+            const float ms = (mn == NEG_INF) ? 0.f : mn;
+            outv = 0.f;
+#pragma unroll
+            for (int w = 0; w < kAttnWarps; ++w) outv += red[w][r][c] * fast_exp2(red[w][r][D] - ms);
+        }
+        part[e] = outv;  // c < D: weighted acc; c == D: max; c == D+1: weighted l
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned int ticket = atomicAdd(&p.counters[h], 1u);
+        sh_last = (ticket == (unsigned int)(splits - 1));
+    }
+    __syncthreads();
+    if (!sh_last) return;
+
+    // ---- last CTA of this head: merge the splits ----------------------------------------
+    __threadfence();
+    const float *hp = p.partials + ((size_t)h * splits * REP) * PW;
+    for (int e = tid; e < REP * D; e += kAttnThreads) {
+        const int r = e / D;
+        const int c = e % D;
+        float mn = NEG_INF;
+        for (int s = 0; s < splits; ++s) mn = fmaxf(mn, __ldcg(hp + ((size_t)s * REP + r) * PW + D));
+        const float ms = (mn == NEG_INF) ? 0.f : mn;
+        float a = 0.f, ll = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float *row = hp + ((size_t)s * REP + r) * PW;
+            const float w = fast_exp2(__ldcg(row + D) - ms);
+            a = fmaf(__ldcg(row + c), w, a);
+            ll = fmaf(__ldcg(row + D + 1), w, ll);
+        }
+        const float o = ll > 0.f ? a / ll : 0.f;
+        reinterpret_cast<T *>(p.out)[(size_t)(h * REP + r) * D + c] = from_float<T>(o);
+        if (c == 0 && p.lse_out) p.lse_out[h * REP + r] = (ms + log2f(ll)) * 0.6931471805599453f;
+    }
+    if (tid == 0) p.counters[h] = 0u;
+}
+
+template <typename T, int D, int REP>
+static cudaError_t launch_attn(const AttnParams &p, int n_kv_heads, cudaStream_t stream) {
+    constexpr int UNITB = kUnitTokens * 2 * D * (int)sizeof(T);
+    constexpr int STAGES = UNITB >= 16384 ? 2 : (UNITB >= 8192 ? 3 : 4);
+    constexpr int SMEM = kAttnWarps * STAGES * UNITB;
+    auto kern = decode_attention_kernel<T, D, REP, STAGES>;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!attr_set[dev]) {
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    dim3 grid(attn_splits(n_kv_heads), n_kv_heads);
+    kern<<<grid, kAttnThreads, SMEM, stream>>>(p);
+    return cudaGetLastError();
+}
+
+template <typename T>
+static cudaError_t dispatch_attn(const AttnParams &p, int n_kv_heads, int rep, int head_dim, cudaStream_t s) {
+#define DA_ATTN_CASE(DD, RR) \
+    if (head_dim == DD && rep == RR) return launch_attn<T, DD, RR>(p, n_kv_heads, s);
+    DA_ATTN_CASE(128, 1) DA_ATTN_CASE(128, 2) DA_ATTN_CASE(128, 4) DA_ATTN_CASE(128, 8)
+    DA_ATTN_CASE(64, 1) DA_ATTN_CASE(64, 2) DA_ATTN_CASE(64, 4) DA_ATTN_CASE(64, 8)
+#undef DA_ATTN_CASE
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace da
+
+extern "C" size_t da_decode_attention_workspace_bytes(int n_kv_heads, int rep, int head_dim) {
+    if (n_kv_heads < 1 || rep < 1 || head_dim < 1) return 0;
+    return (size_t)da::kCounterBytes +
+           (size_t)n_kv_heads * da::attn_splits(n_kv_heads) * rep * (head_dim + 2) * sizeof(float);
+}
+
+extern "C" int da_decode_attention(const void *q, const void *prefix_kv, long long prefix_head_stride,
+                                   int n_prefix_tokens, void *local_k, void *local_v,
+                                   long long local_token_stride, long long local_head_stride,
+                                   int local_capacity, const void *new_k, const void *new_v,
+                                   const int32_t *start_pos_dev, int start_pos_host, int dram_tokens,
+                                   void *out, float *lse_out, void *workspace, size_t workspace_bytes,
+                                   int32_t *status, int n_kv_heads, int rep, int head_dim, int dtype,
+                                   da_stream_t stream) {
+    if (!q || !prefix_kv || !local_k || !local_v || !new_k || !new_v || !out || !workspace || !status)
+        return DA_ERR_NULL;
+    if (n_kv_heads < 1 || n_prefix_tokens < 1 || local_capacity < 1 || dram_tokens < 0) return DA_ERR_SHAPE;
+    if (head_dim != 64 && head_dim != 128) return DA_ERR_UNSUPPORTED;
+    if (rep != 1 && rep != 2 && rep != 4 && rep != 8) return DA_ERR_UNSUPPORTED;
+    if (n_kv_heads * 4 > da::kCounterBytes || n_kv_heads > 65535) return DA_ERR_UNSUPPORTED;
+    if (dtype != DA_F32 && dtype != DA_F16 && dtype != DA_BF16) return DA_ERR_DTYPE;
+    const size_t esz = dtype == DA_F32 ? 4 : 2;
+    const uintptr_t ptrs = (uintptr_t)q | (uintptr_t)prefix_kv | (uintptr_t)local_k | (uintptr_t)local_v |
+                           (uintptr_t)new_k | (uintptr_t)new_v | (uintptr_t)out;
+    if ((ptrs & 15) || ((uintptr_t)workspace & 255)) return DA_ERR_ALIGN;
+    if (((size_t)prefix_head_stride * esz) % 16 || ((size_t)local_token_stride * esz) % 16 ||
+        ((size_t)local_head_stride * esz) % 16)
+        return DA_ERR_ALIGN;
+    if (workspace_bytes < da_decode_attention_workspace_bytes(n_kv_heads, rep, head_dim)) return DA_ERR_WORKSPACE;
+
+    da::AttnParams p;
+    p.q = static_cast<const unsigned char *>(q);
+    p.prefix = static_cast<const unsigned char *>(prefix_kv);
+    p.prefix_head_stride = prefix_head_stride;
+    p.n_prefix_tokens = n_prefix_tokens;
+    p.local_k = static_cast<unsigned char *>(local_k);
+    p.local_v = static_cast<unsigned char *>(local_v);
+    p.local_tok_stride = local_token_stride;
+    p.local_head_stride = local_head_stride;
+    p.local_capacity = local_capacity;
+    p.new_k = static_cast<const unsigned char *>(new_k);
+    p.new_v = static_cast<const unsigned char *>(new_v);
+    p.start_pos_dev = start_pos_dev;
+    p.start_pos_host = start_pos_host;
+    p.dram_tokens = dram_tokens;
+    p.out = static_cast<unsigned char *>(out);
+    p.lse_out = lse_out;
+    p.counters = static_cast<unsigned int *>(workspace);
+    p.partials = reinterpret_cast<float *>(static_cast<unsigned char *>(workspace) + da::kCounterBytes);
+    p.status = status;
+    p.scale_log2 = 1.4426950408889634f / sqrtf((float)head_dim);
+
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t e;
+    switch (dtype) {
+    case DA_F32: e = da::dispatch_attn<float>(p, n_kv_heads, rep, head_dim, s); break;
+    case DA_F16: e = da::dispatch_attn<__half>(p, n_kv_heads, rep, head_dim, s); break;
+    default: e = da::dispatch_attn<__nv_bfloat16>(p, n_kv_heads, rep, head_dim, s); break;
+    }
+    return (int)e;
+}

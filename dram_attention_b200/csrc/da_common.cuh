@@ -1,0 +1,152 @@
+// Shared device helpers: element-type conversion, vector loads, warp reductions,
+// mbarrier / bulk-copy wrappers (sm_90+ PTX, built here for sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/dram_attention_b200.h"
+
+#define DA_FULL_MASK 0xffffffffu
+
+namespace da {
+
+// ---- element types ---------------------------------------------------------
+
+template <typename T> struct ElemTraits;
+template <> struct ElemTraits<float> { static constexpr int kCode = DA_F32; };
+template <> struct ElemTraits<__half> { static constexpr int kCode = DA_F16; };
+template <> struct ElemTraits<__nv_bfloat16> { static constexpr int kCode = DA_BF16; };
+
+__device__ __forceinline__ float to_float(float x) { return x; }
+__device__ __forceinline__ float to_float(__half x) { return __half2float(x); }
+__device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T> __device__ __forceinline__ T from_float(float x);
+template <> __device__ __forceinline__ float from_float<float>(float x) { return x; }
+template <> __device__ __forceinline__ __half from_float<__half>(float x) { return __float2half_rn(x); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) {
+    return __float2bfloat16_rn(x);
+}
+
+// Unpack one 32-bit word holding two 16-bit elements (low half first).
+template <typename T> __device__ __forceinline__ void unpack2(uint32_t w, float &lo, float &hi);
+template <> __device__ __forceinline__ void unpack2<__nv_bfloat16>(uint32_t w, float &lo, float &hi) {
+    lo = __uint_as_float(w << 16);
+    hi = __uint_as_float(w & 0xffff0000u);
+}
+template <> __device__ __forceinline__ void unpack2<__half>(uint32_t w, float &lo, float &hi) {
+    __half2 h = *reinterpret_cast<__half2 *>(&w);
+    float2 f = __half22float2(h);
+    lo = f.x;
+    hi = f.y;
+}
+
+// Convert N consecutive elements, given as raw 32-bit words, to float.
+template <typename T, int N> struct Unpack {
+    static constexpr int kWords = N * (int)sizeof(T) / 4;
+    __device__ __forceinline__ static void run(const uint32_t (&w)[kWords], float (&out)[N]) {
+        if constexpr (sizeof(T) == 4) {
+#pragma unroll
+            for (int i = 0; i < N; ++i) out[i] = __uint_as_float(w[i]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < N / 2; ++i) unpack2<T>(w[i], out[2 * i], out[2 * i + 1]);
+        }
+    }
+};
+
+// Raw load of kWords 32-bit words from a suitably aligned address, widest form.
+template <int kWords> __device__ __forceinline__ void load_words(const void *p, uint32_t (&w)[kWords]) {
+    if constexpr (kWords % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < kWords / 4; ++i) {
+            uint4 v = reinterpret_cast<const uint4 *>(p)[i];
+            w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+        }
+    } else if constexpr (kWords % 2 == 0) {
+#pragma unroll
+        for (int i = 0; i < kWords / 2; ++i) {
+            uint2 v = reinterpret_cast<const uint2 *>(p)[i];
+            w[2 * i] = v.x; w[2 * i + 1] = v.y;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < kWords; ++i) w[i] = reinterpret_cast<const uint32_t *>(p)[i];
+    }
+}
+
+// Pointer forms of the two helpers above, for slices of register arrays.
+template <typename T, int N> __device__ __forceinline__ void load_elems(const void *p, float *out) {
+    constexpr int kWords = N * (int)sizeof(T) / 4;
+    uint32_t w[kWords];
+    load_words<kWords>(p, w);
+    if constexpr (sizeof(T) == 4) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) out[i] = __uint_as_float(w[i]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < N / 2; ++i) unpack2<T>(w[i], out[2 * i], out[2 * i + 1]);
+    }
+}
+
+// ---- small math ------------------------------------------------------------
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// ---- shared-memory barriers and bulk copies ----------------------------------
+
+__device__ __forceinline__ uint32_t smem_addr(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_addr(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait: gives up after `limit` polls and reports false.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, int limit = (1 << 22)) {
+    for (int i = 0; i < limit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+
+// Untiled bulk copy global -> shared of this CTA, completion counted in bytes on
+// `bar`.  Both addresses 16-byte aligned, size a multiple of 16.
+__device__ __forceinline__ void bulk_copy_g2s(void *dst_smem, const void *src_gmem, uint32_t bytes,
+                                              uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+            smem_addr(dst_smem)),
+        "l"(src_gmem), "r"(bytes), "r"(smem_addr(bar))
+        : "memory");
+}
+
+}  // namespace da

@@ -1,0 +1,183 @@
+// Page scorer: score[s, hq, l] = sum_d max(q*min, q*max) over per-page key
+// min/max summaries.  HBM-bound streaming kernel: the summaries of a KV head are
+// read once with 128-bit loads and reused for all `rep` query heads of the group.
+//
+// Mapping (fast path): a page's summary is two rows of D elements.  Sixteen lanes
+// cover one page (each lane owns VEC = D/16 consecutive channels of the min row
+// and the same channels of the max row), so a warp streams two pages per step
+// and a 16-lane shuffle tree finishes the channel sum.
+//
+// max(q*mn, q*mx) with mn <= mx equals max(q,0)*mx + min(q,0)*mn: one of the
+// two terms is an exact zero, so two FMAs per (channel, query head) reproduce
+// the formula without a compare.
+
+#include "da_common.cuh"
+
+namespace da {
+
+constexpr int kScoreThreads = 256;
+constexpr int kScoreWarps = kScoreThreads / 32;
+constexpr int kScoreUnroll = 4;
+
+template <typename T, int VEC, int REP>
+__global__ void __launch_bounds__(kScoreThreads, 2)
+score_pages_kernel(const T *__restrict__ q, const T *__restrict__ summaries, float *__restrict__ scores,
+                   int n_kv_heads, int n_pages) {
+    constexpr int D = 16 * VEC;
+    constexpr int kWords = VEC * (int)sizeof(T) / 4;
+    const int hk = blockIdx.y;
+    const int tok = blockIdx.z;
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int sub = lane & 15;   // channel block inside the page
+    const int half = lane >> 4;  // which page of the pair
+
+    float qpos[REP][VEC], qneg[REP][VEC];
+    {
+        const T *qrow = q + ((size_t)(tok * n_kv_heads + hk) * REP) * D + sub * VEC;
+#pragma unroll
+        for (int r = 0; r < REP; ++r) {
+            uint32_t w[kWords];
+            float f[VEC];
+            load_words<kWords>(qrow + (size_t)r * D, w);
+            Unpack<T, VEC>::run(w, f);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) {
+                qpos[r][i] = fmaxf(f[i], 0.f);
+                qneg[r][i] = fminf(f[i], 0.f);
+            }
+        }
+    }
+
+    const T *base = summaries + (size_t)hk * n_pages * 2 * D + sub * VEC;
+    float *out = scores + ((size_t)(tok * n_kv_heads + hk) * REP) * n_pages;
+    const int n_pairs = (n_pages + 1) >> 1;
+    const int stride = gridDim.x * kScoreWarps;
+
+    for (int pair0 = blockIdx.x * kScoreWarps + warp; pair0 < n_pairs; pair0 += stride * kScoreUnroll) {
+        uint32_t wmn[kScoreUnroll][kWords], wmx[kScoreUnroll][kWords];
+        int page[kScoreUnroll];
+#pragma unroll
+        for (int u = 0; u < kScoreUnroll; ++u) {
+            const int pr = pair0 + u * stride;
+            page[u] = (pr < n_pairs) ? pr * 2 + half : n_pages;  // n_pages = nothing to do
+            const int pg = page[u] < n_pages ? page[u] : n_pages - 1;
+            const T *row = base + (size_t)pg * 2 * D;
+            load_words<kWords>(row, wmn[u]);
+            load_words<kWords>(row + D, wmx[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < kScoreUnroll; ++u) {
+            float mn[VEC], mx[VEC], acc[REP];
+            Unpack<T, VEC>::run(wmn[u], mn);
+            Unpack<T, VEC>::run(wmx[u], mx);
+#pragma unroll
+            for (int r = 0; r < REP; ++r) {
+                float a = 0.f;
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) a = fmaf(qpos[r][i], mx[i], fmaf(qneg[r][i], mn[i], a));
+                acc[r] = a;
+            }
+#pragma unroll
+            for (int off = 8; off >= 1; off >>= 1)
+#pragma unroll
+                for (int r = 0; r < REP; ++r) acc[r] += __shfl_xor_sync(DA_FULL_MASK, acc[r], off);
+            if (sub == 0 && page[u] < n_pages) {
+#pragma unroll
+                for (int r = 0; r < REP; ++r) out[(size_t)r * n_pages + page[u]] = acc[r];
+            }
+        }
+    }
+}
+
+// Any head_dim, any rep: one warp per page, lanes stride over channels.
+template <typename T>
+__global__ void __launch_bounds__(kScoreThreads)
+score_pages_generic_kernel(const T *__restrict__ q, const T *__restrict__ summaries,
+                           float *__restrict__ scores, int n_kv_heads, int rep, int n_pages, int head_dim) {
+    const int hk = blockIdx.y;
+    const int tok = blockIdx.z;
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const T *base = summaries + (size_t)hk * n_pages * 2 * head_dim;
+    for (int page = blockIdx.x * kScoreWarps + warp; page < n_pages; page += gridDim.x * kScoreWarps) {
+        const T *mn = base + (size_t)page * 2 * head_dim;
+        const T *mx = mn + head_dim;
+        for (int r = 0; r < rep; ++r) {
+            const size_t row = (size_t)(tok * n_kv_heads + hk) * rep + r;
+            const T *qrow = q + row * head_dim;
+            float a = 0.f;
+            for (int d = lane; d < head_dim; d += 32) {
+                const float qv = to_float(qrow[d]);
+                a = fmaf(fmaxf(qv, 0.f), to_float(mx[d]), fmaf(fminf(qv, 0.f), to_float(mn[d]), a));
+            }
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) a += __shfl_xor_sync(DA_FULL_MASK, a, off);
+            if (lane == 0) scores[row * n_pages + page] = a;
+        }
+    }
+}
+
+template <typename T, int VEC>
+static cudaError_t launch_fast(const void *q, const void *summaries, float *scores, int n_tokens,
+                               int n_kv_heads, int rep, int n_pages, cudaStream_t stream) {
+    const int n_pairs = (n_pages + 1) / 2;
+    // two resident CTAs per SM; spread them over the heads and tokens of the launch
+    int per_row = (148 * 2) / (n_kv_heads * n_tokens);
+    if (per_row < 1) per_row = 1;
+    int gx = (n_pairs + kScoreWarps * kScoreUnroll - 1) / (kScoreWarps * kScoreUnroll);
+    if (gx > per_row) gx = per_row;
+    if (gx < 1) gx = 1;
+    dim3 grid(gx, n_kv_heads, n_tokens);
+    const T *qq = static_cast<const T *>(q);
+    const T *ss = static_cast<const T *>(summaries);
+    switch (rep) {
+    case 1: score_pages_kernel<T, VEC, 1><<<grid, kScoreThreads, 0, stream>>>(qq, ss, scores, n_kv_heads, n_pages); break;
+    case 2: score_pages_kernel<T, VEC, 2><<<grid, kScoreThreads, 0, stream>>>(qq, ss, scores, n_kv_heads, n_pages); break;
+    case 4: score_pages_kernel<T, VEC, 4><<<grid, kScoreThreads, 0, stream>>>(qq, ss, scores, n_kv_heads, n_pages); break;
+    default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
+template <typename T>
+static cudaError_t launch_generic(const void *q, const void *summaries, float *scores, int n_tokens,
+                                  int n_kv_heads, int rep, int n_pages, int head_dim, cudaStream_t stream) {
+    int gx = (n_pages + kScoreWarps - 1) / kScoreWarps;
+    if (gx > 592) gx = 592;
+    dim3 grid(gx, n_kv_heads, n_tokens);
+    score_pages_generic_kernel<T><<<grid, kScoreThreads, 0, stream>>>(
+        static_cast<const T *>(q), static_cast<const T *>(summaries), scores, n_kv_heads, rep, n_pages, head_dim);
+    return cudaGetLastError();
+}
+
+template <typename T>
+static cudaError_t dispatch(const void *q, const void *summaries, float *scores, int n_tokens, int n_kv_heads,
+                            int rep, int n_pages, int head_dim, cudaStream_t stream) {
+    const bool aligned = (((uintptr_t)q | (uintptr_t)summaries) & 15) == 0;
+    const bool rep_ok = rep == 1 || rep == 2 || rep == 4;
+    if (aligned && rep_ok) {
+        if (head_dim == 128) return launch_fast<T, 8>(q, summaries, scores, n_tokens, n_kv_heads, rep, n_pages, stream);
+        if (head_dim == 64) return launch_fast<T, 4>(q, summaries, scores, n_tokens, n_kv_heads, rep, n_pages, stream);
+    }
+    return launch_generic<T>(q, summaries, scores, n_tokens, n_kv_heads, rep, n_pages, head_dim, stream);
+}
+
+}  // namespace da
+
+extern "C" int da_score_pages(const void *q, const void *summaries, float *scores, int n_tokens,
+                              int n_kv_heads, int rep, int n_pages, int head_dim, int dtype,
+                              da_stream_t stream) {
+    if (!q || !summaries || !scores) return DA_ERR_NULL;
+    if (n_tokens < 1 || n_kv_heads < 1 || rep < 1 || n_pages < 1 || head_dim < 1) return DA_ERR_SHAPE;
+    if (n_kv_heads > 65535 || n_tokens > 65535) return DA_ERR_UNSUPPORTED;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t e;
+    switch (dtype) {
+    case DA_F32: e = da::dispatch<float>(q, summaries, scores, n_tokens, n_kv_heads, rep, n_pages, head_dim, s); break;
+    case DA_F16: e = da::dispatch<__half>(q, summaries, scores, n_tokens, n_kv_heads, rep, n_pages, head_dim, s); break;
+    case DA_BF16: e = da::dispatch<__nv_bfloat16>(q, summaries, scores, n_tokens, n_kv_heads, rep, n_pages, head_dim, s); break;
+    default: return DA_ERR_DTYPE;
+    }
+    return (int)e;
+}

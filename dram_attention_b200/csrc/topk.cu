@@ -1,0 +1,194 @@
+// Per-query-head top-k page selection: radix select on order-preserving 32-bit
+// keys, exact lowest-index tie-break, then the k survivors are ranked by
+// (score descending, page id ascending).  One CTA per (token, query head) row;
+// the result is written straight into the per-KV-head page list.
+
+#include "da_common.cuh"
+
+namespace da {
+
+constexpr int kTopkThreads = 1024;
+constexpr int kTopkWarps = kTopkThreads / 32;
+constexpr int kTopkMaxK = 4096;
+
+// Ascending unsigned order of the key == ascending float order; -0.0 is folded
+// onto +0.0 so that the two compare equal (ties then go by page id).
+__device__ __forceinline__ uint32_t score_key(float x) {
+    uint32_t b = __float_as_uint(x);
+    if ((b << 1) == 0) b = 0;
+    return b ^ ((b >> 31) ? 0xffffffffu : 0x80000000u);
+}
+
+__global__ void __launch_bounds__(kTopkThreads)
+topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_list, int n_kv_heads, int rep,
+                  int n_pages, int k) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    unsigned long long *cand = reinterpret_cast<unsigned long long *>(smem_raw);  // [k]
+    int *rank = reinterpret_cast<int *>(cand + k);                                // [k]
+    __shared__ int hist[256];
+    __shared__ int warp_tot[kTopkWarps];
+    __shared__ int sh_digit, sh_above, sh_count, sh_taken;
+
+    const int row = blockIdx.x;  // (token * n_kv_heads + hk) * rep + r
+    const int r = row % rep;
+    const int hk = (row / rep) % n_kv_heads;
+    const int tok = row / (rep * n_kv_heads);
+    const float *srow = scores + (size_t)row * n_pages;
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+
+    // ---- radix select: key of the k-th largest score -----------------------
+    uint32_t prefix = 0, mask = 0;
+    int need = k;  // how many still to take among keys that match the prefix
+    int count_eq = 0;
+    for (int pass = 0; pass < 4; ++pass) {
+        const int shift = 24 - 8 * pass;
+        if (tid < 256) hist[tid] = 0;
+        __syncthreads();
+        for (int base = 0; base < n_pages; base += kTopkThreads) {
+            const int i = base + tid;
+            uint32_t key = 0;
+            bool in = false;
+            if (i < n_pages) {
+                key = score_key(srow[i]);
+                in = (key & mask) == prefix;
+            }
+            // one shared-memory atomic per distinct digit in the warp
+            const uint32_t digit = in ? ((key >> shift) & 255u) : 256u;
+            const uint32_t peers = __match_any_sync(DA_FULL_MASK, digit);
+            if (in && (peers & ((1u << lane) - 1)) == 0) atomicAdd(&hist[digit], __popc(peers));
+        }
+        __syncthreads();
+        if (warp == 0) {
+            // lane l owns digits 255-8l .. 248-8l (descending); find the digit where the
+            // running count from the top reaches `need`
+            int c[8], tot = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                c[j] = hist[255 - (lane * 8 + j)];
+                tot += c[j];
+            }
+            int incl = tot;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                int v = __shfl_up_sync(DA_FULL_MASK, incl, off);
+                if (lane >= off) incl += v;
+            }
+            int above = incl - tot;  // keys in higher digits than this lane's block
+            if (above < need && incl >= need) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if (above < need && above + c[j] >= need) {
+                        sh_digit = 255 - (lane * 8 + j);
+                        sh_above = above;
+                        sh_count = c[j];
+                        above = need;  // stop
+                    } else {
+                        above += c[j];
+                    }
+                }
+            }
+        }
+        __syncthreads();
+        prefix |= (uint32_t)sh_digit << shift;
+        mask |= 255u << shift;
+        need -= sh_above;
+        count_eq = sh_count;
+        __syncthreads();
+    }
+    // prefix = key of the k-th largest; `need` of the `count_eq` keys equal to it are taken.
+    const uint32_t thr = prefix;
+
+    // ---- gather the survivors ------------------------------------------------
+    if (tid == 0) sh_taken = 0;
+    __syncthreads();
+    const bool take_all_ties = (count_eq == need);
+    for (int base = 0; base < n_pages; base += kTopkThreads) {
+        const int i = base + tid;
+        if (i < n_pages) {
+            const uint32_t key = score_key(srow[i]);
+            if (key > thr || (take_all_ties && key == thr)) {
+                const int pos = atomicAdd(&sh_taken, 1);
+                cand[pos] = ((unsigned long long)(~key) << 32) | (uint32_t)i;
+            }
+        }
+    }
+    __syncthreads();
+    if (!take_all_ties) {
+        // the `need` lowest page ids among keys == thr, by an ordered block scan
+        int taken_ties = 0;  // uniform across the block
+        const int first_slot = sh_taken;
+        __syncthreads();
+        for (int base = 0; base < n_pages && taken_ties < need; base += kTopkThreads) {
+            const int i = base + tid;
+            const bool f = (i < n_pages) && (score_key(srow[i]) == thr);
+            const uint32_t bal = __ballot_sync(DA_FULL_MASK, f);
+            if (lane == 0) warp_tot[warp] = __popc(bal);
+            __syncthreads();
+            int before = 0, total = 0;
+            for (int w = 0; w < kTopkWarps; ++w) {
+                const int c = warp_tot[w];
+                if (w < warp) before += c;
+                total += c;
+            }
+            const int my = taken_ties + before + __popc(bal & ((1u << lane) - 1));
+            if (f && my < need) cand[first_slot + my] = ((unsigned long long)(~thr) << 32) | (uint32_t)i;
+            taken_ties += total;
+            __syncthreads();
+        }
+    }
+    __syncthreads();
+
+    // ---- order the k survivors: rank = number of smaller composite keys --------
+    for (int e = tid; e < k; e += kTopkThreads) rank[e] = 0;
+    __syncthreads();
+    {
+        // element e = tid % kk_pad, segment = tid / kk_pad when k < blockDim
+        int segs = kTopkThreads / k;
+        if (segs < 1) segs = 1;
+        const int seg_len = (k + segs - 1) / segs;
+        for (int e0 = 0; e0 < k; e0 += kTopkThreads / segs) {
+            const int e = e0 + tid % (kTopkThreads / segs);
+            const int seg = tid / (kTopkThreads / segs);
+            if (e < k && seg < segs) {
+                const unsigned long long v = cand[e];
+                const int j0 = seg * seg_len;
+                const int j1 = min(k, j0 + seg_len);
+                int c = 0;
+                for (int j = j0; j < j1; ++j) c += (cand[j] < v);
+                if (c) atomicAdd(&rank[e], c);
+            }
+        }
+    }
+    __syncthreads();
+    const int n_tokens = gridDim.x / (n_kv_heads * rep);
+    int32_t *dst = page_list + (size_t)hk * n_tokens * rep * k + (size_t)(tok * rep + r) * k;
+    for (int e = tid; e < k; e += kTopkThreads) dst[rank[e]] = (int32_t)(cand[e] & 0xffffffffu);
+}
+
+}  // namespace da
+
+extern "C" int da_topk_pages(const float *scores, int32_t *page_list, int n_tokens, int n_kv_heads, int rep,
+                             int n_pages, int k, da_stream_t stream) {
+    if (!scores || !page_list) return DA_ERR_NULL;
+    if (n_tokens < 1 || n_kv_heads < 1 || rep < 1 || n_pages < 1 || k < 1 || k > n_pages) return DA_ERR_SHAPE;
+    if (k > da::kTopkMaxK) return DA_ERR_UNSUPPORTED;
+    const size_t smem = (size_t)k * (sizeof(unsigned long long) + sizeof(int));
+    const int rows = n_tokens * n_kv_heads * rep;
+    // opt in to > 48 KB of dynamic shared memory once per device
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return DA_ERR_UNSUPPORTED;
+    if (!attr_set[dev]) {
+        e = cudaFuncSetAttribute(da::topk_pages_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 da::kTopkMaxK * 12);
+        if (e != cudaSuccess) return (int)e;
+        attr_set[dev] = true;
+    }
+    da::topk_pages_kernel<<<rows, da::kTopkThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+        scores, page_list, n_kv_heads, rep, n_pages, k);
+    return (int)cudaGetLastError();
+}

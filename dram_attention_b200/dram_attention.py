@@ -1,0 +1,156 @@
+"""DRAM Attention operator: same constructor and call signature as the reference's
+DRAMAttention (dram_attention/dram_attention.py:6-238); the generate stage runs on
+hand-written sm_100a kernels."""
+
+from __future__ import annotations
+
+import torch
+
+from . import _native
+from .lru_cache import DummyCache, LRUCache
+
+
+class DRAMAttention(torch.nn.Module):
+    """Long-context decode attention with the prefix KV cache in host DRAM.
+
+    Two caches: a local window of the most recent tokens in HBM, and the prefix in
+    pinned DRAM behind an LRU-managed HBM slot table.  Every generate step scores
+    all prefix pages against the query, makes the top pages resident and attends
+    over the whole slot table plus the local window.
+
+    Args:
+        max_output_length: tokens that may be generated after the prefill.
+        lru_hbm_cache_size: size of the HBM slot table, in tokens.
+        local_cache_size: size of the local window, in tokens.
+        page_size: tokens per page.
+        top_k: tokens (not pages) selected per query head and step.
+        n_kv_heads, head_dim: KV head count and channel count.
+        device: CUDA device of all device-side state.
+        dtype: element type of the caches (bfloat16, float16 or float32).
+    """
+
+    def __init__(self, max_output_length: int, lru_hbm_cache_size: int, local_cache_size: int,
+                 page_size: int, top_k: int, n_kv_heads: int, head_dim: int, device: str = "cuda",
+                 dtype: torch.dtype = torch.bfloat16):
+        super().__init__()
+        self.max_output_length = max_output_length
+        self.page_size = page_size
+        self.dram_kv_cache_size = None  # set by init_cache
+        self.lru_hbm_cache_size = lru_hbm_cache_size
+        self.local_cache_size = local_cache_size
+        self.top_k = top_k
+        self.n_kv_heads = n_kv_heads
+        self.head_dim = head_dim
+        self.num_page = self.lru_hbm_cache_size // self.page_size
+        self.device = device
+        _native.dtype_code(dtype)
+        _native.lib()  # fail here, loudly, if the CUDA library has not been built
+
+        cache_shape = (1, local_cache_size + max_output_length, n_kv_heads, head_dim)
+        self.register_buffer("cache_k", torch.zeros(cache_shape, device=device, dtype=dtype))
+        self.register_buffer("cache_v", torch.zeros(cache_shape, device=device, dtype=dtype))
+        self.lru_cache = None
+        self._ws = {}
+
+    # ---- cache construction ---------------------------------------------------
+    def init_cache(self, k_cache: torch.Tensor, v_cache: torch.Tensor):
+        """Split a prefill KV cache (1, S, Hk, D) into the DRAM prefix and the local
+        window (dram_attention/dram_attention.py:65-105)."""
+        bsz, seqlen, H, D = k_cache.shape
+        assert bsz == 1, "Only support batch size 1"
+        dram_kv_cache_size = seqlen - self.local_cache_size + self.page_size
+        self.dram_kv_cache_size = dram_kv_cache_size // self.page_size * self.page_size
+        L = seqlen - self.dram_kv_cache_size
+        self.cache_k[:, :L].copy_(k_cache[:, self.dram_kv_cache_size:], non_blocking=True)
+        self.cache_v[:, :L].copy_(v_cache[:, self.dram_kv_cache_size:], non_blocking=True)
+
+        dram_k_cache = k_cache[:, :self.dram_kv_cache_size]
+        dram_v_cache = v_cache[:, :self.dram_kv_cache_size]
+        if self.dram_kv_cache_size > self.lru_hbm_cache_size:
+            self.lru_cache = LRUCache(
+                k_cache=dram_k_cache[0].transpose(0, 1), v_cache=dram_v_cache[0].transpose(0, 1),
+                page_size=self.page_size, top_k=self.top_k // self.page_size,
+                lru_hbm_cache_size=self.lru_hbm_cache_size, device=self.device)
+        else:
+            self.lru_cache = DummyCache(
+                k_cache=dram_k_cache[0].transpose(0, 1), v_cache=dram_v_cache[0].transpose(0, 1),
+                device=self.device, page_size=self.page_size)
+
+    # ---- forward ------------------------------------------------------------------
+    def forward(self, xq: torch.Tensor, xk: torch.Tensor, xv: torch.Tensor, *, start_pos, stage: str):
+        """xq (1, s, Hq, D), xk/xv (1, s, Hk, D).  `stage` is "prefill" (dense causal
+        attention, then init_cache) or "generate" (one new token; start_pos is its
+        absolute position, a Python int or an int32 CUDA tensor of shape (1,))."""
+        bsz, seqlen, H, D = xq.shape
+        assert bsz == 1, "Only support batch size 1"
+        if stage == "prefill":
+            output = self._prefill_attention(xq, xk, xv)
+            self.init_cache(xk, xv)
+            return output
+        elif stage == "generate":
+            return self._generate(xq, xk, xv, start_pos)
+        else:
+            raise RuntimeError(f"Unsupported stage: {stage}")
+
+    @staticmethod
+    def _prefill_attention(xq, xk, xv):
+        """Dense causal attention of the prompt.  Not part of the decode path: like
+        the reference (which calls a third-party library here,
+        dram_attention/dram_attention.py:136) this is a library call."""
+        q, k, v = (t.transpose(1, 2) for t in (xq, xk, xv))
+        out = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+        return out.transpose(1, 2).contiguous()
+
+    def _workspace(self, rep: int, dev):
+        ws = self._ws.get(rep)
+        if ws is None:
+            nbytes = _native.lib().da_decode_attention_workspace_bytes(self.n_kv_heads, rep, self.head_dim)
+            buf = torch.zeros(nbytes, dtype=torch.uint8, device=dev)  # counters start at zero
+            status = torch.zeros(1, dtype=torch.int32, device=dev)
+            ws = self._ws[rep] = (buf, nbytes, status)
+        return ws
+
+    def _generate(self, xq: torch.Tensor, xk: torch.Tensor, xv: torch.Tensor, start_pos):
+        bsz, seqlen, n_q_heads, D = xq.shape
+        assert seqlen == 1, "generate takes one token per call"
+        assert self.lru_cache is not None, "init_cache (or a prefill) must come first"
+        _native.require_cuda(xq, "xq")
+        assert xq.dtype == self.cache_k.dtype and xk.dtype == xq.dtype and xv.dtype == xq.dtype
+        assert n_q_heads % self.n_kv_heads == 0 and D == self.head_dim
+        rep = n_q_heads // self.n_kv_heads
+        xq = xq if xq.is_contiguous() else xq.contiguous()
+        xk = xk if xk.is_contiguous() else xk.contiguous()
+        xv = xv if xv.is_contiguous() else xv.contiguous()
+        with torch.cuda.device(xq.device):
+            # score -> select -> LRU update -> fetch (no-ops for a fully resident prefix)
+            self.lru_cache.get_kv_cache_(xq)
+            prefix = self.lru_cache.hbm_kv_cache
+            n_prefix_tokens = (self.lru_cache.num_tokens if isinstance(self.lru_cache, DummyCache)
+                               else self.lru_cache.num_hbm_pages * self.page_size)
+            out = torch.empty_like(xq)
+            if n_prefix_tokens == 0:
+                raise RuntimeError("empty DRAM prefix is not supported")
+            buf, nbytes, status = self._workspace(rep, xq.device)
+            if isinstance(start_pos, torch.Tensor):
+                assert start_pos.dtype == torch.int32 and start_pos.is_cuda and start_pos.numel() == 1
+                pos_dev, pos_host = start_pos.data_ptr(), 0
+            else:
+                pos_dev, pos_host = 0, int(start_pos)
+            _native.check(_native.lib().da_decode_attention(
+                xq.data_ptr(), prefix.data_ptr(), prefix.stride(0), n_prefix_tokens,
+                self.cache_k.data_ptr(), self.cache_v.data_ptr(), self.cache_k.stride(1),
+                self.cache_k.stride(2), self.cache_k.shape[1], xk.data_ptr(), xv.data_ptr(),
+                pos_dev, pos_host, self.dram_kv_cache_size, out.data_ptr(), 0, buf.data_ptr(), nbytes,
+                status.data_ptr(), self.n_kv_heads, rep, self.head_dim, _native.dtype_code(xq.dtype),
+                _native.stream_ptr()), "da_decode_attention")
+        return out
+
+    def check_status(self) -> None:
+        """Synchronises; raises if any kernel of this operator flagged a problem."""
+        for _, _, status in self._ws.values():
+            bits = int(status.item())
+            if bits:
+                status.zero_()
+                raise RuntimeError("dram_attention_b200 device status: " + _native.status_message(bits))
+        if isinstance(self.lru_cache, LRUCache):
+            self.lru_cache.check_status()

@@ -1,0 +1,176 @@
+"""HBM slot table in front of a KV cache that lives in pinned host DRAM.
+
+Mirrors the reference's LRUCache / DummyCache / CacheOutput
+(dram_attention/lru_cache.py) on top of the CUDA kernels: one kernel for the LRU
+table update, one gather-copy kernel for the missed pages."""
+
+from __future__ import annotations
+
+from typing import NamedTuple, Optional
+
+import torch
+
+from . import _native
+from .topk_selector import IPUpperboundTopKSelector, build_pages_
+
+
+class CacheOutput(NamedTuple):
+    k_cache: torch.Tensor
+    v_cache: torch.Tensor
+
+
+class DummyCache(torch.nn.Module):
+    """The whole prefix resident in HBM (no scoring, no eviction); used when the
+    DRAM prefix is not larger than the HBM cache (dram_attention/lru_cache.py:24-37).
+
+    The prefix is stored in the slot payload layout (Hk, tokens, 2, D) so the same
+    attention kernel reads it."""
+
+    def __init__(self, k_cache: torch.Tensor, v_cache: torch.Tensor, device: str, page_size: int = 16,
+                 *args, **kvargs):
+        super().__init__()
+        hk, length, d = k_cache.shape
+        k_dev, v_dev = k_cache.to(device=device), v_cache.to(device=device)
+        _native.require_cuda(k_dev, "k_cache")
+        self.num_kv_heads, self.head_dim, self.num_tokens = hk, d, length
+        self.register_buffer("hbm_kv_cache", torch.empty(hk, max(length, 1), 2 * d, dtype=k_cache.dtype,
+                                                         device=device))
+        if length:
+            with torch.cuda.device(k_dev.device):
+                # one "page" per token: the payload layout is token-major either way
+                build_pages_(k_dev, v_dev, 1, None, None, self.hbm_kv_cache, length)
+
+    def kv_views(self) -> CacheOutput:
+        c = self.hbm_kv_cache.view(self.num_kv_heads, -1, 2, self.head_dim)[:, :self.num_tokens]
+        return CacheOutput(k_cache=c[:, :, 0], v_cache=c[:, :, 1])
+
+    def get_kv_cache_(self, q: torch.Tensor) -> CacheOutput:
+        return self.kv_views()
+
+
+class LRUCache(torch.nn.Module):
+    """LRU-managed HBM page cache over a paged KV cache in pinned DRAM
+    (dram_attention/lru_cache.py:40-265).
+
+    Attributes (names as in the reference; the integer tables are int32 here):
+        current_step: int32 (1,), a view of the per-head step counters.
+        dram_kv_cache: pinned host (num_kv_heads, num_dram_pages, page_size*2*head_dim);
+            inside a page the layout is (page_size, 2, head_dim): token-major, key then value.
+        hbm_kv_cache: device (num_kv_heads, num_hbm_pages, page_size*2*head_dim), same row format.
+        page_access_time: int32 (num_kv_heads, num_hbm_pages), step of last use.
+        dram_page_to_hbm_page_mapping: int32 (num_kv_heads, num_dram_pages), -1 = not resident.
+        hbm_page_to_dram_page_mapping: int32 (num_kv_heads, num_hbm_pages).
+    """
+
+    def __init__(self, k_cache: torch.Tensor, v_cache: torch.Tensor, page_size: int, top_k: int,
+                 lru_hbm_cache_size: Optional[int] = None, hbm_kv_cache_fraction: float = 0.2,
+                 device: str = "cuda"):
+        super().__init__()
+        assert k_cache.shape == v_cache.shape, "Key and value cache shapes must match."
+        num_kv_heads, dram_kv_cache_size, head_dim = k_cache.shape
+        dtype = k_cache.dtype
+        assert dram_kv_cache_size % page_size == 0, "KV cache size must be divisible by page size."
+        num_dram_pages = dram_kv_cache_size // page_size
+        num_hbm_pages = (int(num_dram_pages * hbm_kv_cache_fraction) if lru_hbm_cache_size is None
+                         else lru_hbm_cache_size // page_size)
+        assert num_hbm_pages <= num_dram_pages, "HBM cache size must be smaller than DRAM cache size."
+
+        self.page_size = page_size
+        self.num_kv_heads = num_kv_heads
+        self.head_dim = head_dim
+        self.num_dram_pages = num_dram_pages
+        self.num_hbm_pages = num_hbm_pages
+        self.top_k = top_k
+        page_dim = page_size * 2 * head_dim
+
+        k_dev, v_dev = k_cache.to(device=device), v_cache.to(device=device)
+        _native.require_cuda(k_dev, "k_cache")
+        dev = k_dev.device
+        i32 = dict(dtype=torch.int32, device=dev)
+        self.register_buffer("step_counters", torch.zeros(num_kv_heads, **i32))
+        self.register_buffer("dram_kv_cache", torch.empty(num_kv_heads, num_dram_pages, page_dim, dtype=dtype,
+                                                          device="cpu", pin_memory=True), persistent=False)
+        self.register_buffer("hbm_kv_cache", torch.empty(num_kv_heads, num_hbm_pages, page_dim, dtype=dtype,
+                                                         device=dev))
+        self.register_buffer("page_access_time", torch.zeros(num_kv_heads, num_hbm_pages, **i32))
+        # -1: the DRAM page is not in HBM; otherwise the slot that holds it
+        self.register_buffer("dram_page_to_hbm_page_mapping",
+                             torch.full((num_kv_heads, num_dram_pages), -1, **i32))
+        self.register_buffer("hbm_page_to_dram_page_mapping",
+                             torch.arange(num_dram_pages - num_hbm_pages, num_dram_pages, **i32)
+                             .repeat(num_kv_heads, 1))
+        # warm start: the rightmost pages are resident, slot s <- page Ld - Nh + s, times 0
+        self.dram_page_to_hbm_page_mapping[:, num_dram_pages - num_hbm_pages:] = \
+            torch.arange(num_hbm_pages, **i32)[None]
+        summaries = torch.empty(num_kv_heads, num_dram_pages, 2, head_dim, dtype=dtype, device=dev)
+        with torch.cuda.device(dev):
+            # one pass: pinned DRAM pages, page summaries and the resident slots
+            build_pages_(k_dev, v_dev, page_size, self.dram_kv_cache, summaries, self.hbm_kv_cache,
+                         num_hbm_pages)
+            torch.cuda.current_stream().synchronize()  # k_dev/v_dev may be temporaries
+        self.top_k_selector = IPUpperboundTopKSelector(k_cache, num_dram_pages, device=dev,
+                                                       _summaries=summaries)
+        self.register_buffer("status", torch.zeros(1, **i32), persistent=False)
+        self._miss = {}
+
+    @property
+    def current_step(self) -> torch.Tensor:
+        return self.step_counters[:1]
+
+    def _miss_buffers(self, list_len: int):
+        bufs = self._miss.get(list_len)
+        if bufs is None:
+            dev = self.hbm_kv_cache.device
+            mk = lambda *s: torch.empty(*s, dtype=torch.int32, device=dev)
+            bufs = self._miss[list_len] = (mk(self.num_kv_heads, list_len), mk(self.num_kv_heads, list_len),
+                                           mk(self.num_kv_heads))
+        return bufs
+
+    def _load_int32_(self, page_list: torch.Tensor) -> None:
+        list_len = page_list.shape[1]
+        miss_pages, miss_slots, n_miss = self._miss_buffers(list_len)
+        lib, s = _native.lib(), _native.stream_ptr()
+        _native.check(lib.da_lru_update(
+            page_list.data_ptr(), list_len, self.dram_page_to_hbm_page_mapping.data_ptr(),
+            self.num_dram_pages, self.hbm_page_to_dram_page_mapping.data_ptr(),
+            self.page_access_time.data_ptr(), self.num_hbm_pages, self.step_counters.data_ptr(),
+            self.num_kv_heads, miss_pages.data_ptr(), miss_slots.data_ptr(), n_miss.data_ptr(),
+            self.status.data_ptr(), s), "da_lru_update")
+        page_bytes = self.dram_kv_cache.shape[2] * self.dram_kv_cache.element_size()
+        _native.check(lib.da_fetch_pages(
+            self.dram_kv_cache.data_ptr(), self.hbm_kv_cache.data_ptr(), miss_pages.data_ptr(),
+            miss_slots.data_ptr(), n_miss.data_ptr(), list_len, self.num_kv_heads, self.num_dram_pages,
+            self.num_hbm_pages, page_bytes, s), "da_fetch_pages")
+
+    def kv_views(self) -> CacheOutput:
+        c = self.hbm_kv_cache.view(self.num_kv_heads, self.num_hbm_pages * self.page_size, 2, self.head_dim)
+        k_cache, v_cache = c.unbind(dim=2)
+        return CacheOutput(k_cache=k_cache, v_cache=v_cache)
+
+    def load_(self, top_k_dram_page_index: torch.Tensor) -> CacheOutput:
+        """Make the listed DRAM pages resident (in place) and return the slot table
+        as strided key and value views, each (num_kv_heads, num_hbm_pages*page_size, head_dim)
+        (dram_attention/lru_cache.py:211-240)."""
+        idx = top_k_dram_page_index
+        _native.require_cuda(idx, "top_k_dram_page_index")
+        assert idx.dim() == 2 and idx.shape[0] == self.num_kv_heads
+        if idx.dtype != torch.int32 or not idx.is_contiguous():
+            idx = idx.to(torch.int32).contiguous()
+        with torch.cuda.device(idx.device):
+            self._load_int32_(idx)
+        return self.kv_views()
+
+    def get_kv_cache_(self, q: torch.Tensor) -> CacheOutput:
+        """Score the pages for q (1, S, Hq, D), select top_k pages per query head,
+        make them resident, return the slot table (dram_attention/lru_cache.py:242-265)."""
+        with torch.cuda.device(q.device):
+            _, page_list = self.top_k_selector.page_list_(q, self.top_k)
+            self._load_int32_(page_list)
+        return self.kv_views()
+
+    def check_status(self) -> None:
+        """Synchronises; raises if a kernel flagged a problem since the last check."""
+        bits = int(self.status.item())
+        if bits:
+            self.status.zero_()
+            raise RuntimeError("dram_attention_b200 device status: " + _native.status_message(bits))

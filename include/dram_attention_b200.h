@@ -1,0 +1,226 @@
+/*
+ * dram_attention_b200 -- C ABI of the B200 (sm_100a) kernels behind the
+ * generate stage of DRAM Attention.
+ *
+ * The reference project (long-context/dram-attention) is pure Python: it has no
+ * FFI of its own.  Each entry point below therefore names the Python-level
+ * function of the reference whose GPU work it replaces (file:line inside the
+ * reference project); the Python package `dram_attention_b200` binds these with
+ * ctypes and mirrors the reference's classes on top of them.
+ *
+ * Conventions
+ *   - Every pointer is a raw address: device memory unless the parameter is
+ *     documented as "host".  The library never allocates or frees device memory
+ *     and never synchronises; every call only enqueues work on `stream`
+ *     (a cudaStream_t passed as void*), so a sequence of calls can be captured
+ *     in a CUDA graph.
+ *   - Return value: 0 on success, a negative DA_ERR_* for an argument the host
+ *     code rejected, a positive value = cudaError_t from the launch.
+ *   - Conditions only the device can see (a page id out of range, more distinct
+ *     pages requested than slots, a bounded wait that ran out) set bits in a
+ *     caller-provided int32 status word; the kernels skip the offending access
+ *     and keep running.
+ *   - dtype codes: DA_F32, DA_F16, DA_BF16 (the element type of q/k/v, of the
+ *     page summaries and of the page payloads).
+ *   - Heads: query head hq belongs to KV head hq / rep (contiguous GQA groups).
+ */
+#ifndef DRAM_ATTENTION_B200_H
+#define DRAM_ATTENTION_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DA_F32 0
+#define DA_F16 1
+#define DA_BF16 2
+
+#define DA_OK 0
+#define DA_ERR_NULL (-1)        /* a required pointer is null */
+#define DA_ERR_SHAPE (-2)       /* a size is zero, negative or inconsistent */
+#define DA_ERR_DTYPE (-3)       /* unknown dtype code */
+#define DA_ERR_ALIGN (-4)       /* a pointer or stride breaks the stated alignment */
+#define DA_ERR_UNSUPPORTED (-5) /* valid, but outside what the kernels are built for */
+#define DA_ERR_WORKSPACE (-6)   /* workspace smaller than the *_workspace_bytes value */
+
+/* bits of the device status word */
+#define DA_STATUS_BAD_PAGE_ID 1      /* a listed page id was outside [0, n_dram_pages) */
+#define DA_STATUS_LRU_OVERFLOW 2     /* more distinct non-resident pages than evictable slots */
+#define DA_STATUS_BAD_POSITION 4     /* start_pos - dram_tokens outside the local window */
+#define DA_STATUS_WAIT_TIMEOUT 8     /* a bounded wait on an asynchronous copy ran out */
+
+typedef void *da_stream_t;
+
+#if defined(__GNUC__)
+#define DA_API __attribute__((visibility("default")))
+#else
+#define DA_API
+#endif
+
+/* Library version: major * 10000 + minor * 100 + patch. */
+DA_API int da_version(void);
+
+/* Static, human-readable text for a return code of this library. */
+DA_API const char *da_error_string(int code);
+
+/*
+ * Page scorer.  Replaces max_inner_product()
+ * (dram_attention/max_ip_triton_kernel.py:95-124, formula :72-80 and :127-133)
+ * together with the GQA reshapes around it (dram_attention/topk_selector.py:48-59).
+ *
+ *   score[s, hq, l] = sum_d max(q[s,hq,d] * min[hk,l,d], q[s,hq,d] * max[hk,l,d]),
+ *   hk = hq / rep, products and accumulation in float32.
+ *
+ * q          (n_tokens, n_kv_heads * rep, head_dim), contiguous, `dtype`
+ * summaries  (n_kv_heads, n_pages, 2, head_dim), contiguous, `dtype`;
+ *            [.., 0, :] = per-page channel minimum, [.., 1, :] = maximum
+ * scores     (n_tokens, n_kv_heads * rep, n_pages) float32, written
+ * The summaries are read once per token for all `rep` query heads of a KV head.
+ */
+DA_API int da_score_pages(const void *q, const void *summaries, float *scores,
+                   int n_tokens, int n_kv_heads, int rep, int n_pages, int head_dim,
+                   int dtype, da_stream_t stream);
+
+/*
+ * Per-query-head top-k page selection, written directly as the per-KV-head page
+ * list.  Replaces torch.argsort(ip, descending=True)[..., :k]
+ * (dram_attention/topk_selector.py:61) and the list concatenation of
+ * LRUCache.get_kv_cache_ (dram_attention/lru_cache.py:260-264).
+ *
+ * For every row (s, hq) the k pages with the largest score, in descending
+ * score order, equal scores (including -0.0 and +0.0) in ascending page id.
+ *
+ * scores     (n_tokens, n_kv_heads * rep, n_pages) float32
+ * page_list  (n_kv_heads, n_tokens * rep * k) int32, written:
+ *            page_list[hk][(s * rep + r) * k + j] = j-th page of query head hk*rep+r
+ * Requires 1 <= k <= n_pages and k <= 4096.
+ */
+DA_API int da_topk_pages(const float *scores, int32_t *page_list,
+                  int n_tokens, int n_kv_heads, int rep, int n_pages, int k,
+                  da_stream_t stream);
+
+/*
+ * LRU slot-table update, one call for all KV heads.  Replaces load_lru_cache_()
+ * without its payload copy: _update_page_access_time_
+ * (dram_attention/lru_triton_kernel.py:110-137), the stable argsort of the
+ * timestamps (:170) and the table part of _load_lru_cache_inline_kernel
+ * (:30-78, :99-107), plus the step increment of LRUCache.load_
+ * (dram_attention/lru_cache.py:224).
+ *
+ * Per head: step += 1; every listed page that is resident gets time = step; the
+ * listed pages that are not resident, in order of first appearance, take the
+ * slots with the smallest (time, slot); the evicted pages are unmapped.  The
+ * result equals the reference's sequential walk whenever the distinct listed
+ * pages fit in the slot table; otherwise DA_STATUS_LRU_OVERFLOW is set and the
+ * tables of that head are left as after the hit marking.
+ *
+ * page_list   (n_kv_heads, list_len) int32
+ * dram_to_slot(n_kv_heads, n_dram_pages) int32, -1 = not resident   (in/out)
+ * slot_to_dram(n_kv_heads, n_slots) int32, -1 = empty slot           (in/out)
+ * access_time (n_kv_heads, n_slots) int32, non-negative             (in/out)
+ * step        (n_kv_heads) int32, one counter per head               (in/out)
+ * miss_pages, miss_slots (n_kv_heads, list_len) int32, written: the (page, slot)
+ *             pairs whose payload has to be copied, in list order
+ * n_miss      (n_kv_heads) int32, written
+ * status      (1) int32, bits or-ed in
+ * Requires n_slots <= 8192 and list_len <= 8192.
+ */
+DA_API int da_lru_update(const int32_t *page_list, int list_len,
+                  int32_t *dram_to_slot, int n_dram_pages,
+                  int32_t *slot_to_dram, int32_t *access_time, int n_slots,
+                  int32_t *step, int n_kv_heads,
+                  int32_t *miss_pages, int32_t *miss_slots, int32_t *n_miss,
+                  int32_t *status, da_stream_t stream);
+
+/*
+ * Miss-page fetch: gather-copy of the pages named by da_lru_update from DRAM into
+ * their slots.  Replaces the payload loop of _load_lru_cache_inline_kernel
+ * (dram_attention/lru_triton_kernel.py:81-98).
+ *
+ * dram_pages  (n_kv_heads, n_dram_pages, page_bytes): pinned, device-mapped HOST
+ *             memory (or device memory); read with 128-bit loads by many CTAs
+ * slots       (n_kv_heads, n_slots, page_bytes) device memory, written
+ * miss_pages, miss_slots, n_miss: as written by da_lru_update (device memory; the
+ *             host never reads them)
+ * page_bytes  multiple of 16 with both bases 16-byte aligned for the fast path;
+ *             any other size is copied bytewise.
+ */
+DA_API int da_fetch_pages(const void *dram_pages, void *slots,
+                   const int32_t *miss_pages, const int32_t *miss_slots,
+                   const int32_t *n_miss, int list_len,
+                   int n_kv_heads, int n_dram_pages, int n_slots, size_t page_bytes,
+                   da_stream_t stream);
+
+/* Bytes of workspace da_decode_attention needs for this shape. */
+DA_API size_t da_decode_attention_workspace_bytes(int n_kv_heads, int rep, int head_dim);
+
+/*
+ * Decode attention of one query token over the whole slot table and the local
+ * window, with the append of the new key/value and the merge of the parts.
+ * Replaces _compute_prefix_attention, _compute_suffix_attention and
+ * _combine_attention (dram_attention/dram_attention.py:191-238), i.e. the two
+ * flash_attn_with_kvcache calls and the log-sum-exp merge.
+ *
+ *   T = start_pos - dram_tokens; local_k[T] = new_k, local_v[T] = new_v;
+ *   out[hq] = softmax over {all prefix tokens} U {local tokens 0..T} of
+ *             (q[hq] . k / sqrt(head_dim)), applied to v; float32 softmax and
+ *             accumulation; one split-K pass with a single final merge.
+ *
+ * q            (n_kv_heads * rep, head_dim) `dtype`
+ * prefix_kv    (n_kv_heads, n_prefix_tokens, 2, head_dim) `dtype`: the slot table
+ *              seen as tokens, key then value per token (page payload layout of
+ *              dram_attention/lru_cache.py:121-142); head stride in elements
+ * local_k/v    local window, token t of head h at t * local_token_stride +
+ *              h * local_head_stride (elements); capacity local_capacity tokens
+ * new_k/new_v  (n_kv_heads, head_dim) `dtype`
+ * start_pos_dev  device int32[1], or NULL to use start_pos_host
+ * out          (n_kv_heads * rep, head_dim) `dtype`, written
+ * lse_out      optional (n_kv_heads * rep) float32: log-sum-exp of all logits
+ * workspace    da_decode_attention_workspace_bytes() bytes, 256-byte aligned; the
+ *              first 1024 bytes hold counters that must be ZERO before the first
+ *              call; each call leaves them zero again
+ * status       (1) int32, bits or-ed in
+ * Requires head_dim in {64, 128}, rep in {1, 2, 4, 8}; all bases and strides
+ * multiples of 16 bytes.
+ */
+DA_API int da_decode_attention(const void *q,
+                        const void *prefix_kv, long long prefix_head_stride,
+                        int n_prefix_tokens,
+                        void *local_k, void *local_v,
+                        long long local_token_stride, long long local_head_stride,
+                        int local_capacity,
+                        const void *new_k, const void *new_v,
+                        const int32_t *start_pos_dev, int start_pos_host, int dram_tokens,
+                        void *out, float *lse_out,
+                        void *workspace, size_t workspace_bytes, int32_t *status,
+                        int n_kv_heads, int rep, int head_dim, int dtype,
+                        da_stream_t stream);
+
+/*
+ * Cache construction on the device: splits a prefill K/V into DRAM pages, page
+ * summaries and warm-started slots in one pass.  Replaces the torch code of
+ * IPUpperboundTopKSelector.__init__ (dram_attention/topk_selector.py:24-35) and
+ * of LRUCache.__init__ (dram_attention/lru_cache.py:121-153, :192-209).
+ *
+ * k, v        token t of head h at t * kv_token_stride + h * kv_head_stride
+ *             (elements), n_pages * page_size tokens are read
+ * dram_pages  optional (n_kv_heads, n_pages, page_size, 2, head_dim): pinned,
+ *             device-mapped HOST memory (or device memory), written
+ * summaries   optional (n_kv_heads, n_pages, 2, head_dim), written
+ * slots       optional (n_kv_heads, n_slots, page_size, 2, head_dim), written with
+ *             the last n_slots pages (slot s <- page n_pages - n_slots + s)
+ */
+DA_API int da_build_pages(const void *k, const void *v,
+                   long long kv_token_stride, long long kv_head_stride,
+                   void *dram_pages, void *summaries, void *slots,
+                   int n_kv_heads, int n_pages, int n_slots, int page_size, int head_dim,
+                   int dtype, da_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* DRAM_ATTENTION_B200_H */

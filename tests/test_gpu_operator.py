@@ -1,0 +1,294 @@
+"""GPU parity tests of the whole generate step through the public operator API
+(`DRAMAttention.__call__`), against golden trajectories produced by the
+reference's own code and against the CPU oracle; plus the reference's API tests."""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from oracle import dram_attention_oracle as orc  # noqa: E402
+from dram_attention_b200.synthetic import llama_layer_workload, plumbing_workload  # noqa: E402
+
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def da():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import dram_attention_b200 as pkg
+    pkg._native.lib()
+    return pkg
+
+
+def _spy_lists(module):
+    """Record the page list of every step (a copy of the selector's int32 output)."""
+    lists = []
+    lc = module.lru_cache
+    orig = lc._load_int32_
+
+    def spy(page_list):
+        lists.append(page_list.clone())
+        return orig(page_list)
+
+    lc._load_int32_ = spy
+    return lists
+
+
+def _run(da, ctor, dtype, k, v, xq, xk, xv, device_pos=False):
+    m = da.DRAMAttention(device=DEV, dtype=dtype, **ctor)
+    m.init_cache(k.to(DEV), v.to(DEV))
+    lists = _spy_lists(m)
+    s = k.shape[1]
+    outs, h2ds, times = [], [], []
+    pos = torch.tensor([s], dtype=torch.int32, device=DEV)
+    for i in range(xq.shape[0]):
+        out = m(xq[i].to(DEV), xk[i].to(DEV), xv[i].to(DEV), start_pos=pos if device_pos else s + i,
+                stage="generate")
+        pos.add_(1)
+        assert out.shape == xq[i].shape and out.dtype == dtype
+        outs.append(out[0, 0].float().cpu())
+        h2ds.append(m.lru_cache.hbm_page_to_dram_page_mapping.cpu().numpy().astype(np.int64))
+        times.append(m.lru_cache.page_access_time.cpu().numpy().astype(np.int64))
+    m.check_status()
+    return m, outs, [l.cpu().numpy().astype(np.int64) for l in lists], h2ds, times
+
+
+def test_plumbing_trajectory_matches_reference_run(da, golden_dir):
+    """16 generate steps of the float32 plumbing workload: page lists and LRU tables
+    bit-exact, outputs within 1e-4 of what the reference's own classes produced."""
+    g = np.load(os.path.join(golden_dir, "plumbing_traj.npz"))
+    w = plumbing_workload(seed=0, steps=16)
+    m, outs, lists, h2ds, times = _run(da, w.ctor_kwargs(), torch.float32, w.k, w.v, w.xq, w.xk, w.xv)
+    assert m.dram_kv_cache_size == int(g["dram_tokens"][0]) == 4096
+    for i in range(16):
+        assert np.array_equal(lists[i], g["lists"][i]), i
+        assert np.array_equal(h2ds[i], g["h2d"][i]), i
+        assert np.array_equal(times[i], g["time"][i].astype(np.int64)), i
+        assert np.abs(outs[i].numpy() - g["out"][i]).max() <= 1e-4, i
+    assert np.array_equal(m.lru_cache.dram_page_to_hbm_page_mapping.cpu().numpy(), g["d2h_final"])
+    assert int(m.lru_cache.current_step) == int(g["step"][0])
+
+
+@pytest.mark.parametrize("device_pos", [False, True])
+def test_mini_trajectory_with_exact_ties(da, golden_dir, device_pos):
+    """Inputs are multiples of 1/8 so many page scores tie exactly: selection order,
+    tables and outputs must still equal the reference run."""
+    g = np.load(os.path.join(golden_dir, "mini_traj.npz"))
+    max_out, lru, local, p, top_k, hk, d = [int(x) for x in g["ctor"]]
+    ctor = dict(max_output_length=max_out, lru_hbm_cache_size=lru, local_cache_size=local, page_size=p,
+                top_k=top_k, n_kv_heads=hk, head_dim=d)
+    f = lambda a: torch.from_numpy(a).float() / 8.0
+    m, outs, lists, h2ds, times = _run(da, ctor, torch.float32, f(g["k8"]), f(g["v8"]), f(g["q8"]),
+                                       f(g["xk8"]), f(g["xv8"]), device_pos)
+    for i in range(len(outs)):
+        assert np.array_equal(lists[i], g["lists"][i]), i
+        assert np.array_equal(h2ds[i], g["h2d"][i]), i
+        assert np.abs(outs[i].numpy() - g["out"][i]).max() <= 1e-4, i
+    assert np.array_equal(m.lru_cache.dram_page_to_hbm_page_mapping.cpu().numpy(), g["d2h_final"])
+
+
+def _oracle_follow(w, steps, gpu_lists):
+    """Oracle stepped with the GPU's page lists (so that a near-tie at the k-th score
+    cannot make the two trajectories drift apart); returns its traces."""
+    o = orc.OracleDRAMAttention(dtype=torch.float32, **w.ctor_kwargs())
+    o.init_cache(w.k.float(), w.v.float())
+    s = w.k.shape[1]
+    res = []
+    for i in range(steps):
+        xq = w.xq[i].float()
+        lc = o.lru_cache
+        scores = orc.scores_by_query_head(xq, lc.chunk_min_max)
+        own = orc.build_page_list(orc.select_pages(scores, lc.top_k)).numpy()
+        mp, ms, nm = lc.load_(gpu_lists[i])
+        pk, pv = lc.kv_views()
+        q = xq[0, 0]
+        po, pl = orc.attend(q, pk.transpose(0, 1), pv.transpose(0, 1))
+        t = s + i - o.dram_kv_cache_size
+        o.cache_k[t], o.cache_v[t] = w.xk[i, 0, 0].float(), w.xv[i, 0, 0].float()
+        so, sl = orc.attend(q, o.cache_k[:t + 1], o.cache_v[:t + 1])
+        res.append((scores, own, orc.combine(po, so, pl, sl), lc.h2d.copy(), lc.page_access_time.copy()))
+    return o, res
+
+
+def test_bf16_layer_trajectory_against_oracle(da):
+    """A reduced Llama-shaped bf16 layer (2 KV heads, 16K-token prefix): every step's
+    selection equals the oracle's up to near-ties at the k-th score, LRU tables are
+    bit-exact given the same list, outputs within 2e-2."""
+    steps = 10
+    w = llama_layer_workload(seed=0, steps=steps, dram_tokens=16384, n_kv_heads=2, lru=4096, local=512,
+                             top_k=1024, needles=4, redraw_every=4)
+    m, outs, lists, h2ds, times = _run(da, w.ctor_kwargs(), torch.bfloat16, w.k, w.v, w.xq, w.xk, w.xv, True)
+    o, res = _oracle_follow(w, steps, lists)
+    k = w.top_k // w.page_size
+    rep = w.n_q_heads // w.n_kv_heads
+    for i, (scores, own, out, h2d, tim) in enumerate(res):
+        assert np.array_equal(h2ds[i], h2d), i
+        assert np.array_equal(times[i], tim), i
+        assert (outs[i] - out).abs().max().item() <= 2e-2, i
+        # selection: identical except where scores are within 1e-3 relative of the k-th score
+        sc = scores.reshape(w.n_kv_heads, rep, -1)
+        for h in range(w.n_kv_heads):
+            for r in range(rep):
+                got = set(lists[i][h, r * k:(r + 1) * k].tolist())
+                want = set(own[h, r * k:(r + 1) * k].tolist())
+                if got != want:
+                    kth = torch.sort(sc[h, r], descending=True).values[k - 1].item()
+                    tol = 1e-3 * max(1.0, abs(kth))
+                    for pg in got ^ want:
+                        assert abs(sc[h, r, pg].item() - kth) <= tol, (i, h, r, pg)
+
+
+def test_fully_resident_prefix_uses_no_lru(da):
+    """DRAM prefix not larger than the HBM cache: everything resident
+    (dram_attention/dram_attention.py:100-105)."""
+    g = torch.Generator().manual_seed(3)
+    hk, rep, d, p = 2, 4, 128, 16
+    ctor = dict(max_output_length=4, lru_hbm_cache_size=1024, local_cache_size=128, page_size=p, top_k=256,
+                n_kv_heads=hk, head_dim=d)
+    s = 600
+    k = torch.randn(1, s, hk, d, generator=g).bfloat16()
+    v = torch.randn(1, s, hk, d, generator=g).bfloat16()
+    m = da.DRAMAttention(device=DEV, dtype=torch.bfloat16, **ctor)
+    m.init_cache(k.to(DEV), v.to(DEV))
+    assert isinstance(m.lru_cache, da.lru_cache.DummyCache)
+    o = orc.OracleDRAMAttention(dtype=torch.float32, **ctor)
+    o.init_cache(k.float(), v.float())
+    assert o.lru_cache is None and m.dram_kv_cache_size == o.dram_kv_cache_size
+    for i in range(3):
+        xq = torch.randn(1, 1, hk * rep, d, generator=g).bfloat16()
+        xk = torch.randn(1, 1, hk, d, generator=g).bfloat16()
+        xv = torch.randn(1, 1, hk, d, generator=g).bfloat16()
+        out = m(xq.to(DEV), xk.to(DEV), xv.to(DEV), start_pos=s + i, stage="generate")
+        want = o.generate(xq.float(), xk.float(), xv.float(), s + i).out
+        assert (out[0, 0].float().cpu() - want).abs().max().item() <= 2e-2
+    m.check_status()
+
+
+def test_generate_step_is_graph_capturable(da):
+    """One generate step captured in a CUDA graph with a device-side start_pos and
+    replayed (the calling pattern of the reference's chat example)."""
+    steps = 6
+    w = llama_layer_workload(seed=1, steps=steps, dram_tokens=8192, n_kv_heads=2, lru=2048, local=256,
+                             top_k=512, needles=2)
+    m = da.DRAMAttention(device=DEV, dtype=torch.bfloat16, **w.ctor_kwargs())
+    m.init_cache(w.k.to(DEV), w.v.to(DEV))
+    e = da.DRAMAttention(device=DEV, dtype=torch.bfloat16, **w.ctor_kwargs())  # eager twin
+    e.init_cache(w.k.to(DEV), w.v.to(DEV))
+    s = w.k.shape[1]
+    xq, xk, xv = (t[0].to(DEV).clone() for t in (w.xq, w.xk, w.xv))
+    pos = torch.tensor([s], dtype=torch.int32, device=DEV)
+    out_static = torch.empty_like(xq)
+    # warm-up call on a side stream allocates every workspace, then capture
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        m(xq, xk, xv, start_pos=pos, stage="generate")
+    torch.cuda.current_stream().wait_stream(side)
+    e(xq, xk, xv, start_pos=s, stage="generate")
+    pos.add_(1)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out_static.copy_(m(xq, xk, xv, start_pos=pos, stage="generate"))
+    for i in range(1, steps):
+        xq.copy_(w.xq[i].to(DEV)); xk.copy_(w.xk[i].to(DEV)); xv.copy_(w.xv[i].to(DEV))
+        graph.replay()
+        pos.add_(1)
+        want = e(xq, xk, xv, start_pos=s + i, stage="generate")
+        assert torch.equal(out_static, want), i
+    assert torch.equal(m.lru_cache.hbm_page_to_dram_page_mapping, e.lru_cache.hbm_page_to_dram_page_mapping)
+    assert torch.equal(m.cache_k, e.cache_k)
+    m.check_status()
+    e.check_status()
+
+
+# ---- the reference's operator API tests (dram_attention/dram_attention_test.py) ----
+
+@pytest.fixture
+def op(da):
+    return da.DRAMAttention(max_output_length=64, lru_hbm_cache_size=32 * 1024, local_cache_size=4096 + 512,
+                            page_size=16, top_k=4096, n_kv_heads=8, head_dim=128, device=DEV)
+
+
+def test_init_fields(op):
+    assert (op.max_output_length, op.lru_hbm_cache_size, op.local_cache_size, op.page_size, op.top_k,
+            op.n_kv_heads, op.head_dim) == (64, 32 * 1024, 4096 + 512, 16, 4096, 8, 128)
+    assert op.cache_k.shape == (1, 4096 + 512 + 64, 8, 128) and op.cache_k.dtype == torch.bfloat16
+
+
+def test_prefill_then_generate_shapes(op):
+    seqlen = 66 * 1024
+    xq = torch.randn(1, seqlen, 32, 128, device=DEV, dtype=torch.bfloat16)
+    xk = torch.randn(1, seqlen, 8, 128, device=DEV, dtype=torch.bfloat16)
+    xv = torch.randn(1, seqlen, 8, 128, device=DEV, dtype=torch.bfloat16)
+    out = op(xq, xk, xv, start_pos=0, stage="prefill")
+    assert out.shape == (1, seqlen, 32, 128)
+    assert op.dram_kv_cache_size == (seqlen - 4608 + 16) // 16 * 16
+    xq = torch.randn(1, 1, 32, 128, device=DEV, dtype=torch.bfloat16)
+    xk = torch.randn(1, 1, 8, 128, device=DEV, dtype=torch.bfloat16)
+    xv = torch.randn(1, 1, 8, 128, device=DEV, dtype=torch.bfloat16)
+    out = op(xq, xk, xv, start_pos=64 * 1024 + 4096, stage="generate")
+    assert out.shape == (1, 1, 32, 128)
+    assert torch.isfinite(out.float()).all()
+    op.check_status()
+
+
+def test_invalid_stage_and_batch(op):
+    z = lambda b, h: torch.randn(b, 1, h, 128, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="Unsupported stage"):
+        op(z(1, 8), z(1, 8), z(1, 8), start_pos=0, stage="invalid")
+    with pytest.raises(AssertionError, match="Only support batch size 1"):
+        op(z(2, 8), z(2, 8), z(2, 8), start_pos=0, stage="prefill")
+
+
+# ---- full-size properties (sizes of the Llama-3-8B layer at 128K context) --------
+
+def test_full_size_layer_invariants(da):
+    """At the benchmark's size the oracle is too slow to follow every step, so check
+    properties: slot payload == DRAM page named by the map, maps inverse of each
+    other, listed pages resident and stamped with the step, every row of the page
+    list sorted by (score desc, id asc), needle pages selected."""
+    steps = 4
+    w = llama_layer_workload(seed=0, steps=steps)
+    m = da.DRAMAttention(device=DEV, dtype=torch.bfloat16, **w.ctor_kwargs())
+    m.init_cache(w.k.to(DEV), w.v.to(DEV))
+    lc = m.lru_cache
+    lists = _spy_lists(m)
+    s = w.k.shape[1]
+    k_pages = w.top_k // w.page_size
+    for i in range(steps):
+        out = m(w.xq[i].to(DEV), w.xk[i].to(DEV), w.xv[i].to(DEV), start_pos=s + i, stage="generate")
+        assert torch.isfinite(out.float()).all()
+        scores = lc.top_k_selector._buffers[(1, 4, k_pages)][0][0].cpu()      # (Hq, L)
+        lst = lists[i].cpu().long()                                             # (Hk, 4*k)
+        d2h = lc.dram_page_to_hbm_page_mapping.cpu().long()
+        h2d = lc.hbm_page_to_dram_page_mapping.cpu().long()
+        tim = lc.page_access_time.cpu()
+        for h in range(8):
+            assert torch.equal(d2h[h, h2d[h]], torch.arange(lc.num_hbm_pages))
+            assert int((d2h[h] >= 0).sum()) == lc.num_hbm_pages
+            assert bool((d2h[h, lst[h]] >= 0).all())
+            assert bool((tim[h, d2h[h, lst[h]]] == i + 1).all())
+            for r in range(4):
+                row = lst[h, r * k_pages:(r + 1) * k_pages]
+                sc = scores[h * 4 + r, row]
+                assert bool(((sc[:-1] > sc[1:]) | ((sc[:-1] == sc[1:]) & (row[:-1] < row[1:]))).all())
+                kth = sc[-1]
+                assert int((scores[h * 4 + r] > kth).sum()) <= k_pages - 1
+        # payloads (checksum of checksums over all slots)
+        hbm = lc.hbm_kv_cache.cpu()
+        for h in range(8):
+            assert torch.equal(hbm[h], lc.dram_kv_cache[h, h2d[h]])
+    m.check_status()
+    # the exact oracle on the last step's state: attention over the GPU's own slot table
+    q = w.xq[steps - 1, 0, 0].float()
+    kv = lc.hbm_kv_cache.cpu().float().view(8, -1, 2, 128)
+    po, pl = orc.attend(q, kv[:, :, 0].transpose(0, 1), kv[:, :, 1].transpose(0, 1))
+    t = s + steps - 1 - m.dram_kv_cache_size
+    so, sl = orc.attend(q, m.cache_k[0, :t + 1].cpu().float(), m.cache_v[0, :t + 1].cpu().float())
+    want = orc.combine(po, so, pl, sl)
+    assert (out[0, 0].float().cpu() - want).abs().max().item() <= 2e-2

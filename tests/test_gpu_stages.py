@@ -1,0 +1,432 @@
+"""GPU parity tests, stage by stage: every CUDA kernel is called through the
+C ABI (via the ctypes binding) and compared with the CPU oracle on the same
+inputs.  Integer results are bit-exact; float tolerances are written per test."""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from oracle import dram_attention_oracle as orc  # noqa: E402
+
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def da():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import dram_attention_b200 as pkg
+    pkg._native.lib()
+    return pkg
+
+
+def _g(seed):
+    return torch.Generator().manual_seed(seed)
+
+
+# ------------------------------------------------------------------ scorer ----
+
+def test_scorer_reference_value_case(da, golden_dir):
+    # shape and tolerance of dram_attention/max_ip_triton_kernel_test.py:29-38
+    g = np.load(os.path.join(golden_dir, "scorer_values.npz"))
+    q, mm = torch.from_numpy(g["q"]).to(DEV), torch.from_numpy(g["min_max"]).to(DEV)
+    out = da.max_inner_product(q, mm)
+    assert out.shape == (2, 4, 16) and out.dtype == torch.float32
+    assert torch.allclose(out.cpu(), torch.from_numpy(g["out_ref"]), rtol=1e-3, atol=1e-3)
+    assert torch.allclose(out, da.max_ip_ref(q, mm), rtol=1e-3, atol=1e-3)
+
+
+def test_scorer_output_dtype_follows_query(da):
+    # dram_attention/max_ip_triton_kernel_test.py:18-26
+    q = torch.randn(2, 4, 64, dtype=torch.float16, device=DEV)
+    mm = torch.randn(4, 16, 2, 64, dtype=torch.float16, device=DEV)
+    assert da.max_inner_product(q, mm).dtype == torch.float16
+
+
+def test_scorer_degenerate_and_large_shapes(da):
+    # dram_attention/max_ip_triton_kernel_test.py:41-60
+    q = torch.randn(1, 1, 1, device=DEV)
+    mm = torch.randn(1, 1, 2, 1, device=DEV)
+    out = da.max_inner_product(q, mm)
+    assert out.shape == (1, 1, 1)
+    assert torch.allclose(out, da.max_ip_ref(q, mm), rtol=1e-5, atol=1e-6)
+    q = torch.randn(32, 32, 128, device=DEV)
+    mm = torch.randn(32, 1024, 2, 128, device=DEV)
+    out = da.max_inner_product(q, mm)
+    assert out.shape == (32, 32, 1024)
+    ref = orc.score_pages(q.cpu(), mm.cpu())
+    assert torch.allclose(out.cpu(), ref, rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.parametrize("dtype,d,rep,hk,pages", [
+    (torch.bfloat16, 128, 4, 8, 8192), (torch.bfloat16, 128, 4, 2, 1), (torch.bfloat16, 128, 4, 2, 3),
+    (torch.bfloat16, 128, 2, 3, 513), (torch.bfloat16, 128, 1, 2, 1000), (torch.float16, 128, 4, 2, 77),
+    (torch.float32, 64, 4, 2, 256), (torch.float32, 128, 4, 2, 130), (torch.bfloat16, 64, 2, 2, 65),
+    (torch.bfloat16, 128, 8, 2, 100), (torch.float32, 96, 3, 2, 50), (torch.bfloat16, 128, 4, 8, 65536),
+])
+def test_scorer_folded_matches_oracle(da, dtype, d, rep, hk, pages):
+    from dram_attention_b200.max_ip import score_pages_
+    g = _g(pages + d + rep)
+    keys = torch.randn(hk, pages, 4, d, generator=g).to(dtype)
+    mm = orc.page_minmax(keys.reshape(hk, pages * 4, d), pages)
+    q = torch.randn(1, 1, hk * rep, d, generator=g).to(dtype)
+    scores = torch.empty(1, hk * rep, pages, dtype=torch.float32, device=DEV)
+    score_pages_(q.to(DEV), mm.to(DEV).contiguous(), scores, 1, hk, rep)
+    ref = orc.scores_by_query_head(q, mm).reshape(1, hk * rep, pages)
+    # 1e-3 relative to the score scale (fp32 accumulation on both sides)
+    scale = ref.abs().max().item()
+    assert (scores.cpu() - ref).abs().max().item() <= 1e-3 * max(scale, 1.0)
+    assert torch.allclose(scores.cpu(), ref, rtol=1e-3, atol=1e-3 * max(scale, 1.0))
+
+
+def test_scorer_multi_token(da):
+    from dram_attention_b200.max_ip import score_pages_
+    g = _g(5)
+    hk, rep, d, pages, s = 4, 2, 64, 200, 10
+    mm = torch.sort(torch.randn(hk, pages, 2, d, generator=g), dim=2).values
+    q = torch.randn(1, s, hk * rep, d, generator=g)
+    scores = torch.empty(s, hk * rep, pages, dtype=torch.float32, device=DEV)
+    score_pages_(q.to(DEV), mm.to(DEV), scores, s, hk, rep)
+    ref = orc.scores_by_query_head(q, mm).reshape(s, hk * rep, pages)
+    assert torch.allclose(scores.cpu(), ref, rtol=1e-3, atol=1e-3)
+
+
+# ------------------------------------------------------------------- top-k ----
+
+def _topk(da, scores, hk, rep, k):
+    from dram_attention_b200 import _native
+    s, hq, pages = scores.shape
+    sc = scores.to(DEV).contiguous()
+    out = torch.full((hk, s * rep * k), -7, dtype=torch.int32, device=DEV)
+    _native.check(_native.lib().da_topk_pages(sc.data_ptr(), out.data_ptr(), s, hk, rep, pages, k,
+                                              _native.stream_ptr()))
+    return out.cpu()
+
+
+def _topk_oracle(scores, hk, rep, k):
+    s, hq, pages = scores.shape
+    idx = orc.select_pages(scores.reshape(s, hk, rep, pages), k)
+    return orc.build_page_list(idx).to(torch.int32)
+
+
+@pytest.mark.parametrize("pages,k,hk,rep,s,kind", [
+    (8192, 256, 8, 4, 1, "normal"), (256, 32, 2, 4, 1, "normal"), (1000, 100, 2, 2, 3, "normal"),
+    (65536, 256, 2, 4, 1, "normal"), (65536, 512, 1, 4, 1, "normal"), (5000, 2048, 1, 2, 1, "normal"),
+    (300, 300, 2, 1, 1, "normal"), (4096, 4096, 1, 1, 1, "normal"), (1, 1, 2, 2, 1, "normal"),
+    (8192, 256, 2, 4, 1, "quantised"), (3000, 500, 2, 2, 1, "quantised"), (2048, 64, 2, 2, 1, "constant"),
+    (4096, 100, 2, 2, 1, "zeros"), (1500, 200, 2, 2, 1, "bf16like"), (2000, 128, 2, 2, 1, "negative"),
+])
+def test_topk_bit_exact(da, pages, k, hk, rep, s, kind):
+    g = _g(pages * 7 + k)
+    sc = torch.randn(s, hk * rep, pages, generator=g) * 30
+    if kind == "quantised":
+        sc = torch.round(sc / 8)            # a few dozen distinct values: heavy ties
+    elif kind == "constant":
+        sc = torch.full_like(sc, 3.25)
+    elif kind == "zeros":
+        sc = torch.where(torch.rand(sc.shape, generator=g) < 0.5, torch.zeros_like(sc), -torch.zeros_like(sc))
+        sc[..., ::7] = -1.0
+    elif kind == "bf16like":
+        sc = sc.to(torch.bfloat16).float()  # the reference's own score resolution
+    elif kind == "negative":
+        sc = -sc.abs() - 1
+    got = _topk(da, sc, hk, rep, k)
+    want = _topk_oracle(sc, hk, rep, k)
+    assert torch.equal(got, want)
+
+
+def test_topk_selector_api(da):
+    # IPUpperboundTopKSelector.top_k returns (S, Hk, rep, k) int64 like the reference
+    g = _g(3)
+    hk, rep, d, pages, p = 2, 2, 64, 64, 16
+    keys = torch.randn(hk, pages * p, d, generator=g)
+    q = torch.randn(1, 3, hk * rep, d, generator=g)
+    sel = da.topk_selector.IPUpperboundTopKSelector(keys.to(DEV), pages, device=DEV)
+    assert torch.equal(sel.chunk_min_max.cpu(), orc.page_minmax(keys, pages))
+    idx = sel.top_k(q.to(DEV), 8)
+    assert idx.shape == (3, hk, rep, 8) and idx.dtype == torch.int64
+    want = orc.select_pages(orc.scores_by_query_head(q, orc.page_minmax(keys, pages)), 8)
+    # scores can differ in the last bits between CPU and GPU summation orders: compare as
+    # sets per row unless the k-th gap is tiny (it is not for random normal data)
+    assert torch.equal(idx.cpu(), want)
+
+
+# --------------------------------------------------------------------- LRU ----
+
+class Tables:
+    def __init__(self, hk, ld, nh, page_dim=64, dtype=torch.float32, seed=0, warm=True, times=None):
+        self.hk, self.ld, self.nh = hk, ld, nh
+        self.dram = torch.randn(hk, ld, page_dim, generator=_g(seed)).to(dtype)
+        self.d2h = np.full((hk, ld), -1, np.int64)
+        self.h2d = np.full((hk, nh), -1, np.int64)
+        self.time = np.zeros((hk, nh), np.int64) if times is None else times.astype(np.int64).copy()
+        self.hbm = torch.zeros(hk, nh, page_dim, dtype=dtype)
+        if warm:
+            self.d2h[:, ld - nh:] = np.arange(nh)
+            self.h2d[:] = np.arange(ld - nh, ld)
+            self.hbm = self.dram[:, ld - nh:].clone()
+        self.step = 0
+
+    def to_device(self):
+        i32 = lambda a: torch.from_numpy(a.astype(np.int32)).to(DEV)
+        self.g_d2h, self.g_h2d, self.g_time = i32(self.d2h), i32(self.h2d), i32(self.time)
+        self.g_step = torch.full((self.hk,), self.step, dtype=torch.int32, device=DEV)
+        self.g_dram = self.dram.clone().pin_memory()
+        self.g_hbm = self.hbm.to(DEV)
+        self.g_status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        return self
+
+    def gpu_step(self, lst):
+        from dram_attention_b200 import _native
+        lib, s = _native.lib(), _native.stream_ptr()
+        kk = lst.shape[1]
+        gl = torch.from_numpy(lst.astype(np.int32)).to(DEV)
+        mp = torch.full((self.hk, kk), -9, dtype=torch.int32, device=DEV)
+        ms = torch.full((self.hk, kk), -9, dtype=torch.int32, device=DEV)
+        nm = torch.full((self.hk,), -9, dtype=torch.int32, device=DEV)
+        _native.check(lib.da_lru_update(gl.data_ptr(), kk, self.g_d2h.data_ptr(), self.ld,
+                                        self.g_h2d.data_ptr(), self.g_time.data_ptr(), self.nh,
+                                        self.g_step.data_ptr(), self.hk, mp.data_ptr(), ms.data_ptr(),
+                                        nm.data_ptr(), self.g_status.data_ptr(), s))
+        page_bytes = self.dram.shape[2] * self.dram.element_size()
+        _native.check(lib.da_fetch_pages(self.g_dram.data_ptr(), self.g_hbm.data_ptr(), mp.data_ptr(),
+                                         ms.data_ptr(), nm.data_ptr(), kk, self.hk, self.ld, self.nh,
+                                         page_bytes, s))
+        torch.cuda.synchronize()
+        return mp.cpu().numpy(), ms.cpu().numpy(), nm.cpu().numpy()
+
+    def cpu_step(self, lst, fn=orc.lru_walk):
+        self.step += 1
+        mp, ms, nm = fn(lst.astype(np.int64), self.d2h, self.h2d, self.time, self.step)
+        for h in range(self.hk):
+            m = int(nm[h])
+            if m:
+                self.hbm[h, torch.from_numpy(ms[h, :m])] = self.dram[h, torch.from_numpy(mp[h, :m])]
+        return mp, ms, nm
+
+    def assert_equal(self, tag=""):
+        assert np.array_equal(self.g_d2h.cpu().numpy(), self.d2h), tag
+        assert np.array_equal(self.g_h2d.cpu().numpy(), self.h2d), tag
+        assert np.array_equal(self.g_time.cpu().numpy(), self.time), tag
+        assert torch.equal(self.g_hbm.cpu(), self.hbm), tag
+        assert int(self.g_step[0]) == self.step and int(self.g_step[-1]) == self.step, tag
+
+
+@pytest.mark.parametrize("lists,prefill", [
+    ([[0, 1], [1, 2]], False),     # dram_attention/lru_triton_kernel_test.py:17-76 (cold load)
+    ([[4, 5], [5, 6]], True),      # :78-143 (eviction of the oldest slots)
+    ([[0, 2], [1, 3]], False),     # :145-204 (per-head lists)
+])
+def test_lru_reference_known_answers(da, lists, prefill):
+    t = Tables(2, 8, 4, warm=False, times=np.tile(np.arange(4), (2, 1)))
+    if prefill:
+        t.d2h[:, :4] = np.arange(4)
+        t.h2d[:] = np.arange(4)
+        t.hbm = t.dram[:, :4].clone()
+    t.step = 3  # the kernel increments: the reference test passes step 4
+    t.to_device()
+    lst = np.array(lists)
+    mp, ms, nm = t.gpu_step(lst)
+    hbm, dram = t.g_hbm.cpu(), t.dram
+    for h in range(2):
+        for j in range(2):
+            assert torch.equal(hbm[h, j], dram[h, lst[h, j]])
+            assert int(t.g_d2h[h, lst[h, j]]) == j
+            assert int(t.g_h2d[h, j]) == lst[h, j]
+            assert int(t.g_time[h, j]) == 4
+    assert nm.tolist() == [2, 2] and ms[:, :2].tolist() == [[0, 1], [0, 1]]
+    if prefill:
+        assert t.g_d2h[:, :2].cpu().tolist() == [[-1, -1], [-1, -1]]
+    assert int(t.g_status) == 0 and t.g_step.cpu().tolist() == [4, 4]
+
+
+def test_lru_matches_reference_kernel_runs(da, golden_dir):
+    g = np.load(os.path.join(golden_dir, "lru_kernel_cases.npz"))
+    for c in range(int(g["n_cases"][0])):
+        dram = g[f"c{c}_dram"]
+        lists = g[f"c{c}_lists"]
+        hk, ld, pd = dram.shape
+        nh = g[f"c{c}_h2d"].shape[2]
+        t = Tables(hk, ld, nh, page_dim=pd)
+        t.dram = torch.from_numpy(dram)
+        t.hbm = t.dram[:, ld - nh:].clone()
+        t.to_device()
+        for s in range(lists.shape[0]):
+            t.gpu_step(lists[s])
+            assert np.array_equal(t.g_d2h.cpu().numpy(), g[f"c{c}_d2h"][s]), (c, s)
+            assert np.array_equal(t.g_h2d.cpu().numpy(), g[f"c{c}_h2d"][s]), (c, s)
+            assert np.array_equal(t.g_time.cpu().numpy(), g[f"c{c}_time"][s]), (c, s)
+            assert np.array_equal(t.g_hbm.cpu().numpy(), g[f"c{c}_hbm"][s]), (c, s)
+        assert int(t.g_status) == 0
+
+
+@pytest.mark.parametrize("hk,ld,nh,kk,steps,page_dim,dtype", [
+    (2, 256, 128, 128, 12, 2048, torch.float32),      # plumbing geometry
+    (8, 8192, 2048, 1024, 6, 4096, torch.bfloat16),   # Llama layer geometry
+    (3, 100, 37, 20, 40, 24, torch.float32),          # odd sizes, page not a multiple of 16 bytes... (96 B ok)
+    (2, 70, 33, 33, 30, 3, torch.float32),            # 12-byte pages: bytewise copy path
+    (1, 9000, 8192, 4000, 4, 8, torch.float32),       # largest slot table
+    (2, 5000, 4096, 2048, 5, 64, torch.bfloat16),     # 1M-context layer geometry (per-head)
+    (2, 600, 300, 300, 300, 8, torch.float32),        # many steps: > 8 bits of time
+])
+def test_lru_random_trajectories_bit_exact(da, hk, ld, nh, kk, steps, page_dim, dtype):
+    rng = np.random.default_rng(hk * 1000 + ld)
+    t = Tables(hk, ld, nh, page_dim=page_dim, dtype=dtype, seed=ld).to_device()
+    for s in range(steps):
+        # a hot set that drifts (hits), fresh pages (misses) and duplicates inside the list
+        distinct = int(rng.integers(1, min(kk, nh) + 1))
+        pool = rng.choice(ld, size=distinct, replace=False)
+        lst = rng.choice(pool, size=(hk, kk))
+        mp_c, ms_c, nm_c = t.cpu_step(lst)
+        mp_g, ms_g, nm_g = t.gpu_step(lst)
+        assert np.array_equal(nm_g, nm_c), s
+        for h in range(hk):
+            assert np.array_equal(mp_g[h, :nm_c[h]], mp_c[h, :nm_c[h]]), (s, h)
+            assert np.array_equal(ms_g[h, :nm_c[h]], ms_c[h, :nm_c[h]]), (s, h)
+        t.assert_equal(f"step {s}")
+        # invariants: the two maps are inverse of each other; slots hold their page
+        d2h, h2d = t.g_d2h.cpu().numpy(), t.g_h2d.cpu().numpy()
+        for h in range(hk):
+            assert np.array_equal(d2h[h, h2d[h]], np.arange(nh))
+            assert (d2h[h] >= 0).sum() == nh
+    assert int(t.g_status) == 0
+
+
+def test_lru_overflow_and_bad_page_are_reported(da):
+    t = Tables(1, 16, 4).to_device()
+    lst = np.array([[0, 1, 2, 3, 4, 5]])  # 6 distinct non-resident pages, 4 slots
+    before = (t.g_d2h.clone(), t.g_h2d.clone())
+    t.gpu_step(lst)
+    assert int(t.g_status) & 2
+    assert torch.equal(t.g_d2h, before[0]) and torch.equal(t.g_h2d, before[1])
+    t.g_status.zero_()
+    mp, ms, nm = t.gpu_step(np.array([[99, -3, 1, 1, 15, 99]]))
+    assert int(t.g_status) & 1
+    assert nm.tolist() == [1] and mp[0, 0] == 1
+    assert int(t.g_d2h[0, 1]) == int(ms[0, 0])
+
+
+def test_lru_cache_class_mirrors_reference(da):
+    # dram_attention/lru_cache_test.py:16-98
+    k = torch.randn(4, 1024 * 8, 64, device=DEV)
+    v = torch.randn(4, 1024 * 8, 64, device=DEV)
+    c = da.LRUCache(k, v, page_size=16, top_k=10)
+    assert (c.num_kv_heads, c.num_dram_pages, c.num_hbm_pages, c.head_dim, c.page_size, c.top_k) == \
+        (4, 512, 102, 64, 16, 10)
+    assert torch.all(c.dram_page_to_hbm_page_mapping[:, -102:] == torch.arange(102).cuda())
+    assert torch.all(c.dram_page_to_hbm_page_mapping[:, :-102] == -1)
+    kc, vc = c.load_(torch.randint(0, 512, (4, 10), device=DEV))
+    assert kc.shape == (4, 102 * 16, 64) and vc.shape == (4, 102 * 16, 64)
+    assert c.current_step == 1
+    out = c.get_kv_cache_(torch.randn(1, 10, 4, 64, device=DEV))
+    assert out.k_cache.shape == (4, 102 * 16, 64) and out.v_cache.shape == (4, 102 * 16, 64)
+    assert c.current_step == 2
+    c.get_kv_cache_(torch.randn(1, 10, 4, 64, device=DEV))
+    assert c.current_step == 3
+    assert out.k_cache.device.type == "cuda" and torch.any(out.k_cache != 0) and torch.any(out.v_cache != 0)
+    c.check_status()
+    # the slot table holds exactly the pages the map says, keys and values in place
+    h2d = c.hbm_page_to_dram_page_mapping.cpu().long()
+    kk = k.cpu().view(4, 512, 16, 64)
+    vv = v.cpu().view(4, 512, 16, 64)
+    for h in range(4):
+        assert torch.equal(out.k_cache[h].cpu().view(102, 16, 64), kk[h, h2d[h]])
+        assert torch.equal(out.v_cache[h].cpu().view(102, 16, 64), vv[h, h2d[h]])
+    for page_size in (8, 16, 32):
+        c2 = da.LRUCache(torch.randn(4, 1024 * 8, 64), torch.randn(4, 1024 * 8, 64), page_size=page_size,
+                         top_k=10)
+        assert c2.page_size == page_size and c2.num_dram_pages == 1024 * 8 // page_size and c2.top_k == 10
+    with pytest.raises(AssertionError):
+        da.LRUCache(torch.randn(4, 1007 * 8, 64), torch.randn(4, 1007 * 8, 64), page_size=16, top_k=10)
+    c3 = da.LRUCache(torch.randn(4, 1024 * 8, 64), torch.randn(4, 1024 * 8, 64), page_size=16,
+                     lru_hbm_cache_size=1024, top_k=10)
+    assert c3.num_hbm_pages == 64 and c3.top_k == 10
+
+
+# --------------------------------------------------------------- attention ----
+
+def _attention_case(da, dtype, d, hk, rep, n_prefix, cap, t_new, seed, device_pos, tol, calls=2):
+    from dram_attention_b200 import _native
+    lib = _native.lib()
+    g = _g(seed)
+    hq = hk * rep
+    prefix = torch.randn(hk, n_prefix, 2, d, generator=g).to(dtype)
+    local_k = torch.randn(cap, hk, d, generator=g).to(dtype)
+    local_v = torch.randn(cap, hk, d, generator=g).to(dtype)
+    dram_tokens = 4096
+    ws_bytes = lib.da_decode_attention_workspace_bytes(hk, rep, d)
+    ws = torch.zeros(ws_bytes, dtype=torch.uint8, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    g_prefix, g_lk, g_lv = prefix.to(DEV), local_k.to(DEV), local_v.to(DEV)
+    for call in range(calls):
+        q = (torch.randn(hq, d, generator=g) * 1.5).to(dtype)
+        nk = torch.randn(hk, d, generator=g).to(dtype)
+        nv = torch.randn(hk, d, generator=g).to(dtype)
+        t = t_new + call
+        if t >= cap:
+            break
+        g_q, g_nk, g_nv = q.to(DEV), nk.to(DEV), nv.to(DEV)
+        out = torch.empty(hq, d, dtype=dtype, device=DEV)
+        lse = torch.empty(hq, dtype=torch.float32, device=DEV)
+        pos = torch.tensor([dram_tokens + t], dtype=torch.int32, device=DEV)
+        _native.check(lib.da_decode_attention(
+            g_q.data_ptr(), g_prefix.data_ptr(), g_prefix.stride(0), n_prefix, g_lk.data_ptr(),
+            g_lv.data_ptr(), g_lk.stride(0), g_lk.stride(1), cap, g_nk.data_ptr(), g_nv.data_ptr(),
+            pos.data_ptr() if device_pos else 0, 0 if device_pos else dram_tokens + t, dram_tokens,
+            out.data_ptr(), lse.data_ptr(), ws.data_ptr(), ws_bytes, status.data_ptr(), hk, rep, d,
+            _native.dtype_code(dtype), _native.stream_ptr()))
+        torch.cuda.synchronize()
+        assert int(status) == 0
+        # oracle: append, then prefix part + local part + merge
+        local_k[t], local_v[t] = nk, nv
+        po, pl = orc.attend(q, prefix[:, :, 0].transpose(0, 1), prefix[:, :, 1].transpose(0, 1))
+        so, sl = orc.attend(q, local_k[:t + 1], local_v[:t + 1])
+        want = orc.combine(po, so, pl, sl)
+        want_lse = torch.logaddexp(pl, sl)
+        got = out.float().cpu()
+        assert (got - want).abs().max().item() <= tol, (call, (got - want).abs().max().item())
+        assert torch.allclose(lse.cpu(), want_lse, rtol=1e-4, atol=1e-4)
+        assert torch.equal(g_lk.cpu(), local_k) and torch.equal(g_lv.cpu(), local_v)
+        assert int(ws[:1024].view(torch.int32).abs().sum()) == 0  # tickets back at zero
+
+
+@pytest.mark.parametrize("dtype,d,hk,rep,n_prefix,cap,t_new,device_pos", [
+    (torch.float32, 64, 2, 4, 2048, 272, 240, False),     # plumbing geometry
+    (torch.bfloat16, 128, 8, 4, 32768, 4160, 4080, True), # Llama layer geometry
+    (torch.bfloat16, 128, 2, 4, 160, 64, 0, True),        # first local token only
+    (torch.bfloat16, 128, 2, 4, 24, 64, 15, False),       # prefix not a multiple of 16 tokens
+    (torch.bfloat16, 128, 1, 4, 8, 40, 16, True),         # tiny prefix, unit boundary in local
+    (torch.float16, 128, 2, 2, 1000, 100, 17, False),
+    (torch.float32, 128, 2, 1, 520, 90, 33, True),
+    (torch.bfloat16, 64, 3, 8, 700, 50, 47, False),
+    (torch.bfloat16, 128, 1, 8, 5000, 300, 255, True),
+    (torch.float32, 64, 16, 2, 300, 33, 31, False),
+    (torch.bfloat16, 128, 1, 1, 65536, 8224, 8176, True), # one head of the 1M-context layer
+])
+def test_decode_attention_matches_oracle(da, dtype, d, hk, rep, n_prefix, cap, t_new, device_pos):
+    # tolerances: 1e-4 absolute in float32, 2e-2 absolute in 16-bit types
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    _attention_case(da, dtype, d, hk, rep, n_prefix, cap, t_new, n_prefix + t_new, device_pos, tol)
+
+
+def test_decode_attention_bad_position_is_reported(da):
+    from dram_attention_b200 import _native
+    lib = _native.lib()
+    hk, rep, d, n_prefix, cap = 2, 4, 128, 64, 32
+    z = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=DEV)
+    ws_bytes = lib.da_decode_attention_workspace_bytes(hk, rep, d)
+    ws = torch.zeros(ws_bytes, dtype=torch.uint8, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    prefix, lk, lv, q, nk, nv, out = z(hk, n_prefix, 2, d), z(cap, hk, d), z(cap, hk, d), z(hk * rep, d), \
+        z(hk, d) + 1, z(hk, d) + 1, z(hk * rep, d)
+    _native.check(lib.da_decode_attention(
+        q.data_ptr(), prefix.data_ptr(), prefix.stride(0), n_prefix, lk.data_ptr(), lv.data_ptr(),
+        lk.stride(0), lk.stride(1), cap, nk.data_ptr(), nv.data_ptr(), 0, 1000 + cap, 1000, out.data_ptr(), 0,
+        ws.data_ptr(), ws_bytes, status.data_ptr(), hk, rep, d, 2, _native.stream_ptr()))
+    torch.cuda.synchronize()
+    assert int(status) & 4
+    assert float(lk.abs().sum()) == 0  # nothing appended outside the window
