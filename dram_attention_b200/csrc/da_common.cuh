@@ -132,7 +132,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 }
 
 // Bounded wait: gives up after `limit` polls and reports false.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, int limit = (1 << 22)) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, int limit = (1 << 20)) {
     for (int i = 0; i < limit; ++i)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
