@@ -1,0 +1,423 @@
+#!/usr/bin/env python
+"""Benchmark of the generate stage on the Llama-3-8B-shaped 128K-context decode layer.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+One "step" = one generate step (one new token) of one attention layer: page
+scoring, top-k selection, LRU update, miss fetch, decode attention.  Prints one
+JSON line.
+
+value   decode tok/s with every input resident in HBM: the K timed steps are
+        captured, with their own device-resident inputs, in one CUDA graph and
+        timed with CUDA events (max over ranks).
+e2e     the same metric through the operator API with HOST inputs: per step the
+        query/key/value are copied from pinned host memory, one captured step is
+        replayed, the output is copied back and the stream is synchronised.
+roofline  attention kernel (the dominant launch): algorithmic bytes / its mean
+        launch time, measured with CUDA events around each stage of un-captured
+        steps; peak = the measured HBM copy bandwidth of this pool.
+cpu_baseline  the CPU oracle (a port of the reference's pure-PyTorch path) timed on
+        a bounded sample of the same workload on this box's host cores.
+
+With --gpus N > 1 (launched by torchrun, one rank per GPU) the KV heads are
+sharded over the ranks and the per-head outputs are all-gathered over NCCL
+(total work fixed: strong scaling).  --impl reference times the CPU port of the
+reference path on rank 0 only.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "decode tok/s at 128K ctx (Llama-3-8B attn shape)"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--dram-tokens", type=int, default=131072, help="prefix tokens kept in DRAM")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-steps", type=int, default=16, help="un-captured steps timed stage by stage")
+    return ap.parse_args()
+
+
+def workload_config(args, w):
+    return {
+        "workload": w.name,
+        "batch": 1, "n_q_heads": w.n_q_heads, "n_kv_heads": w.n_kv_heads, "head_dim": w.head_dim,
+        "dram_prefix_tokens": w.dram_tokens, "page_size": w.page_size,
+        "lru_hbm_cache_size": w.lru_hbm_cache_size, "local_cache_size": w.local_cache_size,
+        "top_k": w.top_k, "prefill_len": w.prefill_len,
+        "l2": "inputs larger than L2 (185 MB touched per step vs 126 MB)",
+    }
+
+
+class ClockSampler:
+    """Polls SM clock and throttle reasons through NVML (read-only) in a thread."""
+
+    def __init__(self, index: int, period_s: float = 0.002):
+        self.samples = []  # (t, sm_mhz, reasons)
+        self.period = period_s
+        self.stop_flag = False
+        self.thread = None
+        self.max_mhz = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception as e:  # NVML missing: report that, do not fail the bench
+            self.nv = None
+            self.err = repr(e)
+
+    def _run(self):
+        nv = self.nv
+        while not self.stop_flag:
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                try:
+                    reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                self.samples.append((time.perf_counter(), mhz, reasons))
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def start(self):
+        if self.nv is not None:
+            self.thread = threading.Thread(target=self._run, daemon=True)
+            self.thread.start()
+
+    def stop(self):
+        self.stop_flag = True
+        if self.thread is not None:
+            self.thread.join()
+
+    def summary(self, windows):
+        if self.nv is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvml unavailable: " + self.err]}
+        inside = [s for s in self.samples if any(a <= s[0] <= b for a, b in windows)]
+        use = inside if inside else self.samples
+        names = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
+                 0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown"}
+        bits = 0
+        for s in use:
+            bits |= s[2]
+        return {"sm_mhz": statistics.median(s[1] for s in use) if use else None,
+                "sm_max_mhz": self.max_mhz,
+                "reasons": [n for b, n in names.items() if bits & b],
+                "samples_in_timed_regions": len(inside), "samples": len(self.samples)}
+
+
+def hbm_peak_gbs():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+# --------------------------------------------------------------------------------
+# CPU port of the reference path (oracle) -- cpu_baseline leg and --impl reference
+# --------------------------------------------------------------------------------
+
+def cpu_reference_steps(w, n_warm, n_timed, budget_s=None):
+    """Steps of the CPU oracle on workload w; returns (tok/s, steps timed, threads)."""
+    import torch
+    from oracle import dram_attention_oracle as orc
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    o = orc.OracleDRAMAttention(dtype=torch.float32, **w.ctor_kwargs())
+    o.init_cache(w.k.float(), w.v.float())
+    s = w.k.shape[1]
+    for i in range(n_warm):
+        o.generate(w.xq[i].float(), w.xk[i].float(), w.xv[i].float(), s + i)
+    t0 = time.perf_counter()
+    done = 0
+    for i in range(n_warm, n_warm + n_timed):
+        o.generate(w.xq[i].float(), w.xk[i].float(), w.xv[i].float(), s + i)
+        done += 1
+        if budget_s is not None and time.perf_counter() - t0 > budget_s and done >= 2:
+            break
+    dt = time.perf_counter() - t0
+    return done / dt, done, threads
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    from dram_attention_b200.synthetic import llama_layer_workload
+    k, wu = args.steps, args.warmup
+    w = llama_layer_workload(seed=0, steps=k + wu, dram_tokens=args.dram_tokens, max_out=k + wu)
+    tps, done, threads = cpu_reference_steps(w, wu, k)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tps, "unit": "tok/s", "n_gpus": args.gpus,
+        "steps": done, "warmup": wu, "ms_per_step": 1e3 / tps, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args, w),
+        "cpu_baseline": {"value": tps, "unit": "tok/s", "cores": threads, "kind": "port",
+                         "sample": f"{done} full generate steps of the same layer after {wu} warm-up steps, "
+                                   "CPU port of the reference's pure-PyTorch path (fp32 scores, fp64 attention)"},
+        "e2e": {"value": tps, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------
+# B200 arm
+# --------------------------------------------------------------------------------
+
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+    import dram_attention_b200 as da
+    from dram_attention_b200.sharded import KVHeadShardedDRAMAttention, head_range
+    from dram_attention_b200.synthetic import llama_layer_workload
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun for N > 1")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    K, W = args.steps, max(args.warmup, 3)
+    P = max(0, args.profile_steps)
+    total = (W + K) * 2 + P
+    w = llama_layer_workload(seed=0, steps=total, dram_tokens=args.dram_tokens, max_out=total)
+    hk_all, rep, D = w.n_kv_heads, w.n_q_heads // w.n_kv_heads, w.head_dim
+    lo, hi = head_range(hk_all, rank, world)
+    hk = hi - lo
+    esz = 2
+
+    ctor = w.ctor_kwargs()
+    ctor.pop("n_kv_heads")
+    if world == 1:
+        op = da.DRAMAttention(n_kv_heads=hk_all, device=dev, dtype=w.dtype, **ctor)
+        inner = op
+    else:
+        op = KVHeadShardedDRAMAttention(n_kv_heads=hk_all, presliced=True, device=dev, dtype=w.dtype, **ctor)
+        inner = op.inner
+    inner.init_cache(w.k[:, :, lo:hi].to(dev), w.v[:, :, lo:hi].to(dev))
+    lc = inner.lru_cache
+    S = w.prefill_len
+
+    # this rank's slice of every step's inputs: pinned host copies and device copies
+    hq = w.xq[:, :, :, lo * rep:hi * rep].contiguous().pin_memory()
+    hkk = w.xk[:, :, :, lo:hi].contiguous().pin_memory()
+    hv = w.xv[:, :, :, lo:hi].contiguous().pin_memory()
+    dq, dk, dv = hq.to(dev), hkk.to(dev), hv.to(dev)
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    windows = []
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    # ---------------- value: K captured steps, inputs resident in HBM -----------------
+    step = 0
+    for _ in range(W):
+        op(dq[step], dk[step], dv[step], start_pos=S + step, stage="generate")
+        step += 1
+    torch.cuda.synchronize()
+    outs = torch.empty(K, 1, 1, w.n_q_heads, D, dtype=w.dtype, device=dev)
+    graph = torch.cuda.CUDAGraph()
+    captured = True
+    first = step
+    try:
+        with torch.cuda.graph(graph):
+            for i in range(K):
+                outs[i].copy_(op(dq[first + i], dk[first + i], dv[first + i], start_pos=S + first + i,
+                                 stage="generate"))
+    except Exception as e:  # e.g. a collective that cannot be captured: time eager launches instead
+        captured = False
+        capture_error = repr(e)
+        torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t_a = time.perf_counter()
+    ev0.record()
+    if captured:
+        graph.replay()
+    else:
+        for i in range(K):
+            outs[i].copy_(op(dq[first + i], dk[first + i], dv[first + i], start_pos=S + first + i,
+                             stage="generate"))
+    ev1.record()
+    barrier()
+    windows.append((t_a, time.perf_counter()))
+    step += K
+    ms_value = ev0.elapsed_time(ev1)
+
+    # ---------------- e2e: host inputs, one captured step per call ----------------------
+    xq_s, xk_s, xv_s = dq[0].clone(), dk[0].clone(), dv[0].clone()
+    out_s = torch.empty(1, 1, w.n_q_heads, D, dtype=w.dtype, device=dev)
+    out_h = torch.empty(1, 1, w.n_q_heads, D, dtype=w.dtype).pin_memory()
+    pos = torch.tensor([S + step], dtype=torch.int32, device=dev)
+    step_graph = torch.cuda.CUDAGraph()
+    step_captured = True
+    try:
+        with torch.cuda.graph(step_graph):
+            out_s.copy_(op(xq_s, xk_s, xv_s, start_pos=pos, stage="generate"))
+            pos.add_(1)
+    except Exception:
+        step_captured = False
+        torch.cuda.synchronize()
+
+    def e2e_step(i):
+        xq_s.copy_(hq[i], non_blocking=True)
+        xk_s.copy_(hkk[i], non_blocking=True)
+        xv_s.copy_(hv[i], non_blocking=True)
+        if step_captured:
+            step_graph.replay()
+        else:
+            out_s.copy_(op(xq_s, xk_s, xv_s, start_pos=pos, stage="generate"))
+            pos.add_(1)
+        out_h.copy_(out_s, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(W):
+        e2e_step(step)
+        step += 1
+    barrier()
+    t_a = time.perf_counter()
+    ev0.record()
+    for _ in range(K):
+        e2e_step(step)
+        step += 1
+    ev1.record()
+    barrier()
+    windows.append((t_a, time.perf_counter()))
+    ms_e2e = ev0.elapsed_time(ev1)
+
+    # ---------------- per-stage timing of un-captured steps (roofline) -------------------
+    stage_names = ["score", "topk", "lru", "fetch", "attention"]
+    stage_ms = {n: [] for n in stage_names}
+    misses = []
+    k_pages = w.top_k // w.page_size
+    list_len = rep * k_pages
+    out_p = torch.empty(1, 1, hk * rep, D, dtype=w.dtype, device=dev)
+    t_a = time.perf_counter()
+    for _ in range(P):
+        q, kk, vv = dq[step], dk[step], dv[step]
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+        ev[0].record()
+        lc.top_k_selector.score_(q, k_pages)
+        ev[1].record()
+        page_list = lc.top_k_selector.select_(1, rep, k_pages)
+        ev[2].record()
+        lc.update_tables_(page_list)
+        ev[3].record()
+        lc.fetch_(list_len)
+        ev[4].record()
+        inner.attend_(q, kk, vv, S + step, out_p)
+        ev[5].record()
+        torch.cuda.synchronize()
+        for j, n in enumerate(stage_names):
+            stage_ms[n].append(ev[j].elapsed_time(ev[j + 1]))
+        misses.append(int(lc.last_miss_counts(list_len).sum()))
+        step += 1
+    windows.append((t_a, time.perf_counter()))
+    inner.check_status()
+    sampler.stop()
+
+    # ---------------- reduce over ranks -------------------------------------------------
+    t = torch.tensor([ms_value, ms_e2e], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_value, ms_e2e = float(t[0]), float(t[1])
+
+    mean = lambda xs: (sum(xs) / len(xs)) if xs else None
+    stage_us = {n: (mean(v) * 1e3 if v else None) for n, v in stage_ms.items()}
+    t_local = (S + step - 1) - w.dram_tokens          # local tokens at the last profiled step
+    n_slots_tokens = w.lru_hbm_cache_size
+    b_attn = hk * (n_slots_tokens + t_local + 1) * 2 * D * esz + 2 * hk * rep * D * esz
+    b_score = hk * (w.dram_tokens // w.page_size) * 2 * D * esz + hk * rep * D * esz
+    peak, peak_kind = hbm_peak_gbs()
+    roofline = None
+    if stage_us["attention"]:
+        ach = b_attn / (stage_us["attention"] * 1e-6) / 1e9
+        roofline = {"bound": "hbm", "kernel": "decode_attention_kernel", "achieved": ach, "peak": peak,
+                    "peak_kind": peak_kind + " HBM copy bandwidth", "unit": "GB/s", "frac": ach / peak,
+                    "traffic": None, "algorithmic_bytes_per_launch": b_attn,
+                    "launch_us": stage_us["attention"]}
+    roofline_score = None
+    if stage_us["score"]:
+        ach = b_score / (stage_us["score"] * 1e-6) / 1e9
+        roofline_score = {"bound": "hbm", "kernel": "score_pages_kernel", "achieved": ach, "peak": peak,
+                          "unit": "GB/s", "frac": ach / peak, "algorithmic_bytes_per_launch": b_score,
+                          "launch_us": stage_us["score"]}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": K / (ms_value * 1e-3), "unit": "tok/s", "n_gpus": world,
+            "steps": K, "warmup": W, "ms_per_step": ms_value / K, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": dict(workload_config(args, w),
+                           parallelism=("single GPU" if world == 1 else f"KV heads sharded {world}-way, "
+                                        "NCCL all-gather of per-head outputs"),
+                           timed_region=("one CUDA graph of K steps" if captured else
+                                         "K eager steps (graph capture failed: " + capture_error + ")")),
+            "clocks": sampler.summary(windows),
+            "e2e": {"value": K / (ms_e2e * 1e-3), "unit": "tok/s",
+                    "h2d_bytes_per_step": (hq[0].numel() + hkk[0].numel() + hv[0].numel()) * esz,
+                    "d2h_bytes_per_step": out_h.numel() * esz, "ms_per_step": ms_e2e / K,
+                    "per_step": "pinned H2D of q/k/v, one captured step, D2H of the output, stream sync"},
+            "gpu_launches": 5 * K,
+            "roofline": roofline,
+            "roofline_score": roofline_score,
+            "stage_us": stage_us,
+            "misses_per_step": mean(misses),
+            "fetch_fraction_of_step": (stage_us["fetch"] / sum(v for v in stage_us.values())
+                                       if stage_us["fetch"] else None),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            tps, done, threads = cpu_reference_steps(w, 1, min(32, total - 1), budget_s=15.0)
+            line["cpu_baseline"] = {
+                "value": tps, "unit": "tok/s", "cores": threads, "kind": "port",
+                "sample": f"{done} full generate steps of the same layer (1 warm-up) on the host cores: "
+                          "CPU port of the reference's pure-PyTorch path"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -7,9 +7,10 @@
 // and the same channels of the max row), so a warp streams two pages per step
 // and a 16-lane shuffle tree finishes the channel sum.
 //
-// max(q*mn, q*mx) with mn <= mx equals max(q,0)*mx + min(q,0)*mn: one of the
-// two terms is an exact zero, so two FMAs per (channel, query head) reproduce
-// the formula without a compare.
+// max(q*a, q*b) equals max(q,0)*max(a,b) + min(q,0)*min(a,b): one of the two
+// terms is an exact zero, so after ordering the pair once per channel, two FMAs
+// per (channel, query head) reproduce the formula for all `rep` heads.  (Real
+// summaries already have a <= b; the reference's own tests feed unordered rows.)
 
 #include "da_common.cuh"
 
@@ -72,6 +73,12 @@ score_pages_kernel(const T *__restrict__ q, const T *__restrict__ summaries, flo
             Unpack<T, VEC>::run(wmn[u], mn);
             Unpack<T, VEC>::run(wmx[u], mx);
 #pragma unroll
+            for (int i = 0; i < VEC; ++i) {
+                const float lo = fminf(mn[i], mx[i]);
+                mx[i] = fmaxf(mn[i], mx[i]);
+                mn[i] = lo;
+            }
+#pragma unroll
             for (int r = 0; r < REP; ++r) {
                 float a = 0.f;
 #pragma unroll
@@ -109,7 +116,8 @@ score_pages_generic_kernel(const T *__restrict__ q, const T *__restrict__ summar
             float a = 0.f;
             for (int d = lane; d < head_dim; d += 32) {
                 const float qv = to_float(qrow[d]);
-                a = fmaf(fmaxf(qv, 0.f), to_float(mx[d]), fmaf(fminf(qv, 0.f), to_float(mn[d]), a));
+                const float lo = to_float(mn[d]), hi = to_float(mx[d]);
+                a += fmaxf(qv * lo, qv * hi);
             }
 #pragma unroll
             for (int off = 16; off >= 1; off >>= 1) a += __shfl_xor_sync(DA_FULL_MASK, a, off);

@@ -124,26 +124,33 @@ class DRAMAttention(torch.nn.Module):
         with torch.cuda.device(xq.device):
             # score -> select -> LRU update -> fetch (no-ops for a fully resident prefix)
             self.lru_cache.get_kv_cache_(xq)
-            prefix = self.lru_cache.hbm_kv_cache
-            n_prefix_tokens = (self.lru_cache.num_tokens if isinstance(self.lru_cache, DummyCache)
-                               else self.lru_cache.num_hbm_pages * self.page_size)
             out = torch.empty_like(xq)
-            if n_prefix_tokens == 0:
-                raise RuntimeError("empty DRAM prefix is not supported")
-            buf, nbytes, status = self._workspace(rep, xq.device)
-            if isinstance(start_pos, torch.Tensor):
-                assert start_pos.dtype == torch.int32 and start_pos.is_cuda and start_pos.numel() == 1
-                pos_dev, pos_host = start_pos.data_ptr(), 0
-            else:
-                pos_dev, pos_host = 0, int(start_pos)
-            _native.check(_native.lib().da_decode_attention(
-                xq.data_ptr(), prefix.data_ptr(), prefix.stride(0), n_prefix_tokens,
-                self.cache_k.data_ptr(), self.cache_v.data_ptr(), self.cache_k.stride(1),
-                self.cache_k.stride(2), self.cache_k.shape[1], xk.data_ptr(), xv.data_ptr(),
-                pos_dev, pos_host, self.dram_kv_cache_size, out.data_ptr(), 0, buf.data_ptr(), nbytes,
-                status.data_ptr(), self.n_kv_heads, rep, self.head_dim, _native.dtype_code(xq.dtype),
-                _native.stream_ptr()), "da_decode_attention")
+            self.attend_(xq, xk, xv, start_pos, out)
         return out
+
+    def attend_(self, xq, xk, xv, start_pos, out, lse=None) -> None:
+        """Enqueue the decode attention over the current slot table and the local
+        window (appends xk/xv at start_pos - dram_kv_cache_size first)."""
+        rep = xq.shape[2] // self.n_kv_heads
+        prefix = self.lru_cache.hbm_kv_cache
+        n_prefix_tokens = (self.lru_cache.num_tokens if isinstance(self.lru_cache, DummyCache)
+                           else self.lru_cache.num_hbm_pages * self.page_size)
+        if n_prefix_tokens == 0:
+            raise RuntimeError("empty DRAM prefix is not supported")
+        buf, nbytes, status = self._workspace(rep, xq.device)
+        if isinstance(start_pos, torch.Tensor):
+            assert start_pos.dtype == torch.int32 and start_pos.is_cuda and start_pos.numel() == 1
+            pos_dev, pos_host = start_pos.data_ptr(), 0
+        else:
+            pos_dev, pos_host = 0, int(start_pos)
+        _native.check(_native.lib().da_decode_attention(
+            xq.data_ptr(), prefix.data_ptr(), prefix.stride(0), n_prefix_tokens,
+            self.cache_k.data_ptr(), self.cache_v.data_ptr(), self.cache_k.stride(1),
+            self.cache_k.stride(2), self.cache_k.shape[1], xk.data_ptr(), xv.data_ptr(),
+            pos_dev, pos_host, self.dram_kv_cache_size, out.data_ptr(),
+            0 if lse is None else lse.data_ptr(), buf.data_ptr(), nbytes,
+            status.data_ptr(), self.n_kv_heads, rep, self.head_dim, _native.dtype_code(xq.dtype),
+            _native.stream_ptr()), "da_decode_attention")
 
     def check_status(self) -> None:
         """Synchronises; raises if any kernel of this operator flagged a problem."""

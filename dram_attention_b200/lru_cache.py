@@ -126,21 +126,34 @@ class LRUCache(torch.nn.Module):
                                            mk(self.num_kv_heads))
         return bufs
 
-    def _load_int32_(self, page_list: torch.Tensor) -> None:
+    def update_tables_(self, page_list: torch.Tensor) -> None:
+        """Enqueue the LRU table update for an int32 page list (Hk, list_len): step
+        counters, hit stamps, victim choice, both maps, and the device-side miss list."""
         list_len = page_list.shape[1]
         miss_pages, miss_slots, n_miss = self._miss_buffers(list_len)
-        lib, s = _native.lib(), _native.stream_ptr()
-        _native.check(lib.da_lru_update(
+        _native.check(_native.lib().da_lru_update(
             page_list.data_ptr(), list_len, self.dram_page_to_hbm_page_mapping.data_ptr(),
             self.num_dram_pages, self.hbm_page_to_dram_page_mapping.data_ptr(),
             self.page_access_time.data_ptr(), self.num_hbm_pages, self.step_counters.data_ptr(),
             self.num_kv_heads, miss_pages.data_ptr(), miss_slots.data_ptr(), n_miss.data_ptr(),
-            self.status.data_ptr(), s), "da_lru_update")
+            self.status.data_ptr(), _native.stream_ptr()), "da_lru_update")
+
+    def fetch_(self, list_len: int) -> None:
+        """Enqueue the gather-copy of the pages the last update_tables_ found missing."""
+        miss_pages, miss_slots, n_miss = self._miss_buffers(list_len)
         page_bytes = self.dram_kv_cache.shape[2] * self.dram_kv_cache.element_size()
-        _native.check(lib.da_fetch_pages(
+        _native.check(_native.lib().da_fetch_pages(
             self.dram_kv_cache.data_ptr(), self.hbm_kv_cache.data_ptr(), miss_pages.data_ptr(),
             miss_slots.data_ptr(), n_miss.data_ptr(), list_len, self.num_kv_heads, self.num_dram_pages,
-            self.num_hbm_pages, page_bytes, s), "da_fetch_pages")
+            self.num_hbm_pages, page_bytes, _native.stream_ptr()), "da_fetch_pages")
+
+    def _load_int32_(self, page_list: torch.Tensor) -> None:
+        self.update_tables_(page_list)
+        self.fetch_(page_list.shape[1])
+
+    def last_miss_counts(self, list_len: int) -> torch.Tensor:
+        """int32 (Hk,) device tensor: pages fetched per head by the last step."""
+        return self._miss_buffers(list_len)[2]
 
     def kv_views(self) -> CacheOutput:
         c = self.hbm_kv_cache.view(self.num_kv_heads, self.num_hbm_pages * self.page_size, 2, self.head_dim)

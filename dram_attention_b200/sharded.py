@@ -1,0 +1,86 @@
+"""KV-head sharding of the operator across the GPUs of one node.
+
+The reference has no multi-GPU path.  Every piece of state of the generate stage
+is indexed by KV head (DRAM pages, summaries, slot table, LRU tables, local
+window), and a GQA group is a contiguous run of query heads, so rank g of G simply
+owns KV heads [g*Hk/G, (g+1)*Hk/G) and the query heads of those groups.  The only
+exchange is the all-gather of the per-head outputs: rank-major concatenation of
+(Hq/G, D) blocks is exactly the (1, 1, Hq, D) output.
+"""
+
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+
+def head_range(n_kv_heads: int, rank: int, world_size: int):
+    """KV heads [lo, hi) owned by `rank`; requires world_size to divide n_kv_heads."""
+    if world_size < 1 or not 0 <= rank < world_size:
+        raise ValueError(f"bad rank {rank} for world size {world_size}")
+    if n_kv_heads % world_size != 0:
+        raise ValueError(f"world size {world_size} must divide n_kv_heads {n_kv_heads}")
+    per = n_kv_heads // world_size
+    return rank * per, (rank + 1) * per
+
+
+class KVHeadShardedDRAMAttention(torch.nn.Module):
+    """Same call signature as DRAMAttention, computing only this rank's KV heads and
+    all-gathering the outputs.  Inputs are the full (1, s, Hq, D) / (1, s, Hk, D)
+    tensors (replicated on every rank, as a tensor-parallel caller has them after
+    its own projections) or, with `presliced=True`, only this rank's heads.
+
+    `operator_factory(n_kv_heads=..., **ctor_kwargs)` builds the per-rank operator
+    (DRAMAttention by default; tests inject a stand-in)."""
+
+    def __init__(self, *, n_kv_heads: int, rank: Optional[int] = None, world_size: Optional[int] = None,
+                 process_group=None, operator_factory: Optional[Callable] = None, presliced: bool = False,
+                 **ctor_kwargs):
+        super().__init__()
+        self.group = process_group
+        self.world_size = dist.get_world_size(process_group) if world_size is None else world_size
+        self.rank = dist.get_rank(process_group) if rank is None else rank
+        self.n_kv_heads = n_kv_heads
+        self.lo, self.hi = head_range(n_kv_heads, self.rank, self.world_size)
+        self.presliced = presliced
+        if operator_factory is None:
+            from .dram_attention import DRAMAttention as operator_factory
+        self.inner = operator_factory(n_kv_heads=self.hi - self.lo, **ctor_kwargs)
+        self._gather = {}
+
+    def _kv(self, t: torch.Tensor) -> torch.Tensor:
+        return t if self.presliced else t[:, :, self.lo:self.hi]
+
+    def _q(self, t: torch.Tensor) -> torch.Tensor:
+        if self.presliced:
+            return t
+        rep = t.shape[2] // self.n_kv_heads
+        return t[:, :, self.lo * rep:self.hi * rep]
+
+    def init_cache(self, k_cache: torch.Tensor, v_cache: torch.Tensor):
+        self.inner.init_cache(self._kv(k_cache), self._kv(v_cache))
+
+    def forward(self, xq, xk, xv, *, start_pos, stage: str):
+        local = self.inner(self._q(xq).contiguous(), self._kv(xk).contiguous(), self._kv(xv).contiguous(),
+                           start_pos=start_pos, stage=stage)
+        return self.all_gather_heads(local)
+
+    def all_gather_heads(self, local: torch.Tensor) -> torch.Tensor:
+        """(1, s, Hq/G, D) on every rank -> (1, s, Hq, D) on every rank."""
+        if self.world_size == 1:
+            return local
+        b, s, h, d = local.shape
+        if s == 1:
+            key = (h, d, local.dtype, local.device)
+            out = self._gather.get(key)
+            if out is None:
+                out = self._gather[key] = torch.empty(b, 1, h * self.world_size, d, dtype=local.dtype,
+                                                      device=local.device)
+            dist.all_gather_into_tensor(out.view(-1), local.contiguous().view(-1), group=self.group)
+            return out
+        # several tokens: gather (G, s, h, d) then put the rank axis next to the heads
+        tmp = torch.empty(self.world_size, s, h, d, dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(tmp.view(-1), local.contiguous().view(-1), group=self.group)
+        return tmp.permute(1, 0, 2, 3).reshape(1, s, h * self.world_size, d)

@@ -58,25 +58,38 @@ class IPUpperboundTopKSelector:
             ws = self._buffers[key] = (scores, page_list)
         return ws
 
-    def page_list_(self, q: torch.Tensor, k: int):
-        """Scores and selection for q (1, S, Hq, D).  Returns (scores, page_list):
-        float32 (S, Hq, L) and int32 (Hk, S*rep*k) where row hk holds, for every token
-        and every query head of the group in order, its k pages by descending score
-        (ties by ascending page id).  Both tensors are reused by the next call."""
+    def score_(self, q: torch.Tensor, k: int):
+        """Enqueue the page scorer for q (1, S, Hq, D); returns the float32 score
+        buffer (S, Hq, L) (reused by the next call)."""
         bsz, seq_len, num_q_heads, head_dim = q.shape
         assert bsz == 1, f"Only batch size 1 is supported, but got batch size {bsz}"
         assert num_q_heads % self.num_kv_heads == 0
         _native.require_cuda(q, "q")
         assert q.dtype == self.chunk_min_max.dtype, "query dtype must match the key summaries"
         rep = num_q_heads // self.num_kv_heads
-        k = min(k, self.num_pages)
-        scores, page_list = self._workspace(seq_len, rep, k)
+        scores, _ = self._workspace(seq_len, rep, min(k, self.num_pages))
         qc = q if q.is_contiguous() else q.contiguous()
         score_pages_(qc, self.chunk_min_max, scores, seq_len, self.num_kv_heads, rep)
+        return scores
+
+    def select_(self, seq_len: int, rep: int, k: int):
+        """Enqueue the top-k selection on the scores of the last score_ call with the
+        same (seq_len, rep, k); returns the int32 page list (Hk, S*rep*k)."""
+        k = min(k, self.num_pages)
+        scores, page_list = self._workspace(seq_len, rep, k)
         _native.check(_native.lib().da_topk_pages(
             scores.data_ptr(), page_list.data_ptr(), seq_len, self.num_kv_heads, rep, self.num_pages, k,
             _native.stream_ptr()), "da_topk_pages")
-        return scores, page_list
+        return page_list
+
+    def page_list_(self, q: torch.Tensor, k: int):
+        """Scores and selection for q (1, S, Hq, D).  Returns (scores, page_list):
+        float32 (S, Hq, L) and int32 (Hk, S*rep*k) where row hk holds, for every token
+        and every query head of the group in order, its k pages by descending score
+        (ties by ascending page id).  Both tensors are reused by the next call."""
+        scores = self.score_(q, k)
+        seq_len, rep = q.shape[1], q.shape[2] // self.num_kv_heads
+        return scores, self.select_(seq_len, rep, k)
 
     def top_k(self, q: torch.Tensor, k: int) -> torch.Tensor:
         """Top-k page ids for each token and query head: int64 (S, Hk, rep, k), as

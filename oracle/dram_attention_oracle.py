@@ -16,7 +16,8 @@ flash-attn (>=2.6.3, not vendored); the reference's tests check only shapes at
 that boundary, so attention VALUES are pinned by the published softmax
 attention definition, not by a reference vector.
 
-Arithmetic: all floating point work is done in float32 on float32-upcast
+Arithmetic: page scores are float32 on float32-upcast inputs (the quantity the
+selection is defined on); attention and the merge are float64 on upcast
 inputs; integer work (selection, LRU tables) is exact.
 """
 
@@ -227,8 +228,11 @@ def lru_vectorised(page_list: np.ndarray, d2h: np.ndarray, h2d: np.ndarray,
 def attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """Exact softmax attention of one query token, GQA by contiguous groups.
 
-    q (Hq, D); k, v (T, Hk, D); scale D**-0.5.  Returns float32 out (Hq, D)
-    and lse (Hq,) = log sum exp of the scaled logits.  This is what the
+    q (Hq, D); k, v (T, Hk, D); scale D**-0.5.  Returns out (Hq, D) and
+    lse (Hq,) = log sum exp of the scaled logits, both computed and returned
+    in float64 so that the checker's own rounding stays far below the 1e-4
+    float32 tolerance (with x8 / x10 outlier channels the logits reach ~50
+    and a float32 dot product alone is uncertain by ~1e-5 relative).  This is what the
     reference obtains from flash_attn_with_kvcache(..., return_softmax_lse=True)
     at dram_attention/dram_attention.py:195-205 and :211-223 (for a single
     query row the causal flag changes nothing).
@@ -236,9 +240,9 @@ def attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> Tuple[torch.Ten
     hq, d = q.shape
     t, hk, _ = k.shape
     rep = hq // hk
-    qf = q.to(torch.float32).reshape(hk, rep, d)
-    kf = k.to(torch.float32).permute(1, 0, 2)  # (Hk, T, D)
-    vf = v.to(torch.float32).permute(1, 0, 2)
+    qf = q.to(torch.float64).reshape(hk, rep, d)
+    kf = k.to(torch.float64).permute(1, 0, 2)  # (Hk, T, D)
+    vf = v.to(torch.float64).permute(1, 0, 2)
     logits = torch.bmm(qf, kf.transpose(1, 2)) * (d ** -0.5)  # (Hk, rep, T)
     lse = torch.logsumexp(logits, dim=-1)
     p = torch.exp(logits - lse[..., None])
@@ -267,7 +271,7 @@ class StepTrace:
     miss_pages: Optional[np.ndarray]
     miss_slots: Optional[np.ndarray]
     n_miss: Optional[np.ndarray]
-    out: torch.Tensor                   # (Hq, D) float32
+    out: torch.Tensor                   # (Hq, D) float64
 
 
 class OracleLRUCache:

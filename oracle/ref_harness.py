@@ -12,7 +12,7 @@ algorithm under test except where stated:
      explicit-softmax restatements written from the documented behaviour of
      those calls (in-place append at cache_seqlens, attention over
      [:cache_seqlens + s], scale D**-0.5, GQA by contiguous groups, float32
-     lse of shape (b, Hq, s)).
+     lse of shape (b, Hq, s)); internally float64.
   4. `torch.argsort(..., descending=True)` -> the same call with stable=True,
      so ties resolve to the lowest page id.
 The reference's own LRU Triton kernels run unchanged through Triton's
@@ -48,15 +48,16 @@ def _flash_attn_with_kvcache_cpu(q, k_cache, v_cache, k=None, v=None, rotary_cos
         seqlen = seqlen + s
     hk = k_cache.shape[2]
     rep = hq // hk
-    qf = q[0, 0].float().reshape(hk, rep, d)
-    kf = k_cache[0, :seqlen].float().permute(1, 0, 2)
-    vf = v_cache[0, :seqlen].float().permute(1, 0, 2)
+    qf = q[0, 0].double().reshape(hk, rep, d)
+    kf = k_cache[0, :seqlen].double().permute(1, 0, 2)
+    vf = v_cache[0, :seqlen].double().permute(1, 0, 2)
     logits = torch.bmm(qf, kf.transpose(1, 2)) * (d ** -0.5)
     lse = torch.logsumexp(logits, dim=-1)
     out = torch.bmm(torch.exp(logits - lse[..., None]), vf).reshape(1, 1, hq, d)
-    # flash-attn returns the output in q's dtype and the lse in float32
+    # flash-attn returns the output in q's dtype and the lse in float32; the
+    # arithmetic in between is float64 here so the fixture is accurate to float32
     out = out.to(q.dtype)
-    lse = lse.reshape(1, hq, 1)
+    lse = lse.reshape(1, hq, 1).float()
     return (out, lse) if return_softmax_lse else out
 
 

@@ -11,6 +11,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 from oracle import dram_attention_oracle as orc  # noqa: E402
+from tests.conftest import assert_out_close  # noqa: E402
 
 DEV = "cuda"
 
@@ -349,7 +350,7 @@ def test_lru_cache_class_mirrors_reference(da):
 
 # --------------------------------------------------------------- attention ----
 
-def _attention_case(da, dtype, d, hk, rep, n_prefix, cap, t_new, seed, device_pos, tol, calls=2):
+def _attention_case(da, dtype, d, hk, rep, n_prefix, cap, t_new, seed, device_pos, calls=2):
     from dram_attention_b200 import _native
     lib = _native.lib()
     g = _g(seed)
@@ -387,9 +388,8 @@ def _attention_case(da, dtype, d, hk, rep, n_prefix, cap, t_new, seed, device_po
         so, sl = orc.attend(q, local_k[:t + 1], local_v[:t + 1])
         want = orc.combine(po, so, pl, sl)
         want_lse = torch.logaddexp(pl, sl)
-        got = out.float().cpu()
-        assert (got - want).abs().max().item() <= tol, (call, (got - want).abs().max().item())
-        assert torch.allclose(lse.cpu(), want_lse, rtol=1e-4, atol=1e-4)
+        assert_out_close(out.float().cpu(), want, dtype, call)
+        assert torch.allclose(lse.cpu().double(), want_lse, rtol=1e-4, atol=1e-4)
         assert torch.equal(g_lk.cpu(), local_k) and torch.equal(g_lv.cpu(), local_v)
         assert int(ws[:1024].view(torch.int32).abs().sum()) == 0  # tickets back at zero
 
@@ -408,9 +408,9 @@ def _attention_case(da, dtype, d, hk, rep, n_prefix, cap, t_new, seed, device_po
     (torch.bfloat16, 128, 1, 1, 65536, 8224, 8176, True), # one head of the 1M-context layer
 ])
 def test_decode_attention_matches_oracle(da, dtype, d, hk, rep, n_prefix, cap, t_new, device_pos):
-    # tolerances: 1e-4 absolute in float32, 2e-2 absolute in 16-bit types
-    tol = 1e-4 if dtype == torch.float32 else 2e-2
-    _attention_case(da, dtype, d, hk, rep, n_prefix, cap, t_new, n_prefix + t_new, device_pos, tol)
+    # tolerances (tests/conftest.py:out_tolerance): 1e-4 absolute in float32; 2e-2 absolute
+    # plus half an ulp of the stored value in 16-bit types
+    _attention_case(da, dtype, d, hk, rep, n_prefix, cap, t_new, n_prefix + t_new, device_pos)
 
 
 def test_decode_attention_bad_position_is_reported(da):
