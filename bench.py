@@ -325,8 +325,16 @@ def run_b200(args):
     k_pages = w.top_k // w.page_size
     list_len = rep * k_pages
     out_p = torch.empty(1, 1, hk * rep, D, dtype=w.dtype, device=dev)
+    miss_dev = torch.zeros(max(P, 1), dtype=torch.int32, device=dev)
+    events = []
     t_a = time.perf_counter()
-    for _ in range(P):
+    # Park the GPU behind a ~50 ms spin so that every launch and event of the P steps is
+    # already queued when it starts: the event intervals then hold kernel time, not the
+    # host's launch latency (a stage takes longer to launch from Python than to run).
+    torch.cuda.synchronize()
+    if P:
+        torch.cuda._sleep(100_000_000)
+    for i in range(P):
         q, kk, vv = dq[step], dk[step], dv[step]
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
         ev[0].record()
@@ -340,11 +348,14 @@ def run_b200(args):
         ev[4].record()
         inner.attend_(q, kk, vv, S + step, out_p)
         ev[5].record()
-        torch.cuda.synchronize()
+        miss_dev[i].copy_(lc.last_miss_counts(list_len).sum())
+        events.append(ev)
+        step += 1
+    torch.cuda.synchronize()
+    for ev in events:
         for j, n in enumerate(stage_names):
             stage_ms[n].append(ev[j].elapsed_time(ev[j + 1]))
-        misses.append(int(lc.last_miss_counts(list_len).sum()))
-        step += 1
+    misses = miss_dev[:P].tolist()
     windows.append((t_a, time.perf_counter()))
     inner.check_status()
     sampler.stop()
