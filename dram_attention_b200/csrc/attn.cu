@@ -55,6 +55,54 @@ struct AttnParams {
     float scale_log2;
 };
 
+// Final merge of the per-CTA partials of one head by one CTA of kAttnThreads threads.
+// partial row = acc[D] (already weighted to the row's max), max, l.  `scratch` holds
+// at least splits * REP floats of shared memory.  Loads bypass L1 (the rows were
+// written by other SMs) and are issued in batches so that only a few L2 round trips
+// are exposed.
+template <typename T, int D, int REP>
+__device__ __forceinline__ void merge_splits(const AttnParams &p, int h, int splits, float *scratch) {
+    constexpr int PW = D + 2;
+    constexpr float NEG_INF = -INFINITY;
+    __shared__ float sh_m[REP], sh_l[REP];
+    const int tid = threadIdx.x;
+    const float *hp = p.partials + ((size_t)h * splits * REP) * PW;
+    const int n = splits * REP;
+    for (int e = tid; e < n; e += kAttnThreads) scratch[e] = __ldcg(hp + (size_t)e * PW + D);
+    if (tid < REP) sh_l[tid] = 0.f;
+    __syncthreads();
+    if (tid < REP) {
+        float mn = NEG_INF;
+        for (int s = 0; s < splits; ++s) mn = fmaxf(mn, scratch[s * REP + tid]);
+        sh_m[tid] = (mn == NEG_INF) ? 0.f : mn;
+    }
+    __syncthreads();
+    for (int e = tid; e < n; e += kAttnThreads) {
+        const float w = fast_exp2(scratch[e] - sh_m[e % REP]);
+        scratch[e] = w;
+        atomicAdd(&sh_l[e % REP], w * __ldcg(hp + (size_t)e * PW + D + 1));
+    }
+    __syncthreads();
+    for (int e = tid; e < REP * D; e += kAttnThreads) {
+        const int r = e / D;
+        const int c = e % D;
+        const float *col = hp + (size_t)r * PW + c;
+        float a = 0.f;
+        int s = 0;
+        for (; s + 8 <= splits; s += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = __ldcg(col + (size_t)(s + u) * REP * PW);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) a = fmaf(v[u], scratch[(s + u) * REP + r], a);
+        }
+        for (; s < splits; ++s) a = fmaf(__ldcg(col + (size_t)s * REP * PW), scratch[s * REP + r], a);
+        const float ll = sh_l[r];
+        reinterpret_cast<T *>(p.out)[(size_t)(h * REP + r) * D + c] = from_float<T>(ll > 0.f ? a / ll : 0.f);
+        if (c == 0 && p.lse_out) p.lse_out[h * REP + r] = (sh_m[r] + log2f(ll)) * 0.6931471805599453f;
+    }
+}
+
 template <typename T, int D, int REP, int STAGES>
 __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const AttnParams p) {
     constexpr int E = (int)sizeof(T);
@@ -95,9 +143,11 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     const int units_prefix = (n_prefix + kUnitTokens - 1) / kUnitTokens;
     const int units_local = (n_local + kUnitTokens - 1) / kUnitTokens;
     const int units = units_prefix + units_local;
-    const int per_cta = (units + splits - 1) / splits;
-    const int u0 = x * per_cta;
-    const int u1 = min(units, u0 + per_cta);
+    // Units are dealt round-robin to the (CTA, warp) workers of this head, so every
+    // worker sees the same mix of slot-table units (one bulk copy) and local-window
+    // units (a row gather).
+    const int n_workers = splits * kAttnWarps;
+    const int worker = x * kAttnWarps + warp;
 
     unsigned char *my_stages = smem + (size_t)warp * STAGES * UNITB;
     if (lane == 0) {
@@ -179,9 +229,8 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
         }
     };
 
-    const int span = u1 - u0 - warp;
-    const int n_my = span > 0 ? (span + kAttnWarps - 1) / kAttnWarps : 0;
-    for (int it = 0; it < STAGES && it < n_my; ++it) issue(u0 + warp + it * kAttnWarps, it);
+    const int n_my = units > worker ? (units - worker + n_workers - 1) / n_workers : 0;
+    for (int it = 0; it < STAGES && it < n_my; ++it) issue(worker + it * n_workers, it);
 
     for (int it = 0; it < n_my; ++it) {
         const int s = it % STAGES;
@@ -190,7 +239,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
             if (lane == 0) atomicOr(p.status, DA_STATUS_WAIT_TIMEOUT);
             break;
         }
-        const int u = u0 + warp + it * kAttnWarps;
+        const int u = worker + it * n_workers;
         const int ntok = unit_tokens(u);
         const unsigned char *sb = my_stages + (size_t)s * UNITB;
 
@@ -258,7 +307,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
         }
 
         __syncwarp();
-        if (it + STAGES < n_my) issue(u0 + warp + (it + STAGES) * kAttnWarps, s);
+        if (it + STAGES < n_my) issue(worker + (it + STAGES) * n_workers, s);
     }
 
     // ---- merge the 4 token groups of the warp ---------------------------------------
@@ -327,24 +376,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
 
     // ---- last CTA of this head: merge the splits ----------------------------------------
     __threadfence();
-    const float *hp = p.partials + ((size_t)h * splits * REP) * PW;
-    for (int e = tid; e < REP * D; e += kAttnThreads) {
-        const int r = e / D;
-        const int c = e % D;
-        float mn = NEG_INF;
-        for (int s = 0; s < splits; ++s) mn = fmaxf(mn, __ldcg(hp + ((size_t)s * REP + r) * PW + D));
-        const float ms = (mn == NEG_INF) ? 0.f : mn;
-        float a = 0.f, ll = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const float *row = hp + ((size_t)s * REP + r) * PW;
-            const float w = fast_exp2(__ldcg(row + D) - ms);
-            a = fmaf(__ldcg(row + c), w, a);
-            ll = fmaf(__ldcg(row + D + 1), w, ll);
-        }
-        const float o = ll > 0.f ? a / ll : 0.f;
-        reinterpret_cast<T *>(p.out)[(size_t)(h * REP + r) * D + c] = from_float<T>(o);
-        if (c == 0 && p.lse_out) p.lse_out[h * REP + r] = (ms + log2f(ll)) * 0.6931471805599453f;
-    }
+    merge_splits<T, D, REP>(p, h, splits, &red[0][0][0]);
     if (tid == 0) p.counters[h] = 0u;
 }
 

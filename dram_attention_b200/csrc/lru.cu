@@ -3,9 +3,8 @@
 //
 //   1. hits: every listed page that is resident gets time = step.
 //   2. misses: the first appearance (in list order) of every non-resident page is
-//      found with an atomicMin of the list index into the page's own table entry
-//      (entries of non-resident pages are negative, so codes below -1 are free),
-//      and ranked by a block prefix sum.
+//      found with a shared-memory hash table keyed by page id that keeps the
+//      smallest list index, and ranked by a block prefix sum.
 //   3. victims: slots ordered by (time, slot) with a stable LSD radix sort on the
 //      time in shared memory; only as many 8-bit passes as the step counter has
 //      bytes.
@@ -48,18 +47,35 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int *wsum, int *total
     return before + incl - v;
 }
 
+constexpr int kLruMaxListRounds = kLruMaxList / kLruThreads;
+
+// Shared-memory plan (ints): keyA[n_slots] valA[n_slots] | X[2 * max(n_slots, table)] |
+// mpage[list_len] | hist[256 * 32] | s2d[n_slots].  X is the page hash table
+// (keys, first list index) while misses are found and the sort's second buffer after.
+__host__ __device__ inline int lru_table_size(int list_len) {
+    int t = 64;
+    while (t < 2 * list_len) t <<= 1;
+    return t;
+}
+
 __global__ void __launch_bounds__(kLruThreads)
 lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *dram_to_slot, int n_dram_pages,
                   int32_t *slot_to_dram, int32_t *access_time, int n_slots, int32_t *step_counters,
                   int32_t *__restrict__ miss_pages, int32_t *__restrict__ miss_slots,
                   int32_t *__restrict__ n_miss_out, int32_t *status) {
     extern __shared__ __align__(16) int smem_i[];
+    const int table = lru_table_size(list_len);
+    const int xhalf = n_slots > table ? n_slots : table;
     int *keyA = smem_i;                  // [n_slots] sort keys (access time)
     int *valA = keyA + n_slots;          // [n_slots] slot ids
-    int *keyB = valA + n_slots;
-    int *valB = keyB + n_slots;
-    int *mpage = valB + n_slots;         // [list_len] miss pages in list order
+    int *xbuf = valA + n_slots;          // [2 * xhalf]
+    int *tkey = xbuf;                    // [table] page id or -1
+    int *tval = xbuf + table;            // [table] smallest list index of that page
+    int *keyB = xbuf;                    // [n_slots]   (after the table is dead)
+    int *valB = xbuf + n_slots;          // [n_slots]
+    int *mpage = xbuf + 2 * xhalf;       // [list_len] miss pages in list order
     int *hist = mpage + list_len;        // [256 * 32] digit-major, warp-minor
+    int *s2d_s = hist + 256 * kLruWarps; // [n_slots] slot -> page before this step
     __shared__ int wsum[kLruWarps];
     __shared__ int sh_max;
 
@@ -74,45 +90,73 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
     int32_t *mp_out = miss_pages + (size_t)h * list_len;
     int32_t *ms_out = miss_slots + (size_t)h * list_len;
 
+    // ---- independent global reads first: list, its table entries, times, slot map ------
+    int pg[kLruMaxListRounds], sl[kLruMaxListRounds];
+    int bad = 0;
+#pragma unroll
+    for (int r = 0; r < kLruMaxListRounds; ++r) {
+        const int i = r * kLruThreads + tid;
+        pg[r] = -1;
+        if (r * kLruThreads < list_len && i < list_len) {
+            const int p = list[i];
+            if (p < 0 || p >= n_dram_pages) bad = 1; else pg[r] = p;
+        }
+    }
     const int step = step_counters[h] + 1;
-    if (tid == 0) sh_max = step;
+#pragma unroll
+    for (int r = 0; r < kLruMaxListRounds; ++r) sl[r] = pg[r] >= 0 ? d2s[pg[r]] : 0;
     for (int s = tid; s < n_slots; s += kLruThreads) {
         keyA[s] = tim[s];
         valA[s] = s;
+        s2d_s[s] = s2d[s];
     }
-    __syncthreads();
-
-    // ---- 1. hits, and first-appearance marks for non-resident pages -----------
-    // code(i) = i - list_len - 1 is in [-list_len-1, -2]; the smallest list index wins.
-    int bad = 0;
-    for (int i = tid; i < list_len; i += kLruThreads) {
-        const int p = list[i];
-        if (p < 0 || p >= n_dram_pages) { bad = 1; continue; }
-        const int s = __ldcg(&d2s[p]);
-        if (s >= 0) {
-            if (s < n_slots) { keyA[s] = step; tim[s] = step; }
-        } else {
-            atomicMin(&d2s[p], i - list_len - 1);
-        }
+    for (int x = tid; x < table; x += kLruThreads) {
+        tkey[x] = -1;
+        tval[x] = 0x7fffffff;
     }
+    if (tid == 0) sh_max = step;
     if (bad) atomicOr(status, DA_STATUS_BAD_PAGE_ID);
     __syncthreads();
 
-    // ---- 2. rank the first appearances in list order ---------------------------
-    int n_miss = 0;
-    for (int base = 0; base < list_len; base += kLruThreads) {
-        const int i = base + tid;
-        int p = -1, f = 0;
-        if (i < list_len) {
-            p = list[i];
-            if (p >= 0 && p < n_dram_pages) f = (__ldcg(&d2s[p]) == i - list_len - 1);
+    // ---- 1. hits get the step; non-resident pages go into the hash table -------------
+    const int tmask = table - 1;
+    const int tshift = 32 - (__ffs(table) - 1);
+#pragma unroll
+    for (int r = 0; r < kLruMaxListRounds; ++r) {
+        const int p = pg[r];
+        if (p < 0) { sl[r] = -1; continue; }   // sl[r] becomes the table position of a miss, -1 otherwise
+        const int s = sl[r];
+        sl[r] = -1;
+        if (s >= 0) {
+            if (s < n_slots) { keyA[s] = step; tim[s] = step; }
+        } else {
+            int pos = (int)(((uint32_t)p * 2654435761u) >> tshift) & tmask;
+            for (int probe = 0; probe < table; ++probe) {
+                const int prev = atomicCAS(&tkey[pos], -1, p);
+                if (prev == -1 || prev == p) {
+                    atomicMin(&tval[pos], r * kLruThreads + tid);
+                    sl[r] = pos;
+                    break;
+                }
+                pos = (pos + 1) & tmask;
+            }
         }
-        int total;
-        const int j = n_miss + block_exclusive_scan(f, wsum, &total);
-        if (f) mpage[j] = p;
-        n_miss += total;
     }
     __syncthreads();
+
+    // ---- 2. first appearances, ranked in list order -----------------------------------
+    int n_miss = 0;
+#pragma unroll
+    for (int r = 0; r < kLruMaxListRounds; ++r) {
+        if (r * kLruThreads < list_len) {
+            const int f = (sl[r] >= 0) && (tval[sl[r]] == r * kLruThreads + tid);
+            int total;
+            const int j = n_miss + block_exclusive_scan(f, wsum, &total);
+            if (f) mpage[j] = pg[r];
+            n_miss += total;
+        }
+    }
+    __syncthreads();  // the table is dead from here on; xbuf becomes keyB/valB
 
     if (n_miss > 0) {
         // ---- 3. stable radix sort of the slots by access time --------------------
@@ -189,15 +233,13 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
         // ---- 4. overflow check, then assignment ------------------------------------
         const bool overflow = (n_miss > n_slots) || (kin[min(n_miss, n_slots) - 1] >= step);
         if (overflow) {
-            // undo the marks; tables stay as after the hit marking
-            for (int j = tid; j < n_miss; j += kLruThreads) d2s[mpage[j]] = -1;
             if (tid == 0) atomicOr(status, DA_STATUS_LRU_OVERFLOW);
-            n_miss = 0;
+            n_miss = 0;  // tables stay as after the hit marking
         } else {
             for (int j = tid; j < n_miss; j += kLruThreads) {
                 const int p = mpage[j];
                 const int v = vin[j];
-                const int old = s2d[v];
+                const int old = s2d_s[v];
                 if (old >= 0 && old < n_dram_pages) d2s[old] = -1;
                 s2d[v] = p;
                 d2s[p] = v;
@@ -214,8 +256,12 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
 }
 
 static size_t lru_smem_bytes(int n_slots, int list_len) {
-    return ((size_t)4 * n_slots + list_len + 256 * kLruWarps) * sizeof(int);
+    const int table = lru_table_size(list_len);
+    const int xhalf = n_slots > table ? n_slots : table;
+    return ((size_t)3 * n_slots + 2 * (size_t)xhalf + list_len + 256 * kLruWarps) * sizeof(int);
 }
+
+constexpr size_t kLruMaxSmem = 227 * 1024 - 1024;
 
 }  // namespace da
 
@@ -229,6 +275,7 @@ extern "C" int da_lru_update(const int32_t *page_list, int list_len, int32_t *dr
     if (list_len < 1 || n_dram_pages < 1 || n_slots < 1 || n_kv_heads < 1) return DA_ERR_SHAPE;
     if (n_slots > da::kLruMaxSlots || list_len > da::kLruMaxList) return DA_ERR_UNSUPPORTED;
     const size_t smem = da::lru_smem_bytes(n_slots, list_len);
+    if (smem > da::kLruMaxSmem) return DA_ERR_UNSUPPORTED;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -236,7 +283,7 @@ extern "C" int da_lru_update(const int32_t *page_list, int list_len, int32_t *dr
     if (dev < 0 || dev >= 64) return DA_ERR_UNSUPPORTED;
     if (!attr_set[dev]) {
         e = cudaFuncSetAttribute(da::lru_update_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)da::lru_smem_bytes(da::kLruMaxSlots, da::kLruMaxList));
+                                 (int)da::kLruMaxSmem);
         if (e != cudaSuccess) return (int)e;
         attr_set[dev] = true;
     }

@@ -19,6 +19,55 @@ __device__ __forceinline__ uint32_t score_key(float x) {
     return b ^ ((b >> 31) ? 0xffffffffu : 0x80000000u);
 }
 
+// Where the keys of a row live while the kernel runs.  IPT > 0: n_pages <= IPT * 1024
+// and every thread keeps its IPT keys in registers after one coalesced read (key j of
+// thread t is page j * 1024 + t).  IPT == 0: any length; the row is re-read from
+// global memory (L2) in batches of 8 loads per thread.
+template <int IPT> struct RowKeys {
+    uint32_t k[IPT > 0 ? IPT : 1];
+
+    __device__ __forceinline__ void load(const float *__restrict__ srow, int n, int tid) {
+        if constexpr (IPT > 0) {
+            float v[IPT];
+#pragma unroll
+            for (int j = 0; j < IPT; ++j) {
+                const int i = j * kTopkThreads + tid;
+                v[j] = i < n ? srow[i] : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < IPT; ++j) k[j] = score_key(v[j]);
+        }
+    }
+
+    // f(page, key, valid) for every chunk of 1024 pages in ascending order; every thread
+    // of the block calls f the same number of times.
+    template <typename F>
+    __device__ __forceinline__ void for_each(const float *__restrict__ srow, int n, int tid, F f) const {
+        if constexpr (IPT > 0) {
+#pragma unroll
+            for (int j = 0; j < IPT; ++j) {
+                const int i = j * kTopkThreads + tid;
+                if (j * kTopkThreads < n) f(i, k[j], i < n);
+            }
+        } else {
+            for (int base = 0; base < n; base += 8 * kTopkThreads) {
+                float v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int i = base + j * kTopkThreads + tid;
+                    v[j] = i < n ? srow[i] : 0.f;
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int i = base + j * kTopkThreads + tid;
+                    if (base + j * kTopkThreads < n) f(i, score_key(v[j]), i < n);
+                }
+            }
+        }
+    }
+};
+
+template <int IPT>
 __global__ void __launch_bounds__(kTopkThreads)
 topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_list, int n_kv_heads, int rep,
                   int n_pages, int k) {
@@ -38,6 +87,9 @@ topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_l
     const int lane = tid & 31;
     const int warp = tid >> 5;
 
+    RowKeys<IPT> keys;
+    keys.load(srow, n_pages, tid);
+
     // ---- radix select: key of the k-th largest score -----------------------
     uint32_t prefix = 0, mask = 0;
     int need = k;  // how many still to take among keys that match the prefix
@@ -46,19 +98,13 @@ topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_l
         const int shift = 24 - 8 * pass;
         if (tid < 256) hist[tid] = 0;
         __syncthreads();
-        for (int base = 0; base < n_pages; base += kTopkThreads) {
-            const int i = base + tid;
-            uint32_t key = 0;
-            bool in = false;
-            if (i < n_pages) {
-                key = score_key(srow[i]);
-                in = (key & mask) == prefix;
-            }
+        keys.for_each(srow, n_pages, tid, [&](int, uint32_t key, bool valid) {
+            const bool in = valid && (key & mask) == prefix;
             // one shared-memory atomic per distinct digit in the warp
             const uint32_t digit = in ? ((key >> shift) & 255u) : 256u;
             const uint32_t peers = __match_any_sync(DA_FULL_MASK, digit);
             if (in && (peers & ((1u << lane) - 1)) == 0) atomicAdd(&hist[digit], __popc(peers));
-        }
+        });
         __syncthreads();
         if (warp == 0) {
             // lane l owns digits 255-8l .. 248-8l (descending); find the digit where the
@@ -104,25 +150,21 @@ topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_l
     if (tid == 0) sh_taken = 0;
     __syncthreads();
     const bool take_all_ties = (count_eq == need);
-    for (int base = 0; base < n_pages; base += kTopkThreads) {
-        const int i = base + tid;
-        if (i < n_pages) {
-            const uint32_t key = score_key(srow[i]);
-            if (key > thr || (take_all_ties && key == thr)) {
-                const int pos = atomicAdd(&sh_taken, 1);
-                cand[pos] = ((unsigned long long)(~key) << 32) | (uint32_t)i;
-            }
+    keys.for_each(srow, n_pages, tid, [&](int i, uint32_t key, bool valid) {
+        if (valid && (key > thr || (take_all_ties && key == thr))) {
+            const int pos = atomicAdd(&sh_taken, 1);
+            cand[pos] = ((unsigned long long)(~key) << 32) | (uint32_t)i;
         }
-    }
+    });
     __syncthreads();
     if (!take_all_ties) {
         // the `need` lowest page ids among keys == thr, by an ordered block scan
         int taken_ties = 0;  // uniform across the block
         const int first_slot = sh_taken;
         __syncthreads();
-        for (int base = 0; base < n_pages && taken_ties < need; base += kTopkThreads) {
-            const int i = base + tid;
-            const bool f = (i < n_pages) && (score_key(srow[i]) == thr);
+        keys.for_each(srow, n_pages, tid, [&](int i, uint32_t key, bool valid) {
+            if (taken_ties >= need) return;  // uniform
+            const bool f = valid && key == thr;
             const uint32_t bal = __ballot_sync(DA_FULL_MASK, f);
             if (lane == 0) warp_tot[warp] = __popc(bal);
             __syncthreads();
@@ -136,7 +178,7 @@ topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_l
             if (f && my < need) cand[first_slot + my] = ((unsigned long long)(~thr) << 32) | (uint32_t)i;
             taken_ties += total;
             __syncthreads();
-        }
+        });
     }
     __syncthreads();
 
@@ -144,13 +186,14 @@ topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_l
     for (int e = tid; e < k; e += kTopkThreads) rank[e] = 0;
     __syncthreads();
     {
-        // element e = tid % kk_pad, segment = tid / kk_pad when k < blockDim
+        // with k < 1024 the comparisons of one element are split over several threads
         int segs = kTopkThreads / k;
         if (segs < 1) segs = 1;
+        const int per_sweep = kTopkThreads / segs;
         const int seg_len = (k + segs - 1) / segs;
-        for (int e0 = 0; e0 < k; e0 += kTopkThreads / segs) {
-            const int e = e0 + tid % (kTopkThreads / segs);
-            const int seg = tid / (kTopkThreads / segs);
+        for (int e0 = 0; e0 < k; e0 += per_sweep) {
+            const int e = e0 + tid % per_sweep;
+            const int seg = tid / per_sweep;
             if (e < k && seg < segs) {
                 const unsigned long long v = cand[e];
                 const int j0 = seg * seg_len;
@@ -167,6 +210,26 @@ topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_l
     for (int e = tid; e < k; e += kTopkThreads) dst[rank[e]] = (int32_t)(cand[e] & 0xffffffffu);
 }
 
+template <int IPT>
+static cudaError_t launch_topk(const float *scores, int32_t *page_list, int rows, int n_kv_heads, int rep,
+                               int n_pages, int k, cudaStream_t stream) {
+    // opt in to > 48 KB of dynamic shared memory once per device
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!attr_set[dev]) {
+        e = cudaFuncSetAttribute(topk_pages_kernel<IPT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kTopkMaxK * 12);
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    const size_t smem = (size_t)k * (sizeof(unsigned long long) + sizeof(int));
+    topk_pages_kernel<IPT><<<rows, kTopkThreads, smem, stream>>>(scores, page_list, n_kv_heads, rep, n_pages, k);
+    return cudaGetLastError();
+}
+
 }  // namespace da
 
 extern "C" int da_topk_pages(const float *scores, int32_t *page_list, int n_tokens, int n_kv_heads, int rep,
@@ -174,21 +237,12 @@ extern "C" int da_topk_pages(const float *scores, int32_t *page_list, int n_toke
     if (!scores || !page_list) return DA_ERR_NULL;
     if (n_tokens < 1 || n_kv_heads < 1 || rep < 1 || n_pages < 1 || k < 1 || k > n_pages) return DA_ERR_SHAPE;
     if (k > da::kTopkMaxK) return DA_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)k * (sizeof(unsigned long long) + sizeof(int));
     const int rows = n_tokens * n_kv_heads * rep;
-    // opt in to > 48 KB of dynamic shared memory once per device
-    static bool attr_set[64] = {};
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return (int)e;
-    if (dev < 0 || dev >= 64) return DA_ERR_UNSUPPORTED;
-    if (!attr_set[dev]) {
-        e = cudaFuncSetAttribute(da::topk_pages_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 da::kTopkMaxK * 12);
-        if (e != cudaSuccess) return (int)e;
-        attr_set[dev] = true;
-    }
-    da::topk_pages_kernel<<<rows, da::kTopkThreads, smem, static_cast<cudaStream_t>(stream)>>>(
-        scores, page_list, n_kv_heads, rep, n_pages, k);
-    return (int)cudaGetLastError();
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t e;
+    if (n_pages <= 4 * da::kTopkThreads) e = da::launch_topk<4>(scores, page_list, rows, n_kv_heads, rep, n_pages, k, s);
+    else if (n_pages <= 8 * da::kTopkThreads) e = da::launch_topk<8>(scores, page_list, rows, n_kv_heads, rep, n_pages, k, s);
+    else if (n_pages <= 16 * da::kTopkThreads) e = da::launch_topk<16>(scores, page_list, rows, n_kv_heads, rep, n_pages, k, s);
+    else e = da::launch_topk<0>(scores, page_list, rows, n_kv_heads, rep, n_pages, k, s);
+    return (int)e;
 }

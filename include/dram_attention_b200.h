@@ -126,7 +126,9 @@ DA_API int da_topk_pages(const float *scores, int32_t *page_list,
  *             pairs whose payload has to be copied, in list order
  * n_miss      (n_kv_heads) int32, written
  * status      (1) int32, bits or-ed in
- * Requires n_slots <= 8192 and list_len <= 8192.
+ * Requires n_slots <= 8192, list_len <= 8192 and the shared-memory plan
+ * (3*n_slots + 2*max(n_slots, T) + list_len + 8192 ints, T = power of two >= 2*list_len)
+ * to fit 226 KiB: e.g. 8192 slots with lists up to 4096, or 4096 slots with lists up to 8192.
  */
 DA_API int da_lru_update(const int32_t *page_list, int list_len,
                   int32_t *dram_to_slot, int n_dram_pages,
