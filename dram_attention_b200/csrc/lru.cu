@@ -35,14 +35,16 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int *wsum, int *total
     }
     if (lane == 31) wsum[warp] = incl;
     __syncthreads();
-    int before = 0, tot = 0;
+    // every warp scans the 32 warp totals with shuffles (one read per lane)
+    const int wt = wsum[lane];
+    int wincl = wt;
 #pragma unroll
-    for (int w = 0; w < kLruWarps; ++w) {
-        const int c = wsum[w];
-        if (w < warp) before += c;
-        tot += c;
+    for (int off = 1; off < 32; off <<= 1) {
+        int t = __shfl_up_sync(DA_FULL_MASK, wincl, off);
+        if (lane >= off) wincl += t;
     }
-    *total = tot;
+    const int before = __shfl_sync(DA_FULL_MASK, wincl - wt, warp);
+    *total = __shfl_sync(DA_FULL_MASK, wincl, 31);
     __syncthreads();
     return before + incl - v;
 }
@@ -160,7 +162,13 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
 
     if (n_miss > 0) {
         // ---- 3. stable radix sort of the slots by access time --------------------
-        for (int s = tid; s < n_slots; s += kLruThreads) atomicMax(&sh_max, keyA[s]);
+        {
+            int mx = 0;
+            for (int s = tid; s < n_slots; s += kLruThreads) mx = max(mx, keyA[s]);
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) mx = max(mx, __shfl_xor_sync(DA_FULL_MASK, mx, off));
+            if (lane == 0) atomicMax(&sh_max, mx);
+        }
         __syncthreads();
         const int bits = 32 - __clz(sh_max | 1);
         const int passes = (bits + 7) / 8;

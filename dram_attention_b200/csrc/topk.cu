@@ -100,10 +100,18 @@ topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_l
         __syncthreads();
         keys.for_each(srow, n_pages, tid, [&](int, uint32_t key, bool valid) {
             const bool in = valid && (key & mask) == prefix;
-            // one shared-memory atomic per distinct digit in the warp
-            const uint32_t digit = in ? ((key >> shift) & 255u) : 256u;
-            const uint32_t peers = __match_any_sync(DA_FULL_MASK, digit);
-            if (in && (peers & ((1u << lane) - 1)) == 0) atomicAdd(&hist[digit], __popc(peers));
+            // Scores cluster in a few exponent buckets, so most lanes of a warp share a
+            // digit: the lanes that agree with the first participating lane are counted
+            // with one ballot and one atomic, the rest add one by one.
+            const uint32_t digit = (key >> shift) & 255u;
+            const uint32_t act = __ballot_sync(DA_FULL_MASK, in);
+            if (act) {
+                const int first = __ffs(act) - 1;
+                const uint32_t d0 = __shfl_sync(DA_FULL_MASK, digit, first);
+                const uint32_t same = __ballot_sync(DA_FULL_MASK, in && digit == d0);
+                if (lane == first) atomicAdd(&hist[d0], __popc(same));
+                else if (in && digit != d0) atomicAdd(&hist[digit], 1);
+            }
         });
         __syncthreads();
         if (warp == 0) {
@@ -151,9 +159,13 @@ topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_l
     __syncthreads();
     const bool take_all_ties = (count_eq == need);
     keys.for_each(srow, n_pages, tid, [&](int i, uint32_t key, bool valid) {
-        if (valid && (key > thr || (take_all_ties && key == thr))) {
-            const int pos = atomicAdd(&sh_taken, 1);
-            cand[pos] = ((unsigned long long)(~key) << 32) | (uint32_t)i;
+        const bool take = valid && (key > thr || (take_all_ties && key == thr));
+        const uint32_t bal = __ballot_sync(DA_FULL_MASK, take);
+        if (bal) {
+            int base = 0;
+            if (lane == __ffs(bal) - 1) base = atomicAdd(&sh_taken, __popc(bal));
+            base = __shfl_sync(DA_FULL_MASK, base, __ffs(bal) - 1);
+            if (take) cand[base + __popc(bal & ((1u << lane) - 1))] = ((unsigned long long)(~key) << 32) | (uint32_t)i;
         }
     });
     __syncthreads();
