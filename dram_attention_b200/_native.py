@@ -28,7 +28,7 @@ _SIGNATURES = {
     "da_version": (c_int, []),
     "da_error_string": (c_char_p, [c_int]),
     "da_score_pages": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                               c_void_p]),
+                               c_int, c_void_p]),
     "da_topk_pages": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "da_lru_update": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),

@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     constexpr int NPL = D / 8;                  // channels per lane
     constexpr int CH = NPL / 2;                 // channels per chunk
     constexpr int CHB = CH * E;                 // bytes per chunk
-    constexpr int PW = D + 2;                   // floats per partial row: acc[D], m, l
+    constexpr int PW = PartialRow<D>::kWidth;   // floats per partial row: acc[D], m, l, pad
     constexpr float NEG_INF = -INFINITY;
 
     extern __shared__ __align__(128) unsigned char smem[];
@@ -275,6 +275,8 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
         float outv;
         if (c == D) {
             outv = mn;
+        } else if (c > D + 1) {
+            outv = 0.f;  // padding
         } else {
             const float ms = (mn == NEG_INF) ? 0.f : mn;
             outv = 0.f;
@@ -294,7 +296,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
 
     // ---- last CTA of this head: merge the splits ----------------------------------------
     __threadfence();
-    merge_splits<T, D, REP>(p, h, splits, &red[0][0][0]);
+    merge_splits<T, D, REP>(p, h, splits, reinterpret_cast<float *>(smem));
     if (tid == 0) p.counters[h] = 0u;
 }
 
@@ -334,7 +336,7 @@ static cudaError_t dispatch_attn(const AttnParams &p, int n_kv_heads, int rep, i
 extern "C" size_t da_decode_attention_workspace_bytes(int n_kv_heads, int rep, int head_dim) {
     if (n_kv_heads < 1 || rep < 1 || head_dim < 1) return 0;
     return (size_t)da::kCounterBytes +
-           (size_t)n_kv_heads * da::attn_splits(n_kv_heads) * rep * (head_dim + 2) * sizeof(float);
+           (size_t)n_kv_heads * da::attn_splits(n_kv_heads) * rep * (head_dim + 4) * sizeof(float);
 }
 
 extern "C" int da_decode_attention(const void *q, const void *prefix_kv, long long prefix_head_stride,

@@ -41,51 +41,90 @@ struct AttnParams {
     float scale_log2;
 };
 
+// Floats per partial row: acc[D], max, l, padded to a multiple of 4 so that rows can
+// be read with 128-bit loads.
+template <int D> struct PartialRow { static constexpr int kWidth = D + 4; };
+
 // Final merge of the per-CTA partials of one head by one CTA of kAttnThreads threads.
 // partial row = acc[D] (already weighted to the row's max), max, l.  `scratch` holds
-// at least splits * REP floats of shared memory.  Loads bypass L1 (the rows were
-// written by other SMs) and are issued in batches so that only a few L2 round trips
-// are exposed.
+// at least 2 * splits * REP floats of shared memory (the idle stage buffers).  Loads bypass L1 (the rows were
+// written by other SMs).  The first batch of accumulator rows is requested together
+// with the (max, l) pairs, so about three L2 round trips are exposed in total.
 template <typename T, int D, int REP>
 __device__ __forceinline__ void merge_splits(const AttnParams &p, int h, int splits, float *scratch) {
-    constexpr int PW = D + 2;
+    constexpr int PW = PartialRow<D>::kWidth;
+    constexpr int VPR = D / 4;          // float4 per accumulator row
+    constexpr int BATCH = 13;
     constexpr float NEG_INF = -INFINITY;
     __shared__ float sh_m[REP], sh_l[REP];
     const int tid = threadIdx.x;
     const float *hp = p.partials + ((size_t)h * splits * REP) * PW;
     const int n = splits * REP;
-    for (int e = tid; e < n; e += kAttnThreads) scratch[e] = __ldcg(hp + (size_t)e * PW + D);
-    if (tid < REP) sh_l[tid] = 0.f;
-    __syncthreads();
-    if (tid < REP) {
-        float mn = NEG_INF;
-        for (int s = 0; s < splits; ++s) mn = fmaxf(mn, scratch[s * REP + tid]);
-        sh_m[tid] = (mn == NEG_INF) ? 0.f : mn;
-    }
-    __syncthreads();
-    for (int e = tid; e < n; e += kAttnThreads) {
-        const float w = fast_exp2(scratch[e] - sh_m[e % REP]);
-        scratch[e] = w;
-        atomicAdd(&sh_l[e % REP], w * __ldcg(hp + (size_t)e * PW + D + 1));
-    }
-    __syncthreads();
-    for (int e = tid; e < REP * D; e += kAttnThreads) {
-        const int r = e / D;
-        const int c = e % D;
-        const float *col = hp + (size_t)r * PW + c;
-        float a = 0.f;
-        int s = 0;
-        for (; s + 8 <= splits; s += 8) {
-            float v[8];
+    float *wgt = scratch;        // [n] max, then weight
+    float *lsum = scratch + n;   // [n] l of every partial row
+
+    for (int e0 = 0; e0 < REP * VPR; e0 += kAttnThreads) {
+        const int e = e0 + tid;
+        const bool live = e < REP * VPR;
+        const int r = live ? e / VPR : 0;
+        const int c4 = live ? e % VPR : 0;
+        const float4 *col = reinterpret_cast<const float4 *>(hp + (size_t)r * PW) + c4;
+        constexpr int RS = REP * PW / 4;  // float4 stride between splits
+        float4 v[BATCH];
+        // first batch of accumulator loads goes out before anything is waited on
 #pragma unroll
-            for (int u = 0; u < 8; ++u) v[u] = __ldcg(col + (size_t)(s + u) * REP * PW);
-#pragma unroll
-            for (int u = 0; u < 8; ++u) a = fmaf(v[u], scratch[(s + u) * REP + r], a);
+        for (int u = 0; u < BATCH; ++u)
+            if (u < splits) v[u] = __ldcg(col + (size_t)u * RS);
+        if (e0 == 0) {
+            for (int i = tid; i < n; i += kAttnThreads) {
+                const float2 ml = __ldcg(reinterpret_cast<const float2 *>(hp + (size_t)i * PW + D));
+                wgt[i] = ml.x;
+                lsum[i] = ml.y;
+            }
+            __syncthreads();
+            if (tid < REP) {
+                float mn = NEG_INF;
+                for (int s = 0; s < splits; ++s) mn = fmaxf(mn, wgt[s * REP + tid]);
+                sh_m[tid] = (mn == NEG_INF) ? 0.f : mn;
+            }
+            __syncthreads();
+            for (int i = tid; i < n; i += kAttnThreads) wgt[i] = fast_exp2(wgt[i] - sh_m[i % REP]);
+            __syncthreads();
+            if (tid < REP) {
+                float ll = 0.f;
+                for (int s = 0; s < splits; ++s) ll = fmaf(lsum[s * REP + tid], wgt[s * REP + tid], ll);
+                sh_l[tid] = ll;
+            }
+            __syncthreads();
         }
-        for (; s < splits; ++s) a = fmaf(__ldcg(col + (size_t)s * REP * PW), scratch[s * REP + r], a);
-        const float ll = sh_l[r];
-        reinterpret_cast<T *>(p.out)[(size_t)(h * REP + r) * D + c] = from_float<T>(ll > 0.f ? a / ll : 0.f);
-        if (c == 0 && p.lse_out) p.lse_out[h * REP + r] = (sh_m[r] + log2f(ll)) * 0.6931471805599453f;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s0 = 0; s0 < splits; s0 += BATCH) {
+            if (s0 > 0) {
+#pragma unroll
+                for (int u = 0; u < BATCH; ++u)
+                    if (s0 + u < splits) v[u] = __ldcg(col + (size_t)(s0 + u) * RS);
+            }
+#pragma unroll
+            for (int u = 0; u < BATCH; ++u) {
+                if (s0 + u < splits) {
+                    const float w = wgt[(s0 + u) * REP + r];
+                    a.x = fmaf(v[u].x, w, a.x);
+                    a.y = fmaf(v[u].y, w, a.y);
+                    a.z = fmaf(v[u].z, w, a.z);
+                    a.w = fmaf(v[u].w, w, a.w);
+                }
+            }
+        }
+        if (live) {
+            const float ll = sh_l[r];
+            const float inv = ll > 0.f ? 1.f / ll : 0.f;
+            T *dst = reinterpret_cast<T *>(p.out) + (size_t)(h * REP + r) * D + 4 * c4;
+            dst[0] = from_float<T>(a.x * inv);
+            dst[1] = from_float<T>(a.y * inv);
+            dst[2] = from_float<T>(a.z * inv);
+            dst[3] = from_float<T>(a.w * inv);
+            if (c4 == 0 && p.lse_out) p.lse_out[h * REP + r] = (sh_m[r] + log2f(ll)) * 0.6931471805599453f;
+        }
     }
 }
 

@@ -13,11 +13,10 @@
 //   O += P V     A = P re-packed from the S accumulators (FlashAttention-2 register
 //                reuse), B = value rows with ldmatrix.trans.
 //
-// Shared-memory layout of a stage: 16 key rows then 16 value rows, each row padded
-// by 16 bytes so that the 8 row addresses of an ldmatrix tile fall in distinct
-// banks.  Rows arrive by one small bulk copy (TMA) per row, issued one per lane;
-// the slot table's token-major page layout (key row then value row per token)
-// makes both rows of a token contiguous in HBM.
+// Shared-memory layout of a stage: 16 tokens, each its key row then its value row,
+// padded by 16 bytes per token so that the 8 row addresses of an ldmatrix tile fall
+// in distinct banks.  A token of the slot table arrives by one bulk copy (TMA) of
+// both rows (they are contiguous in the page layout), issued one per lane.
 
 #include "attn_common.cuh"
 
@@ -71,12 +70,11 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_mma_kernel(c
     static_assert(sizeof(T) == 2 && REP <= 8 && D % 32 == 0, "16-bit types, at most 8 query rows");
     constexpr int E = 2;
     constexpr int ROWB = D * E;                   // one key (or value) row in HBM
-    constexpr int PITCH = ROWB + 16;              // padded row in shared memory
-    constexpr int HALFB = kUnitTokens * PITCH;    // the key (or value) half of a stage
-    constexpr int STAGEB = 2 * HALFB;
+    constexpr int PITCH = 2 * ROWB + 16;          // padded token (key row, value row) in shared memory
+    constexpr int STAGEB = kUnitTokens * PITCH;
     constexpr int KSTEPS = D / 16;                // k-steps of the QK contraction
     constexpr int NT = D / 8;                     // n-tiles of the PV contraction
-    constexpr int PW = D + 2;
+    constexpr int PW = PartialRow<D>::kWidth;
     constexpr float NEG_INF = -INFINITY;
 
     extern __shared__ __align__(128) unsigned char smem[];
@@ -154,7 +152,9 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_mma_kernel(c
         return min(kUnitTokens, n_local - (u - units_prefix) * kUnitTokens);
     };
 
-    // One bulk copy per row: lanes 0..15 fetch the key rows, lanes 16..31 the value rows.
+    // Slot-table units: one bulk copy per token (its key and value rows are contiguous in
+    // HBM), issued by lanes 0..15.  Local-window units: one copy per row, key rows by
+    // lanes 0..15 and value rows by lanes 16..31.
     auto issue = [&](int u, int s) {
         uint64_t *bar = &bars[warp][s];
         unsigned char *dst = my_stages + (size_t)s * STAGEB;
@@ -164,20 +164,23 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_mma_kernel(c
         const int tl = lane & 15;
         const int is_v = lane >> 4;
         if (tl < ntok) {
-            const unsigned char *src;
             if (u < units_prefix) {
-                src = p.prefix + ((size_t)h * p.prefix_head_stride +
-                                  ((size_t)u * kUnitTokens + tl) * 2 * D + (size_t)is_v * D) * E;
+                if (!is_v) {
+                    const unsigned char *src =
+                        p.prefix + ((size_t)h * p.prefix_head_stride + ((size_t)u * kUnitTokens + tl) * 2 * D) * E;
+                    bulk_copy_g2s(dst + tl * PITCH, src, 2 * ROWB, bar);
+                }
             } else {
                 const int t = (u - units_prefix) * kUnitTokens + tl;
+                const unsigned char *src;
                 if (t == t_new) {
                     src = (is_v ? p.new_v : p.new_k) + (size_t)h * ROWB;
                 } else {
                     src = (is_v ? p.local_v : p.local_k) +
                           ((size_t)t * p.local_tok_stride + (size_t)h * p.local_head_stride) * E;
                 }
+                bulk_copy_g2s(dst + tl * PITCH + is_v * ROWB, src, ROWB, bar);
             }
-            bulk_copy_g2s(dst + is_v * HALFB + tl * PITCH, src, ROWB, bar);
         }
     };
 
@@ -188,7 +191,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_mma_kernel(c
     const int lm = lane >> 3;   // which 8x8 tile of the x4 load
     const int lr = lane & 7;    // row inside the tile
     const int k_off = lr * PITCH + lm * 16;                               // key tile: rows lr, 16-byte column block lm
-    const int v_off = HALFB + ((lm & 1) * 8 + lr) * PITCH + (lm >> 1) * 16;  // value tile (transposed load)
+    const int v_off = ROWB + ((lm & 1) * 8 + lr) * PITCH + (lm >> 1) * 16;    // value tile (transposed load)
 
     for (int it = 0; it < n_my; ++it) {
         const int s = it % STAGES;
@@ -205,7 +208,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_mma_kernel(c
             // cannot produce NaN (their logits are masked below)
             for (int i = lane; i < (kUnitTokens - ntok) * (ROWB / 16); i += 32) {
                 const int r = ntok + i / (ROWB / 16);
-                reinterpret_cast<uint4 *>(sb + HALFB + r * PITCH)[i % (ROWB / 16)] = make_uint4(0, 0, 0, 0);
+                reinterpret_cast<uint4 *>(sb + ROWB + r * PITCH)[i % (ROWB / 16)] = make_uint4(0, 0, 0, 0);
             }
             __syncwarp();
         }
@@ -291,6 +294,8 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_mma_kernel(c
         float outv;
         if (c == D) {
             outv = mn;
+        } else if (c > D + 1) {
+            outv = 0.f;  // padding
         } else {
             const float ms = (mn == NEG_INF) ? 0.f : mn;
             outv = 0.f;
@@ -309,13 +314,13 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_mma_kernel(c
     if (!sh_last) return;
 
     __threadfence();
-    merge_splits<T, D, REP>(p, h, splits, &red[0][0][0]);
+    merge_splits<T, D, REP>(p, h, splits, reinterpret_cast<float *>(smem));
     if (tid == 0) p.counters[h] = 0u;
 }
 
 template <typename T, int D, int REP>
 static cudaError_t launch_mma(const AttnParams &p, int n_kv_heads, cudaStream_t stream) {
-    constexpr int STAGEB = 2 * kUnitTokens * (D * 2 + 16);
+    constexpr int STAGEB = kUnitTokens * (2 * D * 2 + 16);
     constexpr int STAGES = STAGEB > 8192 ? 3 : 4;
     constexpr int SMEM = kAttnWarps * STAGES * STAGEB;
     auto kern = decode_attention_mma_kernel<T, D, REP, STAGES>;

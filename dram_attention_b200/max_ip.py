@@ -10,13 +10,14 @@ from . import _native
 
 
 def score_pages_(q: torch.Tensor, min_max: torch.Tensor, scores: torch.Tensor,
-                 n_tokens: int, n_kv_heads: int, rep: int) -> None:
+                 n_tokens: int, n_kv_heads: int, rep: int, ordered: bool = False) -> None:
     """Enqueue the page scorer.  q (n_tokens, n_kv_heads*rep, D) contiguous;
-    min_max (n_kv_heads, L, 2, D) contiguous; scores float32 (n_tokens, n_kv_heads*rep, L)."""
+    min_max (n_kv_heads, L, 2, D) contiguous; scores float32 (n_tokens, n_kv_heads*rep, L).
+    `ordered` promises min_max[..., 0, :] <= min_max[..., 1, :] everywhere."""
     n_pages, d = min_max.shape[1], min_max.shape[3]
     _native.check(_native.lib().da_score_pages(
         q.data_ptr(), min_max.data_ptr(), scores.data_ptr(), n_tokens, n_kv_heads, rep, n_pages, d,
-        _native.dtype_code(q.dtype), _native.stream_ptr()), "da_score_pages")
+        _native.dtype_code(q.dtype), int(ordered), _native.stream_ptr()), "da_score_pages")
 
 
 def max_inner_product(q: torch.Tensor, min_max: torch.Tensor) -> torch.Tensor:

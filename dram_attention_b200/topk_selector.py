@@ -69,7 +69,8 @@ class IPUpperboundTopKSelector:
         rep = num_q_heads // self.num_kv_heads
         scores, _ = self._workspace(seq_len, rep, min(k, self.num_pages))
         qc = q if q.is_contiguous() else q.contiguous()
-        score_pages_(qc, self.chunk_min_max, scores, seq_len, self.num_kv_heads, rep)
+        # chunk_min_max comes from aminmax over real keys, so min <= max holds
+        score_pages_(qc, self.chunk_min_max, scores, seq_len, self.num_kv_heads, rep, ordered=True)
         return scores
 
     def select_(self, seq_len: int, rep: int, k: int):

@@ -78,11 +78,15 @@ DA_API const char *da_error_string(int code);
  * summaries  (n_kv_heads, n_pages, 2, head_dim), contiguous, `dtype`;
  *            [.., 0, :] = per-page channel minimum, [.., 1, :] = maximum
  * scores     (n_tokens, n_kv_heads * rep, n_pages) float32, written
+ * summaries_ordered  non-zero promises min <= max in every channel (true for
+ *            summaries built by da_build_pages); 16-bit types then take the tensor-core
+ *            path.  Zero makes no assumption about the two rows (the reference's own
+ *            value test feeds unordered rows).
  * The summaries are read once per token for all `rep` query heads of a KV head.
  */
 DA_API int da_score_pages(const void *q, const void *summaries, float *scores,
                    int n_tokens, int n_kv_heads, int rep, int n_pages, int head_dim,
-                   int dtype, da_stream_t stream);
+                   int dtype, int summaries_ordered, da_stream_t stream);
 
 /*
  * Per-query-head top-k page selection, written directly as the per-KV-head page

@@ -69,14 +69,15 @@ def test_scorer_degenerate_and_large_shapes(da):
     (torch.float32, 64, 4, 2, 256), (torch.float32, 128, 4, 2, 130), (torch.bfloat16, 64, 2, 2, 65),
     (torch.bfloat16, 128, 8, 2, 100), (torch.float32, 96, 3, 2, 50), (torch.bfloat16, 128, 4, 8, 65536),
 ])
-def test_scorer_folded_matches_oracle(da, dtype, d, rep, hk, pages):
+@pytest.mark.parametrize("ordered", [False, True])
+def test_scorer_folded_matches_oracle(da, dtype, d, rep, hk, pages, ordered):
     from dram_attention_b200.max_ip import score_pages_
     g = _g(pages + d + rep)
     keys = torch.randn(hk, pages, 4, d, generator=g).to(dtype)
     mm = orc.page_minmax(keys.reshape(hk, pages * 4, d), pages)
     q = torch.randn(1, 1, hk * rep, d, generator=g).to(dtype)
     scores = torch.empty(1, hk * rep, pages, dtype=torch.float32, device=DEV)
-    score_pages_(q.to(DEV), mm.to(DEV).contiguous(), scores, 1, hk, rep)
+    score_pages_(q.to(DEV), mm.to(DEV).contiguous(), scores, 1, hk, rep, ordered=ordered)
     ref = orc.scores_by_query_head(q, mm).reshape(1, hk * rep, pages)
     # 1e-3 relative to the score scale (fp32 accumulation on both sides)
     scale = ref.abs().max().item()
@@ -91,7 +92,7 @@ def test_scorer_multi_token(da):
     mm = torch.sort(torch.randn(hk, pages, 2, d, generator=g), dim=2).values
     q = torch.randn(1, s, hk * rep, d, generator=g)
     scores = torch.empty(s, hk * rep, pages, dtype=torch.float32, device=DEV)
-    score_pages_(q.to(DEV), mm.to(DEV), scores, s, hk, rep)
+    score_pages_(q.to(DEV), mm.to(DEV), scores, s, hk, rep, ordered=True)
     ref = orc.scores_by_query_head(q, mm).reshape(s, hk * rep, pages)
     assert torch.allclose(scores.cpu(), ref, rtol=1e-3, atol=1e-3)
 
