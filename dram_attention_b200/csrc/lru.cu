@@ -82,6 +82,7 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
     int *s2d_s = hist + 256 * kLruWarps; // [n_slots] slot -> page before this step
     __shared__ int wsum[kLruWarps];
     __shared__ int sh_max;
+    __shared__ unsigned long long wmin[kLruWarps];  // per-warp minima of the few-miss path
 
     const int h = blockIdx.x;
     const int tid = threadIdx.x;
@@ -174,7 +175,6 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
                               ? (((unsigned long long)(uint32_t)keyA[s] << 32) | (uint32_t)s)
                               : ~0ull;
             }
-            unsigned long long *wmin = reinterpret_cast<unsigned long long *>(hist);  // [32]
             __syncthreads();  // keyA fully read before the victims are written over it
             for (int j = 0; j < n_miss; ++j) {
                 unsigned long long v = mine[0];
