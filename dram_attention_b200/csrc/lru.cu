@@ -5,10 +5,9 @@
 //   2. misses: the first appearance (in list order) of every non-resident page is
 //      found with a shared-memory hash table keyed by page id that keeps the
 //      smallest list index, and ranked by a block prefix sum.
-//   3. victims: the slots with the smallest (time, slot).  A handful (the steady
-//      state of a decode run) are pulled out by repeated block-wide minimum; more
-//      than that by a stable LSD radix sort on the time in shared memory, with only
-//      as many 8-bit passes as the step counter has bytes.
+//   3. victims: slots ordered by (time, slot) with a stable LSD radix sort on the
+//      time in shared memory; only as many 8-bit passes as the step counter has
+//      bytes.
 //   4. the j-th miss takes the j-th victim; tables updated; (page, slot) pairs
 //      emitted for the payload copy.
 
@@ -21,7 +20,6 @@ constexpr int kLruWarps = kLruThreads / 32;
 constexpr int kLruMaxSlots = 8192;
 constexpr int kLruMaxList = 8192;
 constexpr int kLruMaxRounds = kLruMaxSlots / kLruThreads;  // items per lane in the sort
-constexpr int kLruFewMisses = 16;  // up to this many victims are extracted one by one instead of sorting
 
 // Exclusive prefix sum over the block of one int per thread; returns the
 // exclusive value and writes the block total to *total.  `wsum` is 32 ints of
@@ -82,7 +80,6 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
     int *s2d_s = hist + 256 * kLruWarps; // [n_slots] slot -> page before this step
     __shared__ int wsum[kLruWarps];
     __shared__ int sh_max;
-    __shared__ unsigned long long wmin[kLruWarps];  // per-warp minima of the few-miss path
 
     const int h = blockIdx.x;
     const int tid = threadIdx.x;
@@ -164,48 +161,7 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
     __syncthreads();  // the table is dead from here on; xbuf becomes keyB/valB
 
     if (n_miss > 0) {
-        int *kin = keyA, *vin = valA;
-        if (n_miss <= kLruFewMisses) {
-            // ---- 3a. few misses: pull the smallest (time, slot) keys out one at a time -----
-            unsigned long long mine[kLruMaxRounds];
-#pragma unroll
-            for (int r = 0; r < kLruMaxRounds; ++r) {
-                const int s = r * kLruThreads + tid;
-                mine[r] = (r * kLruThreads < n_slots && s < n_slots)
-                              ? (((unsigned long long)(uint32_t)keyA[s] << 32) | (uint32_t)s)
-                              : ~0ull;
-            }
-            __syncthreads();  // keyA fully read before the victims are written over it
-            for (int j = 0; j < n_miss; ++j) {
-                unsigned long long v = mine[0];
-#pragma unroll
-                for (int r = 1; r < kLruMaxRounds; ++r) v = mine[r] < v ? mine[r] : v;
-#pragma unroll
-                for (int off = 16; off >= 1; off >>= 1) {
-                    const unsigned long long o = __shfl_xor_sync(DA_FULL_MASK, v, off);
-                    v = o < v ? o : v;
-                }
-                if (lane == 0) wmin[warp] = v;
-                __syncthreads();
-                unsigned long long w = wmin[lane];
-#pragma unroll
-                for (int off = 16; off >= 1; off >>= 1) {
-                    const unsigned long long o = __shfl_xor_sync(DA_FULL_MASK, w, off);
-                    w = o < w ? o : w;
-                }
-#pragma unroll
-                for (int r = 0; r < kLruMaxRounds; ++r)
-                    if (mine[r] == w) mine[r] = ~0ull;   // taken (keys are unique: the slot is in them)
-                if (tid == 0) {
-                    keyB[j] = (int)(w >> 32);
-                    valB[j] = (int)(w & 0xffffffffu);
-                }
-                __syncthreads();
-            }
-            kin = keyB;
-            vin = valB;
-        } else {
-        // ---- 3b. stable radix sort of the slots by access time ---------------------
+        // ---- 3. stable radix sort of the slots by access time --------------------
         {
             int mx = 0;
             for (int s = tid; s < n_slots; s += kLruThreads) mx = max(mx, keyA[s]);
@@ -219,7 +175,7 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
         // warp w owns the contiguous items [w * per_warp, (w + 1) * per_warp)
         const int per_warp = (((n_slots + kLruWarps - 1) / kLruWarps) + 31) / 32 * 32;
         const int rounds = per_warp / 32;  // <= kLruMaxRounds
-        int *kout = keyB, *vout = valB;
+        int *kin = keyA, *vin = valA, *kout = keyB, *vout = valB;
         for (int pass = 0; pass < passes; ++pass) {
             const int shift = 8 * pass;
             for (int x = tid; x < 256 * kLruWarps; x += kLruThreads) hist[x] = 0;
@@ -280,8 +236,7 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
             int *t = kin; kin = kout; kout = t;
             t = vin; vin = vout; vout = t;
         }
-        }
-        // kin/vin now hold (at least the first n_miss of) the slots in eviction order.
+        // kin/vin now hold the slots in eviction order.
 
         // ---- 4. overflow check, then assignment ------------------------------------
         const bool overflow = (n_miss > n_slots) || (kin[min(n_miss, n_slots) - 1] >= step);

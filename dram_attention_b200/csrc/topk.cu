@@ -75,7 +75,6 @@ topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_l
     unsigned long long *cand = reinterpret_cast<unsigned long long *>(smem_raw);  // [k]
     int *rank = reinterpret_cast<int *>(cand + k);                                // [k]
     __shared__ int hist[256];
-    __shared__ int whist[kTopkWarps][256];  // one private histogram per warp
     __shared__ int warp_tot[kTopkWarps];
     __shared__ int sh_digit, sh_above, sh_count, sh_taken;
 
@@ -97,34 +96,23 @@ topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_l
     int count_eq = 0;
     for (int pass = 0; pass < 4; ++pass) {
         const int shift = 24 - 8 * pass;
-        for (int x = tid; x < kTopkWarps * 256; x += kTopkThreads) (&whist[0][0])[x] = 0;
+        if (tid < 256) hist[tid] = 0;
         __syncthreads();
         keys.for_each(srow, n_pages, tid, [&](int, uint32_t key, bool valid) {
             const bool in = valid && (key & mask) == prefix;
-            // Scores cluster in a few exponent buckets, so the lanes of a warp share few
-            // digits: up to four rounds count all lanes that agree with the first remaining
-            // lane by one ballot; whoever is left adds one by one.  The histogram is private
-            // to the warp, so nothing serialises across the block.
+            // Scores cluster in a few exponent buckets, so most lanes of a warp share a
+            // digit: the lanes that agree with the first participating lane are counted
+            // with one ballot and one atomic, the rest add one by one.
             const uint32_t digit = (key >> shift) & 255u;
-            uint32_t rem = __ballot_sync(DA_FULL_MASK, in);
-#pragma unroll
-            for (int round = 0; round < 4; ++round) {
-                if (rem == 0) break;  // warp-uniform
-                const int first = __ffs(rem) - 1;
+            const uint32_t act = __ballot_sync(DA_FULL_MASK, in);
+            if (act) {
+                const int first = __ffs(act) - 1;
                 const uint32_t d0 = __shfl_sync(DA_FULL_MASK, digit, first);
-                const uint32_t same = __ballot_sync(DA_FULL_MASK, ((rem >> lane) & 1u) && digit == d0);
-                if (lane == first) atomicAdd(&whist[warp][d0], __popc(same));
-                rem &= ~same;
+                const uint32_t same = __ballot_sync(DA_FULL_MASK, in && digit == d0);
+                if (lane == first) atomicAdd(&hist[d0], __popc(same));
+                else if (in && digit != d0) atomicAdd(&hist[digit], 1);
             }
-            if ((rem >> lane) & 1u) atomicAdd(&whist[warp][digit], 1);
         });
-        __syncthreads();
-        if (tid < 256) {
-            int c = 0;
-#pragma unroll
-            for (int w = 0; w < kTopkWarps; ++w) c += whist[w][tid];
-            hist[tid] = c;
-        }
         __syncthreads();
         if (warp == 0) {
             // lane l owns digits 255-8l .. 248-8l (descending); find the digit where the
