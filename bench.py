@@ -41,6 +41,9 @@ if ROOT not in sys.path:
 
 METRIC = "decode tok/s at 128K ctx (Llama-3-8B attn shape)"
 FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one attention launch at the default workload, from the ncu
+# capture summarised in profiles/decode_attention_mma_llama128k.md
+ATTN_TRAFFIC_BYTES_128K = 155.5e6
 
 
 def parse_args():
@@ -378,7 +381,8 @@ def run_b200(args):
         ach = b_attn / (stage_us["attention"] * 1e-6) / 1e9
         roofline = {"bound": "hbm", "kernel": "decode_attention_kernel", "achieved": ach, "peak": peak,
                     "peak_kind": peak_kind + " HBM copy bandwidth", "unit": "GB/s", "frac": ach / peak,
-                    "traffic": None, "algorithmic_bytes_per_launch": b_attn,
+                    "traffic": (ATTN_TRAFFIC_BYTES_128K if (world == 1 and args.dram_tokens == 131072) else None),
+                    "algorithmic_bytes_per_launch": b_attn,
                     "launch_us": stage_us["attention"]}
     roofline_score = None
     if stage_us["score"]:
