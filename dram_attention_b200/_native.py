@@ -39,6 +39,10 @@ _SIGNATURES = {
                                     c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
                                     c_void_p, c_void_p, c_size_t, c_void_p, c_int, c_int, c_int, c_int,
                                     c_void_p]),
+    "da_decode_attention_static_capacity": (c_size_t, []),
+    "da_decode_attention_static": (c_int, [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_longlong,
+                                           c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
+                                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "da_build_pages": (c_int, [c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p,
                                c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
 }

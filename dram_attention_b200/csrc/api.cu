@@ -13,6 +13,7 @@ extern "C" const char *da_error_string(int code) {
     case DA_ERR_ALIGN: return "a pointer or stride breaks the required alignment";
     case DA_ERR_UNSUPPORTED: return "shape outside what the kernels are built for";
     case DA_ERR_WORKSPACE: return "workspace too small";
+    case DA_ERR_STATIC_SCRATCH: return "shape needs more scratch than the library's built-in buffer holds; use da_decode_attention with a workspace";
     default: break;
     }
     if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));

@@ -391,3 +391,55 @@ extern "C" int da_decode_attention(const void *q, const void *prefix_kv, long lo
     else e = da::launch_attention_mma(p, n_kv_heads, rep, head_dim, dtype, s);
     return (int)e;
 }
+
+// ---- entry point with built-in scratch ------------------------------------------------
+
+namespace da {
+// Scratch for da_decode_attention_static: the same layout da_decode_attention expects in
+// its workspace (ticket counters, then the per-CTA partials).  2 MiB covers every shape
+// the kernels accept with head_dim <= 128 and rep <= 8 (the largest needs about 1.2 MiB).
+// The array is part of the loaded module: every GPU that loads this library keeps it
+// until the process exits, and it starts out zero-filled.
+constexpr size_t kStaticScratchBytes = 2u << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+}  // namespace da
+
+extern "C" size_t da_decode_attention_static_capacity(void) { return da::kStaticScratchBytes; }
+
+extern "C" int da_decode_attention_static(const void *q, const void *prefix_kv, long long prefix_head_stride,
+                                          int n_prefix_tokens, void *local_k, void *local_v,
+                                          long long local_token_stride, long long local_head_stride,
+                                          int local_capacity, const void *new_k, const void *new_v,
+                                          const int32_t *start_pos_dev, int start_pos_host, int dram_tokens,
+                                          void *out, float *lse_out, int32_t *status, int n_kv_heads, int rep,
+                                          int head_dim, int dtype, da_stream_t stream) {
+    if (n_kv_heads < 1 || rep < 1 || head_dim < 1) return DA_ERR_SHAPE;
+    const size_t need = da_decode_attention_workspace_bytes(n_kv_heads, rep, head_dim);
+    if (need > da::kStaticScratchBytes) return DA_ERR_STATIC_SCRATCH;
+
+    // In host code the array's name is only a handle for the runtime, not a device
+    // address: ask the runtime for the address once per device, with that device
+    // current (it is: the caller's stream belongs to it), and hand that to the kernel.
+    static void *scratch_of_device[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return DA_ERR_UNSUPPORTED;
+    if (scratch_of_device[dev] == nullptr) {
+        void *ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, da::g_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        scratch_of_device[dev] = ptr;
+    }
+    void *scratch = scratch_of_device[dev];
+
+    // All calls share the array and it keeps what the last call left.  The kernel only
+    // needs the ticket counters to be zero on entry; clear them on the caller's stream
+    // (a call that was cut short could have left them half counted).
+    e = cudaMemsetAsync(scratch, 0, da::kCounterBytes, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return (int)e;
+    return da_decode_attention(q, prefix_kv, prefix_head_stride, n_prefix_tokens, local_k, local_v,
+                               local_token_stride, local_head_stride, local_capacity, new_k, new_v,
+                               start_pos_dev, start_pos_host, dram_tokens, out, lse_out, scratch,
+                               da::kStaticScratchBytes, status, n_kv_heads, rep, head_dim, dtype, stream);
+}

@@ -45,6 +45,7 @@ extern "C" {
 #define DA_ERR_ALIGN (-4)       /* a pointer or stride breaks the stated alignment */
 #define DA_ERR_UNSUPPORTED (-5) /* valid, but outside what the kernels are built for */
 #define DA_ERR_WORKSPACE (-6)   /* workspace smaller than the *_workspace_bytes value */
+#define DA_ERR_STATIC_SCRATCH (-7) /* shape needs more scratch than the built-in buffer holds */
 
 /* bits of the device status word */
 #define DA_STATUS_BAD_PAGE_ID 1      /* a listed page id was outside [0, n_dram_pages) */
@@ -202,6 +203,44 @@ DA_API int da_decode_attention(const void *q,
                         const int32_t *start_pos_dev, int start_pos_host, int dram_tokens,
                         void *out, float *lse_out,
                         void *workspace, size_t workspace_bytes, int32_t *status,
+                        int n_kv_heads, int rep, int head_dim, int dtype,
+                        da_stream_t stream);
+
+/*
+ * da_decode_attention for callers that cannot hand over a workspace.  (No counterpart
+ * in the reference; it does not change what is computed.)
+ *
+ * Some hosts of this library may not allocate device memory once they are running:
+ * a serving process whose memory plan is frozen after start-up, a plugin loaded into
+ * a runtime that owns the allocator, code that is entered while the application holds
+ * a capture or a lock under which cudaMalloc is off limits.  For them this variant
+ * keeps the kernel's scratch (ticket counters and split partials) in a buffer that is
+ * part of the library image: da_decode_attention_static_capacity() bytes (2 MiB),
+ * resident on every GPU that loads the library until the process exits.  The call
+ * allocates nothing and calls no allocating routine.
+ *
+ * Arguments and result are those of da_decode_attention without workspace and
+ * workspace_bytes.  Differences to know about:
+ *   - shapes whose workspace (da_decode_attention_workspace_bytes) exceeds the
+ *     capacity are rejected with DA_ERR_STATIC_SCRATCH;
+ *   - the first call on a device looks up the buffer's device address (a host-side
+ *     runtime query); make that first call outside any stream capture;
+ *   - every call clears the counters it needs on `stream` before the kernel, so a
+ *     previous call's leftovers cannot leak in;
+ *   - there is ONE buffer per GPU: two calls that may run at the same time on one GPU
+ *     (different streams, different threads, different operator instances) race on
+ *     it.  Serialise them, or use da_decode_attention with a workspace per caller.
+ */
+DA_API size_t da_decode_attention_static_capacity(void);
+DA_API int da_decode_attention_static(const void *q,
+                        const void *prefix_kv, long long prefix_head_stride,
+                        int n_prefix_tokens,
+                        void *local_k, void *local_v,
+                        long long local_token_stride, long long local_head_stride,
+                        int local_capacity,
+                        const void *new_k, const void *new_v,
+                        const int32_t *start_pos_dev, int start_pos_host, int dram_tokens,
+                        void *out, float *lse_out, int32_t *status,
                         int n_kv_heads, int rep, int head_dim, int dtype,
                         da_stream_t stream);
 
