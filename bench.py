@@ -379,7 +379,7 @@ def run_b200(args):
     roofline = None
     if stage_us["attention"]:
         ach = b_attn / (stage_us["attention"] * 1e-6) / 1e9
-        roofline = {"bound": "hbm", "kernel": "decode_attention_kernel", "achieved": ach, "peak": peak,
+        roofline = {"bound": "hbm", "kernel": "decode_attention_mma_kernel", "achieved": ach, "peak": peak,
                     "peak_kind": peak_kind + " HBM copy bandwidth", "unit": "GB/s", "frac": ach / peak,
                     "traffic": (ATTN_TRAFFIC_BYTES_128K if (world == 1 and args.dram_tokens == 131072) else None),
                     "algorithmic_bytes_per_launch": b_attn,
@@ -387,7 +387,7 @@ def run_b200(args):
     roofline_score = None
     if stage_us["score"]:
         ach = b_score / (stage_us["score"] * 1e-6) / 1e9
-        roofline_score = {"bound": "hbm", "kernel": "score_pages_kernel", "achieved": ach, "peak": peak,
+        roofline_score = {"bound": "hbm", "kernel": "score_pages_mma_kernel", "achieved": ach, "peak": peak,
                           "unit": "GB/s", "frac": ach / peak, "algorithmic_bytes_per_launch": b_score,
                           "launch_us": stage_us["score"]}
 
@@ -422,8 +422,13 @@ def run_b200(args):
                           "CPU port of the reference's pure-PyTorch path"}
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+        # No collective follows the timing all-reduce, so every rank can leave on its own.  The
+        # process group is not torn down: the captured graphs still reference the communicator,
+        # and destroying it under them has been seen to block at exit.
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main():
