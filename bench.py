@@ -322,6 +322,7 @@ def run_b200(args):
     ms_e2e = ev0.elapsed_time(ev1)
 
     # ---------------- per-stage timing of un-captured steps (roofline) -------------------
+    fused = bool(getattr(inner, "_can_fuse", False) and inner.fused_fetch)
     stage_names = ["score", "topk", "lru", "fetch", "attention"]
     stage_ms = {n: [] for n in stage_names}
     misses = []
@@ -347,9 +348,10 @@ def run_b200(args):
         ev[2].record()
         lc.update_tables_(page_list)
         ev[3].record()
-        lc.fetch_(list_len)
+        if not fused:
+            lc.fetch_(list_len)
         ev[4].record()
-        inner.attend_(q, kk, vv, S + step, out_p)
+        inner.attend_(q, kk, vv, S + step, out_p, fetch=fused)
         ev[5].record()
         miss_dev[i].copy_(lc.last_miss_counts(list_len).sum())
         events.append(ev)
@@ -371,6 +373,8 @@ def run_b200(args):
 
     mean = lambda xs: (sum(xs) / len(xs)) if xs else None
     stage_us = {n: (mean(v) * 1e3 if v else None) for n, v in stage_ms.items()}
+    if fused:
+        stage_us["fetch"] = None   # no such launch: the attention kernel reads the missed pages itself
     t_local = (S + step - 1) - w.dram_tokens          # local tokens at the last profiled step
     n_slots_tokens = w.lru_hbm_cache_size
     b_attn = hk * (n_slots_tokens + t_local + 1) * 2 * D * esz + 2 * hk * rep * D * esz
@@ -406,12 +410,13 @@ def run_b200(args):
                     "h2d_bytes_per_step": (hq[0].numel() + hkk[0].numel() + hv[0].numel()) * esz,
                     "d2h_bytes_per_step": out_h.numel() * esz, "ms_per_step": ms_e2e / K,
                     "per_step": "pinned H2D of q/k/v, one captured step, D2H of the output, stream sync"},
-            "gpu_launches": 5 * K,
+            "gpu_launches": (4 if fused else 5) * K,
             "roofline": roofline,
             "roofline_score": roofline_score,
             "stage_us": stage_us,
             "misses_per_step": mean(misses),
-            "fetch_fraction_of_step": (stage_us["fetch"] / sum(v for v in stage_us.values())
+            "fetch": ("inside the attention kernel" if fused else "separate gather-copy launch"),
+            "fetch_fraction_of_step": (stage_us["fetch"] / sum(v for v in stage_us.values() if v)
                                        if stage_us["fetch"] else None),
         }
         if world == 1 and not args.no_cpu_baseline:

@@ -31,7 +31,11 @@ _SIGNATURES = {
                                c_int, c_void_p]),
     "da_topk_pages": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "da_lru_update": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "da_decode_attention_fetch": (c_int, [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_void_p,
+                                          c_void_p, c_void_p, c_longlong, c_longlong, c_int, c_void_p, c_void_p,
+                                          c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p,
+                                          c_int, c_int, c_int, c_int, c_void_p]),
     "da_fetch_pages": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                c_size_t, c_void_p]),
     "da_decode_attention_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),

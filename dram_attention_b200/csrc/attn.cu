@@ -109,22 +109,35 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     }
 
     // tokens of unit u
+    const int n_my = units > worker ? (units - worker + n_workers - 1) / n_workers : 0;
+    // lane i remembers where the warp's i-th unit has to come from (the host checks n_my <= 32
+    // whenever slot_source is given)
+    int my_src = -1;
+    if (p.slot_source && lane < n_my) {
+        const int u = worker + lane * n_workers;
+        if (u < units_prefix) my_src = p.slot_source[(size_t)h * p.n_slots + (u * kUnitTokens) / p.page_tokens];
+    }
+
     auto unit_tokens = [&](int u) -> int {
         if (u < units_prefix) return min(kUnitTokens, n_prefix - u * kUnitTokens);
         return min(kUnitTokens, n_local - (u - units_prefix) * kUnitTokens);
     };
 
     // start the copies of unit u into stage s of this warp
-    auto issue = [&](int u, int s) {
+    auto issue = [&](int u, int s, int it) {
         uint64_t *bar = &bars[warp][s];
         unsigned char *dst = my_stages + (size_t)s * UNITB;
         const int ntok = unit_tokens(u);
+        const int src_page = __shfl_sync(DA_FULL_MASK, my_src, it & 31);
         if (u < units_prefix) {
             if (lane == 0) {
                 const uint32_t bytes = (uint32_t)ntok * TOKB;
                 mbar_arrive_expect_tx(bar, bytes);
+                const size_t tok = (size_t)u * kUnitTokens;
                 const unsigned char *src =
-                    p.prefix + ((size_t)h * p.prefix_head_stride + (size_t)u * kUnitTokens * 2 * D) * E;
+                    src_page < 0 ? p.prefix + ((size_t)h * p.prefix_head_stride + tok * 2 * D) * E
+                                 : p.dram + ((size_t)h * p.dram_head_stride +
+                                             ((size_t)src_page * p.page_tokens + tok % p.page_tokens) * 2 * D) * E;
                 bulk_copy_g2s(dst, src, bytes, bar);
             }
         } else {
@@ -147,8 +160,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
         }
     };
 
-    const int n_my = units > worker ? (units - worker + n_workers - 1) / n_workers : 0;
-    for (int it = 0; it < STAGES && it < n_my; ++it) issue(worker + it * n_workers, it);
+    for (int it = 0; it < STAGES && it < n_my; ++it) issue(worker + it * n_workers, it, it);
 
     for (int it = 0; it < n_my; ++it) {
         const int s = it % STAGES;
@@ -160,6 +172,13 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
         const int u = worker + it * n_workers;
         const int ntok = unit_tokens(u);
         const unsigned char *sb = my_stages + (size_t)s * UNITB;
+        if (__shfl_sync(DA_FULL_MASK, my_src, it & 31) >= 0) {
+            // this unit came from DRAM: write it through to its slot
+            uint4 *slot = reinterpret_cast<uint4 *>(
+                const_cast<unsigned char *>(p.prefix) +
+                ((size_t)h * p.prefix_head_stride + (size_t)u * kUnitTokens * 2 * D) * E);
+            for (int i = lane; i < ntok * (TOKB / 16); i += 32) slot[i] = reinterpret_cast<const uint4 *>(sb)[i];
+        }
 
         // logits (log2 domain) of 4 tokens x REP heads
         float sc[4][REP];
@@ -225,7 +244,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
         }
 
         __syncwarp();
-        if (it + STAGES < n_my) issue(worker + (it + STAGES) * n_workers, s);
+        if (it + STAGES < n_my) issue(worker + (it + STAGES) * n_workers, s, it + STAGES);
     }
 
     // ---- merge the 4 token groups of the warp ---------------------------------------
@@ -339,14 +358,15 @@ extern "C" size_t da_decode_attention_workspace_bytes(int n_kv_heads, int rep, i
            (size_t)n_kv_heads * da::attn_splits(n_kv_heads) * rep * (head_dim + 4) * sizeof(float);
 }
 
-extern "C" int da_decode_attention(const void *q, const void *prefix_kv, long long prefix_head_stride,
+static int decode_attention_common(const void *q, const void *prefix_kv, long long prefix_head_stride,
                                    int n_prefix_tokens, void *local_k, void *local_v,
                                    long long local_token_stride, long long local_head_stride,
                                    int local_capacity, const void *new_k, const void *new_v,
                                    const int32_t *start_pos_dev, int start_pos_host, int dram_tokens,
                                    void *out, float *lse_out, void *workspace, size_t workspace_bytes,
                                    int32_t *status, int n_kv_heads, int rep, int head_dim, int dtype,
-                                   da_stream_t stream) {
+                                   const void *dram_pages, int n_dram_pages, const int32_t *slot_source,
+                                   int n_slots, int page_size, da_stream_t stream) {
     if (!q || !prefix_kv || !local_k || !local_v || !new_k || !new_v || !out || !workspace || !status)
         return DA_ERR_NULL;
     if (n_kv_heads < 1 || n_prefix_tokens < 1 || local_capacity < 1 || dram_tokens < 0) return DA_ERR_SHAPE;
@@ -363,7 +383,7 @@ extern "C" int da_decode_attention(const void *q, const void *prefix_kv, long lo
         return DA_ERR_ALIGN;
     if (workspace_bytes < da_decode_attention_workspace_bytes(n_kv_heads, rep, head_dim)) return DA_ERR_WORKSPACE;
 
-    da::AttnParams p;
+    da::AttnParams p{};
     p.q = static_cast<const unsigned char *>(q);
     p.prefix = static_cast<const unsigned char *>(prefix_kv);
     p.prefix_head_stride = prefix_head_stride;
@@ -384,12 +404,63 @@ extern "C" int da_decode_attention(const void *q, const void *prefix_kv, long lo
     p.partials = reinterpret_cast<float *>(static_cast<unsigned char *>(workspace) + da::kCounterBytes);
     p.status = status;
     p.scale_log2 = 1.4426950408889634f / sqrtf((float)head_dim);
+    if (slot_source) {
+        // units (16 tokens) must not straddle pages, the slot table must be exactly the prefix,
+        // and a warp keeps the sources of its units in its 32 lanes
+        if (!dram_pages) return DA_ERR_NULL;
+        if (page_size < 1 || n_slots < 1 || n_dram_pages < 1) return DA_ERR_SHAPE;
+        if (page_size % da::kUnitTokens != 0 || (long long)n_slots * page_size != n_prefix_tokens)
+            return DA_ERR_UNSUPPORTED;
+        if ((uintptr_t)dram_pages & 15) return DA_ERR_ALIGN;
+        const int units_max = (n_prefix_tokens + da::kUnitTokens - 1) / da::kUnitTokens +
+                              (local_capacity + da::kUnitTokens - 1) / da::kUnitTokens;
+        const int workers = da::attn_splits(n_kv_heads) * da::kAttnWarps;
+        if ((units_max + workers - 1) / workers > 32) return DA_ERR_UNSUPPORTED;
+        p.dram = static_cast<const unsigned char *>(dram_pages);
+        p.dram_head_stride = (long long)n_dram_pages * page_size * 2 * head_dim;
+        p.slot_source = slot_source;
+        p.n_slots = n_slots;
+        p.page_tokens = page_size;
+    }
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     cudaError_t e;
     if (dtype == DA_F32) e = da::dispatch_attn<float>(p, n_kv_heads, rep, head_dim, s);
     else e = da::launch_attention_mma(p, n_kv_heads, rep, head_dim, dtype, s);
     return (int)e;
+}
+
+extern "C" int da_decode_attention(const void *q, const void *prefix_kv, long long prefix_head_stride,
+                                   int n_prefix_tokens, void *local_k, void *local_v,
+                                   long long local_token_stride, long long local_head_stride,
+                                   int local_capacity, const void *new_k, const void *new_v,
+                                   const int32_t *start_pos_dev, int start_pos_host, int dram_tokens,
+                                   void *out, float *lse_out, void *workspace, size_t workspace_bytes,
+                                   int32_t *status, int n_kv_heads, int rep, int head_dim, int dtype,
+                                   da_stream_t stream) {
+    return decode_attention_common(q, prefix_kv, prefix_head_stride, n_prefix_tokens, local_k, local_v,
+                                   local_token_stride, local_head_stride, local_capacity, new_k, new_v,
+                                   start_pos_dev, start_pos_host, dram_tokens, out, lse_out, workspace,
+                                   workspace_bytes, status, n_kv_heads, rep, head_dim, dtype, nullptr, 0,
+                                   nullptr, 0, 0, stream);
+}
+
+extern "C" int da_decode_attention_fetch(const void *q, void *slots, long long slots_head_stride, int n_slots,
+                                         int page_size, const void *dram_pages, int n_dram_pages,
+                                         const int32_t *slot_source, void *local_k, void *local_v,
+                                         long long local_token_stride, long long local_head_stride,
+                                         int local_capacity, const void *new_k, const void *new_v,
+                                         const int32_t *start_pos_dev, int start_pos_host, int dram_tokens,
+                                         void *out, float *lse_out, void *workspace, size_t workspace_bytes,
+                                         int32_t *status, int n_kv_heads, int rep, int head_dim, int dtype,
+                                         da_stream_t stream) {
+    if (!slot_source) return DA_ERR_NULL;
+    if (n_slots < 1 || page_size < 1 || (long long)n_slots * page_size > 0x7fffffffLL) return DA_ERR_SHAPE;
+    return decode_attention_common(q, slots, slots_head_stride, n_slots * page_size, local_k, local_v,
+                                   local_token_stride, local_head_stride, local_capacity, new_k, new_v,
+                                   start_pos_dev, start_pos_host, dram_tokens, out, lse_out, workspace,
+                                   workspace_bytes, status, n_kv_heads, rep, head_dim, dtype, dram_pages,
+                                   n_dram_pages, slot_source, n_slots, page_size, stream);
 }
 
 // ---- entry point with built-in scratch ------------------------------------------------

@@ -39,6 +39,13 @@ struct AttnParams {
     unsigned int *counters;
     int32_t *status;
     float scale_log2;
+    // optional: pages that da_lru_update just assigned to slots are read from DRAM (pinned
+    // host memory) by the warp that owns the unit, and written through to the slot
+    const unsigned char *dram;       // (n_kv_heads, n_dram_pages, page_tokens, 2, D) or null
+    long long dram_head_stride;      // elements
+    const int32_t *slot_source;      // (n_kv_heads, n_slots): DRAM page to read instead, or -1
+    int n_slots;
+    int page_tokens;                 // multiple of 16 when slot_source is set
 };
 
 // Floats per partial row: acc[D], max, l, padded to a multiple of 4 so that rows can

@@ -147,6 +147,15 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_mma_kernel(c
 #pragma unroll
     for (int d = 0; d < NT; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
 
+    const int n_my = units > worker ? (units - worker + n_workers - 1) / n_workers : 0;
+    // lane i remembers where the warp's i-th unit has to come from (the host checks n_my <= 32
+    // whenever slot_source is given)
+    int my_src = -1;
+    if (p.slot_source && lane < n_my) {
+        const int u = worker + lane * n_workers;
+        if (u < units_prefix) my_src = p.slot_source[(size_t)h * p.n_slots + (u * kUnitTokens) / p.page_tokens];
+    }
+
     auto unit_tokens = [&](int u) -> int {
         if (u < units_prefix) return min(kUnitTokens, n_prefix - u * kUnitTokens);
         return min(kUnitTokens, n_local - (u - units_prefix) * kUnitTokens);
@@ -155,10 +164,11 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_mma_kernel(c
     // Slot-table units: one bulk copy per token (its key and value rows are contiguous in
     // HBM), issued by lanes 0..15.  Local-window units: one copy per row, key rows by
     // lanes 0..15 and value rows by lanes 16..31.
-    auto issue = [&](int u, int s) {
+    auto issue = [&](int u, int s, int it) {
         uint64_t *bar = &bars[warp][s];
         unsigned char *dst = my_stages + (size_t)s * STAGEB;
         const int ntok = unit_tokens(u);
+        const int src_page = __shfl_sync(DA_FULL_MASK, my_src, it & 31);
         if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)ntok * 2 * ROWB);
         __syncwarp();
         const int tl = lane & 15;
@@ -166,8 +176,12 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_mma_kernel(c
         if (tl < ntok) {
             if (u < units_prefix) {
                 if (!is_v) {
+                    const size_t tok = (size_t)u * kUnitTokens + tl;
                     const unsigned char *src =
-                        p.prefix + ((size_t)h * p.prefix_head_stride + ((size_t)u * kUnitTokens + tl) * 2 * D) * E;
+                        src_page < 0
+                            ? p.prefix + ((size_t)h * p.prefix_head_stride + tok * 2 * D) * E
+                            : p.dram + ((size_t)h * p.dram_head_stride +
+                                        ((size_t)src_page * p.page_tokens + tok % p.page_tokens) * 2 * D) * E;
                     bulk_copy_g2s(dst + tl * PITCH, src, 2 * ROWB, bar);
                 }
             } else {
@@ -184,8 +198,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_mma_kernel(c
         }
     };
 
-    const int n_my = units > worker ? (units - worker + n_workers - 1) / n_workers : 0;
-    for (int it = 0; it < STAGES && it < n_my; ++it) issue(worker + it * n_workers, it);
+    for (int it = 0; it < STAGES && it < n_my; ++it) issue(worker + it * n_workers, it, it);
 
     // ldmatrix row addresses of this lane inside a stage
     const int lm = lane >> 3;   // which 8x8 tile of the x4 load
@@ -203,6 +216,16 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_mma_kernel(c
         const int u = worker + it * n_workers;
         const int ntok = unit_tokens(u);
         unsigned char *sb = my_stages + (size_t)s * STAGEB;
+        if (__shfl_sync(DA_FULL_MASK, my_src, it & 31) >= 0) {
+            // this unit came from DRAM: write it through to its slot (512 bytes per token)
+            unsigned char *slot = const_cast<unsigned char *>(p.prefix) +
+                                  ((size_t)h * p.prefix_head_stride + (size_t)u * kUnitTokens * 2 * D) * E;
+            for (int i = lane; i < ntok * (2 * ROWB / 16); i += 32) {
+                const int t = i / (2 * ROWB / 16), c = i % (2 * ROWB / 16);
+                reinterpret_cast<uint4 *>(slot + (size_t)t * 2 * ROWB)[c] =
+                    reinterpret_cast<const uint4 *>(sb + t * PITCH)[c];
+            }
+        }
         if (ntok < kUnitTokens) {
             // rows past the end hold stale bytes: zero the value rows so that 0 * garbage
             // cannot produce NaN (their logits are masked below)
@@ -264,7 +287,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_mma_kernel(c
         }
 
         __syncwarp();
-        if (it + STAGES < n_my) issue(worker + (it + STAGES) * n_workers, s);
+        if (it + STAGES < n_my) issue(worker + (it + STAGES) * n_workers, s, it + STAGES);
     }
 
     // ---- this warp's partial: finish the row sum, publish --------------------------------

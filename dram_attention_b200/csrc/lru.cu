@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(kLruThreads)
 lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *dram_to_slot, int n_dram_pages,
                   int32_t *slot_to_dram, int32_t *access_time, int n_slots, int32_t *step_counters,
                   int32_t *__restrict__ miss_pages, int32_t *__restrict__ miss_slots,
-                  int32_t *__restrict__ n_miss_out, int32_t *status) {
+                  int32_t *__restrict__ n_miss_out, int32_t *slot_source, int32_t *status) {
     extern __shared__ __align__(16) int smem_i[];
     const int table = lru_table_size(list_len);
     const int xhalf = n_slots > table ? n_slots : table;
@@ -91,6 +91,17 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
     int32_t *tim = access_time + (size_t)h * n_slots;
     int32_t *mp_out = miss_pages + (size_t)h * list_len;
     int32_t *ms_out = miss_slots + (size_t)h * list_len;
+
+    // slot_source[slot] = DRAM page whose payload still has to be brought into the slot, -1
+    // otherwise: forget the marks of the previous call (its miss list is still in ms_out)
+    int32_t *src_map = slot_source ? slot_source + (size_t)h * n_slots : nullptr;
+    if (src_map) {
+        const int prev = min(n_miss_out[h], list_len);
+        for (int j = tid; j < prev; j += kLruThreads) {
+            const int v = ms_out[j];
+            if (v >= 0 && v < n_slots) src_map[v] = -1;
+        }
+    }
 
     // ---- independent global reads first: list, its table entries, times, slot map ------
     int pg[kLruMaxListRounds], sl[kLruMaxListRounds];
@@ -254,6 +265,7 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
                 tim[v] = step;
                 mp_out[j] = p;
                 ms_out[j] = v;
+                if (src_map) src_map[v] = p;
             }
         }
     }
@@ -276,7 +288,7 @@ constexpr size_t kLruMaxSmem = 227 * 1024 - 1024;
 extern "C" int da_lru_update(const int32_t *page_list, int list_len, int32_t *dram_to_slot, int n_dram_pages,
                              int32_t *slot_to_dram, int32_t *access_time, int n_slots, int32_t *step,
                              int n_kv_heads, int32_t *miss_pages, int32_t *miss_slots, int32_t *n_miss,
-                             int32_t *status, da_stream_t stream) {
+                             int32_t *slot_source, int32_t *status, da_stream_t stream) {
     if (!page_list || !dram_to_slot || !slot_to_dram || !access_time || !step || !miss_pages || !miss_slots ||
         !n_miss || !status)
         return DA_ERR_NULL;
@@ -297,6 +309,6 @@ extern "C" int da_lru_update(const int32_t *page_list, int list_len, int32_t *dr
     }
     da::lru_update_kernel<<<n_kv_heads, da::kLruThreads, smem, static_cast<cudaStream_t>(stream)>>>(
         page_list, list_len, dram_to_slot, n_dram_pages, slot_to_dram, access_time, n_slots, step, miss_pages,
-        miss_slots, n_miss, status);
+        miss_slots, n_miss, slot_source, status);
     return (int)cudaGetLastError();
 }

@@ -13,6 +13,10 @@ from .lru_cache import DummyCache, LRUCache
 class DRAMAttention(torch.nn.Module):
     """Long-context decode attention with the prefix KV cache in host DRAM.
 
+    `fused_fetch` (class attribute, default True): pages that miss the slot table are read
+    from DRAM by the attention kernel itself and written through to their slots, instead of
+    by a separate gather-copy launch before it.  Results are identical either way.
+
     Two caches: a local window of the most recent tokens in HBM, and the prefix in
     pinned DRAM behind an LRU-managed HBM slot table.  Every generate step scores
     all prefix pages against the query, makes the top pages resident and attends
@@ -51,6 +55,9 @@ class DRAMAttention(torch.nn.Module):
         self.register_buffer("cache_v", torch.zeros(cache_shape, device=device, dtype=dtype))
         self.lru_cache = None
         self._ws = {}
+        self._can_fuse = False
+
+    fused_fetch = True
 
     # ---- cache construction ---------------------------------------------------
     def init_cache(self, k_cache: torch.Tensor, v_cache: torch.Tensor):
@@ -71,7 +78,13 @@ class DRAMAttention(torch.nn.Module):
                 k_cache=dram_k_cache[0].transpose(0, 1), v_cache=dram_v_cache[0].transpose(0, 1),
                 page_size=self.page_size, top_k=self.top_k // self.page_size,
                 lru_hbm_cache_size=self.lru_hbm_cache_size, device=self.device)
+            # the fused kernel needs 16-token units inside one page and at most 32 units per warp
+            hk = self.n_kv_heads
+            warps = 4 * max(1, min(296 // hk, 148))
+            units = -(-self.lru_cache.num_hbm_pages * self.page_size // 16) + -(-self.cache_k.shape[1] // 16)
+            self._can_fuse = (self.page_size % 16 == 0) and (-(-units // warps) <= 32)
         else:
+            self._can_fuse = False
             self.lru_cache = DummyCache(
                 k_cache=dram_k_cache[0].transpose(0, 1), v_cache=dram_v_cache[0].transpose(0, 1),
                 device=self.device, page_size=self.page_size)
@@ -122,15 +135,24 @@ class DRAMAttention(torch.nn.Module):
         xk = xk if xk.is_contiguous() else xk.contiguous()
         xv = xv if xv.is_contiguous() else xv.contiguous()
         with torch.cuda.device(xq.device):
-            # score -> select -> LRU update -> fetch (no-ops for a fully resident prefix)
-            self.lru_cache.get_kv_cache_(xq)
             out = torch.empty_like(xq)
-            self.attend_(xq, xk, xv, start_pos, out)
+            if self._can_fuse and self.fused_fetch:
+                # score -> select -> LRU update -> attention that also brings in the misses
+                lc = self.lru_cache
+                _, page_list = lc.top_k_selector.page_list_(xq, lc.top_k)
+                lc.update_tables_(page_list)
+                self.attend_(xq, xk, xv, start_pos, out, fetch=True)
+            else:
+                # score -> select -> LRU update -> fetch (no-ops for a fully resident prefix)
+                self.lru_cache.get_kv_cache_(xq)
+                self.attend_(xq, xk, xv, start_pos, out)
         return out
 
-    def attend_(self, xq, xk, xv, start_pos, out, lse=None) -> None:
+    def attend_(self, xq, xk, xv, start_pos, out, lse=None, fetch=False) -> None:
         """Enqueue the decode attention over the current slot table and the local
-        window (appends xk/xv at start_pos - dram_kv_cache_size first)."""
+        window (appends xk/xv at start_pos - dram_kv_cache_size first).  With `fetch` the
+        kernel also reads the pages the last LRU update marked from DRAM and writes them
+        through to their slots (no fetch_ call needed)."""
         rep = xq.shape[2] // self.n_kv_heads
         prefix = self.lru_cache.hbm_kv_cache
         n_prefix_tokens = (self.lru_cache.num_tokens if isinstance(self.lru_cache, DummyCache)
@@ -143,12 +165,24 @@ class DRAMAttention(torch.nn.Module):
             pos_dev, pos_host = start_pos.data_ptr(), 0
         else:
             pos_dev, pos_host = 0, int(start_pos)
-        _native.check(_native.lib().da_decode_attention(
+        lib = _native.lib()
+        lse_ptr = 0 if lse is None else lse.data_ptr()
+        if fetch:
+            lc = self.lru_cache
+            _native.check(lib.da_decode_attention_fetch(
+                xq.data_ptr(), prefix.data_ptr(), prefix.stride(0), lc.num_hbm_pages, self.page_size,
+                lc.dram_kv_cache.data_ptr(), lc.num_dram_pages, lc.slot_source.data_ptr(),
+                self.cache_k.data_ptr(), self.cache_v.data_ptr(), self.cache_k.stride(1),
+                self.cache_k.stride(2), self.cache_k.shape[1], xk.data_ptr(), xv.data_ptr(),
+                pos_dev, pos_host, self.dram_kv_cache_size, out.data_ptr(), lse_ptr, buf.data_ptr(), nbytes,
+                status.data_ptr(), self.n_kv_heads, rep, self.head_dim, _native.dtype_code(xq.dtype),
+                _native.stream_ptr()), "da_decode_attention_fetch")
+            return
+        _native.check(lib.da_decode_attention(
             xq.data_ptr(), prefix.data_ptr(), prefix.stride(0), n_prefix_tokens,
             self.cache_k.data_ptr(), self.cache_v.data_ptr(), self.cache_k.stride(1),
             self.cache_k.stride(2), self.cache_k.shape[1], xk.data_ptr(), xv.data_ptr(),
-            pos_dev, pos_host, self.dram_kv_cache_size, out.data_ptr(),
-            0 if lse is None else lse.data_ptr(), buf.data_ptr(), nbytes,
+            pos_dev, pos_host, self.dram_kv_cache_size, out.data_ptr(), lse_ptr, buf.data_ptr(), nbytes,
             status.data_ptr(), self.n_kv_heads, rep, self.head_dim, _native.dtype_code(xq.dtype),
             _native.stream_ptr()), "da_decode_attention")
 

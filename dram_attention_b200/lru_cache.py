@@ -111,7 +111,12 @@ class LRUCache(torch.nn.Module):
         self.top_k_selector = IPUpperboundTopKSelector(k_cache, num_dram_pages, device=dev,
                                                        _summaries=summaries)
         self.register_buffer("status", torch.zeros(1, **i32), persistent=False)
+        # slot -> DRAM page whose payload is still to be brought in (-1: slot is up to date);
+        # maintained by the LRU kernel, consumed by the attention kernel that fetches on the fly
+        self.register_buffer("slot_source", torch.full((num_kv_heads, num_hbm_pages), -1, **i32),
+                             persistent=False)
         self._miss = {}
+        self._last_list_len = None
 
     @property
     def current_step(self) -> torch.Tensor:
@@ -121,7 +126,7 @@ class LRUCache(torch.nn.Module):
         bufs = self._miss.get(list_len)
         if bufs is None:
             dev = self.hbm_kv_cache.device
-            mk = lambda *s: torch.empty(*s, dtype=torch.int32, device=dev)
+            mk = lambda *s: torch.zeros(*s, dtype=torch.int32, device=dev)
             bufs = self._miss[list_len] = (mk(self.num_kv_heads, list_len), mk(self.num_kv_heads, list_len),
                                            mk(self.num_kv_heads))
         return bufs
@@ -131,12 +136,18 @@ class LRUCache(torch.nn.Module):
         counters, hit stamps, victim choice, both maps, and the device-side miss list."""
         list_len = page_list.shape[1]
         miss_pages, miss_slots, n_miss = self._miss_buffers(list_len)
+        if self._last_list_len != list_len:
+            # the kernel clears last call's marks from last call's miss list: start clean when
+            # another set of miss buffers comes into use
+            self.slot_source.fill_(-1)
+            n_miss.zero_()
+            self._last_list_len = list_len
         _native.check(_native.lib().da_lru_update(
             page_list.data_ptr(), list_len, self.dram_page_to_hbm_page_mapping.data_ptr(),
             self.num_dram_pages, self.hbm_page_to_dram_page_mapping.data_ptr(),
             self.page_access_time.data_ptr(), self.num_hbm_pages, self.step_counters.data_ptr(),
             self.num_kv_heads, miss_pages.data_ptr(), miss_slots.data_ptr(), n_miss.data_ptr(),
-            self.status.data_ptr(), _native.stream_ptr()), "da_lru_update")
+            self.slot_source.data_ptr(), self.status.data_ptr(), _native.stream_ptr()), "da_lru_update")
 
     def fetch_(self, list_len: int) -> None:
         """Enqueue the gather-copy of the pages the last update_tables_ found missing."""

@@ -130,6 +130,12 @@ DA_API int da_topk_pages(const float *scores, int32_t *page_list,
  * miss_pages, miss_slots (n_kv_heads, list_len) int32, written: the (page, slot)
  *             pairs whose payload has to be copied, in list order
  * n_miss      (n_kv_heads) int32, written
+ * slot_source optional (n_kv_heads, n_slots) int32 for da_decode_attention_fetch: on return
+ *             slot_source[h][s] = the DRAM page that slot s was just given and whose payload
+ *             is not in the slot yet, -1 for every other slot.  The call first clears the
+ *             marks of the previous call using the previous miss list, so when it is used
+ *             the array must start at -1, n_miss at 0, and the same miss buffers must be
+ *             passed every time.  NULL when da_fetch_pages does the copy.
  * status      (1) int32, bits or-ed in
  * Requires n_slots <= 8192, list_len <= 8192 and the shared-memory plan
  * (3*n_slots + 2*max(n_slots, T) + list_len + 8192 ints, T = power of two >= 2*list_len)
@@ -140,7 +146,7 @@ DA_API int da_lru_update(const int32_t *page_list, int list_len,
                   int32_t *slot_to_dram, int32_t *access_time, int n_slots,
                   int32_t *step, int n_kv_heads,
                   int32_t *miss_pages, int32_t *miss_slots, int32_t *n_miss,
-                  int32_t *status, da_stream_t stream);
+                  int32_t *slot_source, int32_t *status, da_stream_t stream);
 
 /*
  * Miss-page fetch: gather-copy of the pages named by da_lru_update from DRAM into
@@ -196,6 +202,39 @@ DA_API size_t da_decode_attention_workspace_bytes(int n_kv_heads, int rep, int h
 DA_API int da_decode_attention(const void *q,
                         const void *prefix_kv, long long prefix_head_stride,
                         int n_prefix_tokens,
+                        void *local_k, void *local_v,
+                        long long local_token_stride, long long local_head_stride,
+                        int local_capacity,
+                        const void *new_k, const void *new_v,
+                        const int32_t *start_pos_dev, int start_pos_host, int dram_tokens,
+                        void *out, float *lse_out,
+                        void *workspace, size_t workspace_bytes, int32_t *status,
+                        int n_kv_heads, int rep, int head_dim, int dtype,
+                        da_stream_t stream);
+
+/*
+ * da_decode_attention with the miss fetch folded in: replaces, in one launch, the payload
+ * loop of _load_lru_cache_inline_kernel (dram_attention/lru_triton_kernel.py:81-98) and
+ * the attention calls of dram_attention/dram_attention.py:191-238.
+ *
+ * The warp that attends over a 16-token unit of a slot marked in `slot_source` (written by
+ * da_lru_update) reads that unit from the DRAM page instead (bulk copies from pinned host
+ * memory, issued stages ahead so the host-link latency overlaps the other units), uses it,
+ * and writes it through to the slot.  Every marked page is read from DRAM exactly once and
+ * no separate da_fetch_pages launch is needed.
+ *
+ * slots        (n_kv_heads, n_slots, page_size, 2, head_dim) `dtype`, read AND written
+ * dram_pages   (n_kv_heads, n_dram_pages, page_size, 2, head_dim): pinned, device-mapped
+ *              host memory (or device memory), 16-byte aligned
+ * slot_source  (n_kv_heads, n_slots) int32 as left by da_lru_update
+ * Other arguments as da_decode_attention.  Requires page_size to be a multiple of 16 and
+ * (slot tokens + local capacity) / 16 units to be at most 32 per warp of the launch
+ * (4 * max(1, min(296 / n_kv_heads, 148)) warps per head); otherwise DA_ERR_UNSUPPORTED
+ * (use da_fetch_pages + da_decode_attention).
+ */
+DA_API int da_decode_attention_fetch(const void *q,
+                        void *slots, long long slots_head_stride, int n_slots, int page_size,
+                        const void *dram_pages, int n_dram_pages, const int32_t *slot_source,
                         void *local_k, void *local_v,
                         long long local_token_stride, long long local_head_stride,
                         int local_capacity,

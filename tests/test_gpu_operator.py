@@ -26,17 +26,27 @@ def da():
     return pkg
 
 
+@pytest.fixture(params=[True, False], ids=["fetch-in-attention", "fetch-kernel"])
+def fused(request, da):
+    """Both ways of bringing missed pages in: inside the attention kernel, or by the
+    gather-copy kernel before it."""
+    old = da.DRAMAttention.fused_fetch
+    da.DRAMAttention.fused_fetch = request.param
+    yield request.param
+    da.DRAMAttention.fused_fetch = old
+
+
 def _spy_lists(module):
     """Record the page list of every step (a copy of the selector's int32 output)."""
     lists = []
     lc = module.lru_cache
-    orig = lc._load_int32_
+    orig = lc.update_tables_
 
     def spy(page_list):
         lists.append(page_list.clone())
         return orig(page_list)
 
-    lc._load_int32_ = spy
+    lc.update_tables_ = spy
     return lists
 
 
@@ -54,12 +64,15 @@ def _run(da, ctor, dtype, k, v, xq, xk, xv, device_pos=False):
         assert out.shape == xq[i].shape and out.dtype == dtype
         outs.append(out[0, 0].float().cpu())
         h2ds.append(m.lru_cache.hbm_page_to_dram_page_mapping.cpu().numpy().astype(np.int64))
+        lc = m.lru_cache
+        for h in range(lc.num_kv_heads):   # every slot holds the page the map names
+            assert torch.equal(lc.hbm_kv_cache[h].cpu(), lc.dram_kv_cache[h, torch.from_numpy(h2ds[-1][h])]), i
         times.append(m.lru_cache.page_access_time.cpu().numpy().astype(np.int64))
     m.check_status()
     return m, outs, [l.cpu().numpy().astype(np.int64) for l in lists], h2ds, times
 
 
-def test_plumbing_trajectory_matches_reference_run(da, golden_dir):
+def test_plumbing_trajectory_matches_reference_run(da, golden_dir, fused):
     """16 generate steps of the float32 plumbing workload: page lists and LRU tables
     bit-exact, outputs within 1e-4 of what the reference's own classes produced."""
     g = np.load(os.path.join(golden_dir, "plumbing_traj.npz"))
@@ -76,7 +89,7 @@ def test_plumbing_trajectory_matches_reference_run(da, golden_dir):
 
 
 @pytest.mark.parametrize("device_pos", [False, True])
-def test_mini_trajectory_with_exact_ties(da, golden_dir, device_pos):
+def test_mini_trajectory_with_exact_ties(da, golden_dir, device_pos, fused):
     """Inputs are multiples of 1/8 so many page scores tie exactly: selection order,
     tables and outputs must still equal the reference run."""
     g = np.load(os.path.join(golden_dir, "mini_traj.npz"))
@@ -116,7 +129,7 @@ def _oracle_follow(w, steps, gpu_lists):
     return o, res
 
 
-def test_bf16_layer_trajectory_against_oracle(da):
+def test_bf16_layer_trajectory_against_oracle(da, fused):
     """A reduced Llama-shaped bf16 layer (2 KV heads, 16K-token prefix): every step's
     selection equals the oracle's up to near-ties at the k-th score, LRU tables are
     bit-exact given the same list, outputs within 2e-2."""
@@ -170,7 +183,7 @@ def test_fully_resident_prefix_uses_no_lru(da):
     m.check_status()
 
 
-def test_generate_step_is_graph_capturable(da):
+def test_generate_step_is_graph_capturable(da, fused):
     """One generate step captured in a CUDA graph with a device-side start_pos and
     replayed (the calling pattern of the reference's chat example)."""
     steps = 6
@@ -255,7 +268,7 @@ def test_invalid_stage_and_batch(op):
 
 # ---- full-size properties (sizes of the Llama-3-8B layer at 128K context) --------
 
-def test_full_size_layer_invariants(da):
+def test_full_size_layer_invariants(da, fused):
     """At the benchmark's size the oracle is too slow to follow every step, so check
     properties: slot payload == DRAM page named by the map, maps inverse of each
     other, listed pages resident and stamped with the step, every row of the page

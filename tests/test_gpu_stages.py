@@ -193,7 +193,7 @@ class Tables:
         _native.check(lib.da_lru_update(gl.data_ptr(), kk, self.g_d2h.data_ptr(), self.ld,
                                         self.g_h2d.data_ptr(), self.g_time.data_ptr(), self.nh,
                                         self.g_step.data_ptr(), self.hk, mp.data_ptr(), ms.data_ptr(),
-                                        nm.data_ptr(), self.g_status.data_ptr(), s))
+                                        nm.data_ptr(), 0, self.g_status.data_ptr(), s))
         page_bytes = self.dram.shape[2] * self.dram.element_size()
         _native.check(lib.da_fetch_pages(self.g_dram.data_ptr(), self.g_hbm.data_ptr(), mp.data_ptr(),
                                          ms.data_ptr(), nm.data_ptr(), kk, self.hk, self.ld, self.nh,
