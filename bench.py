@@ -210,7 +210,7 @@ def run_b200(args):
 
     K, W = args.steps, max(args.warmup, 3)
     P = max(0, args.profile_steps)
-    total = (W + K) * 2 + P
+    total = (W + K) * 2 + 2 * P
     w = llama_layer_workload(seed=0, steps=total, dram_tokens=args.dram_tokens, max_out=total)
     hk_all, rep, D = w.n_kv_heads, w.n_q_heads // w.n_kv_heads, w.head_dim
     lo, hi = head_range(hk_all, rank, world)
@@ -362,6 +362,53 @@ def run_b200(args):
             stage_ms[n].append(ev[j].elapsed_time(ev[j + 1]))
     misses = miss_dev[:P].tolist()
     windows.append((t_a, time.perf_counter()))
+
+    # ---------------- timeline of the overlapped step (two streams), same parking trick ----------
+    overlapped = bool(fused and inner.overlap and getattr(inner, "_can_overlap", False)
+                      and inner._overlap_supported(rep, w.dtype))
+    timeline = None
+    if overlapped and P:
+        side = torch.cuda.Stream(device=dev)
+        main = torch.cuda.current_stream()
+        recs = []
+        torch.cuda.synchronize()
+        torch.cuda._sleep(100_000_000)
+        for i in range(P):
+            q, kk, vv = dq[step], dk[step], dv[step]
+            e = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+            a = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            if not lc.split_valid:
+                lc.reset_split_()
+            e[0].record(main)
+            lc.top_k_selector.score_(q, k_pages)
+            e[1].record(main)
+            page_list = lc.top_k_selector.select_(1, rep, k_pages)
+            e[2].record(main)
+            side.wait_event(e[1])
+            with torch.cuda.stream(side):
+                a[0].record(side)
+                inner.attend_(q, kk, vv, S + step, out_p, phase=1)
+                a[1].record(side)
+            lc.update_tables_(page_list, want_split=True)
+            e[3].record(main)
+            main.wait_event(a[1])
+            inner.attend_(q, kk, vv, S + step, out_p, phase=2)
+            e[4].record(main)
+            lc.split_valid = True
+            recs.append((e, a))
+            step += 1
+        torch.cuda.synchronize()
+        avg = lambda f: sum(f(e, a) for e, a in recs) / len(recs) * 1e3
+        timeline = {
+            "score": avg(lambda e, a: e[0].elapsed_time(e[1])),
+            "topk": avg(lambda e, a: e[1].elapsed_time(e[2])),
+            "lru": avg(lambda e, a: e[2].elapsed_time(e[3])),
+            "attention_phase1_start_after_score": avg(lambda e, a: e[1].elapsed_time(a[0])),
+            "attention_phase1": avg(lambda e, a: a[0].elapsed_time(a[1])),
+            "attention_phase1_end_after_score": avg(lambda e, a: e[1].elapsed_time(a[1])),
+            "attention_phase2_after_lru": avg(lambda e, a: e[3].elapsed_time(e[4])),
+            "step": avg(lambda e, a: e[0].elapsed_time(e[4])),
+        }
     inner.check_status()
     sampler.stop()
 
@@ -410,10 +457,14 @@ def run_b200(args):
                     "h2d_bytes_per_step": (hq[0].numel() + hkk[0].numel() + hv[0].numel()) * esz,
                     "d2h_bytes_per_step": out_h.numel() * esz, "ms_per_step": ms_e2e / K,
                     "per_step": "pinned H2D of q/k/v, one captured step, D2H of the output, stream sync"},
-            "gpu_launches": (4 if fused else 5) * K,
+            "gpu_launches": (5 if (overlapped or not fused) else 4) * K,
             "roofline": roofline,
             "roofline_score": roofline_score,
             "stage_us": stage_us,
+            "overlapped_timeline_us": timeline,
+            "step_layout": ("score -> {top-k -> LRU || attention phase 1} -> attention phase 2 (+fetch)"
+                            if overlapped else ("score -> top-k -> LRU -> attention (+fetch)" if fused else
+                                                "score -> top-k -> LRU -> fetch -> attention")),
             "misses_per_step": mean(misses),
             "fetch": ("inside the attention kernel" if fused else "separate gather-copy launch"),
             "fetch_fraction_of_step": (stage_us["fetch"] / sum(v for v in stage_us.values() if v)

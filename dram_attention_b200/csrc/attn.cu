@@ -21,8 +21,8 @@
 
 namespace da {
 
-template <typename T, int D, int REP, int STAGES>
-__global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const AttnParams p) {
+template <typename T, int D, int REP, int STAGES, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 2 : 1) decode_attention_kernel(const AttnParams p) {
     constexpr int E = (int)sizeof(T);
     constexpr int ROWB = D * E;                 // one key (or value) row
     constexpr int TOKB = 2 * ROWB;              // one token: key row then value row
@@ -32,10 +32,11 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     constexpr int CHB = CH * E;                 // bytes per chunk
     constexpr int PW = PartialRow<D>::kWidth;   // floats per partial row: acc[D], m, l, pad
     constexpr float NEG_INF = -INFINITY;
+    constexpr int THREADS = WARPS * 32;
 
     extern __shared__ __align__(128) unsigned char smem[];
-    __shared__ __align__(8) uint64_t bars[kAttnWarps][STAGES];
-    __shared__ float red[kAttnWarps][REP][PW];
+    __shared__ __align__(8) uint64_t bars[WARPS][STAGES];
+    __shared__ float red[WARPS][REP][PW];
     __shared__ int sh_last;
 
     const int h = blockIdx.y;
@@ -58,14 +59,14 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     }
     const int n_local = t_new + 1;
     const int n_prefix = p.n_prefix_tokens;
-    const int units_prefix = (n_prefix + kUnitTokens - 1) / kUnitTokens;
-    const int units_local = (n_local + kUnitTokens - 1) / kUnitTokens;
-    const int units = units_prefix + units_local;
     // Units are dealt round-robin to the (CTA, warp) workers of this head, so every
     // worker sees the same mix of slot-table units (one bulk copy) and local-window
     // units (a row gather).
-    const int n_workers = splits * kAttnWarps;
-    const int worker = x * kAttnWarps + warp;
+    const int n_workers = splits * WARPS;
+    const int worker = x * WARPS + warp;
+    const UnitPlan plan = plan_units(p, h, n_local, worker, n_workers, lane);
+    const int units_prefix = plan.units_slots;   // units of this launch that come from the slot table
+    const int n_my = plan.n_my;
 
     unsigned char *my_stages = smem + (size_t)warp * STAGES * UNITB;
     if (lane == 0) {
@@ -76,7 +77,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     __syncthreads();
 
     // ---- append the new key/value to the local window -----------------------------
-    if (x == 0 && warp == 0 && pos_ok) {
+    if (x == 0 && warp == 0 && pos_ok && p.phase != 2) {
         const uint4 *sk = reinterpret_cast<const uint4 *>(p.new_k + (size_t)h * ROWB);
         const uint4 *sv = reinterpret_cast<const uint4 *>(p.new_v + (size_t)h * ROWB);
         const size_t off = ((size_t)t_new * p.local_tok_stride + (size_t)h * p.local_head_stride) * E;
@@ -109,17 +110,17 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     }
 
     // tokens of unit u
-    const int n_my = units > worker ? (units - worker + n_workers - 1) / n_workers : 0;
-    // lane i remembers where the warp's i-th unit has to come from (the host checks n_my <= 32
-    // whenever slot_source is given)
-    int my_src = -1;
-    if (p.slot_source && lane < n_my) {
-        const int u = worker + lane * n_workers;
-        if (u < units_prefix) my_src = p.slot_source[(size_t)h * p.n_slots + (u * kUnitTokens) / p.page_tokens];
-    }
-
-    auto unit_tokens = [&](int u) -> int {
-        if (u < units_prefix) return min(kUnitTokens, n_prefix - u * kUnitTokens);
+    // first slot-table token of the warp's it-th unit, and the DRAM page to read it from (or -1)
+    auto unit_base = [&](int u, int it) -> int {
+        const int b = plan_lookup(plan.base, it);
+        return p.phase == 0 ? u * kUnitTokens : b;
+    };
+    auto unit_src = [&](int it) -> int {
+        const int v = plan_lookup(plan.src, it);
+        return p.slot_source ? v : -1;
+    };
+    auto unit_tokens = [&](int u, int base) -> int {
+        if (u < units_prefix) return min(kUnitTokens, n_prefix - base);
         return min(kUnitTokens, n_local - (u - units_prefix) * kUnitTokens);
     };
 
@@ -127,13 +128,14 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     auto issue = [&](int u, int s, int it) {
         uint64_t *bar = &bars[warp][s];
         unsigned char *dst = my_stages + (size_t)s * UNITB;
-        const int ntok = unit_tokens(u);
-        const int src_page = __shfl_sync(DA_FULL_MASK, my_src, it & 31);
+        const int base = unit_base(u, it);
+        const int src_page = unit_src(it);
+        const int ntok = unit_tokens(u, base);
         if (u < units_prefix) {
             if (lane == 0) {
                 const uint32_t bytes = (uint32_t)ntok * TOKB;
                 mbar_arrive_expect_tx(bar, bytes);
-                const size_t tok = (size_t)u * kUnitTokens;
+                const size_t tok = (size_t)base;
                 const unsigned char *src =
                     src_page < 0 ? p.prefix + ((size_t)h * p.prefix_head_stride + tok * 2 * D) * E
                                  : p.dram + ((size_t)h * p.dram_head_stride +
@@ -170,13 +172,14 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
             break;
         }
         const int u = worker + it * n_workers;
-        const int ntok = unit_tokens(u);
+        const int base = unit_base(u, it);
+        const int ntok = unit_tokens(u, base);
         const unsigned char *sb = my_stages + (size_t)s * UNITB;
-        if (__shfl_sync(DA_FULL_MASK, my_src, it & 31) >= 0) {
+        if (unit_src(it) >= 0 && u < units_prefix) {
             // this unit came from DRAM: write it through to its slot
             uint4 *slot = reinterpret_cast<uint4 *>(
                 const_cast<unsigned char *>(p.prefix) +
-                ((size_t)h * p.prefix_head_stride + (size_t)u * kUnitTokens * 2 * D) * E);
+                ((size_t)h * p.prefix_head_stride + (size_t)base * 2 * D) * E);
             for (int i = lane; i < ntok * (TOKB / 16); i += 32) slot[i] = reinterpret_cast<const uint4 *>(sb)[i];
         }
 
@@ -284,13 +287,13 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     __syncthreads();
 
     // ---- merge the warps, write this CTA's partial ------------------------------------
-    float *part = p.partials + ((size_t)(h * splits + x) * REP) * PW;
-    for (int e = tid; e < REP * PW; e += kAttnThreads) {
+    float *part = p.partials + ((size_t)(h * p.part_rows + p.part_offset + x) * REP) * PW;
+    for (int e = tid; e < REP * PW; e += THREADS) {
         const int r = e / PW;
         const int c = e % PW;
         float mn = NEG_INF;
 #pragma unroll
-        for (int w = 0; w < kAttnWarps; ++w) mn = fmaxf(mn, red[w][r][D]);
+        for (int w = 0; w < WARPS; ++w) mn = fmaxf(mn, red[w][r][D]);
         float outv;
         if (c == D) {
             outv = mn;
@@ -300,10 +303,11 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
             const float ms = (mn == NEG_INF) ? 0.f : mn;
             outv = 0.f;
 #pragma unroll
-            for (int w = 0; w < kAttnWarps; ++w) outv += red[w][r][c] * fast_exp2(red[w][r][D] - ms);
+            for (int w = 0; w < WARPS; ++w) outv += red[w][r][c] * fast_exp2(red[w][r][D] - ms);
         }
         part[e] = outv;  // c < D: weighted acc; c == D: max; c == D+1: weighted l
     }
+    if (p.phase == 1) return;   // phase 2 merges
     __threadfence();
     __syncthreads();
     if (tid == 0) {
@@ -315,16 +319,23 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
 
     // ---- last CTA of this head: merge the splits ----------------------------------------
     __threadfence();
-    merge_splits<T, D, REP>(p, h, splits, reinterpret_cast<float *>(smem));
+    merge_splits<T, D, REP, THREADS>(p, h, p.part_rows, reinterpret_cast<float *>(smem));
+    if (p.phase == 2 && p.order_next) {
+        // every CTA of this head is done with the split: install the one for the next step
+        for (int i = tid; i < p.n_slots; i += THREADS)
+            p.order[(size_t)h * p.n_slots + i] = p.order_next[(size_t)h * p.n_slots + i];
+        if (tid == 0) p.n_evictable[h] = p.n_evictable_next[h];
+    }
     if (tid == 0) p.counters[h] = 0u;
 }
 
-template <typename T, int D, int REP>
-static cudaError_t launch_attn(const AttnParams &p, int n_kv_heads, cudaStream_t stream) {
+template <typename T, int D, int REP, int WARPS>
+static cudaError_t launch_attn_w(const AttnParams &p, int n_kv_heads, cudaStream_t stream) {
+
     constexpr int UNITB = kUnitTokens * 2 * D * (int)sizeof(T);
     constexpr int STAGES = UNITB >= 16384 ? 2 : (UNITB >= 8192 ? 3 : 4);
-    constexpr int SMEM = kAttnWarps * STAGES * UNITB;
-    auto kern = decode_attention_kernel<T, D, REP, STAGES>;
+    constexpr int SMEM = WARPS * STAGES * UNITB;
+    auto kern = decode_attention_kernel<T, D, REP, STAGES, WARPS>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -335,9 +346,15 @@ static cudaError_t launch_attn(const AttnParams &p, int n_kv_heads, cudaStream_t
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    dim3 grid(attn_splits(n_kv_heads), n_kv_heads);
-    kern<<<grid, kAttnThreads, SMEM, stream>>>(p);
+    dim3 grid(p.phase == 1 ? attn_splits_phase1(n_kv_heads) : attn_splits(n_kv_heads), n_kv_heads);
+    kern<<<grid, WARPS * 32, SMEM, stream>>>(p);
     return cudaGetLastError();
+}
+
+template <typename T, int D, int REP>
+static cudaError_t launch_attn(const AttnParams &p, int n_kv_heads, cudaStream_t stream) {
+    if (p.phase == 1) return launch_attn_w<T, D, REP, kAttnPhase1Warps>(p, n_kv_heads, stream);
+    return launch_attn_w<T, D, REP, kAttnWarps>(p, n_kv_heads, stream);
 }
 
 template <typename T>
@@ -358,6 +375,8 @@ extern "C" size_t da_decode_attention_workspace_bytes(int n_kv_heads, int rep, i
            (size_t)n_kv_heads * da::attn_splits(n_kv_heads) * rep * (head_dim + 4) * sizeof(float);
 }
 
+extern "C" size_t da_decode_attention_phased_workspace_bytes(int n_kv_heads, int rep, int head_dim);
+
 static int decode_attention_common(const void *q, const void *prefix_kv, long long prefix_head_stride,
                                    int n_prefix_tokens, void *local_k, void *local_v,
                                    long long local_token_stride, long long local_head_stride,
@@ -366,7 +385,9 @@ static int decode_attention_common(const void *q, const void *prefix_kv, long lo
                                    void *out, float *lse_out, void *workspace, size_t workspace_bytes,
                                    int32_t *status, int n_kv_heads, int rep, int head_dim, int dtype,
                                    const void *dram_pages, int n_dram_pages, const int32_t *slot_source,
-                                   int n_slots, int page_size, da_stream_t stream) {
+                                   int n_slots, int page_size, int phase, int32_t *order, int32_t *n_evictable,
+                                   const int32_t *order_next, const int32_t *n_evictable_next,
+                                   da_stream_t stream) {
     if (!q || !prefix_kv || !local_k || !local_v || !new_k || !new_v || !out || !workspace || !status)
         return DA_ERR_NULL;
     if (n_kv_heads < 1 || n_prefix_tokens < 1 || local_capacity < 1 || dram_tokens < 0) return DA_ERR_SHAPE;
@@ -381,7 +402,10 @@ static int decode_attention_common(const void *q, const void *prefix_kv, long lo
     if (((size_t)prefix_head_stride * esz) % 16 || ((size_t)local_token_stride * esz) % 16 ||
         ((size_t)local_head_stride * esz) % 16)
         return DA_ERR_ALIGN;
-    if (workspace_bytes < da_decode_attention_workspace_bytes(n_kv_heads, rep, head_dim)) return DA_ERR_WORKSPACE;
+    if (phase < 0 || phase > 2) return DA_ERR_SHAPE;
+    const size_t ws_need = phase == 0 ? da_decode_attention_workspace_bytes(n_kv_heads, rep, head_dim)
+                                      : da_decode_attention_phased_workspace_bytes(n_kv_heads, rep, head_dim);
+    if (workspace_bytes < ws_need) return DA_ERR_WORKSPACE;
 
     da::AttnParams p{};
     p.q = static_cast<const unsigned char *>(q);
@@ -414,13 +438,26 @@ static int decode_attention_common(const void *q, const void *prefix_kv, long lo
         if ((uintptr_t)dram_pages & 15) return DA_ERR_ALIGN;
         const int units_max = (n_prefix_tokens + da::kUnitTokens - 1) / da::kUnitTokens +
                               (local_capacity + da::kUnitTokens - 1) / da::kUnitTokens;
-        const int workers = da::attn_splits(n_kv_heads) * da::kAttnWarps;
-        if ((units_max + workers - 1) / workers > 32) return DA_ERR_UNSUPPORTED;
+        const int workers = phase == 1 ? da::attn_splits_phase1(n_kv_heads) * da::kAttnPhase1Warps
+                                       : da::attn_splits(n_kv_heads) * da::kAttnWarps;
+        if ((units_max + workers - 1) / workers > da::kMaxUnitsPerWarp) return DA_ERR_UNSUPPORTED;
         p.dram = static_cast<const unsigned char *>(dram_pages);
         p.dram_head_stride = (long long)n_dram_pages * page_size * 2 * head_dim;
         p.slot_source = slot_source;
         p.n_slots = n_slots;
         p.page_tokens = page_size;
+    }
+    p.phase = phase;
+    p.part_rows = da::attn_splits(n_kv_heads);
+    p.part_offset = 0;
+    if (phase != 0) {
+        if (!slot_source || !order || !n_evictable) return DA_ERR_NULL;
+        p.order = order;
+        p.n_evictable = n_evictable;
+        p.order_next = order_next;
+        p.n_evictable_next = n_evictable_next;
+        p.part_rows = da::attn_splits_phase1(n_kv_heads) + da::attn_splits(n_kv_heads);
+        p.part_offset = phase == 2 ? da::attn_splits_phase1(n_kv_heads) : 0;
     }
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -442,7 +479,7 @@ extern "C" int da_decode_attention(const void *q, const void *prefix_kv, long lo
                                    local_token_stride, local_head_stride, local_capacity, new_k, new_v,
                                    start_pos_dev, start_pos_host, dram_tokens, out, lse_out, workspace,
                                    workspace_bytes, status, n_kv_heads, rep, head_dim, dtype, nullptr, 0,
-                                   nullptr, 0, 0, stream);
+                                   nullptr, 0, 0, 0, nullptr, nullptr, nullptr, nullptr, stream);
 }
 
 extern "C" int da_decode_attention_fetch(const void *q, void *slots, long long slots_head_stride, int n_slots,
@@ -460,7 +497,60 @@ extern "C" int da_decode_attention_fetch(const void *q, void *slots, long long s
                                    local_token_stride, local_head_stride, local_capacity, new_k, new_v,
                                    start_pos_dev, start_pos_host, dram_tokens, out, lse_out, workspace,
                                    workspace_bytes, status, n_kv_heads, rep, head_dim, dtype, dram_pages,
-                                   n_dram_pages, slot_source, n_slots, page_size, stream);
+                                   n_dram_pages, slot_source, n_slots, page_size, 0, nullptr, nullptr, nullptr,
+                                   nullptr, stream);
+}
+
+extern "C" int da_decode_attention_phased_supported(int n_kv_heads, int rep, int head_dim, int dtype, int n_slots,
+                                                    int page_size, int local_capacity) {
+    if (n_kv_heads < 1 || n_slots < 1 || page_size < 1 || local_capacity < 1) return 0;
+    if (head_dim != 64 && head_dim != 128) return 0;
+    if (rep != 1 && rep != 2 && rep != 4 && rep != 8) return 0;
+    if (dtype != DA_F32 && dtype != DA_F16 && dtype != DA_BF16) return 0;
+    if (page_size % da::kUnitTokens != 0 || (long long)n_slots * page_size > 0x7fffffffLL) return 0;
+    const int units = n_slots * (page_size / da::kUnitTokens) +
+                      (local_capacity + da::kUnitTokens - 1) / da::kUnitTokens;
+    const int w1 = da::attn_splits_phase1(n_kv_heads) * da::kAttnPhase1Warps;
+    const int w2 = da::attn_splits(n_kv_heads) * da::kAttnWarps;
+    if ((units + w1 - 1) / w1 > da::kMaxUnitsPerWarp || (units + w2 - 1) / w2 > da::kMaxUnitsPerWarp) return 0;
+    // shared memory of a phase-1 CTA: 8 warps x stages x stage bytes + the warp-merge scratch
+    const size_t esz = dtype == DA_F32 ? 4 : 2;
+    size_t stage = (size_t)da::kUnitTokens * (2 * head_dim * esz + (esz == 2 ? 16 : 0));
+    const int stages = esz == 2 ? (stage > 8192 ? 3 : 4) : (stage >= 16384 ? 2 : (stage >= 8192 ? 3 : 4));
+    const size_t smem = (size_t)da::kAttnPhase1Warps * stages * stage +
+                        (size_t)da::kAttnPhase1Warps * rep * (head_dim + 4) * sizeof(float) + 2048;
+    return smem <= 227 * 1024 ? 1 : 0;
+}
+
+extern "C" size_t da_decode_attention_phased_workspace_bytes(int n_kv_heads, int rep, int head_dim) {
+    if (n_kv_heads < 1 || rep < 1 || head_dim < 1) return 0;
+    return (size_t)da::kCounterBytes + (size_t)n_kv_heads *
+                                           (da::attn_splits_phase1(n_kv_heads) + da::attn_splits(n_kv_heads)) * rep *
+                                           (head_dim + 4) * sizeof(float);
+}
+
+extern "C" int da_decode_attention_phased(int phase, int32_t *order, int32_t *n_evictable,
+                                          const int32_t *order_next, const int32_t *n_evictable_next,
+                                          const void *q, void *slots, long long slots_head_stride, int n_slots,
+                                          int page_size, const void *dram_pages, int n_dram_pages,
+                                          const int32_t *slot_source, void *local_k, void *local_v,
+                                          long long local_token_stride, long long local_head_stride,
+                                          int local_capacity, const void *new_k, const void *new_v,
+                                          const int32_t *start_pos_dev, int start_pos_host, int dram_tokens,
+                                          void *out, float *lse_out, void *workspace, size_t workspace_bytes,
+                                          int32_t *status, int n_kv_heads, int rep, int head_dim, int dtype,
+                                          da_stream_t stream) {
+    if (phase != 1 && phase != 2) return DA_ERR_SHAPE;
+    if (!slot_source || !order || !n_evictable) return DA_ERR_NULL;
+    if (!da_decode_attention_phased_supported(n_kv_heads, rep, head_dim, dtype, n_slots, page_size, local_capacity))
+        return DA_ERR_UNSUPPORTED;
+    if (n_slots < 1 || page_size < 1 || (long long)n_slots * page_size > 0x7fffffffLL) return DA_ERR_SHAPE;
+    return decode_attention_common(q, slots, slots_head_stride, n_slots * page_size, local_k, local_v,
+                                   local_token_stride, local_head_stride, local_capacity, new_k, new_v,
+                                   start_pos_dev, start_pos_host, dram_tokens, out, lse_out, workspace,
+                                   workspace_bytes, status, n_kv_heads, rep, head_dim, dtype, dram_pages,
+                                   n_dram_pages, slot_source, n_slots, page_size, phase, order, n_evictable,
+                                   order_next, n_evictable_next, stream);
 }
 
 // ---- entry point with built-in scratch ------------------------------------------------

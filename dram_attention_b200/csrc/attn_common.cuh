@@ -46,18 +46,92 @@ struct AttnParams {
     const int32_t *slot_source;      // (n_kv_heads, n_slots): DRAM page to read instead, or -1
     int n_slots;
     int page_tokens;                 // multiple of 16 when slot_source is set
+    // optional: two launches per step.  phase 1 attends over the local window and the slots
+    // that the coming LRU update cannot evict (it runs beside selection and LRU update);
+    // phase 2 attends over the evictable slots after the update and merges both.  The split
+    // is order[h][0 .. n_evictable[h]) = evictable, the rest not (left by da_lru_update).
+    int phase;                       // 0: one launch over everything
+    int32_t *order;                  // (n_kv_heads, n_slots) split used by phases 1 and 2
+    int32_t *n_evictable;            // (n_kv_heads)
+    const int32_t *order_next;       // what the LRU update of this step left for the next step;
+    const int32_t *n_evictable_next; // copied over `order` by the last CTA of a head in phase 2
+    int part_rows;                   // partial rows per head in the workspace
+    int part_offset;                 // first row this launch writes
 };
+
+constexpr int kMaxUnitsPerWarp = 64;   // two per lane: where each unit of a warp comes from
+// Phase 1 runs beside the selection kernels, whose CTAs need a whole SM each.  Its CTAs are
+// therefore built to fill an SM on their own (8 warps, twice the shared memory), and there
+// are at most 116 of them: wherever the hardware places them, 32 of the 148 SMs stay empty.
+constexpr int kAttnPhase1Warps = 8;
+constexpr int kAttnPhase1Ctas = 116;
+
+__host__ __device__ inline int attn_splits_phase1(int n_kv_heads) {
+    int s = kAttnPhase1Ctas / n_kv_heads;
+    if (s < 1) s = 1;
+    return s;
+}
+
+// Which units a launch covers and where each of this warp's units comes from.
+struct UnitPlan {
+    int units_slots;   // units from the slot table in this launch
+    int units_local;   // units from the local window in this launch
+    int n_my;          // units of this warp: worker, worker + n_workers, ...
+    int base[2];       // lane i: first token (inside the head's slot table) of unit i and 32 + i
+    int src[2];        // lane i: DRAM page to read that unit from instead, or -1
+};
+
+__device__ __forceinline__ UnitPlan plan_units(const AttnParams &p, int h, int n_local, int worker,
+                                               int n_workers, int lane) {
+    UnitPlan pl;
+    const int ups = p.order ? p.page_tokens / kUnitTokens : 1;
+    int n_ev = 0;
+    if (p.order) n_ev = min(max(p.n_evictable[h], 0), p.n_slots);
+    if (p.phase == 0) pl.units_slots = (p.n_prefix_tokens + kUnitTokens - 1) / kUnitTokens;
+    else if (p.phase == 1) pl.units_slots = (p.n_slots - n_ev) * ups;
+    else pl.units_slots = n_ev * ups;
+    pl.units_local = p.phase == 2 ? 0 : (n_local + kUnitTokens - 1) / kUnitTokens;
+    const int units = pl.units_slots + pl.units_local;
+    pl.n_my = units > worker ? (units - worker + n_workers - 1) / n_workers : 0;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        pl.base[k] = -1;
+        pl.src[k] = -1;
+        const int i = 32 * k + lane;
+        const int u = worker + i * n_workers;
+        if (i < pl.n_my && u < pl.units_slots) {
+            int base = u * kUnitTokens;
+            if (p.phase != 0) {
+                int slot = p.order[(size_t)h * p.n_slots + (p.phase == 1 ? n_ev : 0) + u / ups];
+                slot = min(max(slot, 0), p.n_slots - 1);
+                base = slot * p.page_tokens + (u % ups) * kUnitTokens;
+            }
+            pl.base[k] = base;
+            if (p.slot_source && p.phase != 1)
+                pl.src[k] = p.slot_source[(size_t)h * p.n_slots + base / p.page_tokens];
+        }
+    }
+    return pl;
+}
+
+// value of lane (it % 32)'s entry (it / 32) of a two-deep per-lane table
+__device__ __forceinline__ int plan_lookup(const int (&tab)[2], int it) {
+    const int v0 = __shfl_sync(DA_FULL_MASK, tab[0], it & 31);
+    const int v1 = __shfl_sync(DA_FULL_MASK, tab[1], it & 31);
+    return (it & 32) ? v1 : v0;
+}
+
 
 // Floats per partial row: acc[D], max, l, padded to a multiple of 4 so that rows can
 // be read with 128-bit loads.
 template <int D> struct PartialRow { static constexpr int kWidth = D + 4; };
 
-// Final merge of the per-CTA partials of one head by one CTA of kAttnThreads threads.
+// Final merge of the per-CTA partials of one head by one CTA of THREADS threads.
 // partial row = acc[D] (already weighted to the row's max), max, l.  `scratch` holds
 // at least 2 * splits * REP floats of shared memory (the idle stage buffers).  Loads bypass L1 (the rows were
 // written by other SMs).  The first batch of accumulator rows is requested together
 // with the (max, l) pairs, so about three L2 round trips are exposed in total.
-template <typename T, int D, int REP>
+template <typename T, int D, int REP, int THREADS>
 __device__ __forceinline__ void merge_splits(const AttnParams &p, int h, int splits, float *scratch) {
     constexpr int PW = PartialRow<D>::kWidth;
     constexpr int VPR = D / 4;          // float4 per accumulator row
@@ -70,7 +144,7 @@ __device__ __forceinline__ void merge_splits(const AttnParams &p, int h, int spl
     float *wgt = scratch;        // [n] max, then weight
     float *lsum = scratch + n;   // [n] l of every partial row
 
-    for (int e0 = 0; e0 < REP * VPR; e0 += kAttnThreads) {
+    for (int e0 = 0; e0 < REP * VPR; e0 += THREADS) {
         const int e = e0 + tid;
         const bool live = e < REP * VPR;
         const int r = live ? e / VPR : 0;
@@ -83,7 +157,7 @@ __device__ __forceinline__ void merge_splits(const AttnParams &p, int h, int spl
         for (int u = 0; u < BATCH; ++u)
             if (u < splits) v[u] = __ldcg(col + (size_t)u * RS);
         if (e0 == 0) {
-            for (int i = tid; i < n; i += kAttnThreads) {
+            for (int i = tid; i < n; i += THREADS) {
                 const float2 ml = __ldcg(reinterpret_cast<const float2 *>(hp + (size_t)i * PW + D));
                 wgt[i] = ml.x;
                 lsum[i] = ml.y;
@@ -95,7 +169,7 @@ __device__ __forceinline__ void merge_splits(const AttnParams &p, int h, int spl
                 sh_m[tid] = (mn == NEG_INF) ? 0.f : mn;
             }
             __syncthreads();
-            for (int i = tid; i < n; i += kAttnThreads) wgt[i] = fast_exp2(wgt[i] - sh_m[i % REP]);
+            for (int i = tid; i < n; i += THREADS) wgt[i] = fast_exp2(wgt[i] - sh_m[i % REP]);
             __syncthreads();
             if (tid < REP) {
                 float ll = 0.f;

@@ -65,8 +65,8 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void *
                  : "memory");
 }
 
-template <typename T, int D, int REP, int STAGES>
-__global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_mma_kernel(const AttnParams p) {
+template <typename T, int D, int REP, int STAGES, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 2 : 1) decode_attention_mma_kernel(const AttnParams p) {
     static_assert(sizeof(T) == 2 && REP <= 8 && D % 32 == 0, "16-bit types, at most 8 query rows");
     constexpr int E = 2;
     constexpr int ROWB = D * E;                   // one key (or value) row in HBM
@@ -76,10 +76,11 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_mma_kernel(c
     constexpr int NT = D / 8;                     // n-tiles of the PV contraction
     constexpr int PW = PartialRow<D>::kWidth;
     constexpr float NEG_INF = -INFINITY;
+    constexpr int THREADS = WARPS * 32;
 
     extern __shared__ __align__(128) unsigned char smem[];
-    __shared__ __align__(8) uint64_t bars[kAttnWarps][STAGES];
-    __shared__ float red[kAttnWarps][REP][PW];
+    __shared__ __align__(8) uint64_t bars[WARPS][STAGES];
+    __shared__ float red[WARPS][REP][PW];
     __shared__ int sh_last;
 
     const int h = blockIdx.y;
@@ -102,11 +103,11 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_mma_kernel(c
     }
     const int n_local = t_new + 1;
     const int n_prefix = p.n_prefix_tokens;
-    const int units_prefix = (n_prefix + kUnitTokens - 1) / kUnitTokens;
-    const int units_local = (n_local + kUnitTokens - 1) / kUnitTokens;
-    const int units = units_prefix + units_local;
-    const int n_workers = splits * kAttnWarps;
-    const int worker = x * kAttnWarps + warp;
+    const int n_workers = splits * WARPS;
+    const int worker = x * WARPS + warp;
+    const UnitPlan plan = plan_units(p, h, n_local, worker, n_workers, lane);
+    const int units_prefix = plan.units_slots;   // units of this launch that come from the slot table
+    const int n_my = plan.n_my;
 
     unsigned char *my_stages = smem + (size_t)warp * STAGES * STAGEB;
     if (lane == 0) {
@@ -117,7 +118,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_mma_kernel(c
     __syncthreads();
 
     // ---- append the new key/value to the local window -----------------------------
-    if (x == 0 && warp == 0 && pos_ok) {
+    if (x == 0 && warp == 0 && pos_ok && p.phase != 2) {
         const uint4 *sk = reinterpret_cast<const uint4 *>(p.new_k + (size_t)h * ROWB);
         const uint4 *sv = reinterpret_cast<const uint4 *>(p.new_v + (size_t)h * ROWB);
         const size_t off = ((size_t)t_new * p.local_tok_stride + (size_t)h * p.local_head_stride) * E;
@@ -147,17 +148,17 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_mma_kernel(c
 #pragma unroll
     for (int d = 0; d < NT; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
 
-    const int n_my = units > worker ? (units - worker + n_workers - 1) / n_workers : 0;
-    // lane i remembers where the warp's i-th unit has to come from (the host checks n_my <= 32
-    // whenever slot_source is given)
-    int my_src = -1;
-    if (p.slot_source && lane < n_my) {
-        const int u = worker + lane * n_workers;
-        if (u < units_prefix) my_src = p.slot_source[(size_t)h * p.n_slots + (u * kUnitTokens) / p.page_tokens];
-    }
-
-    auto unit_tokens = [&](int u) -> int {
-        if (u < units_prefix) return min(kUnitTokens, n_prefix - u * kUnitTokens);
+    // first slot-table token of the warp's it-th unit, and the DRAM page to read it from (or -1)
+    auto unit_base = [&](int u, int it) -> int {
+        const int b = plan_lookup(plan.base, it);
+        return p.phase == 0 ? u * kUnitTokens : b;
+    };
+    auto unit_src = [&](int it) -> int {
+        const int v = plan_lookup(plan.src, it);
+        return p.slot_source ? v : -1;
+    };
+    auto unit_tokens = [&](int u, int base) -> int {
+        if (u < units_prefix) return min(kUnitTokens, n_prefix - base);
         return min(kUnitTokens, n_local - (u - units_prefix) * kUnitTokens);
     };
 
@@ -167,8 +168,9 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_mma_kernel(c
     auto issue = [&](int u, int s, int it) {
         uint64_t *bar = &bars[warp][s];
         unsigned char *dst = my_stages + (size_t)s * STAGEB;
-        const int ntok = unit_tokens(u);
-        const int src_page = __shfl_sync(DA_FULL_MASK, my_src, it & 31);
+        const int base = unit_base(u, it);
+        const int src_page = unit_src(it);
+        const int ntok = unit_tokens(u, base);
         if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)ntok * 2 * ROWB);
         __syncwarp();
         const int tl = lane & 15;
@@ -176,7 +178,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_mma_kernel(c
         if (tl < ntok) {
             if (u < units_prefix) {
                 if (!is_v) {
-                    const size_t tok = (size_t)u * kUnitTokens + tl;
+                    const size_t tok = (size_t)base + tl;
                     const unsigned char *src =
                         src_page < 0
                             ? p.prefix + ((size_t)h * p.prefix_head_stride + tok * 2 * D) * E
@@ -214,12 +216,13 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_mma_kernel(c
             break;
         }
         const int u = worker + it * n_workers;
-        const int ntok = unit_tokens(u);
+        const int base = unit_base(u, it);
+        const int ntok = unit_tokens(u, base);
         unsigned char *sb = my_stages + (size_t)s * STAGEB;
-        if (__shfl_sync(DA_FULL_MASK, my_src, it & 31) >= 0) {
+        if (unit_src(it) >= 0 && u < units_prefix) {
             // this unit came from DRAM: write it through to its slot (512 bytes per token)
             unsigned char *slot = const_cast<unsigned char *>(p.prefix) +
-                                  ((size_t)h * p.prefix_head_stride + (size_t)u * kUnitTokens * 2 * D) * E;
+                                  ((size_t)h * p.prefix_head_stride + (size_t)base * 2 * D) * E;
             for (int i = lane; i < ntok * (2 * ROWB / 16); i += 32) {
                 const int t = i / (2 * ROWB / 16), c = i % (2 * ROWB / 16);
                 reinterpret_cast<uint4 *>(slot + (size_t)t * 2 * ROWB)[c] =
@@ -307,13 +310,13 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_mma_kernel(c
     __syncthreads();
 
     // ---- merge the warps, write this CTA's partial ------------------------------------
-    float *part = p.partials + ((size_t)(h * splits + x) * REP) * PW;
-    for (int e = tid; e < REP * PW; e += kAttnThreads) {
+    float *part = p.partials + ((size_t)(h * p.part_rows + p.part_offset + x) * REP) * PW;
+    for (int e = tid; e < REP * PW; e += THREADS) {
         const int r = e / PW;
         const int c = e % PW;
         float mn = NEG_INF;
 #pragma unroll
-        for (int w = 0; w < kAttnWarps; ++w) mn = fmaxf(mn, red[w][r][D]);
+        for (int w = 0; w < WARPS; ++w) mn = fmaxf(mn, red[w][r][D]);
         float outv;
         if (c == D) {
             outv = mn;
@@ -323,10 +326,11 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_mma_kernel(c
             const float ms = (mn == NEG_INF) ? 0.f : mn;
             outv = 0.f;
 #pragma unroll
-            for (int w = 0; w < kAttnWarps; ++w) outv += red[w][r][c] * fast_exp2(red[w][r][D] - ms);
+            for (int w = 0; w < WARPS; ++w) outv += red[w][r][c] * fast_exp2(red[w][r][D] - ms);
         }
         part[e] = outv;
     }
+    if (p.phase == 1) return;   // phase 2 merges
     __threadfence();
     __syncthreads();
     if (tid == 0) {
@@ -337,16 +341,23 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_mma_kernel(c
     if (!sh_last) return;
 
     __threadfence();
-    merge_splits<T, D, REP>(p, h, splits, reinterpret_cast<float *>(smem));
+    merge_splits<T, D, REP, THREADS>(p, h, p.part_rows, reinterpret_cast<float *>(smem));
+    if (p.phase == 2 && p.order_next) {
+        // every CTA of this head is done with the split: install the one for the next step
+        for (int i = tid; i < p.n_slots; i += THREADS)
+            p.order[(size_t)h * p.n_slots + i] = p.order_next[(size_t)h * p.n_slots + i];
+        if (tid == 0) p.n_evictable[h] = p.n_evictable_next[h];
+    }
     if (tid == 0) p.counters[h] = 0u;
 }
 
-template <typename T, int D, int REP>
-static cudaError_t launch_mma(const AttnParams &p, int n_kv_heads, cudaStream_t stream) {
+template <typename T, int D, int REP, int WARPS>
+static cudaError_t launch_mma_w(const AttnParams &p, int n_kv_heads, cudaStream_t stream) {
+
     constexpr int STAGEB = kUnitTokens * (2 * D * 2 + 16);
     constexpr int STAGES = STAGEB > 8192 ? 3 : 4;
-    constexpr int SMEM = kAttnWarps * STAGES * STAGEB;
-    auto kern = decode_attention_mma_kernel<T, D, REP, STAGES>;
+    constexpr int SMEM = WARPS * STAGES * STAGEB;
+    auto kern = decode_attention_mma_kernel<T, D, REP, STAGES, WARPS>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -357,9 +368,15 @@ static cudaError_t launch_mma(const AttnParams &p, int n_kv_heads, cudaStream_t 
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    dim3 grid(attn_splits(n_kv_heads), n_kv_heads);
-    kern<<<grid, kAttnThreads, SMEM, stream>>>(p);
+    dim3 grid(p.phase == 1 ? attn_splits_phase1(n_kv_heads) : attn_splits(n_kv_heads), n_kv_heads);
+    kern<<<grid, WARPS * 32, SMEM, stream>>>(p);
     return cudaGetLastError();
+}
+
+template <typename T, int D, int REP>
+static cudaError_t launch_mma(const AttnParams &p, int n_kv_heads, cudaStream_t stream) {
+    if (p.phase == 1) return launch_mma_w<T, D, REP, kAttnPhase1Warps>(p, n_kv_heads, stream);
+    return launch_mma_w<T, D, REP, kAttnWarps>(p, n_kv_heads, stream);
 }
 
 template <typename T>

@@ -64,7 +64,8 @@ __global__ void __launch_bounds__(kLruThreads)
 lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *dram_to_slot, int n_dram_pages,
                   int32_t *slot_to_dram, int32_t *access_time, int n_slots, int32_t *step_counters,
                   int32_t *__restrict__ miss_pages, int32_t *__restrict__ miss_slots,
-                  int32_t *__restrict__ n_miss_out, int32_t *slot_source, int32_t *status) {
+                  int32_t *__restrict__ n_miss_out, int32_t *slot_source, int32_t *order_out,
+                  int32_t *n_evictable_out, int32_t *status) {
     extern __shared__ __align__(16) int smem_i[];
     const int table = lru_table_size(list_len);
     const int xhalf = n_slots > table ? n_slots : table;
@@ -171,7 +172,9 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
     }
     __syncthreads();  // the table is dead from here on; xbuf becomes keyB/valB
 
-    if (n_miss > 0) {
+    const bool want_order = order_out != nullptr;
+    const int n_miss_found = n_miss;
+    if (n_miss > 0 || want_order) {
         // ---- 3. stable radix sort of the slots by access time --------------------
         {
             int mx = 0;
@@ -250,7 +253,8 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
         // kin/vin now hold the slots in eviction order.
 
         // ---- 4. overflow check, then assignment ------------------------------------
-        const bool overflow = (n_miss > n_slots) || (kin[min(n_miss, n_slots) - 1] >= step);
+        const bool overflow =
+            n_miss > 0 && ((n_miss > n_slots) || (kin[min(n_miss, n_slots) - 1] >= step));
         if (overflow) {
             if (tid == 0) atomicOr(status, DA_STATUS_LRU_OVERFLOW);
             n_miss = 0;  // tables stay as after the hit marking
@@ -267,6 +271,32 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
                 ms_out[j] = v;
                 if (src_map) src_map[v] = p;
             }
+        }
+
+        // ---- 5. which slots can be evicted by the NEXT call -------------------------------
+        // Sorted order now: [victims | untouched slots by (time, slot) | slots hit this call].
+        // After this call victims and hits carry the newest stamp, so the next call's victims
+        // come from the front of the untouched run, and no further in than the next list is
+        // long (every list entry is either a hit, which removes a slot from the front, or a
+        // miss, which takes one).  If the untouched run is at least list_len long, those
+        // list_len slots are the only candidates; order_out = that run first, everything else
+        // after it (a rotation of the sorted order by n_miss).  Otherwise every slot is a
+        // candidate.
+        if (want_order) {
+            int touched = 0;  // slots hit by this call (sorted keys still hold the pre-assignment times)
+            for (int i = tid; i < n_slots; i += kLruThreads) touched += (kin[i] >= step);
+            int total;
+            block_exclusive_scan(touched, wsum, &total);
+            const int untouched = n_slots - total - n_miss;
+            const int cap = min(list_len, n_slots);
+            const bool bounded = !overflow && n_miss_found == n_miss && untouched >= cap;
+            int32_t *ord = order_out + (size_t)h * n_slots;
+            for (int i = tid; i < n_slots; i += kLruThreads) {
+                int src = i + n_miss;
+                if (src >= n_slots) src -= n_slots;
+                ord[i] = vin[src];
+            }
+            if (tid == 0) n_evictable_out[h] = bounded ? cap : n_slots;
         }
     }
     if (tid == 0) {
@@ -288,11 +318,13 @@ constexpr size_t kLruMaxSmem = 227 * 1024 - 1024;
 extern "C" int da_lru_update(const int32_t *page_list, int list_len, int32_t *dram_to_slot, int n_dram_pages,
                              int32_t *slot_to_dram, int32_t *access_time, int n_slots, int32_t *step,
                              int n_kv_heads, int32_t *miss_pages, int32_t *miss_slots, int32_t *n_miss,
-                             int32_t *slot_source, int32_t *status, da_stream_t stream) {
+                             int32_t *slot_source, int32_t *order_out, int32_t *n_evictable_out,
+                             int32_t *status, da_stream_t stream) {
     if (!page_list || !dram_to_slot || !slot_to_dram || !access_time || !step || !miss_pages || !miss_slots ||
         !n_miss || !status)
         return DA_ERR_NULL;
     if (list_len < 1 || n_dram_pages < 1 || n_slots < 1 || n_kv_heads < 1) return DA_ERR_SHAPE;
+    if ((order_out == nullptr) != (n_evictable_out == nullptr)) return DA_ERR_NULL;
     if (n_slots > da::kLruMaxSlots || list_len > da::kLruMaxList) return DA_ERR_UNSUPPORTED;
     const size_t smem = da::lru_smem_bytes(n_slots, list_len);
     if (smem > da::kLruMaxSmem) return DA_ERR_UNSUPPORTED;
@@ -309,6 +341,6 @@ extern "C" int da_lru_update(const int32_t *page_list, int list_len, int32_t *dr
     }
     da::lru_update_kernel<<<n_kv_heads, da::kLruThreads, smem, static_cast<cudaStream_t>(stream)>>>(
         page_list, list_len, dram_to_slot, n_dram_pages, slot_to_dram, access_time, n_slots, step, miss_pages,
-        miss_slots, n_miss, slot_source, status);
+        miss_slots, n_miss, slot_source, order_out, n_evictable_out, status);
     return (int)cudaGetLastError();
 }

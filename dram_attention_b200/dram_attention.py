@@ -56,8 +56,14 @@ class DRAMAttention(torch.nn.Module):
         self.lru_cache = None
         self._ws = {}
         self._can_fuse = False
+        self._can_overlap = False
+        self._overlap_ok = {}
+        self._side = None
 
     fused_fetch = True
+    # Two attention launches per step: the first (local window + slots that cannot be evicted this
+    # step) runs on a side stream beside selection and LRU update, the second finishes after them.
+    overlap = True
 
     # ---- cache construction ---------------------------------------------------
     def init_cache(self, k_cache: torch.Tensor, v_cache: torch.Tensor):
@@ -82,9 +88,12 @@ class DRAMAttention(torch.nn.Module):
             hk = self.n_kv_heads
             warps = 4 * max(1, min(296 // hk, 148))
             units = -(-self.lru_cache.num_hbm_pages * self.page_size // 16) + -(-self.cache_k.shape[1] // 16)
-            self._can_fuse = (self.page_size % 16 == 0) and (-(-units // warps) <= 32)
+            self._can_fuse = (self.page_size % 16 == 0) and (-(-units // warps) <= 64)
+            self._can_overlap = self._can_fuse   # refined per GQA group size at the first generate call
+            self._overlap_ok = {}
         else:
             self._can_fuse = False
+            self._can_overlap = False
             self.lru_cache = DummyCache(
                 k_cache=dram_k_cache[0].transpose(0, 1), v_cache=dram_v_cache[0].transpose(0, 1),
                 device=self.device, page_size=self.page_size)
@@ -117,7 +126,9 @@ class DRAMAttention(torch.nn.Module):
     def _workspace(self, rep: int, dev):
         ws = self._ws.get(rep)
         if ws is None:
-            nbytes = _native.lib().da_decode_attention_workspace_bytes(self.n_kv_heads, rep, self.head_dim)
+            lib = _native.lib()
+            nbytes = max(lib.da_decode_attention_workspace_bytes(self.n_kv_heads, rep, self.head_dim),
+                         lib.da_decode_attention_phased_workspace_bytes(self.n_kv_heads, rep, self.head_dim))
             buf = torch.zeros(nbytes, dtype=torch.uint8, device=dev)  # counters start at zero
             status = torch.zeros(1, dtype=torch.int32, device=dev)
             ws = self._ws[rep] = (buf, nbytes, status)
@@ -136,7 +147,9 @@ class DRAMAttention(torch.nn.Module):
         xv = xv if xv.is_contiguous() else xv.contiguous()
         with torch.cuda.device(xq.device):
             out = torch.empty_like(xq)
-            if self._can_fuse and self.fused_fetch:
+            if self._can_overlap and self.fused_fetch and self.overlap and self._overlap_supported(rep, xq.dtype):
+                self._generate_overlapped(xq, xk, xv, start_pos, out)
+            elif self._can_fuse and self.fused_fetch:
                 # score -> select -> LRU update -> attention that also brings in the misses
                 lc = self.lru_cache
                 _, page_list = lc.top_k_selector.page_list_(xq, lc.top_k)
@@ -148,7 +161,39 @@ class DRAMAttention(torch.nn.Module):
                 self.attend_(xq, xk, xv, start_pos, out)
         return out
 
-    def attend_(self, xq, xk, xv, start_pos, out, lse=None, fetch=False) -> None:
+    def _overlap_supported(self, rep: int, dtype) -> bool:
+        ok = self._overlap_ok.get(rep)
+        if ok is None:
+            ok = self._overlap_ok[rep] = bool(_native.lib().da_decode_attention_phased_supported(
+                self.n_kv_heads, rep, self.head_dim, _native.dtype_code(dtype), self.lru_cache.num_hbm_pages,
+                self.page_size, self.cache_k.shape[1]))
+        return ok
+
+    def _generate_overlapped(self, xq, xk, xv, start_pos, out) -> None:
+        """score -> { select -> LRU update  ||  attention phase 1 } -> attention phase 2."""
+        lc = self.lru_cache
+        sel = lc.top_k_selector
+        rep = xq.shape[2] // self.n_kv_heads
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=xq.device)
+            self._fork, self._join = torch.cuda.Event(), torch.cuda.Event()
+        main = torch.cuda.current_stream()
+        if not lc.split_valid:
+            lc.reset_split_()
+        sel.score_(xq, lc.top_k)
+        self._fork.record(main)
+        # selection is launched before phase 1 so that its CTAs find their SMs free
+        page_list = sel.select_(1, rep, lc.top_k)
+        self._side.wait_event(self._fork)
+        with torch.cuda.stream(self._side):
+            self.attend_(xq, xk, xv, start_pos, out, phase=1)
+            self._join.record(self._side)
+        lc.update_tables_(page_list, want_split=True)
+        main.wait_event(self._join)
+        self.attend_(xq, xk, xv, start_pos, out, phase=2)
+        lc.split_valid = True
+
+    def attend_(self, xq, xk, xv, start_pos, out, lse=None, fetch=False, phase=0) -> None:
         """Enqueue the decode attention over the current slot table and the local
         window (appends xk/xv at start_pos - dram_kv_cache_size first).  With `fetch` the
         kernel also reads the pages the last LRU update marked from DRAM and writes them
@@ -167,6 +212,20 @@ class DRAMAttention(torch.nn.Module):
             pos_dev, pos_host = 0, int(start_pos)
         lib = _native.lib()
         lse_ptr = 0 if lse is None else lse.data_ptr()
+        if phase:
+            lc = self.lru_cache
+            _native.check(lib.da_decode_attention_phased(
+                phase, lc.evict_order.data_ptr(), lc.n_evictable.data_ptr(),
+                lc.evict_order_next.data_ptr() if phase == 2 else 0,
+                lc.n_evictable_next.data_ptr() if phase == 2 else 0,
+                xq.data_ptr(), prefix.data_ptr(), prefix.stride(0), lc.num_hbm_pages, self.page_size,
+                lc.dram_kv_cache.data_ptr(), lc.num_dram_pages, lc.slot_source.data_ptr(),
+                self.cache_k.data_ptr(), self.cache_v.data_ptr(), self.cache_k.stride(1),
+                self.cache_k.stride(2), self.cache_k.shape[1], xk.data_ptr(), xv.data_ptr(),
+                pos_dev, pos_host, self.dram_kv_cache_size, out.data_ptr(), lse_ptr, buf.data_ptr(), nbytes,
+                status.data_ptr(), self.n_kv_heads, rep, self.head_dim, _native.dtype_code(xq.dtype),
+                _native.stream_ptr()), "da_decode_attention_phased")
+            return
         if fetch:
             lc = self.lru_cache
             _native.check(lib.da_decode_attention_fetch(

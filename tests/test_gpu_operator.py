@@ -26,14 +26,16 @@ def da():
     return pkg
 
 
-@pytest.fixture(params=[True, False], ids=["fetch-in-attention", "fetch-kernel"])
+@pytest.fixture(params=[(True, True), (True, False), (False, False)],
+                ids=["overlapped", "fetch-in-attention", "fetch-kernel"])
 def fused(request, da):
-    """Both ways of bringing missed pages in: inside the attention kernel, or by the
-    gather-copy kernel before it."""
-    old = da.DRAMAttention.fused_fetch
-    da.DRAMAttention.fused_fetch = request.param
+    """The three ways a generate step can be laid out: two attention launches with the first
+    beside selection and LRU update; one attention launch that also brings the missed pages in;
+    a gather-copy launch followed by the attention launch.  All give the same results."""
+    old = (da.DRAMAttention.fused_fetch, da.DRAMAttention.overlap)
+    da.DRAMAttention.fused_fetch, da.DRAMAttention.overlap = request.param
     yield request.param
-    da.DRAMAttention.fused_fetch = old
+    da.DRAMAttention.fused_fetch, da.DRAMAttention.overlap = old
 
 
 def _spy_lists(module):
@@ -42,9 +44,9 @@ def _spy_lists(module):
     lc = module.lru_cache
     orig = lc.update_tables_
 
-    def spy(page_list):
+    def spy(page_list, **kw):
         lists.append(page_list.clone())
-        return orig(page_list)
+        return orig(page_list, **kw)
 
     lc.update_tables_ = spy
     return lists

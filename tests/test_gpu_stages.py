@@ -180,6 +180,9 @@ class Tables:
         self.g_dram = self.dram.clone().pin_memory()
         self.g_hbm = self.hbm.to(DEV)
         self.g_status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        self.g_order = torch.full((self.hk, self.nh), -5, dtype=torch.int32, device=DEV)
+        self.g_nev = torch.full((self.hk,), -5, dtype=torch.int32, device=DEV)
+        self.prev_split = None
         return self
 
     def gpu_step(self, lst):
@@ -193,13 +196,26 @@ class Tables:
         _native.check(lib.da_lru_update(gl.data_ptr(), kk, self.g_d2h.data_ptr(), self.ld,
                                         self.g_h2d.data_ptr(), self.g_time.data_ptr(), self.nh,
                                         self.g_step.data_ptr(), self.hk, mp.data_ptr(), ms.data_ptr(),
-                                        nm.data_ptr(), 0, self.g_status.data_ptr(), s))
+                                        nm.data_ptr(), 0, self.g_order.data_ptr(), self.g_nev.data_ptr(),
+                                        self.g_status.data_ptr(), s))
         page_bytes = self.dram.shape[2] * self.dram.element_size()
         _native.check(lib.da_fetch_pages(self.g_dram.data_ptr(), self.g_hbm.data_ptr(), mp.data_ptr(),
                                          ms.data_ptr(), nm.data_ptr(), kk, self.hk, self.ld, self.nh,
                                          page_bytes, s))
         torch.cuda.synchronize()
-        return mp.cpu().numpy(), ms.cpu().numpy(), nm.cpu().numpy()
+        mp, ms, nm = mp.cpu().numpy(), ms.cpu().numpy(), nm.cpu().numpy()
+        # the split the previous call left must contain every slot this call evicted
+        if self.prev_split is not None and self.prev_split[2] >= kk:
+            order, nev, _ = self.prev_split
+            for h in range(self.hk):
+                assert set(ms[h, :nm[h]].tolist()) <= set(order[h, :nev[h]].tolist()), h
+        order, nev = self.g_order.cpu().numpy(), self.g_nev.cpu().numpy()
+        if not (int(self.g_status) & 2):
+            for h in range(self.hk):
+                assert sorted(order[h].tolist()) == list(range(self.nh)), h
+                assert nev[h] == self.nh or nev[h] == min(kk, self.nh), h
+        self.prev_split = (order, nev, kk)
+        return mp, ms, nm
 
     def cpu_step(self, lst, fn=orc.lru_walk):
         self.step += 1
