@@ -38,6 +38,7 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 2 : 1) decode_attenti
     __shared__ __align__(8) uint64_t bars[WARPS][STAGES];
     __shared__ float red[WARPS][REP][PW];
     __shared__ int sh_last;
+    __shared__ unsigned char perm_s[WARPS][64];
 
     const int h = blockIdx.y;
     const int x = blockIdx.x;
@@ -110,14 +111,22 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 2 : 1) decode_attenti
     }
 
     // tokens of unit u
-    // first slot-table token of the warp's it-th unit, and the DRAM page to read it from (or -1)
-    auto unit_base = [&](int u, int it) -> int {
-        const int b = plan_lookup(plan.base, it);
+    // The warp visits its units in the order perm[0], perm[1], ...: DRAM-sourced units first.
+    int perm[2] = {0, 0};
+    const bool planned = p.slot_source != nullptr;   // then the host guarantees n_my <= 64
+    if (planned) plan_order(plan, lane, perm, perm_s[warp]);
+    auto unit_index = [&](int it) -> int {
+        const int v = plan_lookup(perm, it);
+        return planned ? v : it;
+    };
+    // first slot-table token of the warp's unit with index idx, and the DRAM page to read it from (or -1)
+    auto unit_base = [&](int u, int idx) -> int {
+        const int b = plan_lookup(plan.base, idx);
         return p.phase == 0 ? u * kUnitTokens : b;
     };
-    auto unit_src = [&](int it) -> int {
-        const int v = plan_lookup(plan.src, it);
-        return p.slot_source ? v : -1;
+    auto unit_src = [&](int idx) -> int {
+        const int v = plan_lookup(plan.src, idx);
+        return planned ? v : -1;
     };
     auto unit_tokens = [&](int u, int base) -> int {
         if (u < units_prefix) return min(kUnitTokens, n_prefix - base);
@@ -125,11 +134,13 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 2 : 1) decode_attenti
     };
 
     // start the copies of unit u into stage s of this warp
-    auto issue = [&](int u, int s, int it) {
+    auto issue = [&](int s, int it) {
+        const int idx = unit_index(it);
+        const int u = worker + idx * n_workers;
         uint64_t *bar = &bars[warp][s];
         unsigned char *dst = my_stages + (size_t)s * UNITB;
-        const int base = unit_base(u, it);
-        const int src_page = unit_src(it);
+        const int base = unit_base(u, idx);
+        const int src_page = unit_src(idx);
         const int ntok = unit_tokens(u, base);
         if (u < units_prefix) {
             if (lane == 0) {
@@ -162,7 +173,7 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 2 : 1) decode_attenti
         }
     };
 
-    for (int it = 0; it < STAGES && it < n_my; ++it) issue(worker + it * n_workers, it, it);
+    for (int it = 0; it < STAGES && it < n_my; ++it) issue(it, it);
 
     for (int it = 0; it < n_my; ++it) {
         const int s = it % STAGES;
@@ -171,11 +182,12 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 2 : 1) decode_attenti
             if (lane == 0) atomicOr(p.status, DA_STATUS_WAIT_TIMEOUT);
             break;
         }
-        const int u = worker + it * n_workers;
-        const int base = unit_base(u, it);
+        const int idx = unit_index(it);
+        const int u = worker + idx * n_workers;
+        const int base = unit_base(u, idx);
         const int ntok = unit_tokens(u, base);
         const unsigned char *sb = my_stages + (size_t)s * UNITB;
-        if (unit_src(it) >= 0 && u < units_prefix) {
+        if (unit_src(idx) >= 0 && u < units_prefix) {
             // this unit came from DRAM: write it through to its slot
             uint4 *slot = reinterpret_cast<uint4 *>(
                 const_cast<unsigned char *>(p.prefix) +
@@ -247,7 +259,7 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 2 : 1) decode_attenti
         }
 
         __syncwarp();
-        if (it + STAGES < n_my) issue(worker + (it + STAGES) * n_workers, s, it + STAGES);
+        if (it + STAGES < n_my) issue(s, it + STAGES);
     }
 
     // ---- merge the 4 token groups of the warp ---------------------------------------
@@ -322,8 +334,16 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 2 : 1) decode_attenti
     merge_splits<T, D, REP, THREADS>(p, h, p.part_rows, reinterpret_cast<float *>(smem));
     if (p.phase == 2 && p.order_next) {
         // every CTA of this head is done with the split: install the one for the next step
-        for (int i = tid; i < p.n_slots; i += THREADS)
-            p.order[(size_t)h * p.n_slots + i] = p.order_next[(size_t)h * p.n_slots + i];
+        const int32_t *__restrict__ src = p.order_next + (size_t)h * p.n_slots;
+        int32_t *__restrict__ dst = p.order + (size_t)h * p.n_slots;
+        for (int i0 = tid; i0 < p.n_slots; i0 += THREADS * 8) {
+            int32_t v[8];   // all loads of a batch in flight before the first store
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = (i0 + u * THREADS < p.n_slots) ? __ldcg(src + i0 + u * THREADS) : 0;
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (i0 + u * THREADS < p.n_slots) dst[i0 + u * THREADS] = v[u];
+        }
         if (tid == 0) p.n_evictable[h] = p.n_evictable_next[h];
     }
     if (tid == 0) p.counters[h] = 0u;

@@ -114,6 +114,29 @@ __device__ __forceinline__ UnitPlan plan_units(const AttnParams &p, int h, int n
     return pl;
 }
 
+// Order in which a warp walks its units: the ones that have to come from DRAM first, so that
+// their host-link latency overlaps everything else the warp does.  perm = position -> unit
+// index (two per lane, like the plan); `scratch` is 64 bytes of shared memory of this warp.
+__device__ __forceinline__ void plan_order(const UnitPlan &pl, int lane, int (&perm)[2], unsigned char *scratch) {
+    const unsigned lt = (1u << lane) - 1;
+    const unsigned f0 = __ballot_sync(DA_FULL_MASK, pl.src[0] >= 0);
+    const unsigned f1 = __ballot_sync(DA_FULL_MASK, pl.src[1] >= 0);
+    const int nf = __popc(f0) + __popc(f1);
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const int i = 32 * k + lane;
+        if (i < pl.n_my) {
+            const int fresh_before = k == 0 ? __popc(f0 & lt) : __popc(f0) + __popc(f1 & lt);
+            const bool fresh = pl.src[k] >= 0;
+            scratch[fresh ? fresh_before : nf + (i - fresh_before)] = (unsigned char)i;
+        }
+    }
+    __syncwarp();
+#pragma unroll
+    for (int k = 0; k < 2; ++k) perm[k] = (32 * k + lane < pl.n_my) ? scratch[32 * k + lane] : 0;
+    __syncwarp();
+}
+
 // value of lane (it % 32)'s entry (it / 32) of a two-deep per-lane table
 __device__ __forceinline__ int plan_lookup(const int (&tab)[2], int it) {
     const int v0 = __shfl_sync(DA_FULL_MASK, tab[0], it & 31);
@@ -135,7 +158,7 @@ template <typename T, int D, int REP, int THREADS>
 __device__ __forceinline__ void merge_splits(const AttnParams &p, int h, int splits, float *scratch) {
     constexpr int PW = PartialRow<D>::kWidth;
     constexpr int VPR = D / 4;          // float4 per accumulator row
-    constexpr int BATCH = 13;
+    constexpr int BATCH = 26;
     constexpr float NEG_INF = -INFINITY;
     __shared__ float sh_m[REP], sh_l[REP];
     const int tid = threadIdx.x;

@@ -5,11 +5,15 @@
 //   2. misses: the first appearance (in list order) of every non-resident page is
 //      found with a shared-memory hash table keyed by page id that keeps the
 //      smallest list index, and ranked by a block prefix sum.
-//   3. victims: slots ordered by (time, slot) with a stable LSD radix sort on the
-//      time in shared memory; only as many 8-bit passes as the step counter has
-//      bytes.
+//   3. victims: the n_miss slots with the smallest (time, slot).  No sort: a radix
+//      select on the time finds the time T of the n_miss-th slot, every slot with
+//      time < T is a victim, and the slots with time == T fill the rest in slot order
+//      (an ordered block scan); the victims are then ranked among themselves by
+//      counting.  One 8-bit select pass per byte of the step counter.
 //   4. the j-th miss takes the j-th victim; tables updated; (page, slot) pairs
 //      emitted for the payload copy.
+//   5. optionally the same select, for position n_miss + list_len, tells which slots
+//      the NEXT call can evict (for the two-launch attention).
 
 #include "da_common.cuh"
 
@@ -19,7 +23,6 @@ constexpr int kLruThreads = 1024;
 constexpr int kLruWarps = kLruThreads / 32;
 constexpr int kLruMaxSlots = 8192;
 constexpr int kLruMaxList = 8192;
-constexpr int kLruMaxRounds = kLruMaxSlots / kLruThreads;  // items per lane in the sort
 
 // Exclusive prefix sum over the block of one int per thread; returns the
 // exclusive value and writes the block total to *total.  `wsum` is 32 ints of
@@ -49,17 +52,86 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int *wsum, int *total
     return before + incl - v;
 }
 
-constexpr int kLruMaxListRounds = kLruMaxList / kLruThreads;
-
-// Shared-memory plan (ints): keyA[n_slots] valA[n_slots] | X[2 * max(n_slots, table)] |
-// mpage[list_len] | hist[256 * 32] | s2d[n_slots].  X is the page hash table
-// (keys, first list index) while misses are found and the sort's second buffer after.
 __host__ __device__ inline int lru_table_size(int list_len) {
     int t = 64;
     while (t < 2 * list_len) t <<= 1;
     return t;
 }
 
+// Time T of the slot at position `need` (1-based) in ascending time order, and how many slots
+// have a smaller time.  tm[] holds the times of this thread's slots (slot r * 1024 + tid), -1
+// for none.  8-bit radix select from the top byte of `bits` down.  hist = 256 ints of shared
+// memory, res = 2 ints.  All threads call; contains barriers.
+template <int SR>
+__device__ __forceinline__ void select_time(const int (&tm)[SR], int need, int bits, int *hist, int *res,
+                                            int &t_out, int &less_out) {
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int passes = (bits + 7) / 8;
+    uint32_t prefix = 0, mask = 0;
+    int less = 0;
+    for (int pass = passes - 1; pass >= 0; --pass) {
+        const int shift = 8 * pass;
+        if (tid < 256) hist[tid] = 0;
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < SR; ++r) {
+            const bool in = tm[r] >= 0 && ((uint32_t)tm[r] & mask) == prefix;
+            const uint32_t digit = ((uint32_t)tm[r] >> shift) & 255u;
+            // stamps cluster on the last few steps: count the lanes that share the first
+            // participating lane's digit with one atomic, the others one by one
+            const uint32_t act = __ballot_sync(DA_FULL_MASK, in);
+            if (act) {
+                const int first = __ffs(act) - 1;
+                const uint32_t d0 = __shfl_sync(DA_FULL_MASK, digit, first);
+                const uint32_t same = __ballot_sync(DA_FULL_MASK, in && digit == d0);
+                if (lane == first) atomicAdd(&hist[d0], __popc(same));
+                else if (in && digit != d0) atomicAdd(&hist[digit], 1);
+            }
+        }
+        __syncthreads();
+        if (warp == 0) {
+            // lane l owns digits 8l .. 8l+7 (ascending): find where the running count reaches `need`
+            int c[8], tot = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                c[j] = hist[lane * 8 + j];
+                tot += c[j];
+            }
+            int incl = tot;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                int v = __shfl_up_sync(DA_FULL_MASK, incl, off);
+                if (lane >= off) incl += v;
+            }
+            int below = incl - tot;
+            const int want = need - less;
+            if (below < want && incl >= want) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if (below < want && below + c[j] >= want) {
+                        res[0] = lane * 8 + j;
+                        res[1] = below;
+                        below = want;
+                    } else {
+                        below += c[j];
+                    }
+                }
+            }
+        }
+        __syncthreads();
+        prefix |= (uint32_t)res[0] << shift;
+        mask |= 255u << shift;
+        less += res[1];
+        __syncthreads();
+    }
+    t_out = (int)prefix;
+    less_out = less;
+}
+
+// SR = slots per thread (n_slots <= SR * 1024), LR = list entries per thread.
+template <int SR, int LR>
 __global__ void __launch_bounds__(kLruThreads)
 lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *dram_to_slot, int n_dram_pages,
                   int32_t *slot_to_dram, int32_t *access_time, int n_slots, int32_t *step_counters,
@@ -68,24 +140,21 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
                   int32_t *n_evictable_out, int32_t *status) {
     extern __shared__ __align__(16) int smem_i[];
     const int table = lru_table_size(list_len);
-    const int xhalf = n_slots > table ? n_slots : table;
-    int *keyA = smem_i;                  // [n_slots] sort keys (access time)
-    int *valA = keyA + n_slots;          // [n_slots] slot ids
-    int *xbuf = valA + n_slots;          // [2 * xhalf]
-    int *tkey = xbuf;                    // [table] page id or -1
-    int *tval = xbuf + table;            // [table] smallest list index of that page
-    int *keyB = xbuf;                    // [n_slots]   (after the table is dead)
-    int *valB = xbuf + n_slots;          // [n_slots]
-    int *mpage = xbuf + 2 * xhalf;       // [list_len] miss pages in list order
-    int *hist = mpage + list_len;        // [256 * 32] digit-major, warp-minor
-    int *s2d_s = hist + 256 * kLruWarps; // [n_slots] slot -> page before this step
+    int *tkey = smem_i;                  // [table] page id or -1; later: victim slots by rank
+    int *tval = tkey + table;            // [table] smallest list index of that page
+    int *tsm = tval + table;             // [n_slots] access times (hits already stamped)
+    int *s2d_s = tsm + n_slots;          // [n_slots] slot -> page before this step
+    int *mpage = s2d_s + n_slots;        // [list_len] miss pages in list order
+    int *vtime = mpage + list_len;       // [list_len] victims: time
+    int *vslot = vtime + list_len;       // [list_len] victims: slot
     __shared__ int wsum[kLruWarps];
+    __shared__ int hist[256];
+    __shared__ int res[2];
     __shared__ int sh_max;
 
     const int h = blockIdx.x;
     const int tid = threadIdx.x;
     const int lane = tid & 31;
-    const int warp = tid >> 5;
     const int32_t *list = page_list + (size_t)h * list_len;
     int32_t *d2s = dram_to_slot + (size_t)h * n_dram_pages;
     int32_t *s2d = slot_to_dram + (size_t)h * n_slots;
@@ -93,36 +162,50 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
     int32_t *mp_out = miss_pages + (size_t)h * list_len;
     int32_t *ms_out = miss_slots + (size_t)h * list_len;
 
-    // slot_source[slot] = DRAM page whose payload still has to be brought into the slot, -1
-    // otherwise: forget the marks of the previous call (its miss list is still in ms_out)
-    int32_t *src_map = slot_source ? slot_source + (size_t)h * n_slots : nullptr;
-    if (src_map) {
-        const int prev = min(n_miss_out[h], list_len);
-        for (int j = tid; j < prev; j += kLruThreads) {
-            const int v = ms_out[j];
-            if (v >= 0 && v < n_slots) src_map[v] = -1;
+    // ---- all independent global reads first ---------------------------------------------
+    int tm[SR], sd[SR];
+#pragma unroll
+    for (int r = 0; r < SR; ++r) {
+        const int s = r * kLruThreads + tid;
+        tm[r] = -1;
+        sd[r] = -1;
+        if (s < n_slots) {
+            tm[r] = tim[s];
+            sd[r] = s2d[s];
         }
     }
-
-    // ---- independent global reads first: list, its table entries, times, slot map ------
-    int pg[kLruMaxListRounds], sl[kLruMaxListRounds];
+    int pg[LR], sl[LR];
     int bad = 0;
 #pragma unroll
-    for (int r = 0; r < kLruMaxListRounds; ++r) {
+    for (int r = 0; r < LR; ++r) {
         const int i = r * kLruThreads + tid;
         pg[r] = -1;
-        if (r * kLruThreads < list_len && i < list_len) {
+        if (i < list_len) {
             const int p = list[i];
             if (p < 0 || p >= n_dram_pages) bad = 1; else pg[r] = p;
         }
     }
     const int step = step_counters[h] + 1;
+    const int prev_miss = min(n_miss_out[h], list_len);
 #pragma unroll
-    for (int r = 0; r < kLruMaxListRounds; ++r) sl[r] = pg[r] >= 0 ? d2s[pg[r]] : 0;
-    for (int s = tid; s < n_slots; s += kLruThreads) {
-        keyA[s] = tim[s];
-        valA[s] = s;
-        s2d_s[s] = s2d[s];
+    for (int r = 0; r < LR; ++r) sl[r] = pg[r] >= 0 ? d2s[pg[r]] : 0;
+
+    // slot_source[slot] = DRAM page whose payload still has to be brought into the slot, -1
+    // otherwise: forget the marks of the previous call (its miss list is still in ms_out)
+    int32_t *src_map = slot_source ? slot_source + (size_t)h * n_slots : nullptr;
+    if (src_map) {
+        for (int j = tid; j < prev_miss; j += kLruThreads) {
+            const int v = ms_out[j];
+            if (v >= 0 && v < n_slots) src_map[v] = -1;
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < SR; ++r) {
+        const int s = r * kLruThreads + tid;
+        if (s < n_slots) {
+            tsm[s] = tm[r];
+            s2d_s[s] = sd[r];
+        }
     }
     for (int x = tid; x < table; x += kLruThreads) {
         tkey[x] = -1;
@@ -136,13 +219,13 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
     const int tmask = table - 1;
     const int tshift = 32 - (__ffs(table) - 1);
 #pragma unroll
-    for (int r = 0; r < kLruMaxListRounds; ++r) {
+    for (int r = 0; r < LR; ++r) {
         const int p = pg[r];
         if (p < 0) { sl[r] = -1; continue; }   // sl[r] becomes the table position of a miss, -1 otherwise
         const int s = sl[r];
         sl[r] = -1;
         if (s >= 0) {
-            if (s < n_slots) { keyA[s] = step; tim[s] = step; }
+            if (s < n_slots) { tsm[s] = step; tim[s] = step; }
         } else {
             int pos = (int)(((uint32_t)p * 2654435761u) >> tshift) & tmask;
             for (int probe = 0; probe < table; ++probe) {
@@ -158,10 +241,10 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
     }
     __syncthreads();
 
-    // ---- 2. first appearances, ranked in list order -----------------------------------
+    // ---- 2. first appearances, ranked in list order; times with the hits applied --------
     int n_miss = 0;
 #pragma unroll
-    for (int r = 0; r < kLruMaxListRounds; ++r) {
+    for (int r = 0; r < LR; ++r) {
         if (r * kLruThreads < list_len) {
             const int f = (sl[r] >= 0) && (tval[sl[r]] == r * kLruThreads + tid);
             int total;
@@ -170,98 +253,80 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
             n_miss += total;
         }
     }
-    __syncthreads();  // the table is dead from here on; xbuf becomes keyB/valB
-
+    int hits = 0, mx = 0;
+#pragma unroll
+    for (int r = 0; r < SR; ++r) {
+        const int s = r * kLruThreads + tid;
+        if (s < n_slots) {
+            tm[r] = tsm[s];
+            hits += (tm[r] >= step);
+            mx = max(mx, tm[r]);
+        }
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) mx = max(mx, __shfl_xor_sync(DA_FULL_MASK, mx, off));
+    if (lane == 0) atomicMax(&sh_max, mx);
+    {
+        int total;
+        block_exclusive_scan(hits, wsum, &total);   // also orders the atomicMax and the table's last use
+        hits = total;
+    }
+    const int bits = 32 - __clz(sh_max | 1);
     const bool want_order = order_out != nullptr;
-    const int n_miss_found = n_miss;
-    if (n_miss > 0 || want_order) {
-        // ---- 3. stable radix sort of the slots by access time --------------------
-        {
-            int mx = 0;
-            for (int s = tid; s < n_slots; s += kLruThreads) mx = max(mx, keyA[s]);
-#pragma unroll
-            for (int off = 16; off >= 1; off >>= 1) mx = max(mx, __shfl_xor_sync(DA_FULL_MASK, mx, off));
-            if (lane == 0) atomicMax(&sh_max, mx);
-        }
-        __syncthreads();
-        const int bits = 32 - __clz(sh_max | 1);
-        const int passes = (bits + 7) / 8;
-        // warp w owns the contiguous items [w * per_warp, (w + 1) * per_warp)
-        const int per_warp = (((n_slots + kLruWarps - 1) / kLruWarps) + 31) / 32 * 32;
-        const int rounds = per_warp / 32;  // <= kLruMaxRounds
-        int *kin = keyA, *vin = valA, *kout = keyB, *vout = valB;
-        for (int pass = 0; pass < passes; ++pass) {
-            const int shift = 8 * pass;
-            for (int x = tid; x < 256 * kLruWarps; x += kLruThreads) hist[x] = 0;
-            __syncthreads();
-            int off[kLruMaxRounds], dig[kLruMaxRounds];
-#pragma unroll
-            for (int r = 0; r < kLruMaxRounds; ++r) {
-                off[r] = 0;
-                dig[r] = -1;
-                if (r < rounds) {
-                    const int i = warp * per_warp + r * 32 + lane;
-                    const bool valid = i < n_slots;
-                    const int d = valid ? ((kin[i] >> shift) & 255) : 256;
-                    const uint32_t peers = __match_any_sync(DA_FULL_MASK, d);
-                    const int leader = __ffs(peers) - 1;
-                    const int pos = __popc(peers & ((1u << lane) - 1));
-                    int base = 0;
-                    if (valid && lane == leader) {
-                        base = hist[d * kLruWarps + warp];
-                        hist[d * kLruWarps + warp] = base + __popc(peers);
-                    }
-                    base = __shfl_sync(DA_FULL_MASK, base, leader);
-                    if (valid) {
-                        off[r] = base + pos;
-                        dig[r] = d;
-                    }
-                    __syncwarp();
-                }
-            }
-            __syncthreads();
-            // exclusive scan of hist in (digit, warp) order: 8 consecutive entries per thread
-            {
-                int c[8], tot = 0;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    c[j] = hist[tid * 8 + j];
-                    tot += c[j];
-                }
-                int total;
-                int run = block_exclusive_scan(tot, wsum, &total);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    hist[tid * 8 + j] = run;
-                    run += c[j];
-                }
-            }
-            __syncthreads();
-#pragma unroll
-            for (int r = 0; r < kLruMaxRounds; ++r) {
-                if (r < rounds && dig[r] >= 0) {
-                    const int i = warp * per_warp + r * 32 + lane;
-                    const int dst = hist[dig[r] * kLruWarps + warp] + off[r];
-                    kout[dst] = kin[i];
-                    vout[dst] = vin[i];
-                }
-            }
-            __syncthreads();
-            int *t = kin; kin = kout; kout = t;
-            t = vin; vin = vout; vout = t;
-        }
-        // kin/vin now hold the slots in eviction order.
+    const int n_found = n_miss;
 
-        // ---- 4. overflow check, then assignment ------------------------------------
-        const bool overflow =
-            n_miss > 0 && ((n_miss > n_slots) || (kin[min(n_miss, n_slots) - 1] >= step));
+    // ---- 3. victims ------------------------------------------------------------------------
+    bool victim[SR];
+#pragma unroll
+    for (int r = 0; r < SR; ++r) victim[r] = false;
+    bool overflow = false;
+    if (n_miss > 0) {
+        overflow = n_miss > n_slots - hits;   // victims must not have been touched by this call
         if (overflow) {
             if (tid == 0) atomicOr(status, DA_STATUS_LRU_OVERFLOW);
             n_miss = 0;  // tables stay as after the hit marking
         } else {
+            int t1, less1;
+            select_time<SR>(tm, n_miss, bits, hist, res, t1, less1);
+            int run_lt = 0, run_eq = 0;   // slots seen so far (in slot order) with time < t1, == t1
+#pragma unroll
+            for (int r = 0; r < SR; ++r) {
+                if (r * kLruThreads < n_slots) {
+                    const int lt = tm[r] >= 0 && tm[r] < t1;
+                    const int eq = tm[r] == t1;
+                    int total;
+                    const int ex = block_exclusive_scan(lt | (eq << 16), wsum, &total);
+                    const int lt_rank = run_lt + (ex & 0xffff);
+                    const int eq_rank = run_eq + (ex >> 16);
+                    if (lt) {
+                        victim[r] = true;
+                        vtime[lt_rank] = tm[r];
+                        vslot[lt_rank] = r * kLruThreads + tid;
+                    } else if (eq && less1 + eq_rank < n_miss) {
+                        victim[r] = true;
+                        tkey[less1 + eq_rank] = r * kLruThreads + tid;   // already in final position
+                    }
+                    run_lt += total & 0xffff;
+                    run_eq += total >> 16;
+                }
+            }
+            __syncthreads();
+            // the less1 victims older than t1 still have to be ordered by (time, slot)
+            for (int j = tid; j < less1; j += kLruThreads) {
+                const int kt = vtime[j], ks = vslot[j];
+                int rank = 0;
+                for (int i = 0; i < less1; ++i) {
+                    const int it = vtime[i], is = vslot[i];
+                    rank += (it < kt) || (it == kt && is < ks);
+                }
+                tkey[rank] = ks;
+            }
+            __syncthreads();
+
+            // ---- 4. the j-th miss takes the j-th victim --------------------------------------
             for (int j = tid; j < n_miss; j += kLruThreads) {
                 const int p = mpage[j];
-                const int v = vin[j];
+                const int v = tkey[j];
                 const int old = s2d_s[v];
                 if (old >= 0 && old < n_dram_pages) d2s[old] = -1;
                 s2d[v] = p;
@@ -272,32 +337,43 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
                 if (src_map) src_map[v] = p;
             }
         }
+    }
 
-        // ---- 5. which slots can be evicted by the NEXT call -------------------------------
-        // Sorted order now: [victims | untouched slots by (time, slot) | slots hit this call].
-        // After this call victims and hits carry the newest stamp, so the next call's victims
-        // come from the front of the untouched run, and no further in than the next list is
-        // long (every list entry is either a hit, which removes a slot from the front, or a
-        // miss, which takes one).  If the untouched run is at least list_len long, those
-        // list_len slots are the only candidates; order_out = that run first, everything else
-        // after it (a rotation of the sorted order by n_miss).  Otherwise every slot is a
-        // candidate.
-        if (want_order) {
-            int touched = 0;  // slots hit by this call (sorted keys still hold the pre-assignment times)
-            for (int i = tid; i < n_slots; i += kLruThreads) touched += (kin[i] >= step);
-            int total;
-            block_exclusive_scan(touched, wsum, &total);
-            const int untouched = n_slots - total - n_miss;
-            const int cap = min(list_len, n_slots);
-            const bool bounded = !overflow && n_miss_found == n_miss && untouched >= cap;
-            int32_t *ord = order_out + (size_t)h * n_slots;
-            for (int i = tid; i < n_slots; i += kLruThreads) {
-                int src = i + n_miss;
-                if (src >= n_slots) src -= n_slots;
-                ord[i] = vin[src];
+    // ---- 5. which slots can be evicted by the NEXT call -------------------------------------
+    // In (time, slot) order the slots are now [victims | untouched | hit by this call].  After
+    // this call victims and hits carry the newest stamp, so the next call's victims come from the
+    // front of the untouched run, and no further in than the next list is long (every list entry
+    // is either a hit, which removes a slot from the front, or a miss, which takes one).  If the
+    // untouched run is at least list_len long, its first list_len slots are the only candidates:
+    // order_out = those first, every other slot after them.  Otherwise every slot is a candidate.
+    if (want_order) {
+        int32_t *ord = order_out + (size_t)h * n_slots;
+        const int cap = min(list_len, n_slots);
+        const int untouched = n_slots - hits - n_miss;
+        const bool bounded = !overflow && n_found == n_miss && untouched >= cap;
+        if (bounded) {
+            int t2, less2;
+            select_time<SR>(tm, n_miss + cap, bits, hist, res, t2, less2);   // tm: times before assignment
+            int run_eq = 0, run_e = 0;
+#pragma unroll
+            for (int r = 0; r < SR; ++r) {
+                if (r * kLruThreads < n_slots) {
+                    const int s = r * kLruThreads + tid;
+                    const int eq = tm[r] == t2;
+                    int total;
+                    const int eq_rank = run_eq + block_exclusive_scan(eq, wsum, &total);
+                    run_eq += total;
+                    const bool front = tm[r] >= 0 && (tm[r] < t2 || (eq && less2 + eq_rank < n_miss + cap));
+                    const int e = front && !victim[r];
+                    const int e_before = run_e + block_exclusive_scan(e, wsum, &total);
+                    run_e += total;
+                    if (s < n_slots) ord[e ? e_before : cap + (s - e_before)] = s;
+                }
             }
-            if (tid == 0) n_evictable_out[h] = bounded ? cap : n_slots;
+        } else {
+            for (int s = tid; s < n_slots; s += kLruThreads) ord[s] = s;
         }
+        if (tid == 0) n_evictable_out[h] = bounded ? cap : n_slots;
     }
     if (tid == 0) {
         n_miss_out[h] = n_miss;
@@ -306,12 +382,33 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
 }
 
 static size_t lru_smem_bytes(int n_slots, int list_len) {
-    const int table = lru_table_size(list_len);
-    const int xhalf = n_slots > table ? n_slots : table;
-    return ((size_t)3 * n_slots + 2 * (size_t)xhalf + list_len + 256 * kLruWarps) * sizeof(int);
+    return ((size_t)2 * lru_table_size(list_len) + 2 * (size_t)n_slots + 3 * (size_t)list_len) * sizeof(int);
 }
 
-constexpr size_t kLruMaxSmem = 227 * 1024 - 1024;
+constexpr size_t kLruMaxSmem = 227 * 1024 - 4096;
+
+template <int SR, int LR>
+static cudaError_t launch_lru(const int32_t *page_list, int list_len, int32_t *dram_to_slot, int n_dram_pages,
+                              int32_t *slot_to_dram, int32_t *access_time, int n_slots, int32_t *step,
+                              int n_kv_heads, int32_t *miss_pages, int32_t *miss_slots, int32_t *n_miss,
+                              int32_t *slot_source, int32_t *order_out, int32_t *n_evictable_out, int32_t *status,
+                              size_t smem, cudaStream_t stream) {
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!attr_set[dev]) {
+        e = cudaFuncSetAttribute(lru_update_kernel<SR, LR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)kLruMaxSmem);
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    lru_update_kernel<SR, LR><<<n_kv_heads, kLruThreads, smem, stream>>>(
+        page_list, list_len, dram_to_slot, n_dram_pages, slot_to_dram, access_time, n_slots, step, miss_pages,
+        miss_slots, n_miss, slot_source, order_out, n_evictable_out, status);
+    return cudaGetLastError();
+}
 
 }  // namespace da
 
@@ -328,19 +425,13 @@ extern "C" int da_lru_update(const int32_t *page_list, int list_len, int32_t *dr
     if (n_slots > da::kLruMaxSlots || list_len > da::kLruMaxList) return DA_ERR_UNSUPPORTED;
     const size_t smem = da::lru_smem_bytes(n_slots, list_len);
     if (smem > da::kLruMaxSmem) return DA_ERR_UNSUPPORTED;
-    static bool attr_set[64] = {};
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return (int)e;
-    if (dev < 0 || dev >= 64) return DA_ERR_UNSUPPORTED;
-    if (!attr_set[dev]) {
-        e = cudaFuncSetAttribute(da::lru_update_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)da::kLruMaxSmem);
-        if (e != cudaSuccess) return (int)e;
-        attr_set[dev] = true;
-    }
-    da::lru_update_kernel<<<n_kv_heads, da::kLruThreads, smem, static_cast<cudaStream_t>(stream)>>>(
-        page_list, list_len, dram_to_slot, n_dram_pages, slot_to_dram, access_time, n_slots, step, miss_pages,
-        miss_slots, n_miss, slot_source, order_out, n_evictable_out, status);
-    return (int)cudaGetLastError();
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t e;
+#define DA_LRU_ARGS page_list, list_len, dram_to_slot, n_dram_pages, slot_to_dram, access_time, n_slots, step, \
+                    n_kv_heads, miss_pages, miss_slots, n_miss, slot_source, order_out, n_evictable_out, status, smem, s
+    if (n_slots <= 2048 && list_len <= 1024) e = da::launch_lru<2, 1>(DA_LRU_ARGS);
+    else if (n_slots <= 4096 && list_len <= 2048) e = da::launch_lru<4, 2>(DA_LRU_ARGS);
+    else e = da::launch_lru<8, 8>(DA_LRU_ARGS);
+#undef DA_LRU_ARGS
+    return (int)e;
 }

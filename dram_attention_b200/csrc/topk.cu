@@ -72,8 +72,8 @@ __global__ void __launch_bounds__(kTopkThreads)
 topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_list, int n_kv_heads, int rep,
                   int n_pages, int k) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    unsigned long long *cand = reinterpret_cast<unsigned long long *>(smem_raw);  // [k]
-    int *rank = reinterpret_cast<int *>(cand + k);                                // [k]
+    unsigned long long *cand = reinterpret_cast<unsigned long long *>(smem_raw);  // [k + 1]
+    int *rank = reinterpret_cast<int *>(cand + k + 1);                            // [k]
     __shared__ int hist[256];
     __shared__ int warp_tot[kTopkWarps];
     __shared__ int sh_digit, sh_above, sh_count, sh_taken;
@@ -155,18 +155,35 @@ topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_l
     const uint32_t thr = prefix;
 
     // ---- gather the survivors ------------------------------------------------
-    if (tid == 0) sh_taken = 0;
-    __syncthreads();
+    // Two sweeps over the keys instead of a shared counter: every warp first counts what it
+    // will take, a scan over the 32 warp totals gives each warp its range of `cand`, and the
+    // second sweep writes without atomics.
     const bool take_all_ties = (count_eq == need);
+    int warp_count = 0;
+    keys.for_each(srow, n_pages, tid, [&](int, uint32_t key, bool valid) {
+        const bool take = valid && (key > thr || (take_all_ties && key == thr));
+        warp_count += __popc(__ballot_sync(DA_FULL_MASK, take));
+    });
+    if (lane == 0) warp_tot[warp] = warp_count;
+    __syncthreads();
+    int warp_base;
+    {
+        const int wt = warp_tot[lane];
+        int incl = wt;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int v = __shfl_up_sync(DA_FULL_MASK, incl, off);
+            if (lane >= off) incl += v;
+        }
+        warp_base = __shfl_sync(DA_FULL_MASK, incl - wt, warp);
+        const int all = __shfl_sync(DA_FULL_MASK, incl, 31);
+        if (tid == 0) sh_taken = all;
+    }
     keys.for_each(srow, n_pages, tid, [&](int i, uint32_t key, bool valid) {
         const bool take = valid && (key > thr || (take_all_ties && key == thr));
         const uint32_t bal = __ballot_sync(DA_FULL_MASK, take);
-        if (bal) {
-            int base = 0;
-            if (lane == __ffs(bal) - 1) base = atomicAdd(&sh_taken, __popc(bal));
-            base = __shfl_sync(DA_FULL_MASK, base, __ffs(bal) - 1);
-            if (take) cand[base + __popc(bal & ((1u << lane) - 1))] = ((unsigned long long)(~key) << 32) | (uint32_t)i;
-        }
+        if (take) cand[warp_base + __popc(bal & ((1u << lane) - 1))] = ((unsigned long long)(~key) << 32) | (uint32_t)i;
+        warp_base += __popc(bal);
     });
     __syncthreads();
     if (!take_all_ties) {
@@ -195,23 +212,31 @@ topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_l
     __syncthreads();
 
     // ---- order the k survivors: rank = number of smaller composite keys --------
+    // The candidate array is read two entries per 128-bit load; with k odd the pad entry is
+    // the largest possible key and counts for nobody.
     for (int e = tid; e < k; e += kTopkThreads) rank[e] = 0;
+    if (tid == 0 && (k & 1)) cand[k] = ~0ull;
     __syncthreads();
     {
         // with k < 1024 the comparisons of one element are split over several threads
+        const int n_pairs = (k + 1) >> 1;
         int segs = kTopkThreads / k;
         if (segs < 1) segs = 1;
         const int per_sweep = kTopkThreads / segs;
-        const int seg_len = (k + segs - 1) / segs;
+        const int seg_pairs = (n_pairs + segs - 1) / segs;
+        const ulonglong2 *pairs = reinterpret_cast<const ulonglong2 *>(cand);
         for (int e0 = 0; e0 < k; e0 += per_sweep) {
             const int e = e0 + tid % per_sweep;
             const int seg = tid / per_sweep;
             if (e < k && seg < segs) {
                 const unsigned long long v = cand[e];
-                const int j0 = seg * seg_len;
-                const int j1 = min(k, j0 + seg_len);
+                const int j0 = seg * seg_pairs;
+                const int j1 = min(n_pairs, j0 + seg_pairs);
                 int c = 0;
-                for (int j = j0; j < j1; ++j) c += (cand[j] < v);
+                for (int j = j0; j < j1; ++j) {
+                    const ulonglong2 w = pairs[j];
+                    c += (w.x < v) + (w.y < v);
+                }
                 if (c) atomicAdd(&rank[e], c);
             }
         }
@@ -233,11 +258,11 @@ static cudaError_t launch_topk(const float *scores, int32_t *page_list, int rows
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
     if (!attr_set[dev]) {
         e = cudaFuncSetAttribute(topk_pages_kernel<IPT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 kTopkMaxK * 12);
+                                 kTopkMaxK * 12 + 8);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    const size_t smem = (size_t)k * (sizeof(unsigned long long) + sizeof(int));
+    const size_t smem = (size_t)(k + 1) * sizeof(unsigned long long) + (size_t)k * sizeof(int);
     topk_pages_kernel<IPT><<<rows, kTopkThreads, smem, stream>>>(scores, page_list, n_kv_heads, rep, n_pages, k);
     return cudaGetLastError();
 }
