@@ -31,7 +31,8 @@ _SIGNATURES = {
                                c_int, c_void_p]),
     "da_topk_pages": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "da_lru_update": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                              c_void_p]),
     "da_decode_attention_fetch": (c_int, [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_void_p,
                                           c_void_p, c_void_p, c_longlong, c_longlong, c_int, c_void_p, c_void_p,
                                           c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p,
@@ -45,7 +46,7 @@ _SIGNATURES = {
                                     c_void_p]),
     "da_decode_attention_phased_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "da_decode_attention_phased_supported": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int]),
-    "da_decode_attention_phased": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+    "da_decode_attention_phased": (c_int, [c_int, c_void_p, c_void_p, c_void_p,
                                            c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_void_p,
                                            c_void_p, c_void_p, c_longlong, c_longlong, c_int, c_void_p, c_void_p,
                                            c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p,

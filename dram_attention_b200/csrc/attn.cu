@@ -319,34 +319,23 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 2 : 1) decode_attenti
         }
         part[e] = outv;  // c < D: weighted acc; c == D: max; c == D+1: weighted l
     }
-    if (p.phase == 1) return;   // phase 2 merges
+    if (p.phase == 1) return;   // phase 2 merges the rows of both launches
     __threadfence();
     __syncthreads();
+    unsigned int *tickets = p.counters;
     if (tid == 0) {
-        const unsigned int ticket = atomicAdd(&p.counters[h], 1u);
+        const unsigned int ticket = atomicAdd(&tickets[h], 1u);
         sh_last = (ticket == (unsigned int)(splits - 1));
     }
     __syncthreads();
     if (!sh_last) return;
 
-    // ---- last CTA of this head: merge the splits ----------------------------------------
+    // ---- last CTA of this head (of this launch) ---------------------------------------------
     __threadfence();
-    merge_splits<T, D, REP, THREADS>(p, h, p.part_rows, reinterpret_cast<float *>(smem));
-    if (p.phase == 2 && p.order_next) {
-        // every CTA of this head is done with the split: install the one for the next step
-        const int32_t *__restrict__ src = p.order_next + (size_t)h * p.n_slots;
-        int32_t *__restrict__ dst = p.order + (size_t)h * p.n_slots;
-        for (int i0 = tid; i0 < p.n_slots; i0 += THREADS * 8) {
-            int32_t v[8];   // all loads of a batch in flight before the first store
-#pragma unroll
-            for (int u = 0; u < 8; ++u) v[u] = (i0 + u * THREADS < p.n_slots) ? __ldcg(src + i0 + u * THREADS) : 0;
-#pragma unroll
-            for (int u = 0; u < 8; ++u)
-                if (i0 + u * THREADS < p.n_slots) dst[i0 + u * THREADS] = v[u];
-        }
-        if (tid == 0) p.n_evictable[h] = p.n_evictable_next[h];
-    }
-    if (tid == 0) p.counters[h] = 0u;
+    merge_splits<T, D, REP, THREADS>(p, h, p.merge_first, p.merge_rows, reinterpret_cast<float *>(smem), nullptr);
+    // every CTA of this head is done with the split: the one the LRU update left becomes current
+    if (p.phase == 2 && tid == 0) p.flip[h] ^= 1;
+    if (tid == 0) tickets[h] = 0u;
 }
 
 template <typename T, int D, int REP, int WARPS>
@@ -405,9 +394,8 @@ static int decode_attention_common(const void *q, const void *prefix_kv, long lo
                                    void *out, float *lse_out, void *workspace, size_t workspace_bytes,
                                    int32_t *status, int n_kv_heads, int rep, int head_dim, int dtype,
                                    const void *dram_pages, int n_dram_pages, const int32_t *slot_source,
-                                   int n_slots, int page_size, int phase, int32_t *order, int32_t *n_evictable,
-                                   const int32_t *order_next, const int32_t *n_evictable_next,
-                                   da_stream_t stream) {
+                                   int n_slots, int page_size, int phase, const int32_t *order, const int32_t *n_evictable,
+                                   int32_t *flip, da_stream_t stream) {
     if (!q || !prefix_kv || !local_k || !local_v || !new_k || !new_v || !out || !workspace || !status)
         return DA_ERR_NULL;
     if (n_kv_heads < 1 || n_prefix_tokens < 1 || local_capacity < 1 || dram_tokens < 0) return DA_ERR_SHAPE;
@@ -468,16 +456,23 @@ static int decode_attention_common(const void *q, const void *prefix_kv, long lo
         p.page_tokens = page_size;
     }
     p.phase = phase;
+    p.n_kv_heads = n_kv_heads;
+    p.counters1 = p.counters + da::kCounterBytes / 8;
     p.part_rows = da::attn_splits(n_kv_heads);
     p.part_offset = 0;
+    p.merge_first = 0;
+    p.merge_rows = p.part_rows;
     if (phase != 0) {
-        if (!slot_source || !order || !n_evictable) return DA_ERR_NULL;
+        if (!slot_source || !order || !n_evictable || !flip) return DA_ERR_NULL;
+        if (n_kv_heads * 8 > da::kCounterBytes) return DA_ERR_UNSUPPORTED;
+        const int sa = da::attn_splits_phase1(n_kv_heads), sb = da::attn_splits(n_kv_heads);
         p.order = order;
         p.n_evictable = n_evictable;
-        p.order_next = order_next;
-        p.n_evictable_next = n_evictable_next;
-        p.part_rows = da::attn_splits_phase1(n_kv_heads) + da::attn_splits(n_kv_heads);
-        p.part_offset = phase == 2 ? da::attn_splits_phase1(n_kv_heads) : 0;
+        p.flip = flip;
+        p.part_rows = sa + sb;                // phase-1 rows, then phase-2 rows
+        p.part_offset = phase == 2 ? sa : 0;
+        p.merge_first = 0;
+        p.merge_rows = sa + sb;
     }
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -499,7 +494,7 @@ extern "C" int da_decode_attention(const void *q, const void *prefix_kv, long lo
                                    local_token_stride, local_head_stride, local_capacity, new_k, new_v,
                                    start_pos_dev, start_pos_host, dram_tokens, out, lse_out, workspace,
                                    workspace_bytes, status, n_kv_heads, rep, head_dim, dtype, nullptr, 0,
-                                   nullptr, 0, 0, 0, nullptr, nullptr, nullptr, nullptr, stream);
+                                   nullptr, 0, 0, 0, nullptr, nullptr, nullptr, stream);
 }
 
 extern "C" int da_decode_attention_fetch(const void *q, void *slots, long long slots_head_stride, int n_slots,
@@ -517,8 +512,7 @@ extern "C" int da_decode_attention_fetch(const void *q, void *slots, long long s
                                    local_token_stride, local_head_stride, local_capacity, new_k, new_v,
                                    start_pos_dev, start_pos_host, dram_tokens, out, lse_out, workspace,
                                    workspace_bytes, status, n_kv_heads, rep, head_dim, dtype, dram_pages,
-                                   n_dram_pages, slot_source, n_slots, page_size, 0, nullptr, nullptr, nullptr,
-                                   nullptr, stream);
+                                   n_dram_pages, slot_source, n_slots, page_size, 0, nullptr, nullptr, nullptr, stream);
 }
 
 extern "C" int da_decode_attention_phased_supported(int n_kv_heads, int rep, int head_dim, int dtype, int n_slots,
@@ -549,9 +543,8 @@ extern "C" size_t da_decode_attention_phased_workspace_bytes(int n_kv_heads, int
                                            (head_dim + 4) * sizeof(float);
 }
 
-extern "C" int da_decode_attention_phased(int phase, int32_t *order, int32_t *n_evictable,
-                                          const int32_t *order_next, const int32_t *n_evictable_next,
-                                          const void *q, void *slots, long long slots_head_stride, int n_slots,
+extern "C" int da_decode_attention_phased(int phase, const int32_t *order, const int32_t *n_evictable,
+                                          int32_t *split_flip, const void *q, void *slots, long long slots_head_stride, int n_slots,
                                           int page_size, const void *dram_pages, int n_dram_pages,
                                           const int32_t *slot_source, void *local_k, void *local_v,
                                           long long local_token_stride, long long local_head_stride,
@@ -561,7 +554,7 @@ extern "C" int da_decode_attention_phased(int phase, int32_t *order, int32_t *n_
                                           int32_t *status, int n_kv_heads, int rep, int head_dim, int dtype,
                                           da_stream_t stream) {
     if (phase != 1 && phase != 2) return DA_ERR_SHAPE;
-    if (!slot_source || !order || !n_evictable) return DA_ERR_NULL;
+    if (!slot_source || !order || !n_evictable || !split_flip) return DA_ERR_NULL;
     if (!da_decode_attention_phased_supported(n_kv_heads, rep, head_dim, dtype, n_slots, page_size, local_capacity))
         return DA_ERR_UNSUPPORTED;
     if (n_slots < 1 || page_size < 1 || (long long)n_slots * page_size > 0x7fffffffLL) return DA_ERR_SHAPE;
@@ -570,7 +563,7 @@ extern "C" int da_decode_attention_phased(int phase, int32_t *order, int32_t *n_
                                    start_pos_dev, start_pos_host, dram_tokens, out, lse_out, workspace,
                                    workspace_bytes, status, n_kv_heads, rep, head_dim, dtype, dram_pages,
                                    n_dram_pages, slot_source, n_slots, page_size, phase, order, n_evictable,
-                                   order_next, n_evictable_next, stream);
+                                   split_flip, stream);
 }
 
 // ---- entry point with built-in scratch ------------------------------------------------

@@ -51,12 +51,14 @@ struct AttnParams {
     // phase 2 attends over the evictable slots after the update and merges both.  The split
     // is order[h][0 .. n_evictable[h]) = evictable, the rest not (left by da_lru_update).
     int phase;                       // 0: one launch over everything
-    int32_t *order;                  // (n_kv_heads, n_slots) split used by phases 1 and 2
-    int32_t *n_evictable;            // (n_kv_heads)
-    const int32_t *order_next;       // what the LRU update of this step left for the next step;
-    const int32_t *n_evictable_next; // copied over `order` by the last CTA of a head in phase 2
+    const int32_t *order;            // [2][n_kv_heads][n_slots]: two copies of the split; flip[h] names the
+    const int32_t *n_evictable;      // [2][n_kv_heads]            one both phases of this step use, the LRU
+    int32_t *flip;                   // [n_kv_heads]               update writes the other, phase 2 flips
+    unsigned int *counters1;         // ticket counters of phase 1 (second half of the counter block)
     int part_rows;                   // partial rows per head in the workspace
     int part_offset;                 // first row this launch writes
+    int merge_first, merge_rows;     // rows the last CTA of a head merges
+    int n_kv_heads;
 };
 
 constexpr int kMaxUnitsPerWarp = 64;   // two per lane: where each unit of a warp comes from
@@ -86,7 +88,12 @@ __device__ __forceinline__ UnitPlan plan_units(const AttnParams &p, int h, int n
     UnitPlan pl;
     const int ups = p.order ? p.page_tokens / kUnitTokens : 1;
     int n_ev = 0;
-    if (p.order) n_ev = min(max(p.n_evictable[h], 0), p.n_slots);
+    const int32_t *order = nullptr;
+    if (p.order) {
+        const int cur = p.flip[h] & 1;
+        order = p.order + ((size_t)cur * p.n_kv_heads + h) * p.n_slots;
+        n_ev = min(max(p.n_evictable[cur * p.n_kv_heads + h], 0), p.n_slots);
+    }
     if (p.phase == 0) pl.units_slots = (p.n_prefix_tokens + kUnitTokens - 1) / kUnitTokens;
     else if (p.phase == 1) pl.units_slots = (p.n_slots - n_ev) * ups;
     else pl.units_slots = n_ev * ups;
@@ -102,7 +109,7 @@ __device__ __forceinline__ UnitPlan plan_units(const AttnParams &p, int h, int n
         if (i < pl.n_my && u < pl.units_slots) {
             int base = u * kUnitTokens;
             if (p.phase != 0) {
-                int slot = p.order[(size_t)h * p.n_slots + (p.phase == 1 ? n_ev : 0) + u / ups];
+                int slot = order[(p.phase == 1 ? n_ev : 0) + u / ups];
                 slot = min(max(slot, 0), p.n_slots - 1);
                 base = slot * p.page_tokens + (u % ups) * kUnitTokens;
             }
@@ -153,16 +160,18 @@ template <int D> struct PartialRow { static constexpr int kWidth = D + 4; };
 // partial row = acc[D] (already weighted to the row's max), max, l.  `scratch` holds
 // at least 2 * splits * REP floats of shared memory (the idle stage buffers).  Loads bypass L1 (the rows were
 // written by other SMs).  The first batch of accumulator rows is requested together
-// with the (max, l) pairs, so about three L2 round trips are exposed in total.
+// with the (max, l) pairs; up to 26 rows make a batch.  With `partial_out` the result is
+// written as one more partial row instead of the output (phase 1 folds its rows this way).
 template <typename T, int D, int REP, int THREADS>
-__device__ __forceinline__ void merge_splits(const AttnParams &p, int h, int splits, float *scratch) {
+__device__ __forceinline__ void merge_splits(const AttnParams &p, int h, int first_row, int splits, float *scratch,
+                                             float *partial_out) {
     constexpr int PW = PartialRow<D>::kWidth;
     constexpr int VPR = D / 4;          // float4 per accumulator row
     constexpr int BATCH = 26;
     constexpr float NEG_INF = -INFINITY;
     __shared__ float sh_m[REP], sh_l[REP];
     const int tid = threadIdx.x;
-    const float *hp = p.partials + ((size_t)h * splits * REP) * PW;
+    const float *hp = p.partials + ((size_t)(h * p.part_rows + first_row) * REP) * PW;
     const int n = splits * REP;
     float *wgt = scratch;        // [n] max, then weight
     float *lsum = scratch + n;   // [n] l of every partial row
@@ -219,7 +228,15 @@ __device__ __forceinline__ void merge_splits(const AttnParams &p, int h, int spl
                 }
             }
         }
-        if (live) {
+        if (live && partial_out) {
+            // not the end yet: one partial row (acc weighted to the common max, max, l)
+            float *dst = partial_out + (size_t)r * PW;
+            reinterpret_cast<float4 *>(dst)[c4] = a;
+            if (c4 == 0) {
+                dst[D] = sh_m[r];
+                dst[D + 1] = sh_l[r];
+            }
+        } else if (live) {
             const float ll = sh_l[r];
             const float inv = ll > 0.f ? 1.f / ll : 0.f;
             T *dst = reinterpret_cast<T *>(p.out) + (size_t)(h * REP + r) * D + 4 * c4;

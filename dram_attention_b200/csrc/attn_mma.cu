@@ -342,33 +342,23 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 2 : 1) decode_attenti
         }
         part[e] = outv;
     }
-    if (p.phase == 1) return;   // phase 2 merges
+    if (p.phase == 1) return;   // phase 2 merges the rows of both launches
     __threadfence();
     __syncthreads();
+    unsigned int *tickets = p.counters;
     if (tid == 0) {
-        const unsigned int ticket = atomicAdd(&p.counters[h], 1u);
+        const unsigned int ticket = atomicAdd(&tickets[h], 1u);
         sh_last = (ticket == (unsigned int)(splits - 1));
     }
     __syncthreads();
     if (!sh_last) return;
 
+    // ---- last CTA of this head (of this launch) ---------------------------------------------
     __threadfence();
-    merge_splits<T, D, REP, THREADS>(p, h, p.part_rows, reinterpret_cast<float *>(smem));
-    if (p.phase == 2 && p.order_next) {
-        // every CTA of this head is done with the split: install the one for the next step
-        const int32_t *__restrict__ src = p.order_next + (size_t)h * p.n_slots;
-        int32_t *__restrict__ dst = p.order + (size_t)h * p.n_slots;
-        for (int i0 = tid; i0 < p.n_slots; i0 += THREADS * 8) {
-            int32_t v[8];   // all loads of a batch in flight before the first store
-#pragma unroll
-            for (int u = 0; u < 8; ++u) v[u] = (i0 + u * THREADS < p.n_slots) ? __ldcg(src + i0 + u * THREADS) : 0;
-#pragma unroll
-            for (int u = 0; u < 8; ++u)
-                if (i0 + u * THREADS < p.n_slots) dst[i0 + u * THREADS] = v[u];
-        }
-        if (tid == 0) p.n_evictable[h] = p.n_evictable_next[h];
-    }
-    if (tid == 0) p.counters[h] = 0u;
+    merge_splits<T, D, REP, THREADS>(p, h, p.merge_first, p.merge_rows, reinterpret_cast<float *>(smem), nullptr);
+    // every CTA of this head is done with the split: the one the LRU update left becomes current
+    if (p.phase == 2 && tid == 0) p.flip[h] ^= 1;
+    if (tid == 0) tickets[h] = 0u;
 }
 
 template <typename T, int D, int REP, int WARPS>

@@ -137,7 +137,7 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
                   int32_t *slot_to_dram, int32_t *access_time, int n_slots, int32_t *step_counters,
                   int32_t *__restrict__ miss_pages, int32_t *__restrict__ miss_slots,
                   int32_t *__restrict__ n_miss_out, int32_t *slot_source, int32_t *order_out,
-                  int32_t *n_evictable_out, int32_t *status) {
+                  int32_t *n_evictable_out, const int32_t *split_flip, int32_t *status) {
     extern __shared__ __align__(16) int smem_i[];
     const int table = lru_table_size(list_len);
     int *tkey = smem_i;                  // [table] page id or -1; later: victim slots by rank
@@ -347,7 +347,9 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
     // untouched run is at least list_len long, its first list_len slots are the only candidates:
     // order_out = those first, every other slot after them.  Otherwise every slot is a candidate.
     if (want_order) {
-        int32_t *ord = order_out + (size_t)h * n_slots;
+        // two buffers, [2][n_kv_heads][...]: the one split_flip[h] does NOT name is written
+        const int wbuf = split_flip ? 1 - (split_flip[h] & 1) : 0;
+        int32_t *ord = order_out + ((size_t)wbuf * gridDim.x + h) * n_slots;
         const int cap = min(list_len, n_slots);
         const int untouched = n_slots - hits - n_miss;
         const bool bounded = !overflow && n_found == n_miss && untouched >= cap;
@@ -373,7 +375,7 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
         } else {
             for (int s = tid; s < n_slots; s += kLruThreads) ord[s] = s;
         }
-        if (tid == 0) n_evictable_out[h] = bounded ? cap : n_slots;
+        if (tid == 0) n_evictable_out[(size_t)wbuf * gridDim.x + h] = bounded ? cap : n_slots;
     }
     if (tid == 0) {
         n_miss_out[h] = n_miss;
@@ -391,8 +393,8 @@ template <int SR, int LR>
 static cudaError_t launch_lru(const int32_t *page_list, int list_len, int32_t *dram_to_slot, int n_dram_pages,
                               int32_t *slot_to_dram, int32_t *access_time, int n_slots, int32_t *step,
                               int n_kv_heads, int32_t *miss_pages, int32_t *miss_slots, int32_t *n_miss,
-                              int32_t *slot_source, int32_t *order_out, int32_t *n_evictable_out, int32_t *status,
-                              size_t smem, cudaStream_t stream) {
+                              int32_t *slot_source, int32_t *order_out, int32_t *n_evictable_out,
+                              const int32_t *split_flip, int32_t *status, size_t smem, cudaStream_t stream) {
     static bool attr_set[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -406,7 +408,7 @@ static cudaError_t launch_lru(const int32_t *page_list, int list_len, int32_t *d
     }
     lru_update_kernel<SR, LR><<<n_kv_heads, kLruThreads, smem, stream>>>(
         page_list, list_len, dram_to_slot, n_dram_pages, slot_to_dram, access_time, n_slots, step, miss_pages,
-        miss_slots, n_miss, slot_source, order_out, n_evictable_out, status);
+        miss_slots, n_miss, slot_source, order_out, n_evictable_out, split_flip, status);
     return cudaGetLastError();
 }
 
@@ -416,19 +418,20 @@ extern "C" int da_lru_update(const int32_t *page_list, int list_len, int32_t *dr
                              int32_t *slot_to_dram, int32_t *access_time, int n_slots, int32_t *step,
                              int n_kv_heads, int32_t *miss_pages, int32_t *miss_slots, int32_t *n_miss,
                              int32_t *slot_source, int32_t *order_out, int32_t *n_evictable_out,
-                             int32_t *status, da_stream_t stream) {
+                             const int32_t *split_flip, int32_t *status, da_stream_t stream) {
     if (!page_list || !dram_to_slot || !slot_to_dram || !access_time || !step || !miss_pages || !miss_slots ||
         !n_miss || !status)
         return DA_ERR_NULL;
     if (list_len < 1 || n_dram_pages < 1 || n_slots < 1 || n_kv_heads < 1) return DA_ERR_SHAPE;
-    if ((order_out == nullptr) != (n_evictable_out == nullptr)) return DA_ERR_NULL;
+    if ((order_out == nullptr) != (n_evictable_out == nullptr) || (order_out == nullptr) != (split_flip == nullptr))
+        return DA_ERR_NULL;
     if (n_slots > da::kLruMaxSlots || list_len > da::kLruMaxList) return DA_ERR_UNSUPPORTED;
     const size_t smem = da::lru_smem_bytes(n_slots, list_len);
     if (smem > da::kLruMaxSmem) return DA_ERR_UNSUPPORTED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     cudaError_t e;
 #define DA_LRU_ARGS page_list, list_len, dram_to_slot, n_dram_pages, slot_to_dram, access_time, n_slots, step, \
-                    n_kv_heads, miss_pages, miss_slots, n_miss, slot_source, order_out, n_evictable_out, status, smem, s
+                    n_kv_heads, miss_pages, miss_slots, n_miss, slot_source, order_out, n_evictable_out, split_flip, status, smem, s
     if (n_slots <= 2048 && list_len <= 1024) e = da::launch_lru<2, 1>(DA_LRU_ARGS);
     else if (n_slots <= 4096 && list_len <= 2048) e = da::launch_lru<4, 2>(DA_LRU_ARGS);
     else e = da::launch_lru<8, 8>(DA_LRU_ARGS);

@@ -215,9 +215,7 @@ class DRAMAttention(torch.nn.Module):
         if phase:
             lc = self.lru_cache
             _native.check(lib.da_decode_attention_phased(
-                phase, lc.evict_order.data_ptr(), lc.n_evictable.data_ptr(),
-                lc.evict_order_next.data_ptr() if phase == 2 else 0,
-                lc.n_evictable_next.data_ptr() if phase == 2 else 0,
+                phase, lc.evict_order.data_ptr(), lc.n_evictable.data_ptr(), lc.evict_flip.data_ptr(),
                 xq.data_ptr(), prefix.data_ptr(), prefix.stride(0), lc.num_hbm_pages, self.page_size,
                 lc.dram_kv_cache.data_ptr(), lc.num_dram_pages, lc.slot_source.data_ptr(),
                 self.cache_k.data_ptr(), self.cache_v.data_ptr(), self.cache_k.stride(1),

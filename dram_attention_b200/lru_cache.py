@@ -118,11 +118,11 @@ class LRUCache(torch.nn.Module):
         # Split of the slots used by the two-launch attention: the first n_evictable[h] entries
         # of evict_order[h] are the slots the coming LRU update may evict.  "Everything" is always
         # a valid split; the LRU kernel leaves a tighter one for the following step in *_next.
-        self.register_buffer("evict_order", torch.arange(num_hbm_pages, **i32).repeat(num_kv_heads, 1),
+        self.register_buffer("evict_order", torch.arange(num_hbm_pages, **i32).repeat(2, num_kv_heads, 1),
+                             persistent=False)    # two copies; evict_flip[h] names the current one
+        self.register_buffer("n_evictable", torch.full((2, num_kv_heads), num_hbm_pages, **i32),
                              persistent=False)
-        self.register_buffer("n_evictable", torch.full((num_kv_heads,), num_hbm_pages, **i32), persistent=False)
-        self.register_buffer("evict_order_next", self.evict_order.clone(), persistent=False)
-        self.register_buffer("n_evictable_next", self.n_evictable.clone(), persistent=False)
+        self.register_buffer("evict_flip", torch.zeros(num_kv_heads, **i32), persistent=False)
         self.split_valid = True    # evict_order / n_evictable describe the tables as they are now
         self._miss = {}
         self._last_list_len = None
@@ -143,8 +143,9 @@ class LRUCache(torch.nn.Module):
     def update_tables_(self, page_list: torch.Tensor, want_split: bool = False) -> None:
         """Enqueue the LRU table update for an int32 page list (Hk, list_len): step
         counters, hit stamps, victim choice, both maps, and the device-side miss list.
-        With `want_split` the kernel also leaves, in evict_order_next / n_evictable_next, which
-        slots the following update can evict (the two-launch attention installs it)."""
+        With `want_split` the kernel also leaves, in the copy of evict_order / n_evictable that
+        evict_flip does not name, which slots the following update can evict (the two-launch
+        attention then flips to it)."""
         list_len = page_list.shape[1]
         miss_pages, miss_slots, n_miss = self._miss_buffers(list_len)
         if self._last_list_len != list_len:
@@ -159,15 +160,16 @@ class LRUCache(torch.nn.Module):
             self.page_access_time.data_ptr(), self.num_hbm_pages, self.step_counters.data_ptr(),
             self.num_kv_heads, miss_pages.data_ptr(), miss_slots.data_ptr(), n_miss.data_ptr(),
             self.slot_source.data_ptr(),
-            self.evict_order_next.data_ptr() if want_split else 0,
-            self.n_evictable_next.data_ptr() if want_split else 0,
+            self.evict_order.data_ptr() if want_split else 0,
+            self.n_evictable.data_ptr() if want_split else 0,
+            self.evict_flip.data_ptr() if want_split else 0,
             self.status.data_ptr(), _native.stream_ptr()), "da_lru_update")
         self.split_valid = False   # until the attention's second launch installs the new split
 
     def reset_split_(self) -> None:
         """Make "every slot may be evicted" the current split (always correct)."""
         self.evict_order.copy_(torch.arange(self.num_hbm_pages, dtype=torch.int32,
-                                            device=self.evict_order.device)[None].expand_as(self.evict_order))
+                                            device=self.evict_order.device).expand_as(self.evict_order))
         self.n_evictable.fill_(self.num_hbm_pages)
         self.split_valid = True
 

@@ -136,14 +136,16 @@ DA_API int da_topk_pages(const float *scores, int32_t *page_list,
  *             marks of the previous call using the previous miss list, so when it is used
  *             the array must start at -1, n_miss at 0, and the same miss buffers must be
  *             passed every time.  NULL when da_fetch_pages does the copy.
- * order_out, n_evictable_out  optional (n_kv_heads, n_slots) / (n_kv_heads) int32, both or
- *             neither, for da_decode_attention_phased: on return the first
- *             n_evictable_out[h] entries of order_out[h] are the only slots the NEXT call can
- *             evict, provided its list is not longer than this one; the other slots follow.
- *             (Every list entry either hits, which takes a slot out of the eviction order's
- *             front, or misses, which consumes one, so victims come from the first list_len
- *             slots that this call did not touch; when fewer than list_len slots were left
- *             untouched the count is n_slots.)  Asking for it makes the call always sort.
+ * split_order, split_count, split_flip  optional, all or none, for da_decode_attention_phased:
+ *             split_order is [2][n_kv_heads][n_slots] int32, split_count [2][n_kv_heads],
+ *             split_flip [n_kv_heads].  The call writes copy 1 - split_flip[h] (it never
+ *             touches the copy split_flip[h] names, which the attention of this step is
+ *             using): afterwards the first split_count entries of that copy's split_order[h]
+ *             are the only slots the NEXT call can evict, provided its list is not longer
+ *             than this one; the other slots follow.  (Every list entry either hits, which
+ *             takes a slot out of the eviction order's front, or misses, which consumes one,
+ *             so victims come from the first list_len slots this call did not touch; when
+ *             fewer than list_len slots were left untouched the count is n_slots.)
  * status      (1) int32, bits or-ed in
  * Requires n_slots <= 8192, list_len <= 8192 and the shared-memory plan
  * (3*n_slots + 2*max(n_slots, T) + list_len + 8192 ints, T = power of two >= 2*list_len)
@@ -154,8 +156,8 @@ DA_API int da_lru_update(const int32_t *page_list, int list_len,
                   int32_t *slot_to_dram, int32_t *access_time, int n_slots,
                   int32_t *step, int n_kv_heads,
                   int32_t *miss_pages, int32_t *miss_slots, int32_t *n_miss,
-                  int32_t *slot_source, int32_t *order_out, int32_t *n_evictable_out,
-                  int32_t *status, da_stream_t stream);
+                  int32_t *slot_source, int32_t *split_order, int32_t *split_count,
+                  const int32_t *split_flip, int32_t *status, da_stream_t stream);
 
 /*
  * Miss-page fetch: gather-copy of the pages named by da_lru_update from DRAM into
@@ -265,17 +267,13 @@ DA_API int da_decode_attention_fetch(const void *q,
  *            CTAs that each fill an SM, so 32 SMs stay free for the selection kernels.
  *   phase 2  (after da_lru_update and after phase 1): attends over the evictable slots,
  *            reading freshly assigned ones from DRAM as da_decode_attention_fetch does,
- *            merges the partials of both phases, writes the output, and installs
- *            order_next / n_evictable_next (left by this step's da_lru_update) as the
- *            split for the next step.
+ *            merges the partials of both phases, writes the output, and flips
+ *            split_flip[h], which makes the split this step's da_lru_update wrote current.
  *
- * order, n_evictable   the split both phases of one step use: the first n_evictable[h]
- *            entries of order[h] are the evictable slots.  Before the first step: any
- *            permutation of the slots with n_evictable = n_slots (everything in phase 2),
- *            or the order da_lru_update would leave.  Read in phase 1, read and overwritten
- *            in phase 2.
- * order_next, n_evictable_next   phase 2 only: the order_out / n_evictable_out that this
- *            step's da_lru_update wrote (a different buffer than `order`).
+ * split_order, split_count, split_flip   as for da_lru_update: copy split_flip[h] is the split
+ *            both phases of one step use (first split_count entries of split_order[h] = the
+ *            evictable slots).  Before the first step: both copies any permutation of the slots
+ *            with split_count = n_slots (everything in phase 2), split_flip = 0.
  * workspace  da_decode_attention_phased_workspace_bytes() bytes, shared by both phases.
  * The list handed to da_lru_update must not be longer than in the step before.
  */
@@ -284,8 +282,8 @@ DA_API size_t da_decode_attention_phased_workspace_bytes(int n_kv_heads, int rep
  * per warp in either phase, the phase-1 CTA fits an SM's shared memory), else 0. */
 DA_API int da_decode_attention_phased_supported(int n_kv_heads, int rep, int head_dim, int dtype,
                         int n_slots, int page_size, int local_capacity);
-DA_API int da_decode_attention_phased(int phase, int32_t *order, int32_t *n_evictable,
-                        const int32_t *order_next, const int32_t *n_evictable_next,
+DA_API int da_decode_attention_phased(int phase, const int32_t *split_order, const int32_t *split_count,
+                        int32_t *split_flip,
                         const void *q,
                         void *slots, long long slots_head_stride, int n_slots, int page_size,
                         const void *dram_pages, int n_dram_pages, const int32_t *slot_source,

@@ -180,8 +180,9 @@ class Tables:
         self.g_dram = self.dram.clone().pin_memory()
         self.g_hbm = self.hbm.to(DEV)
         self.g_status = torch.zeros(1, dtype=torch.int32, device=DEV)
-        self.g_order = torch.full((self.hk, self.nh), -5, dtype=torch.int32, device=DEV)
-        self.g_nev = torch.full((self.hk,), -5, dtype=torch.int32, device=DEV)
+        self.g_order = torch.full((2, self.hk, self.nh), -5, dtype=torch.int32, device=DEV)
+        self.g_nev = torch.full((2, self.hk), -5, dtype=torch.int32, device=DEV)
+        self.g_flip = torch.zeros(self.hk, dtype=torch.int32, device=DEV)   # copy 1 gets written
         self.prev_split = None
         return self
 
@@ -197,7 +198,7 @@ class Tables:
                                         self.g_h2d.data_ptr(), self.g_time.data_ptr(), self.nh,
                                         self.g_step.data_ptr(), self.hk, mp.data_ptr(), ms.data_ptr(),
                                         nm.data_ptr(), 0, self.g_order.data_ptr(), self.g_nev.data_ptr(),
-                                        self.g_status.data_ptr(), s))
+                                        self.g_flip.data_ptr(), self.g_status.data_ptr(), s))
         page_bytes = self.dram.shape[2] * self.dram.element_size()
         _native.check(lib.da_fetch_pages(self.g_dram.data_ptr(), self.g_hbm.data_ptr(), mp.data_ptr(),
                                          ms.data_ptr(), nm.data_ptr(), kk, self.hk, self.ld, self.nh,
@@ -209,7 +210,8 @@ class Tables:
             order, nev, _ = self.prev_split
             for h in range(self.hk):
                 assert set(ms[h, :nm[h]].tolist()) <= set(order[h, :nev[h]].tolist()), h
-        order, nev = self.g_order.cpu().numpy(), self.g_nev.cpu().numpy()
+        order, nev = self.g_order[1].cpu().numpy(), self.g_nev[1].cpu().numpy()
+        assert int(self.g_order[0].max()) == -5 and int(self.g_nev[0].max()) == -5   # current copy untouched
         if not (int(self.g_status) & 2):
             for h in range(self.hk):
                 assert sorted(order[h].tolist()) == list(range(self.nh)), h
