@@ -149,6 +149,7 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 2 : 1) decode_attenti
 #pragma unroll
     for (int d = 0; d < NT; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
 
+    const uint64_t stream_policy = l2_policy_evict_first();   // the KV stream is read once per step
     // The warp visits its units in the order perm[0], perm[1], ...: DRAM-sourced units first.
     int perm[2] = {0, 0};
     const bool planned = p.slot_source != nullptr;   // then the host guarantees n_my <= 64
@@ -195,7 +196,7 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 2 : 1) decode_attenti
                             ? p.prefix + ((size_t)h * p.prefix_head_stride + tok * 2 * D) * E
                             : p.dram + ((size_t)h * p.dram_head_stride +
                                         ((size_t)src_page * p.page_tokens + tok % p.page_tokens) * 2 * D) * E;
-                    bulk_copy_g2s(dst + tl * PITCH, src, 2 * ROWB, bar);
+                    bulk_copy_g2s_hint(dst + tl * PITCH, src, 2 * ROWB, bar, stream_policy);
                 }
             } else {
                 const int t = (u - units_prefix) * kUnitTokens + tl;
@@ -206,7 +207,7 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 2 : 1) decode_attenti
                     src = (is_v ? p.local_v : p.local_k) +
                           ((size_t)t * p.local_tok_stride + (size_t)h * p.local_head_stride) * E;
                 }
-                bulk_copy_g2s(dst + tl * PITCH + is_v * ROWB, src, ROWB, bar);
+                bulk_copy_g2s_hint(dst + tl * PITCH + is_v * ROWB, src, ROWB, bar, stream_policy);
             }
         }
     };

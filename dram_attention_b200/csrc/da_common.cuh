@@ -149,4 +149,23 @@ __device__ __forceinline__ void bulk_copy_g2s(void *dst_smem, const void *src_gm
         : "memory");
 }
 
+
+// Same, with an L2 eviction-priority hint for the lines it brings in.  Streaming reads that
+// nobody will touch again soon should be marked evict-first so that they do not push small,
+// latency-critical data (scores, tables) of concurrently running kernels out of L2.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+
+__device__ __forceinline__ void bulk_copy_g2s_hint(void *dst_smem, const void *src_gmem, uint32_t bytes,
+                                                   uint64_t *bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+            smem_addr(dst_smem)),
+        "l"(src_gmem), "r"(bytes), "r"(smem_addr(bar)), "l"(policy)
+        : "memory");
+}
+
 }  // namespace da
