@@ -54,6 +54,7 @@ def parse_args():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--dram-tokens", type=int, default=131072, help="prefix tokens kept in DRAM")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the scorer / top-k sweep over page counts")
     ap.add_argument("--profile-steps", type=int, default=16, help="un-captured steps timed stage by stage")
     return ap.parse_args()
 
@@ -126,6 +127,21 @@ class ClockSampler:
                 "sm_max_mhz": self.max_mhz,
                 "reasons": [n for b, n in names.items() if bits & b],
                 "samples_in_timed_regions": len(inside), "samples": len(self.samples)}
+
+
+def upload_graph(graph, torch):
+    """Places the instantiated graph on the device before it is timed (otherwise its first
+    launch pays a one-time set-up of several microseconds per captured step).  Returns False
+    when the handle or the binding is not available; the caller then parks the GPU behind a
+    spin while the host launches instead."""
+    try:
+        from cuda.bindings import runtime as rt
+        exec_handle = rt.cudaGraphExec_t(int(graph.raw_cuda_graph_exec()))
+        (err,) = rt.cudaGraphUpload(exec_handle, torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        return int(err) == 0
+    except Exception:
+        return False
 
 
 def hbm_peak_gbs():
@@ -210,7 +226,7 @@ def run_b200(args):
 
     K, W = args.steps, max(args.warmup, 3)
     P = max(0, args.profile_steps)
-    total = (W + K) * 2 + 2 * P
+    total = (W + K) * 2 + 2 * P + K + 4
     w = llama_layer_workload(seed=0, steps=total, dram_tokens=args.dram_tokens, max_out=total)
     hk_all, rep, D = w.n_kv_heads, w.n_q_heads // w.n_kv_heads, w.head_dim
     lo, hi = head_range(hk_all, rank, world)
@@ -251,34 +267,41 @@ def run_b200(args):
         op(dq[step], dk[step], dv[step], start_pos=S + step, stage="generate")
         step += 1
     torch.cuda.synchronize()
-    outs = torch.empty(K, 1, 1, w.n_q_heads, D, dtype=w.dtype, device=dev)
+    # every call returns a tensor of its own (inside a capture: of the graph's memory pool), so the K
+    # outputs are kept by reference and no copy kernel sits between two steps
+    outs = []
     graph = torch.cuda.CUDAGraph()
     captured = True
     first = step
     try:
         with torch.cuda.graph(graph):
             for i in range(K):
-                outs[i].copy_(op(dq[first + i], dk[first + i], dv[first + i], start_pos=S + first + i,
-                                 stage="generate"))
+                outs.append(op(dq[first + i], dk[first + i], dv[first + i], start_pos=S + first + i,
+                               stage="generate"))
     except Exception as e:  # e.g. a collective that cannot be captured: time eager launches instead
         captured = False
         capture_error = repr(e)
         torch.cuda.synchronize()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # The graph can be timed only once (a second replay of the same steps finds its pages resident),
+    # so its one-time device set-up is done before the timed region.
+    uploaded = captured and upload_graph(graph, torch)
     barrier()
     t_a = time.perf_counter()
+    if captured and not uploaded:
+        torch.cuda._sleep(20_000_000)
     ev0.record()
     if captured:
         graph.replay()
     else:
-        for i in range(K):
-            outs[i].copy_(op(dq[first + i], dk[first + i], dv[first + i], start_pos=S + first + i,
-                             stage="generate"))
+        outs = [op(dq[first + i], dk[first + i], dv[first + i], start_pos=S + first + i, stage="generate")
+                for i in range(K)]
     ev1.record()
     barrier()
     windows.append((t_a, time.perf_counter()))
     step += K
     ms_value = ev0.elapsed_time(ev1)
+    assert len(outs) == K and all(bool(torch.isfinite(o.float()).all()) for o in outs), "a timed step left no output"
 
     # ---------------- e2e: host inputs, one captured step per call ----------------------
     # q, k and v of a step sit back to back in one pinned buffer and cross the link in one copy
@@ -288,7 +311,6 @@ def run_b200(args):
     xq_s = d_in[:nq].view(dq[0].shape)
     xk_s = d_in[nq:nq + nk].view(dk[0].shape)
     xv_s = d_in[nq + nk:].view(dv[0].shape)
-    out_s = torch.empty(1, 1, w.n_q_heads, D, dtype=w.dtype, device=dev)
     out_h = torch.empty(1, 1, w.n_q_heads, D, dtype=w.dtype).pin_memory()
     pos = torch.tensor([S + step], dtype=torch.int32, device=dev)
     # The captured step includes the two copies across the host link: q|k|v from a fixed pinned
@@ -300,9 +322,8 @@ def run_b200(args):
     try:
         with torch.cuda.graph(step_graph):
             d_in.copy_(h_stage, non_blocking=True)
-            out_s.copy_(op(xq_s, xk_s, xv_s, start_pos=pos, stage="generate"))
+            out_h.copy_(op(xq_s, xk_s, xv_s, start_pos=pos, stage="generate"), non_blocking=True)
             pos.add_(1)
-            out_h.copy_(out_s, non_blocking=True)
     except Exception:
         step_captured = False
         torch.cuda.synchronize()
@@ -313,9 +334,8 @@ def run_b200(args):
             step_graph.replay()
         else:
             d_in.copy_(h_in[i], non_blocking=True)
-            out_s.copy_(op(xq_s, xk_s, xv_s, start_pos=pos, stage="generate"))
+            out_h.copy_(op(xq_s, xk_s, xv_s, start_pos=pos, stage="generate"), non_blocking=True)
             pos.add_(1)
-            out_h.copy_(out_s, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     for _ in range(W):
@@ -461,6 +481,100 @@ def run_b200(args):
         kernel_us["score"] = launch_us(lambda: lc.top_k_selector.score_(qf, k_pages))
         windows.append((t_a, time.perf_counter()))
         inner.check_status()
+
+    # ---------------- miss fetch: what it costs in a steady step, and a cold step against the host link ----
+    fetch_report = None
+    if world == 1 and P and captured:
+        t_a = time.perf_counter()
+        page_bytes = w.page_size * 2 * D * esz
+        # (1) the same K-step graph with ONE query repeated: after the first step nothing misses,
+        #     so the difference to `value` is the time the fetch leaves exposed.
+        g0 = torch.cuda.CUDAGraph()
+        first0 = step
+        with torch.cuda.graph(g0):
+            outs0 = [op(dq[first0], dk[first0 + i], dv[first0 + i], start_pos=S + first0 + i, stage="generate")
+                     for i in range(K)]
+        g0.replay()                      # brings the repeated query's pages in; also sets the graph up
+        torch.cuda.synchronize()
+        ev0.record()
+        g0.replay()
+        ev1.record()
+        torch.cuda.synchronize()
+        ms_nomiss = ev0.elapsed_time(ev1)
+        step += K
+        # (2) one step whose query is re-drawn from N(0,1): most of its pages are not resident
+        gq = torch.Generator().manual_seed(1)
+        q_cold = torch.randn(1, 1, hk * rep, D, generator=gq).to(w.dtype).to(dev)
+        torch.cuda.synchronize()
+        torch.cuda._sleep(20_000_000)    # the step is queued before the GPU starts it
+        ev0.record()
+        op(q_cold, dk[step], dv[step], start_pos=S + step, stage="generate")
+        ev1.record()
+        torch.cuda.synchronize()
+        cold_us = ev0.elapsed_time(ev1) * 1e3
+        cold_misses = int(lc.last_miss_counts(list_len).sum())
+        step += 1
+        inner.check_status()
+        # (3) the host link itself: one pinned-host -> device copy of 64 MiB
+        hbuf = torch.zeros(64 << 20, dtype=torch.uint8).pin_memory()
+        dbuf = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
+        link = []
+        for _ in range(6):
+            torch.cuda.synchronize()
+            ev0.record()
+            dbuf.copy_(hbuf, non_blocking=True)
+            ev1.record()
+            torch.cuda.synchronize()
+            link.append((64 << 20) / (ev0.elapsed_time(ev1) * 1e-3) / 1e9)
+        link_gbs = max(link[1:])
+        steady_us = ms_value / K * 1e3
+        fetch_us = max(cold_us - steady_us, 1e-3)
+        fetch_report = {
+            "steady_misses_per_step": (sum(misses) / len(misses)) if misses else None,
+            "steady_bytes_per_step": (sum(misses) / len(misses) * page_bytes) if misses else None,
+            "step_us_without_misses": ms_nomiss / K * 1e3,
+            "exposed_fraction_of_step": max(0.0, 1.0 - ms_nomiss / ms_value),
+            "cold_step": {"query": "re-drawn from N(0,1)", "misses": cold_misses,
+                          "bytes": cold_misses * page_bytes, "step_us": cold_us,
+                          "fetch_gbs": cold_misses * page_bytes / (fetch_us * 1e-6) / 1e9,
+                          "host_link_gbs": link_gbs,
+                          "frac_of_host_link": cold_misses * page_bytes / (fetch_us * 1e-6) / 1e9 / link_gbs,
+                          "host_link_peak": "best of 5 pinned host -> device copies of 64 MiB on this box "
+                                            "(PCIe Gen5 x16: 63 GB/s nominal)"},
+        }
+        windows.append((t_a, time.perf_counter()))
+
+    # ---------------- page scorer + top-k over a sweep of page counts (8 KV heads, GQA 4, bf16) -----------
+    sweep = None
+    if world == 1 and P and not args.no_sweep:
+        from dram_attention_b200.topk_selector import IPUpperboundTopKSelector
+        t_a = time.perf_counter()
+        peak_now, _ = hbm_peak_gbs()
+        gs = torch.Generator(device=dev).manual_seed(0)
+        s_hk, s_rep, s_pg, l_max = 8, 4, 16, 65536
+        mm = torch.empty(s_hk, l_max, 2, D, dtype=torch.bfloat16, device=dev)
+        for h in range(s_hk):
+            keys = torch.randn(l_max, s_pg, D, generator=gs, device=dev).to(torch.bfloat16)
+            mn, mx = torch.aminmax(keys, dim=1)
+            mm[h, :, 0], mm[h, :, 1] = mn, mx
+            del keys
+        q_s = torch.randn(1, 1, s_hk * s_rep, D, generator=gs, device=dev).to(torch.bfloat16)
+        sweep = []
+        for n_pages in (512, 2048, 8192, 32768, 65536):
+            shape_only = torch.empty(s_hk, n_pages * s_pg, D, dtype=torch.bfloat16, device="meta")
+            sel = IPUpperboundTopKSelector(shape_only, n_pages, device=dev, _summaries=mm[:, :n_pages].contiguous())
+            kk_pages = min(256, n_pages)
+            sel.score_(q_s, kk_pages)
+            sel.select_(1, s_rep, kk_pages)
+            t_score = launch_us(lambda: sel.score_(q_s, kk_pages))
+            t_topk = launch_us(lambda: sel.select_(1, s_rep, kk_pages))
+            nbytes = s_hk * n_pages * 2 * D * 2 + s_hk * s_rep * D * 2
+            sweep.append({"pages": n_pages, "score_us": t_score, "score_gbs": nbytes / (t_score * 1e-6) / 1e9,
+                          "score_frac_of_peak": nbytes / (t_score * 1e-6) / 1e9 / peak_now,
+                          "topk_us": t_topk, "k": kk_pages})
+            del sel
+        del mm
+        windows.append((t_a, time.perf_counter()))
     sampler.stop()
 
     # ---------------- reduce over ranks -------------------------------------------------
@@ -503,7 +617,9 @@ def run_b200(args):
             "config": dict(workload_config(args, w),
                            parallelism=("single GPU" if world == 1 else f"KV heads sharded {world}-way, "
                                         "NCCL all-gather of per-head outputs"),
-                           timed_region=("one CUDA graph of K steps" if captured else
+                           timed_region=("one CUDA graph of K steps, " +
+                                         ("uploaded to the device" if uploaded else "launched behind a spin kernel") +
+                                         " before the first event" if captured else
                                          "K eager steps (graph capture failed: " + capture_error + ")")),
             "clocks": sampler.summary(windows),
             "e2e": {"value": K / (ms_e2e * 1e-3), "unit": "tok/s",
@@ -521,6 +637,8 @@ def run_b200(args):
                                                 "score -> top-k -> LRU -> fetch -> attention")),
             "misses_per_step": mean(misses),
             "fetch": ("inside the attention kernel" if fused else "separate gather-copy launch"),
+            "fetch_report": fetch_report,
+            "scorer_sweep": sweep,
             "fetch_fraction_of_step": (stage_us["fetch"] / sum(v for v in stage_us.values() if v)
                                        if stage_us["fetch"] else None),
         }

@@ -48,7 +48,6 @@ class KVHeadShardedDRAMAttention(torch.nn.Module):
         if operator_factory is None:
             from .dram_attention import DRAMAttention as operator_factory
         self.inner = operator_factory(n_kv_heads=self.hi - self.lo, **ctor_kwargs)
-        self._gather = {}
 
     def _kv(self, t: torch.Tensor) -> torch.Tensor:
         return t if self.presliced else t[:, :, self.lo:self.hi]
@@ -73,11 +72,9 @@ class KVHeadShardedDRAMAttention(torch.nn.Module):
             return local
         b, s, h, d = local.shape
         if s == 1:
-            key = (h, d, local.dtype, local.device)
-            out = self._gather.get(key)
-            if out is None:
-                out = self._gather[key] = torch.empty(b, 1, h * self.world_size, d, dtype=local.dtype,
-                                                      device=local.device)
+            # rank-major concatenation is the head order; a tensor of its own per call, like the
+            # single-GPU operator's result
+            out = torch.empty(b, 1, h * self.world_size, d, dtype=local.dtype, device=local.device)
             dist.all_gather_into_tensor(out.view(-1), local.contiguous().view(-1), group=self.group)
             return out
         # several tokens: gather (G, s, h, d) then put the rank axis next to the heads

@@ -270,48 +270,88 @@ def test_invalid_stage_and_batch(op):
 
 # ---- full-size properties (sizes of the Llama-3-8B layer at 128K context) --------
 
+def _check_layer_invariants(da, w, steps, modules=None):
+    """Steps one operator (or several independent ones, round-robin) over the workload(s)
+    and checks after every step: maps inverse of each other, listed pages resident and
+    stamped with the step, every row of the page list sorted by (score desc, id asc) and
+    holding the k best, slot payload == DRAM page named by the map; after the last step
+    the exact attention over the GPU's own slot table.  Returns the outputs per module."""
+    ws = w if isinstance(w, list) else [w]
+    ms = modules or []
+    if not ms:
+        for wi in ws:
+            m = da.DRAMAttention(device=DEV, dtype=torch.bfloat16, **wi.ctor_kwargs())
+            m.init_cache(wi.k.to(DEV), wi.v.to(DEV))
+            ms.append(m)
+    lists = [_spy_lists(m) for m in ms]
+    outs = [[] for _ in ms]
+    for i in range(steps):
+        for wi, m, lst_log, out_log in zip(ws, ms, lists, outs):
+            lc = m.lru_cache
+            hk, rep = wi.n_kv_heads, wi.n_q_heads // wi.n_kv_heads
+            s = wi.k.shape[1]
+            k_pages = wi.top_k // wi.page_size
+            out = m(wi.xq[i].to(DEV), wi.xk[i].to(DEV), wi.xv[i].to(DEV), start_pos=s + i, stage="generate")
+            assert torch.isfinite(out.float()).all()
+            out_log.append(out.clone())
+            scores = lc.top_k_selector._buffers[(1, rep, k_pages)][0][0].cpu()      # (Hq, L)
+            lst = lst_log[i].cpu().long()                                             # (Hk, rep*k)
+            d2h = lc.dram_page_to_hbm_page_mapping.cpu().long()
+            h2d = lc.hbm_page_to_dram_page_mapping.cpu().long()
+            tim = lc.page_access_time.cpu()
+            hbm = lc.hbm_kv_cache.cpu()
+            for h in range(hk):
+                assert torch.equal(d2h[h, h2d[h]], torch.arange(lc.num_hbm_pages))
+                assert int((d2h[h] >= 0).sum()) == lc.num_hbm_pages
+                assert bool((d2h[h, lst[h]] >= 0).all())
+                assert bool((tim[h, d2h[h, lst[h]]] == i + 1).all())
+                for r in range(rep):
+                    row = lst[h, r * k_pages:(r + 1) * k_pages]
+                    sc = scores[h * rep + r, row]
+                    assert bool(((sc[:-1] > sc[1:]) | ((sc[:-1] == sc[1:]) & (row[:-1] < row[1:]))).all())
+                    kth = sc[-1]
+                    assert int((scores[h * rep + r] > kth).sum()) <= k_pages - 1
+                # payloads (checksum of checksums over all slots)
+                assert torch.equal(hbm[h], lc.dram_kv_cache[h, h2d[h]])
+            m.check_status()
+    # the exact oracle on the last step's state: attention over the GPU's own slot table
+    for wi, m, out_log in zip(ws, ms, outs):
+        lc = m.lru_cache
+        hk, d = wi.n_kv_heads, wi.head_dim
+        s = wi.k.shape[1]
+        q = wi.xq[steps - 1, 0, 0].float()
+        kv = lc.hbm_kv_cache.cpu().float().view(hk, -1, 2, d)
+        po, pl = orc.attend(q, kv[:, :, 0].transpose(0, 1), kv[:, :, 1].transpose(0, 1))
+        t = s + steps - 1 - m.dram_kv_cache_size
+        so, sl = orc.attend(q, m.cache_k[0, :t + 1].cpu().float(), m.cache_v[0, :t + 1].cpu().float())
+        want = orc.combine(po, so, pl, sl)
+        assert_out_close(out_log[-1][0, 0].float().cpu(), want, torch.bfloat16)
+    return outs
+
+
 def test_full_size_layer_invariants(da, fused):
     """At the benchmark's size the oracle is too slow to follow every step, so check
-    properties: slot payload == DRAM page named by the map, maps inverse of each
-    other, listed pages resident and stamped with the step, every row of the page
-    list sorted by (score desc, id asc), needle pages selected."""
+    properties (see _check_layer_invariants)."""
+    _check_layer_invariants(da, llama_layer_workload(seed=0, steps=4), 4)
+
+
+def test_batched_sequences_are_independent(da):
+    """Batched decode = one operator per sequence (the reference asserts batch 1,
+    dram_attention/dram_attention.py:133): three 64K-token sequences stepped round-robin,
+    with a query re-draw that churns the slots, keep every invariant, and a sequence
+    stepped between the others gives bit-identical outputs to the same sequence alone."""
     steps = 4
-    w = llama_layer_workload(seed=0, steps=steps)
-    m = da.DRAMAttention(device=DEV, dtype=torch.bfloat16, **w.ctor_kwargs())
-    m.init_cache(w.k.to(DEV), w.v.to(DEV))
-    lc = m.lru_cache
-    lists = _spy_lists(m)
-    s = w.k.shape[1]
-    k_pages = w.top_k // w.page_size
-    for i in range(steps):
-        out = m(w.xq[i].to(DEV), w.xk[i].to(DEV), w.xv[i].to(DEV), start_pos=s + i, stage="generate")
-        assert torch.isfinite(out.float()).all()
-        scores = lc.top_k_selector._buffers[(1, 4, k_pages)][0][0].cpu()      # (Hq, L)
-        lst = lists[i].cpu().long()                                             # (Hk, 4*k)
-        d2h = lc.dram_page_to_hbm_page_mapping.cpu().long()
-        h2d = lc.hbm_page_to_dram_page_mapping.cpu().long()
-        tim = lc.page_access_time.cpu()
-        for h in range(8):
-            assert torch.equal(d2h[h, h2d[h]], torch.arange(lc.num_hbm_pages))
-            assert int((d2h[h] >= 0).sum()) == lc.num_hbm_pages
-            assert bool((d2h[h, lst[h]] >= 0).all())
-            assert bool((tim[h, d2h[h, lst[h]]] == i + 1).all())
-            for r in range(4):
-                row = lst[h, r * k_pages:(r + 1) * k_pages]
-                sc = scores[h * 4 + r, row]
-                assert bool(((sc[:-1] > sc[1:]) | ((sc[:-1] == sc[1:]) & (row[:-1] < row[1:]))).all())
-                kth = sc[-1]
-                assert int((scores[h * 4 + r] > kth).sum()) <= k_pages - 1
-        # payloads (checksum of checksums over all slots)
-        hbm = lc.hbm_kv_cache.cpu()
-        for h in range(8):
-            assert torch.equal(hbm[h], lc.dram_kv_cache[h, h2d[h]])
-    m.check_status()
-    # the exact oracle on the last step's state: attention over the GPU's own slot table
-    q = w.xq[steps - 1, 0, 0].float()
-    kv = lc.hbm_kv_cache.cpu().float().view(8, -1, 2, 128)
-    po, pl = orc.attend(q, kv[:, :, 0].transpose(0, 1), kv[:, :, 1].transpose(0, 1))
-    t = s + steps - 1 - m.dram_kv_cache_size
-    so, sl = orc.attend(q, m.cache_k[0, :t + 1].cpu().float(), m.cache_v[0, :t + 1].cpu().float())
-    want = orc.combine(po, so, pl, sl)
-    assert_out_close(out[0, 0].float().cpu(), want, torch.bfloat16)
+    ws = [llama_layer_workload(seed=sd, steps=steps, dram_tokens=65536, needles=0, redraw_every=2)
+          for sd in (0, 1, 2)]
+    together = _check_layer_invariants(da, ws, steps)
+    alone = _check_layer_invariants(da, ws[1], steps)
+    for a, b in zip(together[1], alone[0]):
+        assert torch.equal(a, b)
+
+
+def test_million_token_layer_shard(da):
+    """One GPU's share (2 of 8 KV heads, 4-way sharding) of a layer with a 1,048,576-token
+    prefix: 65,536 pages per head, 4,096 slots, 512 pages per query head."""
+    w = llama_layer_workload(seed=0, steps=2, dram_tokens=1048576, n_kv_heads=2, lru=65536, local=8192,
+                             top_k=8192, needles=32)
+    _check_layer_invariants(da, w, 2)
