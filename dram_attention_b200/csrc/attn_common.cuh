@@ -160,14 +160,14 @@ template <int D> struct PartialRow { static constexpr int kWidth = D + 4; };
 // partial row = acc[D] (already weighted to the row's max), max, l.  `scratch` holds
 // at least 2 * splits * REP floats of shared memory (the idle stage buffers).  Loads bypass L1 (the rows were
 // written by other SMs).  The first batch of accumulator rows is requested together
-// with the (max, l) pairs; up to 26 rows make a batch.  With `partial_out` the result is
+// with the (max, l) pairs; up to 52 rows make a batch (the accumulators of the main loop are dead by then).  With `partial_out` the result is
 // written as one more partial row instead of the output (phase 1 folds its rows this way).
 template <typename T, int D, int REP, int THREADS>
 __device__ __forceinline__ void merge_splits(const AttnParams &p, int h, int first_row, int splits, float *scratch,
                                              float *partial_out) {
     constexpr int PW = PartialRow<D>::kWidth;
     constexpr int VPR = D / 4;          // float4 per accumulator row
-    constexpr int BATCH = 26;
+    constexpr int BATCH = 52;
     constexpr float NEG_INF = -INFINITY;
     __shared__ float sh_m[REP], sh_l[REP];
     const int tid = threadIdx.x;
