@@ -19,10 +19,13 @@ roofline  attention kernel (the dominant launch): algorithmic bytes / its mean
 cpu_baseline  the CPU oracle (a port of the reference's pure-PyTorch path) timed on
         a bounded sample of the same workload on this box's host cores.
 
-With --gpus N > 1 (launched by torchrun, one rank per GPU) the KV heads are
-sharded over the ranks and the per-head outputs are all-gathered over NCCL
-(total work fixed: strong scaling).  --impl reference times the CPU port of the
-reference path on rank 0 only.
+With --gpus N > 1 (launched by torchrun, one rank per GPU) every GPU decodes a sequence
+of its own (same layer shape, its own seed): no collective on the path, weak scaling,
+value = N sequences' tokens / max-over-ranks time.  The same run also times ONE sequence
+with its KV heads sharded over the ranks ("kv_head_sharded"; per-head outputs all-gathered
+by a peer-memory kernel over NVLink, or by the process group's all-gather where symmetric
+memory is not available); --shard kv-heads makes that the headline instead (strong
+scaling).  --impl reference times the CPU port of the reference path on rank 0 only.
 """
 
 from __future__ import annotations
@@ -54,6 +57,12 @@ def parse_args():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--dram-tokens", type=int, default=131072, help="prefix tokens kept in DRAM")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--shard", default="sequence", choices=["sequence", "kv-heads"],
+                    help="N > 1: one independent sequence per GPU, no collective (weak scaling, default; the "
+                         "KV-head-sharded step is timed as well and reported beside it), or only the KV heads "
+                         "of ONE sequence sharded over the GPUs (strong scaling)")
+    ap.add_argument("--library-gather", action="store_true",
+                    help="N > 1: all-gather through the process group instead of the peer-memory kernel")
     ap.add_argument("--no-sweep", action="store_true", help="skip the scorer / top-k sweep over page counts")
     ap.add_argument("--profile-steps", type=int, default=16, help="un-captured steps timed stage by stage")
     return ap.parse_args()
@@ -191,7 +200,7 @@ def run_reference(args):
     line = {
         "impl": "reference", "metric": METRIC, "value": tps, "unit": "tok/s", "n_gpus": args.gpus,
         "steps": done, "warmup": wu, "ms_per_step": 1e3 / tps, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(args, w),
         "cpu_baseline": {"value": tps, "unit": "tok/s", "cores": threads, "kind": "port",
                          "sample": f"{done} full generate steps of the same layer after {wu} warm-up steps, "
@@ -199,7 +208,7 @@ def run_reference(args):
         "e2e": {"value": tps, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    print(json.dumps(line), file=RESULT_OUT, flush=True)
 
 
 # --------------------------------------------------------------------------------
@@ -222,24 +231,29 @@ def run_b200(args):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # stdout carries the JSON line only
         dist.init_process_group("nccl", device_id=dev)
 
     K, W = args.steps, max(args.warmup, 3)
     P = max(0, args.profile_steps)
     total = (W + K) * 2 + 2 * P + K + 4
-    w = llama_layer_workload(seed=0, steps=total, dram_tokens=args.dram_tokens, max_out=total)
+    # N > 1, default: every GPU decodes its own sequence (same shapes, its own seed); no collective
+    by_seq = world > 1 and args.shard == "sequence"
+    n_seq = world if by_seq else 1
+    w = llama_layer_workload(seed=(rank if by_seq else 0), steps=total, dram_tokens=args.dram_tokens, max_out=total)
     hk_all, rep, D = w.n_kv_heads, w.n_q_heads // w.n_kv_heads, w.head_dim
-    lo, hi = head_range(hk_all, rank, world)
+    lo, hi = (0, hk_all) if by_seq else head_range(hk_all, rank, world)
     hk = hi - lo
     esz = 2
 
     ctor = w.ctor_kwargs()
     ctor.pop("n_kv_heads")
-    if world == 1:
+    if world == 1 or by_seq:
         op = da.DRAMAttention(n_kv_heads=hk_all, device=dev, dtype=w.dtype, **ctor)
         inner = op
     else:
-        op = KVHeadShardedDRAMAttention(n_kv_heads=hk_all, presliced=True, device=dev, dtype=w.dtype, **ctor)
+        op = KVHeadShardedDRAMAttention(n_kv_heads=hk_all, presliced=True, device=dev, dtype=w.dtype,
+                                        peer_gather=not args.library_gather, **ctor)
         inner = op.inner
     inner.init_cache(w.k[:, :, lo:hi].to(dev), w.v[:, :, lo:hi].to(dev))
     lc = inner.lru_cache
@@ -575,7 +589,51 @@ def run_b200(args):
             del sel
         del mm
         windows.append((t_a, time.perf_counter()))
+    # ---------------- N > 1, by sequence: the KV-head-sharded step of ONE sequence, timed beside it -------
+    sharded_report = None
+    if by_seq:
+        t_a = time.perf_counter()
+        n_sh = W + K + 2
+        w0 = w if rank == 0 else llama_layer_workload(seed=0, steps=n_sh, dram_tokens=args.dram_tokens,
+                                                      max_out=n_sh)
+        lo0, hi0 = head_range(hk_all, rank, world)
+        sh = KVHeadShardedDRAMAttention(n_kv_heads=hk_all, presliced=True, device=dev, dtype=w.dtype,
+                                        peer_gather=not args.library_gather,
+                                        **dict(ctor, max_output_length=max(ctor["max_output_length"], n_sh)))
+        sh.inner.init_cache(w0.k[:, :, lo0:hi0].to(dev), w0.v[:, :, lo0:hi0].to(dev))
+        sq = w0.xq[:n_sh, :, :, lo0 * rep:hi0 * rep].contiguous().to(dev)
+        sk = w0.xk[:n_sh, :, :, lo0:hi0].contiguous().to(dev)
+        sv = w0.xv[:n_sh, :, :, lo0:hi0].contiguous().to(dev)
+        S0 = w0.prefill_len
+        for i in range(W):
+            sh(sq[i], sk[i], sv[i], start_pos=S0 + i, stage="generate")
+        torch.cuda.synchronize()
+        g_sh = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g_sh):
+            outs_sh = [sh(sq[W + i], sk[W + i], sv[W + i], start_pos=S0 + W + i, stage="generate")
+                       for i in range(K)]
+        up = upload_graph(g_sh, torch)
+        barrier()
+        if not up:
+            torch.cuda._sleep(20_000_000)
+        ev0.record()
+        g_sh.replay()
+        ev1.record()
+        barrier()
+        sh.check_status()
+        ms_sh = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device=dev)
+        dist.all_reduce(ms_sh, op=dist.ReduceOp.MAX)
+        ms_sh = float(ms_sh[0])
+        sharded_report = {
+            "what": f"ONE sequence, its {hk_all} KV heads sharded {world}-way, K steps in one graph per rank, max over ranks",
+            "value": K / (ms_sh * 1e-3), "unit": "tok/s", "ms_per_step": ms_sh / K, "scaling": "strong",
+            "gather": ("peer stores over NVLink (da_gather_heads)" if sh._peer is not None
+                       else "NCCL all_gather_into_tensor"),
+        }
+        windows.append((t_a, time.perf_counter()))
     sampler.stop()
+    if world > 1:
+        op.check_status()     # includes the gather kernel's bounded waits
 
     # ---------------- reduce over ranks -------------------------------------------------
     t = torch.tensor([ms_value, ms_e2e], dtype=torch.float64, device=dev)
@@ -611,23 +669,30 @@ def run_b200(args):
 
     if rank == 0:
         line = {
-            "metric": METRIC, "value": K / (ms_value * 1e-3), "unit": "tok/s", "n_gpus": world,
+            "metric": METRIC, "value": n_seq * K / (ms_value * 1e-3), "unit": "tok/s", "n_gpus": world,
             "steps": K, "warmup": W, "ms_per_step": ms_value / K, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": dict(workload_config(args, w),
-                           parallelism=("single GPU" if world == 1 else f"KV heads sharded {world}-way, "
-                                        "NCCL all-gather of per-head outputs"),
+            "scaling": ("weak" if (world == 1 or by_seq) else "strong"), "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": dict(workload_config(args, w), batch=n_seq,
+                           parallelism=("single GPU" if world == 1 else
+                                        f"{world} independent sequences, one per GPU, no collective on the path"
+                                        if by_seq else f"KV heads sharded {world}-way, " +
+                                        ("all-gather of per-head outputs by peer stores over NVLink (da_gather_heads)"
+                                         if getattr(op, "_peer", None) is not None else
+                                         "NCCL all-gather of per-head outputs")),
                            timed_region=("one CUDA graph of K steps, " +
                                          ("uploaded to the device" if uploaded else "launched behind a spin kernel") +
                                          " before the first event" if captured else
                                          "K eager steps (graph capture failed: " + capture_error + ")")),
             "clocks": sampler.summary(windows),
-            "e2e": {"value": K / (ms_e2e * 1e-3), "unit": "tok/s",
-                    "h2d_bytes_per_step": (hq[0].numel() + hkk[0].numel() + hv[0].numel()) * esz,
-                    "d2h_bytes_per_step": out_h.numel() * esz, "ms_per_step": ms_e2e / K,
+            "e2e": {"value": n_seq * K / (ms_e2e * 1e-3), "unit": "tok/s",
+                    "h2d_bytes_per_step": (hq[0].numel() + hkk[0].numel() + hv[0].numel()) * esz * world,
+                    "d2h_bytes_per_step": out_h.numel() * esz * world, "ms_per_step": ms_e2e / K,
                     "per_step": "host writes q|k|v into a pinned staging buffer; one graph replay = H2D copy, the step, "
                                 "D2H copy of the output; stream sync"},
-            "gpu_launches": (5 if (overlapped or not fused) else 4) * K,
+            "gpu_launches": ((5 if (overlapped or not fused) else 4) + (1 if (world > 1 and not by_seq) else 0))
+                            * K * world,
+            "kv_head_sharded": sharded_report,
             "roofline": roofline,
             "roofline_score": roofline_score,
             "stage_us_with_event_overhead": stage_us,
@@ -648,7 +713,7 @@ def run_b200(args):
                 "value": tps, "unit": "tok/s", "cores": threads, "kind": "port",
                 "sample": f"{done} full generate steps of the same layer (1 warm-up) on the host cores: "
                           "CPU port of the reference's pure-PyTorch path"}
-        print(json.dumps(line), flush=True)
+        print(json.dumps(line), file=RESULT_OUT, flush=True)
     if world > 1:
         # No collective follows the timing all-reduce, so every rank can leave on its own.  The
         # process group is not torn down: the captured graphs still reference the communicator,
@@ -659,8 +724,18 @@ def run_b200(args):
         os._exit(0)
 
 
+RESULT_OUT = sys.stdout
+
+
 def main():
+    global RESULT_OUT
     args = parse_args()
+    # The JSON line must be the only thing on stdout, but libraries (the NCCL version banner, for one)
+    # write to file descriptor 1 directly: keep a private copy of it for the result and point
+    # descriptor 1 at stderr for everything else.
+    sys.stdout.flush()
+    RESULT_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -6,6 +6,12 @@ window), and a GQA group is a contiguous run of query heads, so rank g of G simp
 owns KV heads [g*Hk/G, (g+1)*Hk/G) and the query heads of those groups.  The only
 exchange is the all-gather of the per-head outputs: rank-major concatenation of
 (Hq/G, D) blocks is exactly the (1, 1, Hq, D) output.
+
+For one token per call (decode) the gather is a kernel of this package over NVLink peer
+memory (csrc/gather.cu: every rank stores its rows into every rank's buffer and waits,
+bounded, on its own flags); the buffers come from torch's symmetric-memory allocator.
+`peer_gather=False`, several tokens per call, CPU tensors, or a platform where the
+symmetric allocation fails fall back to `all_gather_into_tensor` of the process group.
 """
 
 from __future__ import annotations
@@ -37,7 +43,7 @@ class KVHeadShardedDRAMAttention(torch.nn.Module):
 
     def __init__(self, *, n_kv_heads: int, rank: Optional[int] = None, world_size: Optional[int] = None,
                  process_group=None, operator_factory: Optional[Callable] = None, presliced: bool = False,
-                 **ctor_kwargs):
+                 peer_gather: bool = True, **ctor_kwargs):
         super().__init__()
         self.group = process_group
         self.world_size = dist.get_world_size(process_group) if world_size is None else world_size
@@ -48,6 +54,54 @@ class KVHeadShardedDRAMAttention(torch.nn.Module):
         if operator_factory is None:
             from .dram_attention import DRAMAttention as operator_factory
         self.inner = operator_factory(n_kv_heads=self.hi - self.lo, **ctor_kwargs)
+        self.peer_gather = peer_gather
+        self._peer = None          # (handle, buffer, seq, status, bytes_per_rank) once set up
+        self._peer_failed = None   # why the peer path is not in use, if it is not
+
+    # ---- gather over peer memory --------------------------------------------------
+    def _peer_setup(self, local: torch.Tensor):
+        """Collective (every rank calls it at its first decode step): allocates the symmetric
+        gather buffer and exchanges the peer mappings."""
+        import os
+        from . import _native
+        # plain peer stores only: the allocator need not bind the buffer to an NVLink multicast object
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+        nbytes = local.numel() * local.element_size()
+        total = _native.lib().da_gather_heads_buffer_bytes(nbytes, self.world_size)
+        if total == 0 or nbytes % 16 != 0:
+            raise RuntimeError(f"{nbytes} bytes per rank on {self.world_size} ranks: outside the gather kernel's range")
+        buf = symm_mem.empty(total, dtype=torch.uint8, device=local.device)
+        buf.zero_()
+        group = self.group if self.group is not None else dist.group.WORLD
+        handle = symm_mem.rendezvous(buf, group)
+        torch.cuda.synchronize(local.device)
+        dist.barrier(group=self.group)     # every buffer is zero before anybody's first push
+        seq = torch.zeros(1, dtype=torch.int32, device=local.device)
+        status = torch.zeros(1, dtype=torch.int32, device=local.device)
+        return handle, buf, seq, status, nbytes
+
+    def _peer_gather(self, local: torch.Tensor) -> torch.Tensor:
+        from . import _native
+        handle, buf, seq, status, nbytes = self._peer
+        b, s, h, d = local.shape
+        assert local.numel() * local.element_size() == nbytes, "the shard's output size changed between calls"
+        out = torch.empty(b, 1, h * self.world_size, d, dtype=local.dtype, device=local.device)
+        src = local if local.is_contiguous() else local.contiguous()
+        with torch.cuda.device(local.device):
+            _native.check(_native.lib().da_gather_heads(
+                src.data_ptr(), nbytes, handle.buffer_ptrs_dev, seq.data_ptr(), self.rank, self.world_size,
+                out.data_ptr(), status.data_ptr(), _native.stream_ptr()), "da_gather_heads")
+        return out
+
+    def check_status(self) -> None:
+        """Synchronising check of the device-side status words (tests, debugging)."""
+        if hasattr(self.inner, "check_status"):
+            self.inner.check_status()
+        if self._peer is not None:
+            code = int(self._peer[3].item())
+            if code:
+                raise RuntimeError(f"peer gather reported status {code} (8 = a wait on another rank ran out)")
 
     def _kv(self, t: torch.Tensor) -> torch.Tensor:
         return t if self.presliced else t[:, :, self.lo:self.hi]
@@ -71,6 +125,20 @@ class KVHeadShardedDRAMAttention(torch.nn.Module):
         if self.world_size == 1:
             return local
         b, s, h, d = local.shape
+        if s == 1 and self.peer_gather and local.is_cuda and self._peer_failed is None:
+            if self._peer is None:
+                try:
+                    self._peer = self._peer_setup(local)
+                except Exception as e:   # no symmetric memory on this platform: library gather
+                    self._peer_failed = repr(e)
+                # all ranks take the same path
+                ok = torch.tensor([0 if self._peer is None else 1], dtype=torch.int32, device=local.device)
+                dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+                if int(ok.item()) == 0:
+                    self._peer = None
+                    self._peer_failed = self._peer_failed or "another rank could not set up its gather buffer"
+            if self._peer is not None:
+                return self._peer_gather(local)
         if s == 1:
             # rank-major concatenation is the head order; a tensor of its own per call, like the
             # single-GPU operator's result

@@ -355,6 +355,29 @@ DA_API int da_build_pages(const void *k, const void *v,
                    int n_kv_heads, int n_pages, int n_slots, int page_size, int head_dim,
                    int dtype, da_stream_t stream);
 
+/*
+ * All-gather of the per-rank attention outputs over NVLink peer memory, for KV-head
+ * sharding on the GPUs of one node (no counterpart in the reference, which runs on one
+ * GPU; it replaces the library all-gather that would otherwise follow the attention
+ * launch).  One launch of one CTA: the rank's rows are stored into every rank's gather
+ * buffer, one flag per peer is released, the CTA waits (bounded: DA_STATUS_WAIT_TIMEOUT
+ * after ~2^22 polls) until every source rank's flag for this step is set in its own
+ * buffer, copies the assembled block to `out` and advances *seq.
+ *
+ * local         bytes_per_rank bytes, device memory, 16-byte aligned (this rank's rows)
+ * peer_buffers  DEVICE array of `world` pointers; entry g = rank g's gather buffer of
+ *               da_gather_heads_buffer_bytes(bytes_per_rank, world) bytes, mapped into
+ *               this process (symmetric / IPC memory), zero before the first call
+ * seq           (1) int32 device memory, zero before the first call, same value on all
+ *               ranks (every rank makes the same sequence of calls)
+ * out           world * bytes_per_rank bytes: rank-major concatenation
+ * Every rank of the group must make the call for a step; ranks run on different GPUs.
+ */
+DA_API size_t da_gather_heads_buffer_bytes(int bytes_per_rank, int world);
+DA_API int da_gather_heads(const void *local, int bytes_per_rank, void *const *peer_buffers,
+                    int32_t *seq, int rank, int world, void *out, int32_t *status,
+                    da_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
