@@ -60,10 +60,10 @@ __host__ __device__ inline int lru_table_size(int list_len) {
 
 // Time T of the slot at position `need` (1-based) in ascending time order, and how many slots
 // have a smaller time.  tm[] holds the times of this thread's slots (slot r * 1024 + tid), -1
-// for none.  8-bit radix select from the top byte of `bits` down.  hist = 256 ints of shared
+// for none.  8-bit radix select from the top byte of `bits` down.  hist2 = 2 x 256 ints of shared
 // memory, res = 2 ints.  All threads call; contains barriers.
 template <int SR>
-__device__ __forceinline__ void select_time(const int (&tm)[SR], int need, int bits, int *hist, int *res,
+__device__ __forceinline__ void select_time(const int (&tm)[SR], int need, int bits, int *hist2, int *res,
                                             int &t_out, int &less_out) {
     const int tid = threadIdx.x;
     const int lane = tid & 31;
@@ -71,10 +71,14 @@ __device__ __forceinline__ void select_time(const int (&tm)[SR], int need, int b
     const int passes = (bits + 7) / 8;
     uint32_t prefix = 0, mask = 0;
     int less = 0;
-    for (int pass = passes - 1; pass >= 0; --pass) {
+    if (tid < 256) hist2[tid] = 0;
+    __syncthreads();
+    for (int pass = passes - 1, buf = 0; pass >= 0; --pass, buf ^= 1) {
         const int shift = 8 * pass;
-        if (tid < 256) hist[tid] = 0;
-        __syncthreads();
+        int *hist = hist2 + 256 * buf;
+        // the other histogram was last read before the previous pass's final barrier: clear it now for
+        // the next pass, so that a pass costs two barriers
+        if (tid < 256) hist2[256 * (buf ^ 1) + tid] = 0;
 #pragma unroll
         for (int r = 0; r < SR; ++r) {
             const bool in = tm[r] >= 0 && ((uint32_t)tm[r] & mask) == prefix;
@@ -124,8 +128,9 @@ __device__ __forceinline__ void select_time(const int (&tm)[SR], int need, int b
         prefix |= (uint32_t)res[0] << shift;
         mask |= 255u << shift;
         less += res[1];
-        __syncthreads();
+        // (no barrier: res[] is next written after the next pass's histogram barrier)
     }
+    __syncthreads();   // the caller may reuse hist2 / res right away
     t_out = (int)prefix;
     less_out = less;
 }
@@ -148,7 +153,7 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
     int *vtime = mpage + list_len;       // [list_len] victims: time
     int *vslot = vtime + list_len;       // [list_len] victims: slot
     __shared__ int wsum[kLruWarps];
-    __shared__ int hist[256];
+    __shared__ int hist[512];
     __shared__ int res[2];
     __shared__ int sh_max;
 

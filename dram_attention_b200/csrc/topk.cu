@@ -11,6 +11,10 @@ constexpr int kTopkThreads = 1024;
 constexpr int kTopkWarps = kTopkThreads / 32;
 constexpr int kTopkMaxK = 4096;
 
+// Candidates the ranking step can take: k plus half as many again (the selection stops
+// refining its threshold as soon as the keys above it and its whole bucket fit).
+__host__ __device__ inline int topk_candidate_capacity(int k) { return k + (k >> 1); }
+
 // Ascending unsigned order of the key == ascending float order; -0.0 is folded
 // onto +0.0 so that the two compare equal (ties then go by page id).
 __device__ __forceinline__ uint32_t score_key(float x) {
@@ -72,9 +76,10 @@ __global__ void __launch_bounds__(kTopkThreads)
 topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_list, int n_kv_heads, int rep,
                   int n_pages, int k) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    unsigned long long *cand = reinterpret_cast<unsigned long long *>(smem_raw);  // [k + 1]
-    int *rank = reinterpret_cast<int *>(cand + k + 1);                            // [k]
-    __shared__ int hist[256];
+    const int cap = topk_candidate_capacity(k);
+    unsigned long long *cand = reinterpret_cast<unsigned long long *>(smem_raw);  // [cap + 2]
+    int *rank = reinterpret_cast<int *>(cand + cap + 2);                          // [cap]
+    __shared__ int hist2[2][256];   // the histogram of pass p is hist2[p & 1]; the other one is cleared meanwhile
     __shared__ int warp_tot[kTopkWarps];
     __shared__ int sh_digit, sh_above, sh_count, sh_taken;
 
@@ -87,17 +92,22 @@ topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_l
     const int lane = tid & 31;
     const int warp = tid >> 5;
 
+    if (tid < 256) hist2[0][tid] = 0;
     RowKeys<IPT> keys;
     keys.load(srow, n_pages, tid);
+    __syncthreads();
 
     // ---- radix select: key of the k-th largest score -----------------------
     uint32_t prefix = 0, mask = 0;
     int need = k;  // how many still to take among keys that match the prefix
     int count_eq = 0;
+    bool early = false;
     for (int pass = 0; pass < 4; ++pass) {
         const int shift = 24 - 8 * pass;
-        if (tid < 256) hist[tid] = 0;
-        __syncthreads();
+        int *hist = hist2[pass & 1];
+        // the other histogram was last read before the previous pass's final barrier: clear it for
+        // the next pass now, so that a pass costs two barriers
+        if (tid < 256) hist2[(pass + 1) & 1][tid] = 0;
         keys.for_each(srow, n_pages, tid, [&](int, uint32_t key, bool valid) {
             const bool in = valid && (key & mask) == prefix;
             // Scores cluster in a few exponent buckets, so most lanes of a warp share a
@@ -149,19 +159,32 @@ topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_l
         mask |= 255u << shift;
         need -= sh_above;
         count_eq = sh_count;
-        __syncthreads();
+        // (no barrier here: sh_* are next written after the next pass's histogram barrier, which no
+        // thread passes before it has read them)
+        // The keys above this bucket (k - need of them) are in; if the bucket itself is small, all
+        // of it can go to the ranking step, which then decides - no need to refine the threshold.
+        if (pass < 3 && k - need + count_eq <= cap) {
+            early = true;
+            break;
+        }
     }
-    // prefix = key of the k-th largest; `need` of the `count_eq` keys equal to it are taken.
+    // Without the early exit: prefix = key of the k-th largest; `need` of the `count_eq` keys equal
+    // to it are taken.  With it: every key whose masked bits are >= prefix is a candidate.
     const uint32_t thr = prefix;
+    const int m = early ? k - need + count_eq : k;   // candidates that get ranked
 
     // ---- gather the survivors ------------------------------------------------
     // Two sweeps over the keys instead of a shared counter: every warp first counts what it
     // will take, a scan over the 32 warp totals gives each warp its range of `cand`, and the
     // second sweep writes without atomics.
-    const bool take_all_ties = (count_eq == need);
+    const bool take_all_ties = early || (count_eq == need);
+    auto taken = [&](uint32_t key) -> bool {
+        if (early) return (key & mask) >= thr;
+        return key > thr || (take_all_ties && key == thr);
+    };
     int warp_count = 0;
     keys.for_each(srow, n_pages, tid, [&](int, uint32_t key, bool valid) {
-        const bool take = valid && (key > thr || (take_all_ties && key == thr));
+        const bool take = valid && taken(key);
         warp_count += __popc(__ballot_sync(DA_FULL_MASK, take));
     });
     if (lane == 0) warp_tot[warp] = warp_count;
@@ -180,7 +203,7 @@ topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_l
         if (tid == 0) sh_taken = all;
     }
     keys.for_each(srow, n_pages, tid, [&](int i, uint32_t key, bool valid) {
-        const bool take = valid && (key > thr || (take_all_ties && key == thr));
+        const bool take = valid && taken(key);
         const uint32_t bal = __ballot_sync(DA_FULL_MASK, take);
         if (take) cand[warp_base + __popc(bal & ((1u << lane) - 1))] = ((unsigned long long)(~key) << 32) | (uint32_t)i;
         warp_base += __popc(bal);
@@ -211,24 +234,24 @@ topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_l
     }
     __syncthreads();
 
-    // ---- order the k survivors: rank = number of smaller composite keys --------
-    // The candidate array is read two entries per 128-bit load; with k odd the pad entry is
+    // ---- order the m candidates: rank = number of smaller composite keys; the first k leave ----
+    // The candidate array is read two entries per 128-bit load; with m odd the pad entry is
     // the largest possible key and counts for nobody.
-    for (int e = tid; e < k; e += kTopkThreads) rank[e] = 0;
-    if (tid == 0 && (k & 1)) cand[k] = ~0ull;
+    for (int e = tid; e < m; e += kTopkThreads) rank[e] = 0;
+    if (tid == 0 && (m & 1)) cand[m] = ~0ull;
     __syncthreads();
     {
-        // with k < 1024 the comparisons of one element are split over several threads
-        const int n_pairs = (k + 1) >> 1;
-        int segs = kTopkThreads / k;
+        // with m < 1024 the comparisons of one element are split over several threads
+        const int n_pairs = (m + 1) >> 1;
+        int segs = kTopkThreads / m;
         if (segs < 1) segs = 1;
         const int per_sweep = kTopkThreads / segs;
         const int seg_pairs = (n_pairs + segs - 1) / segs;
         const ulonglong2 *pairs = reinterpret_cast<const ulonglong2 *>(cand);
-        for (int e0 = 0; e0 < k; e0 += per_sweep) {
+        for (int e0 = 0; e0 < m; e0 += per_sweep) {
             const int e = e0 + tid % per_sweep;
             const int seg = tid / per_sweep;
-            if (e < k && seg < segs) {
+            if (e < m && seg < segs) {
                 const unsigned long long v = cand[e];
                 const int j0 = seg * seg_pairs;
                 const int j1 = min(n_pairs, j0 + seg_pairs);
@@ -244,7 +267,10 @@ topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_l
     __syncthreads();
     const int n_tokens = gridDim.x / (n_kv_heads * rep);
     int32_t *dst = page_list + (size_t)hk * n_tokens * rep * k + (size_t)(tok * rep + r) * k;
-    for (int e = tid; e < k; e += kTopkThreads) dst[rank[e]] = (int32_t)(cand[e] & 0xffffffffu);
+    for (int e = tid; e < m; e += kTopkThreads) {
+        const int rk = rank[e];
+        if (rk < k) dst[rk] = (int32_t)(cand[e] & 0xffffffffu);
+    }
 }
 
 template <int IPT>
@@ -258,11 +284,12 @@ static cudaError_t launch_topk(const float *scores, int32_t *page_list, int rows
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
     if (!attr_set[dev]) {
         e = cudaFuncSetAttribute(topk_pages_kernel<IPT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 kTopkMaxK * 12 + 8);
+                                 topk_candidate_capacity(kTopkMaxK) * 12 + 16);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    const size_t smem = (size_t)(k + 1) * sizeof(unsigned long long) + (size_t)k * sizeof(int);
+    const int cap = topk_candidate_capacity(k);
+    const size_t smem = (size_t)(cap + 2) * sizeof(unsigned long long) + (size_t)cap * sizeof(int);
     topk_pages_kernel<IPT><<<rows, kTopkThreads, smem, stream>>>(scores, page_list, n_kv_heads, rep, n_pages, k);
     return cudaGetLastError();
 }
