@@ -195,18 +195,26 @@ __device__ __forceinline__ void merge_splits(const AttnParams &p, int h, int fir
                 lsum[i] = ml.y;
             }
             __syncthreads();
-            if (tid < REP) {
+            // one warp per query row: common max, weights exp2(max_s - max), weighted row sum
+            const int lane = tid & 31;
+            for (int r = tid >> 5; r < REP; r += THREADS / 32) {
                 float mn = NEG_INF;
-                for (int s = 0; s < splits; ++s) mn = fmaxf(mn, wgt[s * REP + tid]);
-                sh_m[tid] = (mn == NEG_INF) ? 0.f : mn;
-            }
-            __syncthreads();
-            for (int i = tid; i < n; i += THREADS) wgt[i] = fast_exp2(wgt[i] - sh_m[i % REP]);
-            __syncthreads();
-            if (tid < REP) {
+                for (int s = lane; s < splits; s += 32) mn = fmaxf(mn, wgt[s * REP + r]);
+#pragma unroll
+                for (int off = 16; off >= 1; off >>= 1) mn = fmaxf(mn, __shfl_xor_sync(DA_FULL_MASK, mn, off));
+                const float ms = (mn == NEG_INF) ? 0.f : mn;
                 float ll = 0.f;
-                for (int s = 0; s < splits; ++s) ll = fmaf(lsum[s * REP + tid], wgt[s * REP + tid], ll);
-                sh_l[tid] = ll;
+                for (int s = lane; s < splits; s += 32) {
+                    const float w = fast_exp2(wgt[s * REP + r] - ms);
+                    wgt[s * REP + r] = w;
+                    ll = fmaf(lsum[s * REP + r], w, ll);
+                }
+#pragma unroll
+                for (int off = 16; off >= 1; off >>= 1) ll += __shfl_xor_sync(DA_FULL_MASK, ll, off);
+                if (lane == 0) {
+                    sh_m[r] = ms;
+                    sh_l[r] = ll;
+                }
             }
             __syncthreads();
         }

@@ -23,6 +23,19 @@ __device__ __forceinline__ uint32_t score_key(float x) {
     return b ^ ((b >> 31) ? 0xffffffffu : 0x80000000u);
 }
 
+__device__ __forceinline__ float key_score(uint32_t key) {
+    return __uint_as_float(key ^ ((key >> 31) ? 0x80000000u : 0xffffffffu));
+}
+
+// Bucket 0..255 of a score in a linear division of [lo, lo + 256 / scale).  Monotone
+// non-decreasing in x (subtraction of a constant, multiplication by a positive constant,
+// truncation and clamping all are), which is all the selection needs: a key in a higher
+// bucket is strictly larger than a key in a lower one, equal keys share a bucket.
+__device__ __forceinline__ int linear_bucket(float x, float lo, float scale) {
+    const int b = (int)((x - lo) * scale);
+    return min(max(b, 0), 255);
+}
+
 // Where the keys of a row live while the kernel runs.  IPT > 0: n_pages <= IPT * 1024
 // and every thread keeps its IPT keys in registers after one coalesced read (key j of
 // thread t is page j * 1024 + t).  IPT == 0: any length; the row is re-read from
@@ -71,6 +84,37 @@ template <int IPT> struct RowKeys {
     }
 };
 
+// Warp 0: over 256 counters taken from the highest index down, the index where the running
+// count reaches `need`, the count above it, and its own count.  Lane l owns indices
+// 255-8l .. 248-8l.  With `above_of` every index also gets the count above it.
+__device__ __forceinline__ void descending_crossing(const int *hist, int need, int lane, int *digit_out,
+                                                    int *above_out, int *count_out, int *above_of = nullptr) {
+    int c[8], tot = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        c[j] = hist[255 - (lane * 8 + j)];
+        tot += c[j];
+    }
+    int incl = tot;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        int v = __shfl_up_sync(DA_FULL_MASK, incl, off);
+        if (lane >= off) incl += v;
+    }
+    int above = incl - tot;  // keys at higher indices than this lane's block
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int idx = 255 - (lane * 8 + j);
+        if (above_of) above_of[idx] = above;
+        if (above < need && above + c[j] >= need) {
+            *digit_out = idx;
+            *above_out = above;
+            *count_out = c[j];
+        }
+        above += c[j];
+    }
+}
+
 template <int IPT>
 __global__ void __launch_bounds__(kTopkThreads)
 topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_list, int n_kv_heads, int rep,
@@ -82,6 +126,8 @@ topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_l
     __shared__ int hist2[2][256];   // the histogram of pass p is hist2[p & 1]; the other one is cleared meanwhile
     __shared__ int warp_tot[kTopkWarps];
     __shared__ int sh_digit, sh_above, sh_count, sh_taken;
+    __shared__ uint32_t sh_kmin, sh_kmax;
+    __shared__ int above_of[256];   // linear level 1: candidates in higher buckets, per bucket
 
     const int row = blockIdx.x;  // (token * n_kv_heads + hk) * rep + r
     const int r = row % rep;
@@ -92,17 +138,101 @@ topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_l
     const int lane = tid & 31;
     const int warp = tid >> 5;
 
-    if (tid < 256) hist2[0][tid] = 0;
+    if (tid < 256) {
+        hist2[0][tid] = 0;
+        hist2[1][tid] = 0;
+    }
+    if (tid == 0) {
+        sh_kmin = 0xffffffffu;
+        sh_kmax = 0u;
+    }
     RowKeys<IPT> keys;
     keys.load(srow, n_pages, tid);
     __syncthreads();
+
+    // ---- fast path: one or two histograms over LINEAR buckets of the row's value range ----
+    // The radix digits of a float cluster (a row's scores share a few exponents), which makes
+    // the first radix passes both slow (every thread hits the same few counters) and weak
+    // (the k-th key's bucket still holds thousands).  256 equal-width buckets between the
+    // row's minimum and maximum spread the keys out: the bucket of the k-th key typically
+    // holds a few dozen, so the keys above it plus that bucket already fit the ranking step.
+    // If they do not, the bucket is divided once more; if that fails too (extreme outliers,
+    // massive ties) the exact radix select below takes over from scratch.
+    int lin_levels = 0;        // 0: radix select decides; 1, 2: candidates = linear buckets
+    float lin_lo = 0.f, lin_scale = 0.f, lin_lo2 = 0.f, lin_scale2 = 0.f;
+    int lin_b = 0, lin_b2 = 0, lin_m = 0;
+    {
+        uint32_t kmn = 0xffffffffu, kmx = 0u;
+        keys.for_each(srow, n_pages, tid, [&](int, uint32_t key, bool valid) {
+            if (valid) {
+                kmn = min(kmn, key);
+                kmx = max(kmx, key);
+            }
+        });
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            kmn = min(kmn, __shfl_xor_sync(DA_FULL_MASK, kmn, off));
+            kmx = max(kmx, __shfl_xor_sync(DA_FULL_MASK, kmx, off));
+        }
+        if (lane == 0) {
+            atomicMin(&sh_kmin, kmn);
+            atomicMax(&sh_kmax, kmx);
+        }
+        __syncthreads();
+        const float lo = key_score(sh_kmin), hi = key_score(sh_kmax);
+        const float width = hi - lo;
+        if (width > 0.f && width < 3.0e38f) {   // also false for NaN
+            lin_lo = lo;
+            lin_scale = 256.f / width;
+            int need_lin = k, above_total = 0;
+            for (int level = 1; level <= 2; ++level) {
+                int *hist = hist2[level - 1];
+                keys.for_each(srow, n_pages, tid, [&](int, uint32_t key, bool valid) {
+                    if (!valid) return;
+                    const float x = key_score(key);
+                    const int b1 = linear_bucket(x, lin_lo, lin_scale);
+                    if (level == 1) atomicAdd(&hist[b1], 1);
+                    else if (b1 == lin_b) atomicAdd(&hist[linear_bucket(x, lin_lo2, lin_scale2)], 1);
+                });
+                __syncthreads();
+                if (warp == 0)
+                    descending_crossing(hist, need_lin, lane, &sh_digit, &sh_above, &sh_count,
+                                        level == 1 ? above_of : nullptr);
+                __syncthreads();
+                const int b = sh_digit, above = sh_above, cnt = sh_count;
+                if (level == 1) {
+                    lin_b = b;
+                    lin_lo2 = lin_lo + (float)b / lin_scale;
+                    lin_scale2 = lin_scale * 256.f;
+                } else {
+                    lin_b2 = b;
+                }
+                above_total += above;
+                need_lin -= above;
+                if (above_total + cnt <= cap) {
+                    lin_levels = level;
+                    lin_m = above_total + cnt;
+                    break;
+                }
+            }
+        }
+        if (lin_levels == 0) {
+            // the radix select starts from clean histograms
+            __syncthreads();
+            if (tid < 256) {
+                hist2[0][tid] = 0;
+                hist2[1][tid] = 0;
+            }
+            __syncthreads();
+        }
+    }
 
     // ---- radix select: key of the k-th largest score -----------------------
     uint32_t prefix = 0, mask = 0;
     int need = k;  // how many still to take among keys that match the prefix
     int count_eq = 0;
     bool early = false;
-    for (int pass = 0; pass < 4; ++pass) {
+    for (int pass = 0; pass < 4 && lin_levels == 0; ++pass) {
         const int shift = 24 - 8 * pass;
         int *hist = hist2[pass & 1];
         // the other histogram was last read before the previous pass's final barrier: clear it for
@@ -124,36 +254,7 @@ topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_l
             }
         });
         __syncthreads();
-        if (warp == 0) {
-            // lane l owns digits 255-8l .. 248-8l (descending); find the digit where the
-            // running count from the top reaches `need`
-            int c[8], tot = 0;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                c[j] = hist[255 - (lane * 8 + j)];
-                tot += c[j];
-            }
-            int incl = tot;
-#pragma unroll
-            for (int off = 1; off < 32; off <<= 1) {
-                int v = __shfl_up_sync(DA_FULL_MASK, incl, off);
-                if (lane >= off) incl += v;
-            }
-            int above = incl - tot;  // keys in higher digits than this lane's block
-            if (above < need && incl >= need) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    if (above < need && above + c[j] >= need) {
-                        sh_digit = 255 - (lane * 8 + j);
-                        sh_above = above;
-                        sh_count = c[j];
-                        above = need;  // stop
-                    } else {
-                        above += c[j];
-                    }
-                }
-            }
-        }
+        if (warp == 0) descending_crossing(hist, need, lane, &sh_digit, &sh_above, &sh_count);
         __syncthreads();
         prefix |= (uint32_t)sh_digit << shift;
         mask |= 255u << shift;
@@ -170,15 +271,52 @@ topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_l
     }
     // Without the early exit: prefix = key of the k-th largest; `need` of the `count_eq` keys equal
     // to it are taken.  With it: every key whose masked bits are >= prefix is a candidate.
+    const int n_tokens = gridDim.x / (n_kv_heads * rep);
+    int32_t *dst = page_list + (size_t)hk * n_tokens * rep * k + (size_t)(tok * rep + r) * k;
+
+    if (lin_levels == 1) {
+        // ---- candidates sorted by bucket as they are gathered, then ranked inside their bucket ----
+        // Bucket b's candidates go to cand[above_of[b] ...] (a counter per bucket hands out the
+        // places; hist2[1] is still all zero), so a candidate's final rank is above_of[b] plus
+        // its rank among the handful of keys of its own bucket.
+        const int *count_of = hist2[0];
+        int *fill = hist2[1];
+        keys.for_each(srow, n_pages, tid, [&](int i, uint32_t key, bool valid) {
+            if (!valid) return;
+            const int b = linear_bucket(key_score(key), lin_lo, lin_scale);
+            if (b >= lin_b) {
+                const int at = above_of[b] + atomicAdd(&fill[b], 1);
+                cand[at] = ((unsigned long long)(~key) << 32) | (uint32_t)i;
+            }
+        });
+        __syncthreads();
+        for (int e = tid; e < lin_m; e += kTopkThreads) {
+            const unsigned long long v = cand[e];
+            const int b = linear_bucket(key_score(~(uint32_t)(v >> 32)), lin_lo, lin_scale);
+            const int first = above_of[b];
+            const int last = first + count_of[b];
+            int c = first;
+            for (int j = first; j < last; ++j) c += cand[j] < v;
+            if (c < k) dst[c] = (int32_t)(v & 0xffffffffu);
+        }
+        return;
+    }
+
     const uint32_t thr = prefix;
-    const int m = early ? k - need + count_eq : k;   // candidates that get ranked
+    const int m = lin_levels ? lin_m : (early ? k - need + count_eq : k);   // candidates that get ranked
 
     // ---- gather the survivors ------------------------------------------------
     // Two sweeps over the keys instead of a shared counter: every warp first counts what it
     // will take, a scan over the 32 warp totals gives each warp its range of `cand`, and the
     // second sweep writes without atomics.
-    const bool take_all_ties = early || (count_eq == need);
+    const bool take_all_ties = lin_levels != 0 || early || (count_eq == need);
     auto taken = [&](uint32_t key) -> bool {
+        if (lin_levels) {
+            const float x = key_score(key);
+            const int b1 = linear_bucket(x, lin_lo, lin_scale);
+            if (lin_levels == 1 || b1 != lin_b) return b1 >= lin_b;
+            return linear_bucket(x, lin_lo2, lin_scale2) >= lin_b2;
+        }
         if (early) return (key & mask) >= thr;
         return key > thr || (take_all_ties && key == thr);
     };
@@ -256,6 +394,7 @@ topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_l
                 const int j0 = seg * seg_pairs;
                 const int j1 = min(n_pairs, j0 + seg_pairs);
                 int c = 0;
+#pragma unroll 4
                 for (int j = j0; j < j1; ++j) {
                     const ulonglong2 w = pairs[j];
                     c += (w.x < v) + (w.y < v);
@@ -265,8 +404,6 @@ topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_l
         }
     }
     __syncthreads();
-    const int n_tokens = gridDim.x / (n_kv_heads * rep);
-    int32_t *dst = page_list + (size_t)hk * n_tokens * rep * k + (size_t)(tok * rep + r) * k;
     for (int e = tid; e < m; e += kTopkThreads) {
         const int rk = rank[e];
         if (rk < k) dst[rk] = (int32_t)(cand[e] & 0xffffffffu);
