@@ -59,7 +59,10 @@ class DRAMAttention(torch.nn.Module):
         self._can_overlap = False
         self._overlap_ok = {}
         self._side = None
+        self._prefill_status = None
 
+    # stage="prefill": this package's tcgen05 kernel where it applies (16-bit, head_dim 128)
+    prefill_kernel = True
     fused_fetch = True
     # Two attention launches per step: the first (local window + slots that cannot be evicted this
     # step) runs on a side stream beside selection and LRU update, the second finishes after them.
@@ -114,11 +117,26 @@ class DRAMAttention(torch.nn.Module):
         else:
             raise RuntimeError(f"Unsupported stage: {stage}")
 
-    @staticmethod
-    def _prefill_attention(xq, xk, xv):
-        """Dense causal attention of the prompt.  Not part of the decode path: like
-        the reference (which calls a third-party library here,
-        dram_attention/dram_attention.py:136) this is a library call."""
+    def _prefill_attention(self, xq, xk, xv):
+        """Dense causal attention of the prompt (the reference calls a third-party library
+        here, dram_attention/dram_attention.py:136).  16-bit tensors with head_dim 128 on a CUDA
+        device go through this package's tensor-core kernel (da_prefill_attention); other
+        shapes (the float32 test configuration) use torch's scaled_dot_product_attention."""
+        bsz, seqlen, n_q_heads, head_dim = xq.shape
+        lib = _native.lib()
+        if (self.prefill_kernel and xq.is_cuda and xq.dtype in (torch.bfloat16, torch.float16)
+                and xk.dtype == xq.dtype and xv.dtype == xq.dtype
+                and lib.da_prefill_attention_supported(head_dim, _native.dtype_code(xq.dtype))):
+            q, k, v = (t if t.is_contiguous() else t.contiguous() for t in (xq, xk, xv))
+            out = torch.empty_like(q)
+            if self._prefill_status is None:
+                self._prefill_status = torch.zeros(1, dtype=torch.int32, device=q.device)
+            with torch.cuda.device(q.device):
+                _native.check(lib.da_prefill_attention(
+                    q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), seqlen, n_q_heads, k.shape[2],
+                    head_dim, n_q_heads * head_dim, k.shape[2] * head_dim, _native.dtype_code(q.dtype),
+                    self._prefill_status.data_ptr(), _native.stream_ptr()), "da_prefill_attention")
+            return out
         q, k, v = (t.transpose(1, 2) for t in (xq, xk, xv))
         out = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
         return out.transpose(1, 2).contiguous()
@@ -245,7 +263,10 @@ class DRAMAttention(torch.nn.Module):
 
     def check_status(self) -> None:
         """Synchronises; raises if any kernel of this operator flagged a problem."""
-        for _, _, status in self._ws.values():
+        statuses = [status for _, _, status in self._ws.values()]
+        if self._prefill_status is not None:
+            statuses.append(self._prefill_status)
+        for status in statuses:
             bits = int(status.item())
             if bits:
                 status.zero_()

@@ -356,6 +356,27 @@ DA_API int da_build_pages(const void *k, const void *v,
                    int dtype, da_stream_t stream);
 
 /*
+ * Dense causal attention of the prompt: replaces the flash_attn_func call of the prefill
+ * stage (dram_attention/dram_attention.py:136) for 16-bit element types and head_dim 128.
+ * tcgen05 tensor-core kernel (operands by TMA into shared memory, accumulators in tensor
+ * memory), one CTA per 128 query rows and query head; softmax scale 1/sqrt(head_dim), GQA
+ * by contiguous groups, float32 softmax and accumulation.
+ *
+ * q            (seq_len, n_q_heads, head_dim), unit channel stride, heads packed, rows
+ *              q_row_stride elements apart
+ * k, v         (seq_len, n_kv_heads, head_dim), rows kv_row_stride elements apart
+ * out          (seq_len, n_q_heads, head_dim) contiguous, same dtype
+ * All base pointers 16-byte aligned, row strides multiples of 8 elements.
+ * da_prefill_attention_supported: 1 for head_dim 128 with DA_BF16 / DA_F16; for anything
+ * else da_prefill_attention returns DA_ERR_UNSUPPORTED and the caller keeps its library call.
+ */
+DA_API int da_prefill_attention_supported(int head_dim, int dtype);
+DA_API int da_prefill_attention(const void *q, const void *k, const void *v, void *out,
+                         int seq_len, int n_q_heads, int n_kv_heads, int head_dim,
+                         long long q_row_stride, long long kv_row_stride, int dtype,
+                         int32_t *status, da_stream_t stream);
+
+/*
  * All-gather of the per-rank attention outputs over NVLink peer memory, for KV-head
  * sharding on the GPUs of one node (no counterpart in the reference, which runs on one
  * GPU; it replaces the library all-gather that would otherwise follow the attention
