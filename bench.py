@@ -153,6 +153,16 @@ def upload_graph(graph, torch):
         return False
 
 
+def tensor_peak_tflops():
+    """Measured dense bf16 throughput of this pool's GPUs (burst figure: the kernel is timed alone)."""
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured"
+    except Exception:
+        return 1590.0, "fallback"
+
+
 def hbm_peak_gbs():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
@@ -589,6 +599,43 @@ def run_b200(args):
             del sel
         del mm
         windows.append((t_a, time.perf_counter()))
+    # ---------------- prefill stage (off the decode path): the tcgen05 causal attention kernel ---------------
+    prefill = None
+    if world == 1 and P and not args.no_sweep:
+        t_a = time.perf_counter()
+        pf_s = 32768
+        gp = torch.Generator(device=dev).manual_seed(2)
+        pq = torch.randn(1, pf_s, w.n_q_heads, D, generator=gp, device=dev).to(w.dtype)
+        pk = torch.randn(1, pf_s, hk_all, D, generator=gp, device=dev).to(w.dtype)
+        pv = torch.randn(1, pf_s, hk_all, D, generator=gp, device=dev).to(w.dtype)
+        flops = 4.0 * pf_s * pf_s / 2 * w.n_q_heads * D          # causal: half of the square
+        peak_tf, peak_tf_kind = tensor_peak_tflops()
+
+        def time_prefill(use_kernel):
+            inner.prefill_kernel = use_kernel
+            for _ in range(2):
+                inner._prefill_attention(pq, pk, pv)
+            torch.cuda.synchronize()
+            ev0.record()
+            for _ in range(3):
+                inner._prefill_attention(pq, pk, pv)
+            ev1.record()
+            torch.cuda.synchronize()
+            return ev0.elapsed_time(ev1) / 3
+
+        ms_own, ms_lib = time_prefill(True), time_prefill(False)
+        inner.prefill_kernel = True
+        inner.check_status()
+        prefill = {"what": f"causal attention of a {pf_s}-token prompt, {w.n_q_heads}/{hk_all} heads, bf16 "
+                           "(stage=\"prefill\"; not part of the decode metric)",
+                   "kernel": "prefill_attention_kernel (tcgen05.mma, TMEM accumulators, TMA operands)",
+                   "ms": ms_own, "tflops": flops / ms_own / 1e9, "peak_tflops": peak_tf,
+                   "peak_kind": peak_tf_kind + " cuBLAS bf16 GEMM (burst)", "frac": flops / ms_own / 1e9 / peak_tf,
+                   "library_ms": ms_lib, "library_tflops": flops / ms_lib / 1e9,
+                   "library": "torch scaled_dot_product_attention on the same tensors"}
+        del pq, pk, pv
+        windows.append((t_a, time.perf_counter()))
+
     # ---------------- N > 1, by sequence: the KV-head-sharded step of ONE sequence, timed beside it -------
     sharded_report = None
     if by_seq:
@@ -704,6 +751,7 @@ def run_b200(args):
             "fetch": ("inside the attention kernel" if fused else "separate gather-copy launch"),
             "fetch_report": fetch_report,
             "scorer_sweep": sweep,
+            "prefill": prefill,
             "fetch_fraction_of_step": (stage_us["fetch"] / sum(v for v in stage_us.values() if v)
                                        if stage_us["fetch"] else None),
         }

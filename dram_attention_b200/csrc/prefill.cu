@@ -2,25 +2,29 @@
 // head_dim 128, on the 5th-generation tensor cores: tcgen05.mma with both operands in shared
 // memory (filled by TMA tensor copies, 128-byte swizzle) and the accumulators in tensor memory.
 //
-// One CTA of 128 threads per (128 query rows, query head).  Thread t owns query row t, which
-// is lane t of tensor memory, so the softmax needs no shuffles: a row's 128 logits come back
-// with tcgen05.ld as plain registers of its thread.  Per 128-key tile:
+// One CTA per (128 query rows, query head): four softmax warps and one issuing warp.  Softmax
+// thread t owns query row t, which is lane t of tensor memory, so the softmax needs no
+// shuffles: a row's 128 logits come back with tcgen05.ld as plain registers of its thread.
+// One lane of the fifth warp issues every TMA copy and every MMA; the two roles meet only at
+// mbarriers (S ready, P ready, product complete), never at a CTA-wide barrier, so a softmax
+// warp is never held up by another warp's pace.  Per 128-key tile:
 //
 //   S = Q K^T      8 MMAs (M128 N128 K16), Q and the key tile K-major      -> TMEM columns 0..127 / 128..255
 //   softmax        row max / exp2 / row sum in registers (log2 domain, online rescale);
 //                  P is written as 16-bit values into shared memory in the swizzled K-major
 //                  layout an A operand has
-//   O_tile = P V   8 MMAs, the value tile as an MN-major B operand          -> TMEM columns 256..383
-//   O = O * alpha + O_tile in registers (128 floats per thread)
+//   O += P V       8 MMAs, the value tile as an MN-major B operand, accumulating over all
+//                  tiles                                                    -> TMEM columns 256..383
 //
-// The loop is software-pipelined so that the tensor core is never waited on in line: S of
-// tile j+1 is issued (into a second S buffer) before the softmax of tile j starts, and the
-// product P V of tile j is added to the registers one iteration later, after the softmax of
-// tile j+1.  Key and value tiles are double-buffered (a key stage is refilled as soon as its S
-// is complete, a value stage once its product is).  One thread issues all TMA and MMA
-// instructions; completion comes back through mbarriers, and every wait on one is bounded (a
-// wait that runs out sets DA_STATUS_WAIT_TIMEOUT, and the CTA frees its tensor memory and
-// leaves).
+// O never leaves tensor memory until the end: the exponentials of a row are taken against a
+// reference that follows the row maximum lazily, and O is rescaled in place (tcgen05.ld / st)
+// only when a tile's maximum outgrows the reference by more than 2^8 - after the first tiles,
+// hardly ever.  The loop is software-pipelined so that the tensor core is not waited on in
+// line: S of tile j+1 is issued (into a second S buffer) before the softmax of tile j starts,
+// and the product of tile j runs during the softmax of tile j+1.  Key and value tiles are double-buffered (a key stage is refilled as soon as its S
+// is complete, a value stage once its product is).  Every wait on an mbarrier is bounded: a
+// wait that runs out sets DA_STATUS_WAIT_TIMEOUT and a flag that makes both roles leave their
+// loops; the CTA then frees its tensor memory and returns.
 //
 // GQA: query head hq reads KV head hq / rep.  Causal: key tiles above the diagonal are
 // skipped, the diagonal tile is masked per element.  Rows past the end of the prompt are
@@ -32,7 +36,8 @@
 
 namespace da {
 
-constexpr int kPfRows = 128;    // query rows per CTA (= threads, = TMEM lanes)
+constexpr int kPfRows = 128;    // query rows per CTA (= softmax threads, = TMEM lanes)
+constexpr int kPfThreads = kPfRows + 32;   // plus the warp that issues copies and MMAs
 constexpr int kPfKeys = 128;    // keys per tile
 constexpr int kPfDim = 128;     // head_dim
 constexpr int kPfBoxBytes = kPfRows * 128;            // one TMA box: 128 rows x 64 elements
@@ -45,7 +50,6 @@ struct PrefillParams {
     int seq_len, n_q_heads, rep;
     float scale_log2;
     int32_t *status;
-    int is_bf16;
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------
@@ -72,6 +76,10 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void proxy_fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
 
 __device__ __forceinline__ void tc_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar))
@@ -115,6 +123,20 @@ __device__ __forceinline__ void tmem_wait32(uint32_t (&r)[32]) {
         : "memory");
 }
 
+__device__ __forceinline__ void tmem_store32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_wait_store() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
 // f(chunk, values) for the four 32-column chunks starting at taddr, the load of a chunk in
 // flight while the previous one is processed
 template <typename F>
@@ -154,8 +176,9 @@ __device__ __forceinline__ uint32_t instr_desc(bool bf16, bool b_mn_major) {
            ((uint32_t)(kPfRows >> 4) << 24);
 }
 
-__device__ __forceinline__ uint32_t pack16(float lo, float hi, bool bf16) {
-    if (bf16) {
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack16(float lo, float hi) {
+    if constexpr (BF16) {
         __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
         return *reinterpret_cast<uint32_t *>(&v);
     }
@@ -163,7 +186,8 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi, bool bf16) {
     return *reinterpret_cast<uint32_t *>(&v);
 }
 
-__global__ void __launch_bounds__(kPfRows, 1)
+template <bool BF16>
+__global__ void __launch_bounds__(kPfThreads, 1)
 prefill_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const PrefillParams p) {
     extern __shared__ unsigned char smem_raw[];
@@ -173,8 +197,9 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     unsigned char *sK = sQ + kPfTileBytes;            // two stages
     unsigned char *sV = sK + 2 * kPfTileBytes;        // two stages
     unsigned char *sP = sV + 2 * kPfTileBytes;        // two buffers
-    __shared__ __align__(8) uint64_t bar_q, bar_k[2], bar_v[2], bar_s[2], bar_pv;
+    __shared__ __align__(8) uint64_t bar_q, bar_k[2], bar_v[2], bar_s[2], bar_p[2], bar_pv;
     __shared__ uint32_t tmem_holder;
+    __shared__ int sh_abort;
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -183,7 +208,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int hq = blockIdx.y;
     const int hk = hq / p.rep;
     const int q0 = qt * kPfRows;
-    const bool bf16 = p.is_bf16 != 0;
+    constexpr bool bf16 = BF16;
 
     if (tid == 0) {
         mbar_init(&bar_q, 1);
@@ -192,9 +217,11 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             mbar_init(&bar_k[b], 1);
             mbar_init(&bar_v[b], 1);
             mbar_init(&bar_s[b], 1);
+            mbar_init(&bar_p[b], kPfRows);     // every softmax thread arrives
         }
         mbar_init(&bar_pv, 1);
         mbar_fence_init();
+        sh_abort = 0;
     }
     __syncwarp();
     if (warp == 0) tmem_alloc(&tmem_holder, kPfTmemCols);
@@ -202,171 +229,234 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_holder;
-    const uint32_t tmem_row = tmem + ((uint32_t)(warp * 32) << 16);   // this warp's 32 lanes
-    // columns: S of even tiles 0..127, S of odd tiles 128..255, the P V product of one tile 256..383
+    // columns: S of even tiles 0..127, S of odd tiles 128..255, O 256..383
     const uint32_t tmem_o = 2 * kPfKeys;
 
     // keys 0 .. q0 + 127 are visible to this tile's rows
     const int last_key = min(p.seq_len, q0 + kPfRows);
     const int n_tiles = (last_key + kPfKeys - 1) / kPfKeys;
-
-    auto load_tile = [&](unsigned char *dst, const CUtensorMap *map, int j, uint64_t *bar) {
-        mbar_arrive_expect_tx(bar, kPfTileBytes);
-        tma_load_3d(dst, map, 0, hk, j * kPfKeys, bar);
-        tma_load_3d(dst + kPfBoxBytes, map, 64, hk, j * kPfKeys, bar);
-    };
-    const uint32_t idesc_s = instr_desc(bf16, false), idesc_o = instr_desc(bf16, true);
-    // S(j) = Q K(j)^T into the S buffer of j's parity; K(j) has arrived when this is called
-    auto issue_s = [&](int j) {
-        tc_fence_after();
-        const uint32_t a0 = smem_addr(sQ), b0 = smem_addr(sK + (j & 1) * kPfTileBytes);
-#pragma unroll
-        for (int ks = 0; ks < kPfDim / 16; ++ks) {
-            const uint32_t off = (ks >> 2) * kPfBoxBytes + (ks & 3) * 32;
-            tc_mma(tmem + (j & 1) * kPfKeys, desc_k_major(a0 + off), desc_k_major(b0 + off), idesc_s, ks > 0);
-        }
+    volatile int *abort_flag = &sh_abort;
+    // a wait that ran out: say so, and let every role leave its loop at its next tile
+    auto give_up = [&]() {
+        atomicOr(p.status, DA_STATUS_WAIT_TIMEOUT);
+        *abort_flag = 1;
     };
 
-    bool ok = true;
-    if (tid == 0) {
-        mbar_arrive_expect_tx(&bar_q, kPfTileBytes);
-        tma_load_3d(sQ, &map_q, 0, hq, q0, &bar_q);
-        tma_load_3d(sQ + kPfBoxBytes, &map_q, 64, hq, q0, &bar_q);
-        load_tile(sK, &map_k, 0, &bar_k[0]);
-        if (n_tiles > 1) load_tile(sK + kPfTileBytes, &map_k, 1, &bar_k[1]);
-        load_tile(sV, &map_v, 0, &bar_v[0]);
-        ok = mbar_wait_bounded(&bar_q, 0) && mbar_wait_bounded(&bar_k[0], 0);
-        if (ok) issue_s(0);
-        tc_commit(&bar_s[0]);   // also on failure: arrives at once, nobody is left waiting
-    }
-    __syncwarp();
-
-    float o[kPfDim];
-#pragma unroll
-    for (int i = 0; i < kPfDim; ++i) o[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
-
-    // O = O * alpha(j_prev) + the P V product of tile j_prev, once its MMAs are complete (the
-    // rescale by a tile's alpha waits for that tile's product, so it is one fused multiply-add)
-    float alpha_pending = 1.f;
-    auto add_product = [&](int j_prev) {
-        ok = mbar_wait_bounded(&bar_pv, (uint32_t)(j_prev & 1)) && ok;
-        tc_fence_after();
-        tmem_for_chunks(tmem_row + tmem_o, [&](int c, const uint32_t (&t)[32]) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha_pending, __uint_as_float(t[i]));
-        });
-    };
-
-    for (int j = 0; j < n_tiles; ++j) {
-        const int b = j & 1;
-        const uint32_t use = (uint32_t)((j >> 1) & 1);     // parity of this use of a two-deep buffer
-        ok = mbar_wait_bounded(&bar_s[b], use) && ok;
-        tc_fence_after();
-        if (tid == 0) {
-            // the tensor core goes on with the next tile's logits while this tile's softmax runs
-            if (j + 1 < n_tiles) {
-                ok = mbar_wait_bounded(&bar_k[b ^ 1], (uint32_t)(((j + 1) >> 1) & 1)) && ok;
-                if (ok) issue_s(j + 1);
-                tc_commit(&bar_s[b ^ 1]);
-            }
-            if (j + 2 < n_tiles) load_tile(sK + b * kPfTileBytes, &map_k, j + 2, &bar_k[b]);   // S(j) is complete
-        }
-        __syncwarp();
-
-        // ---- softmax of this thread's row -----------------------------------------------------
-        const uint32_t tmem_s = (uint32_t)b * kPfKeys;
-        const int qpos = q0 + tid;
-        const int key0 = j * kPfKeys;
-        const bool diagonal = key0 + kPfKeys - 1 > q0;      // some key of the tile is masked for some row
-        // keys of this tile visible to this row (all 128 below the diagonal)
-        const int n_vis = diagonal ? min(max(qpos - key0 + 1, 0), kPfKeys) : kPfKeys;
-        float mx = -INFINITY;
-        tmem_for_chunks(tmem_row + tmem_s, [&](int c, const uint32_t (&s)[32]) {
-            if (!diagonal) {
-#pragma unroll
-                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[i]));
-            } else {
-#pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    if (c * 32 + i < n_vis) mx = fmaxf(mx, __uint_as_float(s[i]));
-            }
-        });
-        const float m_new = fmaxf(m_run, mx * p.scale_log2);
-        const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
-        const float alpha = fast_exp2(m_run - m_safe);
-        float row_sum = 0.f;
-        unsigned char *sPb = sP + b * kPfTileBytes;          // last read by the product of tile j-2: complete
-        tmem_for_chunks(tmem_row + tmem_s, [&](int c, const uint32_t (&s)[32]) {
-            uint32_t packed[16];
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-                float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), p.scale_log2, -m_safe));
-                float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), p.scale_log2, -m_safe));
-                if (diagonal) {
-                    if (c * 32 + i >= n_vis) p0 = 0.f;
-                    if (c * 32 + i + 1 >= n_vis) p1 = 0.f;
-                }
-                row_sum += p0 + p1;
-                packed[i >> 1] = pack16(p0, p1, bf16);
-            }
-            // row `tid` of P, keys 32c .. 32c+31 = 64 bytes = four 16-byte chunks of the row's box
-            unsigned char *row = sPb + (c >> 1) * kPfBoxBytes + tid * 128;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const int chunk = (c & 1) * 4 + q;                     // chunk inside the 128-byte row
-                const int phys = chunk ^ (tid & 7);                    // 128-byte swizzle
-                *reinterpret_cast<uint4 *>(row + phys * 16) =
-                    make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-            }
-        });
-        l_run = l_run * alpha + row_sum;
-        m_run = m_new;
-        if (j > 0) add_product(j - 1);
-        alpha_pending = alpha;
-        proxy_fence_async_smem();     // P must be visible to the tensor core's reads of shared memory
-        tc_fence_before();
-        const bool abort_now = __syncthreads_or(!ok);
-        if (abort_now) {
-            ok = false;
-            break;
-        }
-
-        // ---- O_tile = P V (accumulated into registers one iteration later) ------------------------
-        if (tid == 0) {
-            // the value stage of tile j+1 was last read by the product of tile j-1: complete
-            if (j + 1 < n_tiles) load_tile(sV + (b ^ 1) * kPfTileBytes, &map_v, j + 1, &bar_v[b ^ 1]);
-            ok = mbar_wait_bounded(&bar_v[b], use) && ok;
-            if (ok) {
+    if (warp == kPfRows / 32) {
+        // =================== the issuing warp: all TMA copies and all MMAs, by one lane ===================
+        if ((tid & 31) == 0) {
+            auto load_tile = [&](unsigned char *dst, const CUtensorMap *map, int j, uint64_t *bar) {
+                mbar_arrive_expect_tx(bar, kPfTileBytes);
+                tma_load_3d(dst, map, 0, hk, j * kPfKeys, bar);
+                tma_load_3d(dst + kPfBoxBytes, map, 64, hk, j * kPfKeys, bar);
+            };
+            const uint32_t idesc_s = instr_desc(bf16, false), idesc_o = instr_desc(bf16, true);
+            // S(j) = Q K(j)^T into the S buffer of j's parity; K(j) has arrived when this is called
+            auto issue_s = [&](int j) {
                 tc_fence_after();
-                const uint32_t a0 = smem_addr(sPb), b0 = smem_addr(sV + b * kPfTileBytes);
+                const uint32_t a0 = smem_addr(sQ), b0 = smem_addr(sK + (j & 1) * kPfTileBytes);
+#pragma unroll
+                for (int ks = 0; ks < kPfDim / 16; ++ks) {
+                    const uint32_t off = (ks >> 2) * kPfBoxBytes + (ks & 3) * 32;
+                    tc_mma(tmem + (j & 1) * kPfKeys, desc_k_major(a0 + off), desc_k_major(b0 + off), idesc_s, ks > 0);
+                }
+                tc_commit(&bar_s[j & 1]);
+            };
+            mbar_arrive_expect_tx(&bar_q, kPfTileBytes);
+            tma_load_3d(sQ, &map_q, 0, hq, q0, &bar_q);
+            tma_load_3d(sQ + kPfBoxBytes, &map_q, 64, hq, q0, &bar_q);
+            load_tile(sK, &map_k, 0, &bar_k[0]);
+            if (n_tiles > 1) load_tile(sK + kPfTileBytes, &map_k, 1, &bar_k[1]);
+            load_tile(sV, &map_v, 0, &bar_v[0]);
+            bool ok = mbar_wait_bounded(&bar_q, 0) && mbar_wait_bounded(&bar_k[0], 0);
+            if (ok) issue_s(0);
+            for (int j = 0; ok && j < n_tiles; ++j) {
+                const int b = j & 1;
+                const uint32_t use = (uint32_t)((j >> 1) & 1);     // parity of this use of a two-deep buffer
+                if (*abort_flag) break;
+                // S(j) complete: its key stage can take tile j+2
+                ok = mbar_wait_bounded(&bar_s[b], use);
+                if (!ok) break;
+                if (j + 2 < n_tiles) load_tile(sK + b * kPfTileBytes, &map_k, j + 2, &bar_k[b]);
+                // S(j+1) goes into the other S buffer, whose last reader was the softmax of tile j-1:
+                // done, or its P would not have been ready for the product issued one round ago
+                if (j + 1 < n_tiles) {
+                    ok = mbar_wait_bounded(&bar_k[b ^ 1], (uint32_t)(((j + 1) >> 1) & 1));
+                    if (!ok) break;
+                    issue_s(j + 1);
+                }
+                // O += P(j) V(j) once every softmax thread has written its row of P (and has
+                // rescaled its row of O if it had to)
+                ok = mbar_wait_bounded(&bar_p[b], use);
+                if (ok && j > 0) ok = mbar_wait_bounded(&bar_pv, (uint32_t)((j - 1) & 1));   // frees V's other stage
+                if (!ok) break;
+                if (j + 1 < n_tiles) load_tile(sV + (b ^ 1) * kPfTileBytes, &map_v, j + 1, &bar_v[b ^ 1]);
+                ok = mbar_wait_bounded(&bar_v[b], use);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a0 = smem_addr(sP + b * kPfTileBytes), b0 = smem_addr(sV + b * kPfTileBytes);
 #pragma unroll
                 for (int ks = 0; ks < kPfKeys / 16; ++ks) {
                     const uint32_t a_off = (ks >> 2) * kPfBoxBytes + (ks & 3) * 32;
                     const uint32_t b_off = ks * 16 * 128;               // 16 keys further down the tile
-                    tc_mma(tmem + tmem_o, desc_k_major(a0 + a_off), desc_mn_major(b0 + b_off), idesc_o, ks > 0);
+                    tc_mma(tmem + tmem_o, desc_k_major(a0 + a_off), desc_mn_major(b0 + b_off), idesc_o,
+                           (j > 0 || ks > 0) ? 1u : 0u);
                 }
+                tc_commit(&bar_pv);
             }
-            tc_commit(&bar_pv);
+            if (!ok) give_up();
         }
-        __syncwarp();
-    }
-    if (ok && n_tiles > 0) add_product(n_tiles - 1);
+    } else {
+        // =================== the softmax warps: thread t = query row t = TMEM lane t ===================
+        const uint32_t tmem_row = tmem + ((uint32_t)(warp * 32) << 16);   // this warp's 32 lanes
+        // m_used: the (log2-domain) reference the exponentials of this row are taken against.  It
+        // follows the row maximum lazily: O, which accumulates in tensor memory over all tiles, is
+        // rescaled only when a tile's maximum exceeds the reference by more than 8 (probabilities
+        // stay below 2^8, well inside the 16-bit range; the common factor cancels in the division
+        // by l at the end).  After the first few tiles that hardly ever happens, so a tile normally
+        // costs one read of S from tensor memory and nothing else.
+        float m_used = -INFINITY, l_run = 0.f;
+        constexpr float kRescaleSlack = 8.f;
+        bool ok = true;
 
-    // ---- write this row -------------------------------------------------------------------------
-    const bool failed = __syncthreads_or(!ok);
-    if (failed) {
-        if (tid == 0) atomicOr(p.status, DA_STATUS_WAIT_TIMEOUT);
-    } else if (q0 + tid < p.seq_len) {
-        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-        uint4 *dst = reinterpret_cast<uint4 *>(static_cast<unsigned char *>(p.out) +
-                                               ((size_t)(q0 + tid) * p.n_q_heads + hq) * kPfDim * 2);
+        for (int j = 0; j < n_tiles; ++j) {
+            const int b = j & 1;
+            const uint32_t use = (uint32_t)((j >> 1) & 1);
+            if (*abort_flag) {
+                ok = false;
+                break;
+            }
+            // S(j) was committed after the product of tile j-2 was issued: P's buffer b is free too
+            ok = mbar_wait_bounded(&bar_s[b], use);
+            if (!__all_sync(DA_FULL_MASK, ok)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+
+            // ---- this thread's row of S, read once ------------------------------------------------
+            const uint32_t tmem_s = (uint32_t)b * kPfKeys;
+            const int qpos = q0 + tid;
+            const int key0 = j * kPfKeys;
+            const bool diagonal = key0 + kPfKeys - 1 > q0;      // some key of the tile is masked for some row
+            const int n_vis = diagonal ? min(max(qpos - key0 + 1, 0), kPfKeys) : kPfKeys;   // keys this row sees
+            uint32_t s0[32], s1[32], s2[32], s3[32];
+            tmem_issue32(tmem_row + tmem_s, s0);
+            tmem_issue32(tmem_row + tmem_s + 32, s1);
+            tmem_issue32(tmem_row + tmem_s + 64, s2);
+            tmem_issue32(tmem_row + tmem_s + 96, s3);
+            tmem_wait32(s0);
+            tmem_wait32(s1);
+            tmem_wait32(s2);
+            tmem_wait32(s3);
+            float mx = -INFINITY;
+            auto chunk_max = [&](int c, const uint32_t (&s)[32]) {
+                if (!diagonal) {
 #pragma unroll
-        for (int c = 0; c < kPfDim / 8; ++c) {
-            dst[c] = make_uint4(pack16(o[8 * c] * inv, o[8 * c + 1] * inv, bf16),
-                                pack16(o[8 * c + 2] * inv, o[8 * c + 3] * inv, bf16),
-                                pack16(o[8 * c + 4] * inv, o[8 * c + 5] * inv, bf16),
-                                pack16(o[8 * c + 6] * inv, o[8 * c + 7] * inv, bf16));
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[i]));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (c * 32 + i < n_vis) mx = fmaxf(mx, __uint_as_float(s[i]));
+                }
+            };
+            chunk_max(0, s0);
+            chunk_max(1, s1);
+            chunk_max(2, s2);
+            chunk_max(3, s3);
+            const float m_tile = mx * p.scale_log2;
+
+            // ---- move the reference if this tile outgrows it (whole warp together: the tensor-memory
+            //      accesses are warp-wide) ---------------------------------------------------------------
+            const bool grow = m_tile > m_used + kRescaleSlack;     // also true on the first tile (-inf)
+            if (__any_sync(DA_FULL_MASK, grow)) {
+                const float m_next = grow ? m_tile : m_used;
+                const float alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_next);
+                if (j > 0) {
+                    // O holds the products up to tile j-1: wait for the last of them, scale the row
+                    ok = mbar_wait_bounded(&bar_pv, (uint32_t)((j - 1) & 1));
+                    if (!__all_sync(DA_FULL_MASK, ok)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+#pragma unroll
+                    for (int c = 0; c < kPfDim / 32; ++c) {
+                        uint32_t t[32];
+                        tmem_issue32(tmem_row + tmem_o + c * 32, t);
+                        tmem_wait32(t);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) t[i] = __float_as_uint(__uint_as_float(t[i]) * alpha);
+                        tmem_store32(tmem_row + tmem_o + c * 32, t);
+                    }
+                    tmem_wait_store();
+                }
+                l_run *= alpha;
+                m_used = m_next;
+            }
+            const float m_ref = (m_used == -INFINITY) ? 0.f : m_used;
+
+            // ---- P = exp2(S * scale - reference) as 16-bit values into shared memory ----------------
+            float row_sum = 0.f;
+            unsigned char *sPb = sP + b * kPfTileBytes;
+            auto chunk_p = [&](int c, const uint32_t (&s)[32]) {
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), p.scale_log2, -m_ref));
+                    float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), p.scale_log2, -m_ref));
+                    if (diagonal) {
+                        if (c * 32 + i >= n_vis) p0 = 0.f;
+                        if (c * 32 + i + 1 >= n_vis) p1 = 0.f;
+                    }
+                    row_sum += p0 + p1;
+                    packed[i >> 1] = pack16<BF16>(p0, p1);
+                }
+                // row `tid` of P, keys 32c .. 32c+31 = 64 bytes = four 16-byte chunks of the row's box
+                unsigned char *row = sPb + (c >> 1) * kPfBoxBytes + tid * 128;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int chunk = (c & 1) * 4 + q;                     // chunk inside the 128-byte row
+                    const int phys = chunk ^ (tid & 7);                    // 128-byte swizzle
+                    *reinterpret_cast<uint4 *>(row + phys * 16) =
+                        make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                }
+            };
+            chunk_p(0, s0);
+            chunk_p(1, s1);
+            chunk_p(2, s2);
+            chunk_p(3, s3);
+            l_run += row_sum;
+            proxy_fence_async_smem();     // P must be visible to the tensor core's reads of shared memory
+            tc_fence_before();            // ... and this thread's tensor-memory accesses ordered before the arrival
+            mbar_arrive(&bar_p[b]);
+        }
+
+        // ---- this row of O, normalised ---------------------------------------------------------------
+        if (ok && n_tiles > 0) {
+            ok = mbar_wait_bounded(&bar_pv, (uint32_t)((n_tiles - 1) & 1));
+            ok = __all_sync(DA_FULL_MASK, ok);
+        }
+        if (!ok) {
+            if ((tid & 31) == 0) give_up();
+        } else {
+            tc_fence_after();
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            const bool live = q0 + tid < p.seq_len;
+            unsigned char *dst = static_cast<unsigned char *>(p.out) +
+                                 ((size_t)(live ? q0 + tid : 0) * p.n_q_heads + hq) * kPfDim * 2;
+            tmem_for_chunks(tmem_row + tmem_o, [&](int c, const uint32_t (&t)[32]) {
+                if (!live) return;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int i = 8 * q;
+                    reinterpret_cast<uint4 *>(dst)[4 * c + q] =
+                        make_uint4(pack16<BF16>(__uint_as_float(t[i]) * inv, __uint_as_float(t[i + 1]) * inv),
+                                   pack16<BF16>(__uint_as_float(t[i + 2]) * inv, __uint_as_float(t[i + 3]) * inv),
+                                   pack16<BF16>(__uint_as_float(t[i + 4]) * inv, __uint_as_float(t[i + 5]) * inv),
+                                   pack16<BF16>(__uint_as_float(t[i + 6]) * inv, __uint_as_float(t[i + 7]) * inv));
+                }
+            });
         }
     }
     tc_fence_before();
@@ -435,8 +525,11 @@ extern "C" int da_prefill_attention(const void *q, const void *k, const void *v,
     if (e != cudaSuccess) return (int)e;
     if (dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
     if (!attr_set[dev]) {
-        e = cudaFuncSetAttribute(da::prefill_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        e = cudaFuncSetAttribute(da::prefill_attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  da::kPfSmemBytes);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(da::prefill_attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     da::kPfSmemBytes);
         if (e != cudaSuccess) return (int)e;
         attr_set[dev] = true;
     }
@@ -447,9 +540,9 @@ extern "C" int da_prefill_attention(const void *q, const void *k, const void *v,
     p.rep = n_q_heads / n_kv_heads;
     p.scale_log2 = 1.4426950408889634f / sqrtf((float)head_dim);
     p.status = status;
-    p.is_bf16 = bf16 ? 1 : 0;
     const dim3 grid((seq_len + da::kPfRows - 1) / da::kPfRows, n_q_heads);
-    da::prefill_attention_kernel<<<grid, da::kPfRows, da::kPfSmemBytes, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv,
-                                                                                                           p);
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    if (bf16) da::prefill_attention_kernel<true><<<grid, da::kPfThreads, da::kPfSmemBytes, cs>>>(mq, mk, mv, p);
+    else da::prefill_attention_kernel<false><<<grid, da::kPfThreads, da::kPfSmemBytes, cs>>>(mq, mk, mv, p);
     return (int)cudaGetLastError();
 }
