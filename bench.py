@@ -63,6 +63,9 @@ def parse_args():
                          "of ONE sequence sharded over the GPUs (strong scaling)")
     ap.add_argument("--library-gather", action="store_true",
                     help="N > 1: all-gather through the process group instead of the peer-memory kernel")
+    ap.add_argument("--prefill-tokens", type=int, default=32768, help="prompt length of the prefill report")
+    ap.add_argument("--only-prefill", action="store_true",
+                    help="time just the prefill kernel at --prefill-tokens (a small launch to profile) and exit")
     ap.add_argument("--no-sweep", action="store_true", help="skip the scorer / top-k sweep over page counts")
     ap.add_argument("--profile-steps", type=int, default=16, help="un-captured steps timed stage by stage")
     return ap.parse_args()
@@ -244,6 +247,26 @@ def run_b200(args):
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # stdout carries the JSON line only
         dist.init_process_group("nccl", device_id=dev)
 
+    if args.only_prefill:
+        # one small job for a profiler: three launches of the prefill kernel, checked for finiteness
+        op = da.DRAMAttention(max_output_length=8, lru_hbm_cache_size=2048, local_cache_size=512, page_size=16,
+                              top_k=512, n_kv_heads=8, head_dim=128, device=dev, dtype=torch.bfloat16)
+        g = torch.Generator(device=dev).manual_seed(2)
+        s_pf = args.prefill_tokens
+        q, k, v = (torch.randn(1, s_pf, h, 128, generator=g, device=dev).to(torch.bfloat16) for h in (32, 8, 8))
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        out = op._prefill_attention(q, k, v)
+        torch.cuda.synchronize()
+        ev0.record()
+        for _ in range(2):
+            out = op._prefill_attention(q, k, v)
+        ev1.record()
+        torch.cuda.synchronize()
+        op.check_status()
+        ms = ev0.elapsed_time(ev1) / 2
+        print(json.dumps({"prefill_tokens": s_pf, "ms": ms, "tflops": 4.0 * s_pf * s_pf / 2 * 32 * 128 / ms / 1e9,
+                          "finite": bool(torch.isfinite(out.float()).all())}), file=RESULT_OUT, flush=True)
+        return
     K, W = args.steps, max(args.warmup, 3)
     P = max(0, args.profile_steps)
     total = (W + K) * 2 + 2 * P + K + 4
@@ -603,7 +626,7 @@ def run_b200(args):
     prefill = None
     if world == 1 and P and not args.no_sweep:
         t_a = time.perf_counter()
-        pf_s = 32768
+        pf_s = args.prefill_tokens
         gp = torch.Generator(device=dev).manual_seed(2)
         pq = torch.randn(1, pf_s, w.n_q_heads, D, generator=gp, device=dev).to(w.dtype)
         pk = torch.randn(1, pf_s, hk_all, D, generator=gp, device=dev).to(w.dtype)
