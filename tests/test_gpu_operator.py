@@ -355,3 +355,9 @@ def test_million_token_layer_shard(da):
     w = llama_layer_workload(seed=0, steps=2, dram_tokens=1048576, n_kv_heads=2, lru=65536, local=8192,
                              top_k=8192, needles=32)
     _check_layer_invariants(da, w, 2)
+
+
+def test_single_kv_head_shard(da):
+    """One GPU's share at 8-way KV-head sharding of the 128K layer: one KV head, four query heads."""
+    w = llama_layer_workload(seed=0, steps=3, n_kv_heads=1)
+    _check_layer_invariants(da, w, 3)
