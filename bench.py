@@ -66,6 +66,8 @@ def parse_args():
     ap.add_argument("--prefill-tokens", type=int, default=32768, help="prompt length of the prefill report")
     ap.add_argument("--only-prefill", action="store_true",
                     help="time just the prefill kernel at --prefill-tokens (a small launch to profile) and exit")
+    ap.add_argument("--clock-period-ms", type=float, default=2.0,
+                    help="NVML polling period while the GPU works alone; the end-to-end loop is polled 10x slower")
     ap.add_argument("--no-sweep", action="store_true", help="skip the scorer / top-k sweep over page counts")
     ap.add_argument("--profile-steps", type=int, default=16, help="un-captured steps timed stage by stage")
     return ap.parse_args()
@@ -115,8 +117,23 @@ class ClockSampler:
                 pass
             time.sleep(self.period)
 
+    def sample_now(self):
+        """One sample taken by the caller's thread (brackets a region the poller is kept slow in)."""
+        if self.nv is None:
+            return
+        nv = self.nv
+        try:
+            mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+            try:
+                reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+            except Exception:
+                reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+            self.samples.append((time.perf_counter(), mhz, reasons))
+        except Exception:
+            pass
+
     def start(self):
-        if self.nv is not None:
+        if self.nv is not None and self.period > 0:
             self.thread = threading.Thread(target=self._run, daemon=True)
             self.thread.start()
 
@@ -298,7 +315,7 @@ def run_b200(args):
     hv = w.xv[:, :, :, lo:hi].contiguous().pin_memory()
     dq, dk, dv = hq.to(dev), hkk.to(dev), hv.to(dev)
 
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(local_rank, period_s=args.clock_period_ms * 1e-3)
     sampler.start()
     windows = []
 
@@ -388,18 +405,26 @@ def run_b200(args):
             pos.add_(1)
         cur_stream.synchronize()
 
+    # NVML queries take driver locks that the launch path also wants: polled every 2 ms they cost
+    # this host-bound loop ~20 us per step.  So the poller is slowed tenfold here and the region is
+    # bracketed by one sample on each side, taken outside the events.
+    fast_period = sampler.period
+    sampler.period = 10 * fast_period
     for _ in range(W):
         e2e_step(step)
         step += 1
     barrier()
     t_a = time.perf_counter()
+    sampler.sample_now()
     ev0.record()
     for _ in range(K):
         e2e_step(step)
         step += 1
     ev1.record()
     barrier()
+    sampler.sample_now()
     windows.append((t_a, time.perf_counter()))
+    sampler.period = fast_period
     ms_e2e = ev0.elapsed_time(ev1)
 
     # ---------------- per-stage timing of un-captured steps (roofline) -------------------
