@@ -795,7 +795,7 @@ def run_b200(args):
             "roofline_score": roofline_score,
             "stage_us_with_event_overhead": stage_us,
             "overlapped_timeline_us": timeline,
-            "step_layout": ("score -> {top-k -> LRU || attention phase 1} -> attention phase 2 (+fetch)"
+            "step_layout": ("{score -> top-k -> LRU || attention phase 1} -> attention phase 2 (+fetch)"
                             if overlapped else ("score -> top-k -> LRU -> attention (+fetch)" if fused else
                                                 "score -> top-k -> LRU -> fetch -> attention")),
             "misses_per_step": mean(misses),

@@ -331,7 +331,8 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 2 : 1) decode_attenti
     if (!sh_last) return;
 
     // ---- last CTA of this head (of this launch) ---------------------------------------------
-    __threadfence();
+    // Every other CTA fenced its partial row before it took its ticket, and the merge reads the
+    // rows with L2 loads issued after the barrier that follows the ticket: no fence on this side.
     merge_splits<T, D, REP, THREADS>(p, h, p.merge_first, p.merge_rows, reinterpret_cast<float *>(smem), nullptr);
     // every CTA of this head is done with the split: the one the LRU update left becomes current
     if (p.phase == 2 && tid == 0) p.flip[h] ^= 1;

@@ -67,6 +67,8 @@ class DRAMAttention(torch.nn.Module):
     # Two attention launches per step: the first (local window + slots that cannot be evicted this
     # step) runs on a side stream beside selection and LRU update, the second finishes after them.
     overlap = True
+    # ... and that first launch forks off before the page scorer rather than after it
+    fork_before_score = True
 
     # ---- cache construction ---------------------------------------------------
     def init_cache(self, k_cache: torch.Tensor, v_cache: torch.Tensor):
@@ -188,7 +190,7 @@ class DRAMAttention(torch.nn.Module):
         return ok
 
     def _generate_overlapped(self, xq, xk, xv, start_pos, out) -> None:
-        """score -> { select -> LRU update  ||  attention phase 1 } -> attention phase 2."""
+        """{ score -> select -> LRU update  ||  attention phase 1 } -> attention phase 2."""
         lc = self.lru_cache
         sel = lc.top_k_selector
         rep = xq.shape[2] // self.n_kv_heads
@@ -198,14 +200,22 @@ class DRAMAttention(torch.nn.Module):
         main = torch.cuda.current_stream()
         if not lc.split_valid:
             lc.reset_split_()
+        # Phase 1 needs nothing this step computes (only the split the previous step left), so it
+        # forks off before the scorer: its CTAs move onto the SMs as the scorer's short CTAs leave
+        # them.  The scorer is launched first so that the chain score -> select -> update is not
+        # the one that waits for SMs.
+        if self.fork_before_score:
+            self._fork.record(main)
         sel.score_(xq, lc.top_k)
-        self._fork.record(main)
-        # selection is launched before phase 1 so that its CTAs find their SMs free
-        page_list = sel.select_(1, rep, lc.top_k)
+        if not self.fork_before_score:
+            self._fork.record(main)
+            page_list = sel.select_(1, rep, lc.top_k)     # ahead of phase 1, so that its CTAs find SMs free
         self._side.wait_event(self._fork)
         with torch.cuda.stream(self._side):
             self.attend_(xq, xk, xv, start_pos, out, phase=1)
             self._join.record(self._side)
+        if self.fork_before_score:
+            page_list = sel.select_(1, rep, lc.top_k)
         lc.update_tables_(page_list, want_split=True)
         main.wait_event(self._join)
         self.attend_(xq, xk, xv, start_pos, out, phase=2)
