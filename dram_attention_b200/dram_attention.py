@@ -67,7 +67,8 @@ class DRAMAttention(torch.nn.Module):
     # Two attention launches per step: the first (local window + slots that cannot be evicted this
     # step) runs on a side stream beside selection and LRU update, the second finishes after them.
     overlap = True
-    # ... and that first launch forks off before the page scorer rather than after it
+    # ... and, when the step is being captured into a CUDA graph, that first launch forks off before
+    # the page scorer rather than after it
     fork_before_score = True
 
     # ---- cache construction ---------------------------------------------------
@@ -204,17 +205,21 @@ class DRAMAttention(torch.nn.Module):
         # forks off before the scorer: its CTAs move onto the SMs as the scorer's short CTAs leave
         # them.  The scorer is launched first so that the chain score -> select -> update is not
         # the one that waits for SMs.
-        if self.fork_before_score:
+        # Only inside a graph capture: a graph dispatches the scorer's CTAs ahead of phase 1's (node
+        # order), whereas two eager launches that become ready together (a backlogged GPU) may be
+        # dispatched either way round, and phase 1 first would starve the scorer of SMs.
+        early = self.fork_before_score and torch.cuda.is_current_stream_capturing()
+        if early:
             self._fork.record(main)
         sel.score_(xq, lc.top_k)
-        if not self.fork_before_score:
+        if not early:
             self._fork.record(main)
             page_list = sel.select_(1, rep, lc.top_k)     # ahead of phase 1, so that its CTAs find SMs free
         self._side.wait_event(self._fork)
         with torch.cuda.stream(self._side):
             self.attend_(xq, xk, xv, start_pos, out, phase=1)
             self._join.record(self._side)
-        if self.fork_before_score:
+        if early:
             page_list = sel.select_(1, rep, lc.top_k)
         lc.update_tables_(page_list, want_split=True)
         main.wait_event(self._join)
