@@ -46,7 +46,7 @@ METRIC = "decode tok/s at 128K ctx (Llama-3-8B attn shape)"
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one attention launch at the default workload, from the ncu
 # capture summarised in profiles/decode_attention_mma_llama128k.md
-ATTN_TRAFFIC_BYTES_128K = 155.5e6
+ATTN_TRAFFIC_BYTES_128K = 154.4e6
 
 
 def parse_args():
