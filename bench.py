@@ -66,6 +66,9 @@ def parse_args():
     ap.add_argument("--prefill-tokens", type=int, default=32768, help="prompt length of the prefill report")
     ap.add_argument("--only-prefill", action="store_true",
                     help="time just the prefill kernel at --prefill-tokens (a small launch to profile) and exit")
+    ap.add_argument("--settle-steps", type=int, default=192,
+                    help="untimed decode steps before the warm-up, so that the slot table holds what the query "
+                         "stream uses rather than the warm start of the cache construction (steady-state decode)")
     ap.add_argument("--clock-period-ms", type=float, default=2.0,
                     help="NVML polling period while the GPU works alone; the end-to-end loop is polled 10x slower")
     ap.add_argument("--no-sweep", action="store_true", help="skip the scorer / top-k sweep over page counts")
@@ -286,7 +289,8 @@ def run_b200(args):
         return
     K, W = args.steps, max(args.warmup, 3)
     P = max(0, args.profile_steps)
-    total = (W + K) * 2 + 2 * P + K + 4
+    settle = max(0, args.settle_steps)
+    total = settle + (W + K) * 2 + 2 * P + K + 4
     # N > 1, default: every GPU decodes its own sequence (same shapes, its own seed); no collective
     by_seq = world > 1 and args.shard == "sequence"
     n_seq = world if by_seq else 1
@@ -327,7 +331,7 @@ def run_b200(args):
 
     # ---------------- value: K captured steps, inputs resident in HBM -----------------
     step = 0
-    for _ in range(W):
+    for _ in range(settle + W):     # the settle steps are part of the set-up, the last W are the warm-up
         op(dq[step], dk[step], dv[step], start_pos=S + step, stage="generate")
         step += 1
     torch.cuda.synchronize()
@@ -691,7 +695,7 @@ def run_b200(args):
     sharded_report = None
     if by_seq:
         t_a = time.perf_counter()
-        n_sh = W + K + 2
+        n_sh = settle + W + K + 2
         w0 = w if rank == 0 else llama_layer_workload(seed=0, steps=n_sh, dram_tokens=args.dram_tokens,
                                                       max_out=n_sh)
         lo0, hi0 = head_range(hk_all, rank, world)
@@ -703,12 +707,13 @@ def run_b200(args):
         sk = w0.xk[:n_sh, :, :, lo0:hi0].contiguous().to(dev)
         sv = w0.xv[:n_sh, :, :, lo0:hi0].contiguous().to(dev)
         S0 = w0.prefill_len
-        for i in range(W):
+        w_sh = settle + W
+        for i in range(w_sh):
             sh(sq[i], sk[i], sv[i], start_pos=S0 + i, stage="generate")
         torch.cuda.synchronize()
         g_sh = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g_sh):
-            outs_sh = [sh(sq[W + i], sk[W + i], sv[W + i], start_pos=S0 + W + i, stage="generate")
+            outs_sh = [sh(sq[w_sh + i], sk[w_sh + i], sv[w_sh + i], start_pos=S0 + w_sh + i, stage="generate")
                        for i in range(K)]
         up = upload_graph(g_sh, torch)
         barrier()
@@ -778,6 +783,7 @@ def run_b200(args):
                                         ("all-gather of per-head outputs by peer stores over NVLink (da_gather_heads)"
                                          if getattr(op, "_peer", None) is not None else
                                          "NCCL all-gather of per-head outputs")),
+                           settle_steps=settle,
                            timed_region=("one CUDA graph of K steps, " +
                                          ("uploaded to the device" if uploaded else "launched behind a spin kernel") +
                                          " before the first event" if captured else
