@@ -7,15 +7,22 @@ One "step" = one generate step (one new token) of one attention layer: page
 scoring, top-k selection, LRU update, miss fetch, decode attention.  Prints one
 JSON line.
 
+Set-up (untimed): cache construction, then --settle-steps decode steps, so that the slot
+table holds what the query stream uses (steady-state decode), then W warm-up steps.
+
 value   decode tok/s with every input resident in HBM: the K timed steps are
-        captured, with their own device-resident inputs, in one CUDA graph and
-        timed with CUDA events (max over ranks).
+        captured, with their own device-resident inputs, in one CUDA graph, the
+        graph is uploaded, and one replay is timed with CUDA events (max over ranks).
 e2e     the same metric through the operator API with HOST inputs: per step the
-        query/key/value are copied from pinned host memory, one captured step is
-        replayed, the output is copied back and the stream is synchronised.
-roofline  attention kernel (the dominant launch): algorithmic bytes / its mean
-        launch time, measured with CUDA events around each stage of un-captured
-        steps; peak = the measured HBM copy bandwidth of this pool.
+        query/key/value are written into a pinned staging buffer, one captured graph
+        (host->device copy, the step, device->host copy of the output) is replayed
+        and the stream is synchronised.
+roofline  attention kernel (the dominant launch): algorithmic bytes / its launch
+        time, measured as the difference of two replayed graphs (L2 eviction +
+        kernel, eviction alone); peak = the measured HBM copy bandwidth of this pool.
+fetch_report, scorer_sweep, prefill  the miss fetch (exposed share of a step, a cold
+        step against the host link), scorer/top-k over 512..65536 pages, and the
+        prefill kernel's TFLOP/s; extras, not part of the metric.
 cpu_baseline  the CPU oracle (a port of the reference's pure-PyTorch path) timed on
         a bounded sample of the same workload on this box's host cores.
 
