@@ -21,8 +21,9 @@
 // only when a tile's maximum outgrows the reference by more than 2^8 - after the first tiles,
 // hardly ever.  The loop is software-pipelined so that the tensor core is not waited on in
 // line: S of tile j+1 is issued (into a second S buffer) before the softmax of tile j starts,
-// and the product of tile j runs during the softmax of tile j+1.  Key and value tiles are double-buffered (a key stage is refilled as soon as its S
-// is complete, a value stage once its product is).  Every wait on an mbarrier is bounded: a
+// and the product of tile j runs during the softmax of tile j+1.  Key and value tiles are
+// double-buffered (a key stage is refilled as soon as its S is complete, a value stage once
+// its product is).  Every wait on an mbarrier is bounded: a
 // wait that runs out sets DA_STATUS_WAIT_TIMEOUT and a flag that makes both roles leave their
 // loops; the CTA then frees its tensor memory and returns.
 //
