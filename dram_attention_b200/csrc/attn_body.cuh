@@ -1,0 +1,269 @@
+// The decode-attention kernel without its arithmetic: unit scheduling, the asynchronous copies
+// into per-warp stage rings, the append of the new keys/values, the publication of the partials
+// and the ticket that elects the merging CTA.  The arithmetic (how a 16-token unit in shared
+// memory updates the running softmax state) comes from a `Math` policy: CUDA-core FMAs for
+// float32 (attn.cu), warp-level tensor-core MMAs for 16-bit types (attn_mma.cu).
+//
+// Work unit = 16 consecutive tokens of one KV head.  A warp owns a private ring of stages with
+// one mbarrier each, so the main loop has no CTA-wide synchronisation.  Units are dealt
+// round-robin to the (CTA, warp) workers of a head; a warp plans 64 of its units at a time
+// (two per lane: where the unit lies, whether it has to come from DRAM) and walks a round with
+// the DRAM-sourced units first.
+//
+// Math policy interface:
+//   Elem, kD, kPitch (bytes between two tokens of a stage), kStages, kPerTokenCopy
+//   struct State; init(State&, p, h, lane, rows); consume(State&, stage, avail, lane);
+//   publish(State&, red, lane, rows)   red = float [rows][D + 4] of this warp
+#pragma once
+
+#include "attn_common.cuh"
+
+namespace da {
+
+template <typename Math, int WARPS>
+__device__ __forceinline__ void decode_attention_body(const AttnParams &p, unsigned char *smem) {
+    using T = typename Math::Elem;
+    constexpr int D = Math::kD;
+    constexpr int E = (int)sizeof(T);
+    constexpr int ROWB = D * E;                  // one key (or value) row in HBM
+    constexpr int TOKB = 2 * ROWB;               // one token of the slot table: key row, value row
+    constexpr int PITCH = Math::kPitch;          // the same token in a stage
+    constexpr int STAGEB = kUnitTokens * PITCH;
+    constexpr int STAGES = Math::kStages;
+    constexpr int PW = PartialRow<D>::kWidth;
+    constexpr int THREADS = WARPS * 32;
+    constexpr float NEG_INF = -INFINITY;
+    static_assert(STAGES * STAGEB >= kAttnMaxRows * PW * (int)sizeof(float), "a warp's ring holds its partial");
+
+    __shared__ __align__(8) uint64_t bars[WARPS][STAGES];
+    __shared__ int sh_last;
+    __shared__ unsigned char perm_s[WARPS][kRoundUnits];
+
+    const int h = blockIdx.y;
+    const int x = blockIdx.x;
+    const int splits = gridDim.x;
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int rows = p.n_q * p.rep;
+
+    // ---- position and unit range ------------------------------------------------
+    const int pos = p.start_pos_dev ? *p.start_pos_dev : p.start_pos_host;
+    int t0 = pos - p.dram_tokens;   // index of the first new token in the local window
+    bool pos_ok = true;
+    if (t0 < 0 || t0 + p.s_total > p.local_capacity) {
+        pos_ok = false;
+        if (tid == 0 && x == 0) atomicOr(p.status, DA_STATUS_BAD_POSITION);
+        t0 = t0 < 0 ? 0 : p.local_capacity - p.s_total;
+    }
+    const int n_local = t0 + p.s_total;
+    const int n_prefix = p.n_prefix_tokens;
+    const int n_workers = splits * WARPS;
+    const int worker = x * WARPS + warp;
+    const LaunchUnits lu = launch_units(p, h, n_local);
+    const int units_prefix = lu.units_slots;
+    const int units = lu.units_slots + lu.units_local;
+    const int total_my = units > worker ? (units - worker + n_workers - 1) / n_workers : 0;
+
+    unsigned char *my_stages = smem + (size_t)warp * STAGES * STAGEB;
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < STAGES; ++s) mbar_init(&bars[warp][s], 1);
+    }
+    mbar_fence_init();
+    __syncthreads();
+
+    // ---- append the new keys/values to the local window ----------------------------
+    if (x == 0 && warp == 0 && pos_ok && p.phase != 2 && p.q_tok0 == 0) {
+        for (int i = 0; i < p.s_total; ++i) {
+            const size_t srco = ((size_t)i * p.n_kv_heads + h) * ROWB;
+            const uint4 *sk = reinterpret_cast<const uint4 *>(p.new_k + srco);
+            const uint4 *sv = reinterpret_cast<const uint4 *>(p.new_v + srco);
+            const size_t off = ((size_t)(t0 + i) * p.local_tok_stride + (size_t)h * p.local_head_stride) * E;
+            uint4 *dk = reinterpret_cast<uint4 *>(p.local_k + off);
+            uint4 *dv = reinterpret_cast<uint4 *>(p.local_v + off);
+            for (int c = lane; c < ROWB / 16; c += 32) {
+                dk[c] = sk[c];
+                dv[c] = sv[c];
+            }
+        }
+    }
+
+    typename Math::State st;
+    Math::init(st, p, h, lane, rows);
+
+    const uint64_t stream_policy = l2_policy_evict_first();   // the KV stream is read once per step
+    const bool planned = p.slot_source != nullptr || lu.order != nullptr;
+    bool dead = false;
+
+    for (int round = 0; round * kRoundUnits < total_my && !dead; ++round) {
+        UnitPlan plan;
+        int perm[2] = {0, 0};
+        if (planned) {
+            plan = plan_round(p, lu, h, worker, n_workers, lane, round, total_my);
+            plan_order(plan, lane, perm, perm_s[warp]);
+        } else {
+            plan.n_round = min(kRoundUnits, total_my - round * kRoundUnits);
+            plan.base[0] = plan.base[1] = plan.src[0] = plan.src[1] = -1;
+        }
+        const int n_round = plan.n_round;
+        const int g0 = round * kRoundUnits;   // units this warp has consumed before this round
+
+        auto unit_index = [&](int it) -> int {
+            const int v = plan_lookup(perm, it);
+            return planned ? v : it;
+        };
+        // first slot-table token of the unit with index idx of this round
+        auto unit_base = [&](int u, int idx) -> int {
+            const int b = plan_lookup(plan.base, idx);
+            return planned ? b : u * kUnitTokens;
+        };
+        auto unit_src = [&](int idx) -> int {
+            const int v = plan_lookup(plan.src, idx);
+            return planned ? v : -1;
+        };
+        // tokens that exist from the unit's first token on (before any causal cut)
+        auto unit_avail = [&](int u, int base) -> int {
+            if (u < units_prefix) return n_prefix - base;
+            return n_local - (u - units_prefix) * kUnitTokens;
+        };
+
+        // start the copies of the unit at position `it` of this round into stage s
+        auto issue = [&](int s, int it) {
+            const int idx = unit_index(it);
+            const int u = worker + (g0 + idx) * n_workers;
+            uint64_t *bar = &bars[warp][s];
+            unsigned char *dst = my_stages + (size_t)s * STAGEB;
+            const int base = unit_base(u, idx);
+            const int src_page = unit_src(idx);
+            const int ntok = min(kUnitTokens, unit_avail(u, base));
+            if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)ntok * TOKB);
+            __syncwarp();
+            if (u < units_prefix) {
+                const size_t tok = (size_t)base;
+                const unsigned char *src =
+                    src_page < 0 ? p.prefix + ((size_t)h * p.prefix_head_stride + tok * 2 * D) * E
+                                 : p.dram + ((size_t)h * p.dram_head_stride +
+                                             ((size_t)src_page * p.page_tokens + tok % p.page_tokens) * 2 * D) * E;
+                if constexpr (Math::kPerTokenCopy) {
+                    // a token's key and value rows are contiguous in HBM: one copy per token
+                    if (lane < ntok) bulk_copy_g2s_hint(dst + lane * PITCH, src + (size_t)lane * TOKB, TOKB, bar,
+                                                         stream_policy);
+                } else {
+                    if (lane == 0) bulk_copy_g2s_hint(dst, src, (uint32_t)ntok * TOKB, bar, stream_policy);
+                }
+            } else {
+                // local window: one copy per row, key rows by lanes 0..15, value rows by lanes 16..31
+                const int tl = lane & 15;
+                const int is_v = lane >> 4;
+                if (tl < ntok) {
+                    const int t = (u - units_prefix) * kUnitTokens + tl;
+                    const unsigned char *src;
+                    if (t >= t0) {   // one of this call's new tokens: straight from the inputs
+                        src = (is_v ? p.new_v : p.new_k) + ((size_t)(t - t0) * p.n_kv_heads + h) * ROWB;
+                    } else {
+                        src = (is_v ? p.local_v : p.local_k) +
+                              ((size_t)t * p.local_tok_stride + (size_t)h * p.local_head_stride) * E;
+                    }
+                    bulk_copy_g2s_hint(dst + tl * PITCH + is_v * ROWB, src, ROWB, bar, stream_policy);
+                }
+            }
+        };
+
+        for (int it = 0; it < STAGES && it < n_round; ++it) issue((g0 + it) % STAGES, it);
+
+        for (int it = 0; it < n_round; ++it) {
+            const int g = g0 + it;
+            const int s = g % STAGES;
+            const bool arrived = mbar_wait_bounded(&bars[warp][s], (uint32_t)((g / STAGES) & 1));
+            if (!__all_sync(DA_FULL_MASK, arrived)) {
+                if (lane == 0) atomicOr(p.status, DA_STATUS_WAIT_TIMEOUT);
+                dead = true;
+                break;
+            }
+            const int idx = unit_index(it);
+            const int u = worker + (g0 + idx) * n_workers;
+            const int base = unit_base(u, idx);
+            const int avail = unit_avail(u, base);
+            const int ntok = min(kUnitTokens, avail);
+            unsigned char *sb = my_stages + (size_t)s * STAGEB;
+            if (u < units_prefix && unit_src(idx) >= 0) {
+                // this unit came from DRAM: write it through to its slot
+                unsigned char *slot = const_cast<unsigned char *>(p.prefix) +
+                                      ((size_t)h * p.prefix_head_stride + (size_t)base * 2 * D) * E;
+                for (int i = lane; i < ntok * (TOKB / 16); i += 32) {
+                    const int t = i / (TOKB / 16), c = i % (TOKB / 16);
+                    reinterpret_cast<uint4 *>(slot + (size_t)t * TOKB)[c] =
+                        reinterpret_cast<const uint4 *>(sb + t * PITCH)[c];
+                }
+            }
+            if (ntok < kUnitTokens) {
+                // rows past the end hold stale bytes: zero the value rows so that 0 * garbage
+                // cannot produce NaN (their logits are masked)
+                for (int i = lane; i < (kUnitTokens - ntok) * (ROWB / 16); i += 32) {
+                    const int r = ntok + i / (ROWB / 16);
+                    reinterpret_cast<uint4 *>(sb + ROWB + r * PITCH)[i % (ROWB / 16)] = make_uint4(0, 0, 0, 0);
+                }
+                __syncwarp();
+            }
+
+            Math::consume(st, sb, avail, lane, p.scale_log2);
+
+            __syncwarp();
+            if (it + STAGES < n_round) issue(s, it + STAGES);
+        }
+    }
+
+    // ---- this warp's partial into its own (now idle) ring ----------------------------------
+    float *red = reinterpret_cast<float *>(my_stages);
+    Math::publish(st, red, lane, rows);
+    __syncthreads();
+
+    // ---- merge the warps, write this CTA's partial ------------------------------------
+    float *part = p.partials + ((size_t)(h * p.part_rows + p.part_offset + x) * rows) * PW;
+    for (int e = tid; e < rows * PW; e += THREADS) {
+        const int r = e / PW;
+        const int c = e % PW;
+        float mn = NEG_INF;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w)
+            mn = fmaxf(mn, reinterpret_cast<const float *>(smem + (size_t)w * STAGES * STAGEB)[r * PW + D]);
+        float outv;
+        if (c == D) {
+            outv = mn;
+        } else if (c > D + 1) {
+            outv = 0.f;  // padding
+        } else {
+            const float ms = (mn == NEG_INF) ? 0.f : mn;
+            outv = 0.f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) {
+                const float *rw = reinterpret_cast<const float *>(smem + (size_t)w * STAGES * STAGEB) + r * PW;
+                outv += rw[c] * fast_exp2(rw[D] - ms);
+            }
+        }
+        part[e] = outv;  // c < D: weighted acc; c == D: max; c == D + 1: weighted l
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned int ticket = atomicAdd(&p.counters[h], 1u);
+        sh_last = (ticket == (unsigned int)(p.ticket_target - 1));
+    }
+    __syncthreads();
+    if (!sh_last) return;
+
+    // ---- the CTA of this head that finished last (of both launches, when there are two) --------
+    __threadfence();   // the other CTAs fenced their rows before their tickets: pair that here
+    int first = 0, n_rows = p.part_rows;
+    if (p.phase != 0 && __ldcg(p.redo + h) != 0) {
+        first = p.splits1;                 // the head was redone by phase 2: leave phase 1's rows out
+        n_rows = p.part_rows - p.splits1;
+    }
+    merge_splits<T, D, THREADS>(p, h, first, n_rows, rows, reinterpret_cast<float *>(smem));
+    // every CTA of this head is done with the eviction front: the one the LRU update left becomes current
+    if (p.phase != 0 && tid == 0) p.flip[h] ^= 1;
+    if (tid == 0) p.counters[h] = 0u;
+}
+
+}  // namespace da

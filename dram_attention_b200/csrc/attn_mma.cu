@@ -18,7 +18,7 @@
 // in distinct banks.  A token of the slot table arrives by one bulk copy (TMA) of
 // both rows (they are contiguous in the page layout), issued one per lane.
 
-#include "attn_common.cuh"
+#include "attn_body.cuh"
 
 namespace da {
 
@@ -36,6 +36,14 @@ template <> struct MmaTraits<__nv_bfloat16> {
             : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
             : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
     }
+    __device__ __forceinline__ static void mma16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                 uint32_t b0, uint32_t b1) {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+            "{%0,%1,%2,%3};"
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
 };
 template <> struct MmaTraits<__half> {
     __device__ __forceinline__ static uint32_t pack(float lo, float hi) {
@@ -48,6 +56,14 @@ template <> struct MmaTraits<__half> {
             "{%0,%1,%2,%3};"
             : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
             : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+    }
+    __device__ __forceinline__ static void mma16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                 uint32_t b0, uint32_t b1) {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+            "{%0,%1,%2,%3};"
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
     }
 };
 
@@ -65,192 +81,70 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void *
                  : "memory");
 }
 
-template <typename T, int D, int REP, int STAGES, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 2 : 1) decode_attention_mma_kernel(const AttnParams p) {
-    static_assert(sizeof(T) == 2 && REP <= 8 && D % 32 == 0, "16-bit types, at most 8 query rows");
-    constexpr int E = 2;
-    constexpr int ROWB = D * E;                   // one key (or value) row in HBM
-    constexpr int PITCH = 2 * ROWB + 16;          // padded token (key row, value row) in shared memory
-    constexpr int STAGEB = kUnitTokens * PITCH;
-    constexpr int KSTEPS = D / 16;                // k-steps of the QK contraction
-    constexpr int NT = D / 8;                     // n-tiles of the PV contraction
-    constexpr int PW = PartialRow<D>::kWidth;
-    constexpr float NEG_INF = -INFINITY;
-    constexpr int THREADS = WARPS * 32;
+// Arithmetic of a 16-token unit on tensor cores.  FULL = false: at most 8 query rows (rows 8..15
+// of the A operand are zero and their accumulators are never read); FULL = true: up to 16 rows
+// (several query tokens per call).
+template <typename T, int D_, bool FULL>
+struct MmaMath {
+    using Elem = T;
+    static constexpr int kD = D_;
+    static constexpr int ROWB = kD * 2;                   // one key (or value) row in HBM
+    static constexpr int kPitch = 2 * ROWB + 16;          // padded token (key row, value row) in shared memory
+    static constexpr int STAGEB = kUnitTokens * kPitch;
+    static constexpr int kStages = STAGEB > 8192 ? 3 : 4;
+    static constexpr bool kPerTokenCopy = true;
+    static constexpr int KSTEPS = kD / 16;                // k-steps of the QK contraction
+    static constexpr int NT = kD / 8;                     // n-tiles of the PV contraction
+    static constexpr int NR = FULL ? 2 : 1;               // query rows per lane: lane / 4 (and + 8)
+    static_assert(sizeof(T) == 2 && kD % 32 == 0, "16-bit element types");
 
-    extern __shared__ __align__(128) unsigned char smem[];
-    __shared__ __align__(8) uint64_t bars[WARPS][STAGES];
-    __shared__ float red[WARPS][REP][PW];
-    __shared__ int sh_last;
-    __shared__ unsigned char perm_s[WARPS][64];
+    struct State {
+        uint32_t qa[NR][2][KSTEPS];   // A fragments of Q: [row half][k half][k-step]
+        float m_run[NR];              // row max (quad-uniform)
+        float l_part[NR];             // this lane's share of the row sum
+        float o[NT][4];
+        int back[NR];                 // tokens at the end of a unit's range that the row must not see
+    };
 
-    const int h = blockIdx.y;
-    const int x = blockIdx.x;
-    const int splits = gridDim.x;
-    const int tid = threadIdx.x;
-    const int lane = tid & 31;
-    const int warp = tid >> 5;
-    const int row = lane >> 2;  // query row of this lane's accumulators
-    const int qd = lane & 3;    // position inside the quad
-
-    // ---- position and unit range ------------------------------------------------
-    const int pos = p.start_pos_dev ? *p.start_pos_dev : p.start_pos_host;
-    int t_new = pos - p.dram_tokens;
-    bool pos_ok = true;
-    if (t_new < 0 || t_new >= p.local_capacity) {
-        pos_ok = false;
-        if (tid == 0 && x == 0) atomicOr(p.status, DA_STATUS_BAD_POSITION);
-        t_new = t_new < 0 ? 0 : p.local_capacity - 1;
-    }
-    const int n_local = t_new + 1;
-    const int n_prefix = p.n_prefix_tokens;
-    const int n_workers = splits * WARPS;
-    const int worker = x * WARPS + warp;
-    const UnitPlan plan = plan_units(p, h, n_local, worker, n_workers, lane);
-    const int units_prefix = plan.units_slots;   // units of this launch that come from the slot table
-    const int n_my = plan.n_my;
-
-    unsigned char *my_stages = smem + (size_t)warp * STAGES * STAGEB;
-    if (lane == 0) {
+    __device__ __forceinline__ static void init(State &st, const AttnParams &p, int h, int lane, int rows) {
+        const int qd = lane & 3;
+        const int hq = p.n_kv_heads * p.rep;
 #pragma unroll
-        for (int s = 0; s < STAGES; ++s) mbar_init(&bars[warp][s], 1);
-    }
-    mbar_fence_init();
-    __syncthreads();
-
-    // ---- append the new key/value to the local window -----------------------------
-    if (x == 0 && warp == 0 && pos_ok && p.phase != 2) {
-        const uint4 *sk = reinterpret_cast<const uint4 *>(p.new_k + (size_t)h * ROWB);
-        const uint4 *sv = reinterpret_cast<const uint4 *>(p.new_v + (size_t)h * ROWB);
-        const size_t off = ((size_t)t_new * p.local_tok_stride + (size_t)h * p.local_head_stride) * E;
-        uint4 *dk = reinterpret_cast<uint4 *>(p.local_k + off);
-        uint4 *dv = reinterpret_cast<uint4 *>(p.local_v + off);
-        for (int i = lane; i < ROWB / 16; i += 32) {
-            dk[i] = sk[i];
-            dv[i] = sv[i];
-        }
-    }
-
-    // ---- Q as A-operand fragments: rows >= REP are zero -------------------------------
-    uint32_t qa0[KSTEPS], qa2[KSTEPS];
-    {
-        const unsigned char *qrow = p.q + ((size_t)(h * REP + (row < REP ? row : 0))) * ROWB;
+        for (int half = 0; half < NR; ++half) {
+            const int r = (lane >> 2) + 8 * half;
+            const bool live = r < rows;
+            const int tok = p.q_tok0 + (live ? r / p.rep : 0);
+            const unsigned char *qrow = p.q + ((size_t)tok * hq + (size_t)h * p.rep + (live ? r % p.rep : 0)) * ROWB;
 #pragma unroll
-        for (int ks = 0; ks < KSTEPS; ++ks) {
-            const uint32_t w0 = *reinterpret_cast<const uint32_t *>(qrow + (16 * ks + 2 * qd) * E);
-            const uint32_t w2 = *reinterpret_cast<const uint32_t *>(qrow + (16 * ks + 8 + 2 * qd) * E);
-            qa0[ks] = row < REP ? w0 : 0u;
-            qa2[ks] = row < REP ? w2 : 0u;
+            for (int ks = 0; ks < KSTEPS; ++ks) {
+                const uint32_t w0 = *reinterpret_cast<const uint32_t *>(qrow + (16 * ks + 2 * qd) * 2);
+                const uint32_t w2 = *reinterpret_cast<const uint32_t *>(qrow + (16 * ks + 8 + 2 * qd) * 2);
+                st.qa[half][0][ks] = live ? w0 : 0u;
+                st.qa[half][1][ks] = live ? w2 : 0u;
+            }
+            st.back[half] = live ? p.s_total - 1 - tok : 0;
+            st.m_run[half] = -INFINITY;
+            st.l_part[half] = 0.f;
         }
+#pragma unroll
+        for (int d = 0; d < NT; ++d) st.o[d][0] = st.o[d][1] = st.o[d][2] = st.o[d][3] = 0.f;
     }
 
-    float m_run = NEG_INF, l_part = 0.f;  // row max (quad-uniform); this lane's share of the row sum
-    float o[NT][4];
-#pragma unroll
-    for (int d = 0; d < NT; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+    __device__ __forceinline__ static void mma(float (&d)[4], const State &st, int ks, uint32_t b0, uint32_t b1) {
+        if constexpr (FULL) MmaTraits<T>::mma16(d, st.qa[0][0][ks], st.qa[1][0][ks], st.qa[0][1][ks], st.qa[1][1][ks], b0, b1);
+        else MmaTraits<T>::mma(d, st.qa[0][0][ks], st.qa[0][1][ks], b0, b1);
+    }
 
-    const uint64_t stream_policy = l2_policy_evict_first();   // the KV stream is read once per step
-    // The warp visits its units in the order perm[0], perm[1], ...: DRAM-sourced units first.
-    int perm[2] = {0, 0};
-    const bool planned = p.slot_source != nullptr;   // then the host guarantees n_my <= 64
-    if (planned) plan_order(plan, lane, perm, perm_s[warp]);
-    auto unit_index = [&](int it) -> int {
-        const int v = plan_lookup(perm, it);
-        return planned ? v : it;
-    };
-    // first slot-table token of the warp's unit with index idx, and the DRAM page to read it from (or -1)
-    auto unit_base = [&](int u, int idx) -> int {
-        const int b = plan_lookup(plan.base, idx);
-        return p.phase == 0 ? u * kUnitTokens : b;
-    };
-    auto unit_src = [&](int idx) -> int {
-        const int v = plan_lookup(plan.src, idx);
-        return planned ? v : -1;
-    };
-    auto unit_tokens = [&](int u, int base) -> int {
-        if (u < units_prefix) return min(kUnitTokens, n_prefix - base);
-        return min(kUnitTokens, n_local - (u - units_prefix) * kUnitTokens);
-    };
-
-    // Slot-table units: one bulk copy per token (its key and value rows are contiguous in
-    // HBM), issued by lanes 0..15.  Local-window units: one copy per row, key rows by
-    // lanes 0..15 and value rows by lanes 16..31.
-    auto issue = [&](int s, int it) {
-        const int idx = unit_index(it);
-        const int u = worker + idx * n_workers;
-        uint64_t *bar = &bars[warp][s];
-        unsigned char *dst = my_stages + (size_t)s * STAGEB;
-        const int base = unit_base(u, idx);
-        const int src_page = unit_src(idx);
-        const int ntok = unit_tokens(u, base);
-        if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)ntok * 2 * ROWB);
-        __syncwarp();
-        const int tl = lane & 15;
-        const int is_v = lane >> 4;
-        if (tl < ntok) {
-            if (u < units_prefix) {
-                if (!is_v) {
-                    const size_t tok = (size_t)base + tl;
-                    const unsigned char *src =
-                        src_page < 0
-                            ? p.prefix + ((size_t)h * p.prefix_head_stride + tok * 2 * D) * E
-                            : p.dram + ((size_t)h * p.dram_head_stride +
-                                        ((size_t)src_page * p.page_tokens + tok % p.page_tokens) * 2 * D) * E;
-                    bulk_copy_g2s_hint(dst + tl * PITCH, src, 2 * ROWB, bar, stream_policy);
-                }
-            } else {
-                const int t = (u - units_prefix) * kUnitTokens + tl;
-                const unsigned char *src;
-                if (t == t_new) {
-                    src = (is_v ? p.new_v : p.new_k) + (size_t)h * ROWB;
-                } else {
-                    src = (is_v ? p.local_v : p.local_k) +
-                          ((size_t)t * p.local_tok_stride + (size_t)h * p.local_head_stride) * E;
-                }
-                bulk_copy_g2s_hint(dst + tl * PITCH + is_v * ROWB, src, ROWB, bar, stream_policy);
-            }
-        }
-    };
-
-    for (int it = 0; it < STAGES && it < n_my; ++it) issue(it, it);
-
-    // ldmatrix row addresses of this lane inside a stage
-    const int lm = lane >> 3;   // which 8x8 tile of the x4 load
-    const int lr = lane & 7;    // row inside the tile
-    const int k_off = lr * PITCH + lm * 16;                               // key tile: rows lr, 16-byte column block lm
-    const int v_off = ROWB + ((lm & 1) * 8 + lr) * PITCH + (lm >> 1) * 16;    // value tile (transposed load)
-
-    for (int it = 0; it < n_my; ++it) {
-        const int s = it % STAGES;
-        const bool arrived = mbar_wait_bounded(&bars[warp][s], (uint32_t)((it / STAGES) & 1));
-        if (!__all_sync(DA_FULL_MASK, arrived)) {
-            if (lane == 0) atomicOr(p.status, DA_STATUS_WAIT_TIMEOUT);
-            break;
-        }
-        const int idx = unit_index(it);
-        const int u = worker + idx * n_workers;
-        const int base = unit_base(u, idx);
-        const int ntok = unit_tokens(u, base);
-        unsigned char *sb = my_stages + (size_t)s * STAGEB;
-        if (unit_src(idx) >= 0 && u < units_prefix) {
-            // this unit came from DRAM: write it through to its slot (512 bytes per token)
-            unsigned char *slot = const_cast<unsigned char *>(p.prefix) +
-                                  ((size_t)h * p.prefix_head_stride + (size_t)base * 2 * D) * E;
-            for (int i = lane; i < ntok * (2 * ROWB / 16); i += 32) {
-                const int t = i / (2 * ROWB / 16), c = i % (2 * ROWB / 16);
-                reinterpret_cast<uint4 *>(slot + (size_t)t * 2 * ROWB)[c] =
-                    reinterpret_cast<const uint4 *>(sb + t * PITCH)[c];
-            }
-        }
-        if (ntok < kUnitTokens) {
-            // rows past the end hold stale bytes: zero the value rows so that 0 * garbage
-            // cannot produce NaN (their logits are masked below)
-            for (int i = lane; i < (kUnitTokens - ntok) * (ROWB / 16); i += 32) {
-                const int r = ntok + i / (ROWB / 16);
-                reinterpret_cast<uint4 *>(sb + ROWB + r * PITCH)[i % (ROWB / 16)] = make_uint4(0, 0, 0, 0);
-            }
-            __syncwarp();
-        }
+    // `avail` = tokens that exist from the unit's first token on; a row sees the first avail - back
+    __device__ __forceinline__ static void consume(State &st, const unsigned char *sb, int avail, int lane,
+                                                   float scale_log2) {
+        constexpr float NEG_INF = -INFINITY;
+        const int qd = lane & 3;
+        // ldmatrix row addresses of this lane inside a stage
+        const int lm = lane >> 3;   // which 8x8 tile of the x4 load
+        const int lr = lane & 7;    // row inside the tile
+        const int k_off = lr * kPitch + lm * 16;                               // key tile: rows lr, 16-byte column block lm
+        const int v_off = ROWB + ((lm & 1) * 8 + lr) * kPitch + (lm >> 1) * 16;    // value tile (transposed load)
 
         // ---- S = Q K^T for 16 tokens (two n-tiles of 8) --------------------------------
         float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
@@ -258,118 +152,97 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 2 : 1) decode_attenti
         for (int kp = 0; kp < KSTEPS / 2; ++kp) {
             uint32_t b[4];
             ldmatrix_x4(b, sb + k_off + kp * 64);                 // tokens 0..7, channels 32kp .. 32kp+31
-            MmaTraits<T>::mma(s0, qa0[2 * kp], qa2[2 * kp], b[0], b[1]);
-            MmaTraits<T>::mma(s0, qa0[2 * kp + 1], qa2[2 * kp + 1], b[2], b[3]);
-            ldmatrix_x4(b, sb + k_off + 8 * PITCH + kp * 64);     // tokens 8..15
-            MmaTraits<T>::mma(s1, qa0[2 * kp], qa2[2 * kp], b[0], b[1]);
-            MmaTraits<T>::mma(s1, qa0[2 * kp + 1], qa2[2 * kp + 1], b[2], b[3]);
+            mma(s0, st, 2 * kp, b[0], b[1]);
+            mma(s0, st, 2 * kp + 1, b[2], b[3]);
+            ldmatrix_x4(b, sb + k_off + 8 * kPitch + kp * 64);    // tokens 8..15
+            mma(s1, st, 2 * kp, b[0], b[1]);
+            mma(s1, st, 2 * kp + 1, b[2], b[3]);
         }
-        // this lane: row `row`, tokens 2qd, 2qd+1, 8+2qd, 9+2qd
-        float v0 = s0[0] * p.scale_log2, v1 = s0[1] * p.scale_log2;
-        float v2 = s1[0] * p.scale_log2, v3 = s1[1] * p.scale_log2;
-        if (2 * qd >= ntok) v0 = NEG_INF;
-        if (2 * qd + 1 >= ntok) v1 = NEG_INF;
-        if (8 + 2 * qd >= ntok) v2 = NEG_INF;
-        if (9 + 2 * qd >= ntok) v3 = NEG_INF;
-
-        // ---- online softmax (log2 domain) -----------------------------------------------
-        float mx = fmaxf(fmaxf(v0, v1), fmaxf(v2, v3));
-        mx = fmaxf(mx, __shfl_xor_sync(DA_FULL_MASK, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(DA_FULL_MASK, mx, 2));
-        const float mnew = fmaxf(m_run, mx);
-        const float msafe = (mnew == NEG_INF) ? 0.f : mnew;
-        const float alpha = fast_exp2(m_run - msafe);
-        v0 = fast_exp2(v0 - msafe);
-        v1 = fast_exp2(v1 - msafe);
-        v2 = fast_exp2(v2 - msafe);
-        v3 = fast_exp2(v3 - msafe);
-        l_part = l_part * alpha + ((v0 + v1) + (v2 + v3));
-        m_run = mnew;
+        uint32_t pa[NR][2];
 #pragma unroll
-        for (int d = 0; d < NT; ++d) {
-            o[d][0] *= alpha;
-            o[d][1] *= alpha;
+        for (int half = 0; half < NR; ++half) {
+            // this lane: row lane/4 + 8*half, tokens 2qd, 2qd+1, 8+2qd, 9+2qd
+            const int lim = avail - st.back[half];
+            float v0 = s0[2 * half] * scale_log2, v1 = s0[2 * half + 1] * scale_log2;
+            float v2 = s1[2 * half] * scale_log2, v3 = s1[2 * half + 1] * scale_log2;
+            if (2 * qd >= lim) v0 = NEG_INF;
+            if (2 * qd + 1 >= lim) v1 = NEG_INF;
+            if (8 + 2 * qd >= lim) v2 = NEG_INF;
+            if (9 + 2 * qd >= lim) v3 = NEG_INF;
+
+            // ---- online softmax (log2 domain) -----------------------------------------------
+            float mx = fmaxf(fmaxf(v0, v1), fmaxf(v2, v3));
+            mx = fmaxf(mx, __shfl_xor_sync(DA_FULL_MASK, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(DA_FULL_MASK, mx, 2));
+            const float mnew = fmaxf(st.m_run[half], mx);
+            const float msafe = (mnew == NEG_INF) ? 0.f : mnew;
+            const float alpha = fast_exp2(st.m_run[half] - msafe);
+            v0 = fast_exp2(v0 - msafe);
+            v1 = fast_exp2(v1 - msafe);
+            v2 = fast_exp2(v2 - msafe);
+            v3 = fast_exp2(v3 - msafe);
+            st.l_part[half] = st.l_part[half] * alpha + ((v0 + v1) + (v2 + v3));
+            st.m_run[half] = mnew;
+#pragma unroll
+            for (int d = 0; d < NT; ++d) {
+                st.o[d][2 * half] *= alpha;
+                st.o[d][2 * half + 1] *= alpha;
+            }
+            pa[half][0] = MmaTraits<T>::pack(v0, v1);  // tokens 0..7 block of P
+            pa[half][1] = MmaTraits<T>::pack(v2, v3);  // tokens 8..15 block of P
         }
-        const uint32_t pa0 = MmaTraits<T>::pack(v0, v1);  // tokens 0..7 block of P
-        const uint32_t pa2 = MmaTraits<T>::pack(v2, v3);  // tokens 8..15 block of P
 
         // ---- O += P V ---------------------------------------------------------------------
 #pragma unroll
         for (int dp = 0; dp < NT / 2; ++dp) {
             uint32_t b[4];
             ldmatrix_x4_trans(b, sb + v_off + dp * 32);           // channels 16dp .. 16dp+15, all 16 tokens
-            MmaTraits<T>::mma(o[2 * dp], pa0, pa2, b[0], b[1]);
-            MmaTraits<T>::mma(o[2 * dp + 1], pa0, pa2, b[2], b[3]);
+            if constexpr (FULL) {
+                MmaTraits<T>::mma16(st.o[2 * dp], pa[0][0], pa[1][0], pa[0][1], pa[1][1], b[0], b[1]);
+                MmaTraits<T>::mma16(st.o[2 * dp + 1], pa[0][0], pa[1][0], pa[0][1], pa[1][1], b[2], b[3]);
+            } else {
+                MmaTraits<T>::mma(st.o[2 * dp], pa[0][0], pa[0][1], b[0], b[1]);
+                MmaTraits<T>::mma(st.o[2 * dp + 1], pa[0][0], pa[0][1], b[2], b[3]);
+            }
         }
-
-        __syncwarp();
-        if (it + STAGES < n_my) issue(s, it + STAGES);
     }
 
-    // ---- this warp's partial: finish the row sum, publish --------------------------------
-    l_part += __shfl_xor_sync(DA_FULL_MASK, l_part, 1);
-    l_part += __shfl_xor_sync(DA_FULL_MASK, l_part, 2);
-    if (row < REP) {
+    // finish the row sums, write this warp's rows
+    __device__ __forceinline__ static void publish(State &st, float *red, int lane, int rows) {
+        constexpr int PW = PartialRow<kD>::kWidth;
+        const int qd = lane & 3;
 #pragma unroll
-        for (int d = 0; d < NT; ++d) {
-            red[warp][row][8 * d + 2 * qd] = o[d][0];
-            red[warp][row][8 * d + 2 * qd + 1] = o[d][1];
-        }
-        if (qd == 0) {
-            red[warp][row][D] = m_run;
-            red[warp][row][D + 1] = l_part;
-        }
-    }
-    __syncthreads();
-
-    // ---- merge the warps, write this CTA's partial ------------------------------------
-    float *part = p.partials + ((size_t)(h * p.part_rows + p.part_offset + x) * REP) * PW;
-    for (int e = tid; e < REP * PW; e += THREADS) {
-        const int r = e / PW;
-        const int c = e % PW;
-        float mn = NEG_INF;
+        for (int half = 0; half < NR; ++half) {
+            float l = st.l_part[half];
+            l += __shfl_xor_sync(DA_FULL_MASK, l, 1);
+            l += __shfl_xor_sync(DA_FULL_MASK, l, 2);
+            const int r = (lane >> 2) + 8 * half;
+            if (r < rows) {
 #pragma unroll
-        for (int w = 0; w < WARPS; ++w) mn = fmaxf(mn, red[w][r][D]);
-        float outv;
-        if (c == D) {
-            outv = mn;
-        } else if (c > D + 1) {
-            outv = 0.f;  // padding
-        } else {
-            const float ms = (mn == NEG_INF) ? 0.f : mn;
-            outv = 0.f;
-#pragma unroll
-            for (int w = 0; w < WARPS; ++w) outv += red[w][r][c] * fast_exp2(red[w][r][D] - ms);
+                for (int d = 0; d < NT; ++d) {
+                    red[r * PW + 8 * d + 2 * qd] = st.o[d][2 * half];
+                    red[r * PW + 8 * d + 2 * qd + 1] = st.o[d][2 * half + 1];
+                }
+                if (qd == 0) {
+                    red[r * PW + kD] = st.m_run[half];
+                    red[r * PW + kD + 1] = l;
+                }
+            }
         }
-        part[e] = outv;
     }
-    if (p.phase == 1) return;   // phase 2 merges the rows of both launches
-    __threadfence();
-    __syncthreads();
-    unsigned int *tickets = p.counters;
-    if (tid == 0) {
-        const unsigned int ticket = atomicAdd(&tickets[h], 1u);
-        sh_last = (ticket == (unsigned int)(splits - 1));
-    }
-    __syncthreads();
-    if (!sh_last) return;
+};
 
-    // ---- last CTA of this head (of this launch) ---------------------------------------------
-    // Every other CTA fenced its partial row before it took its ticket, and the merge reads the
-    // rows with L2 loads issued after the barrier that follows the ticket: no fence on this side.
-    merge_splits<T, D, REP, THREADS>(p, h, p.merge_first, p.merge_rows, reinterpret_cast<float *>(smem), nullptr);
-    // every CTA of this head is done with the split: the one the LRU update left becomes current
-    if (p.phase == 2 && tid == 0) p.flip[h] ^= 1;
-    if (tid == 0) tickets[h] = 0u;
+template <typename T, int D, bool FULL, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 2 : 1) decode_attention_mma_kernel(const AttnParams p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    decode_attention_body<MmaMath<T, D, FULL>, WARPS>(p, smem);
 }
 
-template <typename T, int D, int REP, int WARPS>
-static cudaError_t launch_mma_w(const AttnParams &p, int n_kv_heads, cudaStream_t stream) {
-
-    constexpr int STAGEB = kUnitTokens * (2 * D * 2 + 16);
-    constexpr int STAGES = STAGEB > 8192 ? 3 : 4;
-    constexpr int SMEM = WARPS * STAGES * STAGEB;
-    auto kern = decode_attention_mma_kernel<T, D, REP, STAGES, WARPS>;
+template <typename T, int D, bool FULL, int WARPS>
+static cudaError_t launch_mma_w(const AttnParams &p, int n_kv_heads, int splits, cudaStream_t stream) {
+    using M = MmaMath<T, D, FULL>;
+    constexpr int SMEM = WARPS * M::kStages * M::STAGEB;
+    auto kern = decode_attention_mma_kernel<T, D, FULL, WARPS>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -380,31 +253,33 @@ static cudaError_t launch_mma_w(const AttnParams &p, int n_kv_heads, cudaStream_
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    dim3 grid(p.phase == 1 ? attn_splits_phase1(n_kv_heads) : attn_splits(n_kv_heads), n_kv_heads);
+    dim3 grid(splits, n_kv_heads);
     kern<<<grid, WARPS * 32, SMEM, stream>>>(p);
     return cudaGetLastError();
 }
 
-template <typename T, int D, int REP>
-static cudaError_t launch_mma(const AttnParams &p, int n_kv_heads, cudaStream_t stream) {
-    if (p.phase == 1) return launch_mma_w<T, D, REP, kAttnPhase1Warps>(p, n_kv_heads, stream);
-    return launch_mma_w<T, D, REP, kAttnWarps>(p, n_kv_heads, stream);
+template <typename T, int D>
+static cudaError_t launch_mma(const AttnParams &p, int n_kv_heads, int splits, cudaStream_t stream) {
+    const int rows = p.n_q * p.rep;
+    if (rows > 8) {
+        if (p.phase == 1) return launch_mma_w<T, D, true, kAttnPhase1Warps>(p, n_kv_heads, splits, stream);
+        return launch_mma_w<T, D, true, kAttnWarps>(p, n_kv_heads, splits, stream);
+    }
+    if (p.phase == 1) return launch_mma_w<T, D, false, kAttnPhase1Warps>(p, n_kv_heads, splits, stream);
+    return launch_mma_w<T, D, false, kAttnWarps>(p, n_kv_heads, splits, stream);
 }
 
 template <typename T>
-static cudaError_t dispatch_mma(const AttnParams &p, int n_kv_heads, int rep, int head_dim, cudaStream_t s) {
-#define DA_MMA_CASE(DD, RR) \
-    if (head_dim == DD && rep == RR) return launch_mma<T, DD, RR>(p, n_kv_heads, s);
-    DA_MMA_CASE(128, 1) DA_MMA_CASE(128, 2) DA_MMA_CASE(128, 4) DA_MMA_CASE(128, 8)
-    DA_MMA_CASE(64, 1) DA_MMA_CASE(64, 2) DA_MMA_CASE(64, 4) DA_MMA_CASE(64, 8)
-#undef DA_MMA_CASE
+static cudaError_t dispatch_mma(const AttnParams &p, int n_kv_heads, int head_dim, int splits, cudaStream_t s) {
+    if (head_dim == 128) return launch_mma<T, 128>(p, n_kv_heads, splits, s);
+    if (head_dim == 64) return launch_mma<T, 64>(p, n_kv_heads, splits, s);
     return cudaErrorInvalidValue;
 }
 
-cudaError_t launch_attention_mma(const AttnParams &p, int n_kv_heads, int rep, int head_dim, int dtype,
+cudaError_t launch_attention_mma(const AttnParams &p, int n_kv_heads, int head_dim, int dtype, int splits,
                                  cudaStream_t stream) {
-    if (dtype == DA_BF16) return dispatch_mma<__nv_bfloat16>(p, n_kv_heads, rep, head_dim, stream);
-    if (dtype == DA_F16) return dispatch_mma<__half>(p, n_kv_heads, rep, head_dim, stream);
+    if (dtype == DA_BF16) return dispatch_mma<__nv_bfloat16>(p, n_kv_heads, head_dim, splits, stream);
+    if (dtype == DA_F16) return dispatch_mma<__half>(p, n_kv_heads, head_dim, splits, stream);
     return cudaErrorInvalidValue;
 }
 

@@ -12,8 +12,10 @@
 //      counting.  One 8-bit select pass per byte of the step counter.
 //   4. the j-th miss takes the j-th victim; tables updated; (page, slot) pairs
 //      emitted for the payload copy.
-//   5. optionally the same select, for position n_miss + list_len, tells which slots
-//      the NEXT call can evict (for the two-launch attention).
+//   5. optionally (two-launch attention) the eviction FRONT: the same select, for position
+//      n_miss + split_cap, names the slots that are first in eviction order after this call;
+//      and the call reports whether one of its own victims lay outside the front that was
+//      current when it ran (the attention then redoes that head).
 
 #include "da_common.cuh"
 
@@ -142,7 +144,8 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
                   int32_t *slot_to_dram, int32_t *access_time, int n_slots, int32_t *step_counters,
                   int32_t *__restrict__ miss_pages, int32_t *__restrict__ miss_slots,
                   int32_t *__restrict__ n_miss_out, int32_t *slot_source, int32_t *order_out,
-                  int32_t *n_evictable_out, const int32_t *split_flip, int32_t *status) {
+                  int32_t *n_evictable_out, int32_t *split_flip, int32_t *split_redo, int split_cap,
+                  int split_advance, int32_t *status) {
     extern __shared__ __align__(16) int smem_i[];
     const int table = lru_table_size(list_len);
     int *tkey = smem_i;                  // [table] page id or -1; later: victim slots by rank
@@ -152,10 +155,12 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
     int *mpage = s2d_s + n_slots;        // [list_len] miss pages in list order
     int *vtime = mpage + list_len;       // [list_len] victims: time
     int *vslot = vtime + list_len;       // [list_len] victims: slot
+    unsigned char *in_front = reinterpret_cast<unsigned char *>(vslot + list_len);   // [n_slots] slot is in the current front
     __shared__ int wsum[kLruWarps];
     __shared__ int hist[512];
     __shared__ int res[2];
     __shared__ int sh_max;
+    __shared__ int sh_redo;
 
     const int h = blockIdx.x;
     const int tid = threadIdx.x;
@@ -192,6 +197,11 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
     }
     const int step = step_counters[h] + 1;
     const int prev_miss = min(n_miss_out[h], list_len);
+    // the eviction front the attention launch beside this update works from
+    const bool want_order = order_out != nullptr;
+    const int cur = want_order ? (split_flip[h] & 1) : 0;
+    const int32_t *front_cur = want_order ? order_out + ((size_t)cur * gridDim.x + h) * n_slots : nullptr;
+    const int n_front = want_order ? min(max(n_evictable_out[(size_t)cur * gridDim.x + h], 0), n_slots) : n_slots;
 #pragma unroll
     for (int r = 0; r < LR; ++r) sl[r] = pg[r] >= 0 ? d2s[pg[r]] : 0;
 
@@ -216,9 +226,19 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
         tkey[x] = -1;
         tval[x] = 0x7fffffff;
     }
-    if (tid == 0) sh_max = step;
+    for (int x = tid; x < n_slots; x += kLruThreads) in_front[x] = n_front >= n_slots;
+    if (tid == 0) {
+        sh_max = step;
+        sh_redo = 0;
+    }
     if (bad) atomicOr(status, DA_STATUS_BAD_PAGE_ID);
     __syncthreads();
+    if (n_front < n_slots) {
+        for (int x = tid; x < n_front; x += kLruThreads) {
+            const int v = front_cur[x];
+            if (v >= 0 && v < n_slots) in_front[v] = 1;
+        }
+    }
 
     // ---- 1. hits get the step; non-resident pages go into the hash table -------------
     const int tmask = table - 1;
@@ -277,7 +297,6 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
         hits = total;
     }
     const int bits = 32 - __clz(sh_max | 1);
-    const bool want_order = order_out != nullptr;
     const int n_found = n_miss;
 
     // ---- 3. victims ------------------------------------------------------------------------
@@ -340,24 +359,25 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
                 mp_out[j] = p;
                 ms_out[j] = v;
                 if (src_map) src_map[v] = p;
+                if (!in_front[v]) sh_redo = 1;   // evicted a slot the attention beside us is reading
             }
         }
     }
 
-    // ---- 5. which slots can be evicted by the NEXT call -------------------------------------
+    // ---- 5. the eviction front after this call -------------------------------------------------
     // In (time, slot) order the slots are now [victims | untouched | hit by this call].  After
     // this call victims and hits carry the newest stamp, so the next call's victims come from the
-    // front of the untouched run, and no further in than the next list is long (every list entry
-    // is either a hit, which removes a slot from the front, or a miss, which takes one).  If the
-    // untouched run is at least list_len long, its first list_len slots are the only candidates:
-    // order_out = those first, every other slot after them.  Otherwise every slot is a candidate.
+    // front of the untouched run: how far in depends on how many of those slots it hits and how
+    // many pages it misses.  The first split_cap slots of the run are written as the new front
+    // (order_out = those first, every other slot after them); the next call checks its victims
+    // against it (sh_redo above).  With fewer than split_cap untouched slots every slot is in the front.
     if (want_order) {
         // two buffers, [2][n_kv_heads][...]: the one split_flip[h] does NOT name is written
-        const int wbuf = split_flip ? 1 - (split_flip[h] & 1) : 0;
+        const int wbuf = 1 - cur;
         int32_t *ord = order_out + ((size_t)wbuf * gridDim.x + h) * n_slots;
-        const int cap = min(list_len, n_slots);
+        const int cap = min(max(split_cap, 0), n_slots);
         const int untouched = n_slots - hits - n_miss;
-        const bool bounded = !overflow && n_found == n_miss && untouched >= cap;
+        const bool bounded = !overflow && n_found == n_miss && untouched >= cap && cap > 0 && cap < n_slots;
         if (bounded) {
             int t2, less2;
             select_time<SR>(tm, n_miss + cap, bits, hist, res, t2, less2);   // tm: times before assignment
@@ -382,14 +402,20 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
         }
         if (tid == 0) n_evictable_out[(size_t)wbuf * gridDim.x + h] = bounded ? cap : n_slots;
     }
+    __syncthreads();   // sh_redo
     if (tid == 0) {
         n_miss_out[h] = n_miss;
         step_counters[h] = step;
+        if (want_order) {
+            split_redo[h] = sh_redo;
+            if (split_advance) split_flip[h] = 1 - cur;
+        }
     }
 }
 
 static size_t lru_smem_bytes(int n_slots, int list_len) {
-    return ((size_t)2 * lru_table_size(list_len) + 2 * (size_t)n_slots + 3 * (size_t)list_len) * sizeof(int);
+    return ((size_t)2 * lru_table_size(list_len) + 2 * (size_t)n_slots + 3 * (size_t)list_len) * sizeof(int) +
+           (((size_t)n_slots + 15) & ~(size_t)15);
 }
 
 constexpr size_t kLruMaxSmem = 227 * 1024 - 4096;
@@ -399,7 +425,8 @@ static cudaError_t launch_lru(const int32_t *page_list, int list_len, int32_t *d
                               int32_t *slot_to_dram, int32_t *access_time, int n_slots, int32_t *step,
                               int n_kv_heads, int32_t *miss_pages, int32_t *miss_slots, int32_t *n_miss,
                               int32_t *slot_source, int32_t *order_out, int32_t *n_evictable_out,
-                              const int32_t *split_flip, int32_t *status, size_t smem, cudaStream_t stream) {
+                              int32_t *split_flip, int32_t *split_redo, int split_cap, int split_advance,
+                              int32_t *status, size_t smem, cudaStream_t stream) {
     static bool attr_set[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -413,7 +440,8 @@ static cudaError_t launch_lru(const int32_t *page_list, int list_len, int32_t *d
     }
     lru_update_kernel<SR, LR><<<n_kv_heads, kLruThreads, smem, stream>>>(
         page_list, list_len, dram_to_slot, n_dram_pages, slot_to_dram, access_time, n_slots, step, miss_pages,
-        miss_slots, n_miss, slot_source, order_out, n_evictable_out, split_flip, status);
+        miss_slots, n_miss, slot_source, order_out, n_evictable_out, split_flip, split_redo, split_cap,
+        split_advance, status);
     return cudaGetLastError();
 }
 
@@ -423,12 +451,14 @@ extern "C" int da_lru_update(const int32_t *page_list, int list_len, int32_t *dr
                              int32_t *slot_to_dram, int32_t *access_time, int n_slots, int32_t *step,
                              int n_kv_heads, int32_t *miss_pages, int32_t *miss_slots, int32_t *n_miss,
                              int32_t *slot_source, int32_t *order_out, int32_t *n_evictable_out,
-                             const int32_t *split_flip, int32_t *status, da_stream_t stream) {
+                             int32_t *split_flip, int32_t *split_redo, int split_cap, int split_advance,
+                             int32_t *status, da_stream_t stream) {
     if (!page_list || !dram_to_slot || !slot_to_dram || !access_time || !step || !miss_pages || !miss_slots ||
         !n_miss || !status)
         return DA_ERR_NULL;
     if (list_len < 1 || n_dram_pages < 1 || n_slots < 1 || n_kv_heads < 1) return DA_ERR_SHAPE;
-    if ((order_out == nullptr) != (n_evictable_out == nullptr) || (order_out == nullptr) != (split_flip == nullptr))
+    if ((order_out == nullptr) != (n_evictable_out == nullptr) || (order_out == nullptr) != (split_flip == nullptr) ||
+        (order_out == nullptr) != (split_redo == nullptr))
         return DA_ERR_NULL;
     if (n_slots > da::kLruMaxSlots || list_len > da::kLruMaxList) return DA_ERR_UNSUPPORTED;
     const size_t smem = da::lru_smem_bytes(n_slots, list_len);
@@ -436,7 +466,8 @@ extern "C" int da_lru_update(const int32_t *page_list, int list_len, int32_t *dr
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     cudaError_t e;
 #define DA_LRU_ARGS page_list, list_len, dram_to_slot, n_dram_pages, slot_to_dram, access_time, n_slots, step, \
-                    n_kv_heads, miss_pages, miss_slots, n_miss, slot_source, order_out, n_evictable_out, split_flip, status, smem, s
+                    n_kv_heads, miss_pages, miss_slots, n_miss, slot_source, order_out, n_evictable_out, split_flip, \
+                    split_redo, split_cap, split_advance, status, smem, s
     if (n_slots <= 2048 && list_len <= 1024) e = da::launch_lru<2, 1>(DA_LRU_ARGS);
     else if (n_slots <= 4096 && list_len <= 2048) e = da::launch_lru<4, 2>(DA_LRU_ARGS);
     else e = da::launch_lru<8, 8>(DA_LRU_ARGS);

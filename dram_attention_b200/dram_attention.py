@@ -64,12 +64,16 @@ class DRAMAttention(torch.nn.Module):
     # stage="prefill": this package's tcgen05 kernel where it applies (16-bit, head_dim 128)
     prefill_kernel = True
     fused_fetch = True
-    # Two attention launches per step: the first (local window + slots that cannot be evicted this
-    # step) runs on a side stream beside selection and LRU update, the second finishes after them.
+    # Two attention launches per step: the first (local window + every slot outside the eviction
+    # front) runs on a side stream beside scoring, selection and LRU update; the second (the few
+    # slots of the front, with the miss fetch) follows the update without waiting for the first.
     overlap = True
     # ... and, when the step is being captured into a CUDA graph, that first launch forks off before
     # the page scorer rather than after it
     fork_before_score = True
+    # CTAs per KV head of the two launches (0: the library's defaults)
+    phase1_ctas = 0
+    phase2_ctas = 0
 
     # ---- cache construction ---------------------------------------------------
     def init_cache(self, k_cache: torch.Tensor, v_cache: torch.Tensor):
@@ -90,11 +94,8 @@ class DRAMAttention(torch.nn.Module):
                 k_cache=dram_k_cache[0].transpose(0, 1), v_cache=dram_v_cache[0].transpose(0, 1),
                 page_size=self.page_size, top_k=self.top_k // self.page_size,
                 lru_hbm_cache_size=self.lru_hbm_cache_size, device=self.device)
-            # the fused kernel needs 16-token units inside one page and at most 32 units per warp
-            hk = self.n_kv_heads
-            warps = 4 * max(1, min(296 // hk, 148))
-            units = -(-self.lru_cache.num_hbm_pages * self.page_size // 16) + -(-self.cache_k.shape[1] // 16)
-            self._can_fuse = (self.page_size % 16 == 0) and (-(-units // warps) <= 64)
+            # the kernel that fetches on the fly needs its 16-token units inside one page
+            self._can_fuse = self.page_size % 16 == 0
             self._can_overlap = self._can_fuse   # refined per GQA group size at the first generate call
             self._overlap_ok = {}
         else:
@@ -108,7 +109,9 @@ class DRAMAttention(torch.nn.Module):
     def forward(self, xq: torch.Tensor, xk: torch.Tensor, xv: torch.Tensor, *, start_pos, stage: str):
         """xq (1, s, Hq, D), xk/xv (1, s, Hk, D).  `stage` is "prefill" (dense causal
         attention, then init_cache) or "generate" (one new token; start_pos is its
-        absolute position, a Python int or an int32 CUDA tensor of shape (1,))."""
+        absolute position, a Python int or an int32 CUDA tensor of shape (1,)).  Generate also
+        takes s > 1 tokens (appended at start_pos .. start_pos + s - 1), as the reference does for
+        the unaligned tail of a prompt."""
         bsz, seqlen, H, D = xq.shape
         assert bsz == 1, "Only support batch size 1"
         if stage == "prefill":
@@ -144,21 +147,21 @@ class DRAMAttention(torch.nn.Module):
         out = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
         return out.transpose(1, 2).contiguous()
 
-    def _workspace(self, rep: int, dev):
-        ws = self._ws.get(rep)
+    def _workspace(self, rep: int, dev, seqlen: int = 1):
+        ws = self._ws.get((rep, seqlen))
         if ws is None:
             lib = _native.lib()
-            nbytes = max(lib.da_decode_attention_workspace_bytes(self.n_kv_heads, rep, self.head_dim),
+            nbytes = max(lib.da_decode_attention_tokens_workspace_bytes(self.n_kv_heads, rep, self.head_dim, seqlen),
                          lib.da_decode_attention_phased_workspace_bytes(self.n_kv_heads, rep, self.head_dim))
             buf = torch.zeros(nbytes, dtype=torch.uint8, device=dev)  # counters start at zero
             status = torch.zeros(1, dtype=torch.int32, device=dev)
-            ws = self._ws[rep] = (buf, nbytes, status)
+            ws = self._ws[(rep, seqlen)] = (buf, nbytes, status)
         return ws
 
     def _generate(self, xq: torch.Tensor, xk: torch.Tensor, xv: torch.Tensor, start_pos):
         bsz, seqlen, n_q_heads, D = xq.shape
-        assert seqlen == 1, "generate takes one token per call"
         assert self.lru_cache is not None, "init_cache (or a prefill) must come first"
+        assert xk.shape[1] == seqlen and xv.shape[1] == seqlen
         _native.require_cuda(xq, "xq")
         assert xq.dtype == self.cache_k.dtype and xk.dtype == xq.dtype and xv.dtype == xq.dtype
         assert n_q_heads % self.n_kv_heads == 0 and D == self.head_dim
@@ -168,7 +171,13 @@ class DRAMAttention(torch.nn.Module):
         xv = xv if xv.is_contiguous() else xv.contiguous()
         with torch.cuda.device(xq.device):
             out = torch.empty_like(xq)
-            if self._can_overlap and self.fused_fetch and self.overlap and self._overlap_supported(rep, xq.dtype):
+            if seqlen > 1:
+                # several tokens: one scoring / selection / LRU update over all of them (list of
+                # seqlen * rep * k pages per KV head), the gather-copy of the misses, then the
+                # attention of every token over the same slot table
+                self.lru_cache.get_kv_cache_(xq)
+                self.attend_(xq, xk, xv, start_pos, out)
+            elif self._can_overlap and self.fused_fetch and self.overlap and self._overlap_supported(rep, xq.dtype):
                 self._generate_overlapped(xq, xk, xv, start_pos, out)
             elif self._can_fuse and self.fused_fetch:
                 # score -> select -> LRU update -> attention that also brings in the misses
@@ -191,7 +200,7 @@ class DRAMAttention(torch.nn.Module):
         return ok
 
     def _generate_overlapped(self, xq, xk, xv, start_pos, out) -> None:
-        """{ score -> select -> LRU update  ||  attention phase 1 } -> attention phase 2."""
+        """{ score -> select -> LRU update -> attention phase 2 }  ||  attention phase 1."""
         lc = self.lru_cache
         sel = lc.top_k_selector
         rep = xq.shape[2] // self.n_kv_heads
@@ -199,8 +208,6 @@ class DRAMAttention(torch.nn.Module):
             self._side = torch.cuda.Stream(device=xq.device)
             self._fork, self._join = torch.cuda.Event(), torch.cuda.Event()
         main = torch.cuda.current_stream()
-        if not lc.split_valid:
-            lc.reset_split_()
         # Phase 1 needs nothing this step computes (only the split the previous step left), so it
         # forks off before the scorer: its CTAs move onto the SMs as the scorer's short CTAs leave
         # them.  The scorer is launched first so that the chain score -> select -> update is not
@@ -221,10 +228,10 @@ class DRAMAttention(torch.nn.Module):
             self._join.record(self._side)
         if early:
             page_list = sel.select_(1, rep, lc.top_k)
-        lc.update_tables_(page_list, want_split=True)
-        main.wait_event(self._join)
+        lc.update_tables_(page_list, advance_split=False)
+        # phase 2 needs the update, not phase 1: whichever of the two launches finishes last merges
         self.attend_(xq, xk, xv, start_pos, out, phase=2)
-        lc.split_valid = True
+        main.wait_event(self._join)
 
     def attend_(self, xq, xk, xv, start_pos, out, lse=None, fetch=False, phase=0) -> None:
         """Enqueue the decode attention over the current slot table and the local
@@ -232,12 +239,13 @@ class DRAMAttention(torch.nn.Module):
         kernel also reads the pages the last LRU update marked from DRAM and writes them
         through to their slots (no fetch_ call needed)."""
         rep = xq.shape[2] // self.n_kv_heads
+        seqlen = xq.shape[1]
         prefix = self.lru_cache.hbm_kv_cache
         n_prefix_tokens = (self.lru_cache.num_tokens if isinstance(self.lru_cache, DummyCache)
                            else self.lru_cache.num_hbm_pages * self.page_size)
         if n_prefix_tokens == 0:
             raise RuntimeError("empty DRAM prefix is not supported")
-        buf, nbytes, status = self._workspace(rep, xq.device)
+        buf, nbytes, status = self._workspace(rep, xq.device, seqlen)
         if isinstance(start_pos, torch.Tensor):
             assert start_pos.dtype == torch.int32 and start_pos.is_cuda and start_pos.numel() == 1
             pos_dev, pos_host = start_pos.data_ptr(), 0
@@ -249,6 +257,7 @@ class DRAMAttention(torch.nn.Module):
             lc = self.lru_cache
             _native.check(lib.da_decode_attention_phased(
                 phase, lc.evict_order.data_ptr(), lc.n_evictable.data_ptr(), lc.evict_flip.data_ptr(),
+                lc.evict_redo.data_ptr(), int(self.phase1_ctas), int(self.phase2_ctas),
                 xq.data_ptr(), prefix.data_ptr(), prefix.stride(0), lc.num_hbm_pages, self.page_size,
                 lc.dram_kv_cache.data_ptr(), lc.num_dram_pages, lc.slot_source.data_ptr(),
                 self.cache_k.data_ptr(), self.cache_v.data_ptr(), self.cache_k.stride(1),
@@ -268,13 +277,13 @@ class DRAMAttention(torch.nn.Module):
                 status.data_ptr(), self.n_kv_heads, rep, self.head_dim, _native.dtype_code(xq.dtype),
                 _native.stream_ptr()), "da_decode_attention_fetch")
             return
-        _native.check(lib.da_decode_attention(
-            xq.data_ptr(), prefix.data_ptr(), prefix.stride(0), n_prefix_tokens,
+        _native.check(lib.da_decode_attention_tokens(
+            xq.data_ptr(), seqlen, prefix.data_ptr(), prefix.stride(0), n_prefix_tokens,
             self.cache_k.data_ptr(), self.cache_v.data_ptr(), self.cache_k.stride(1),
             self.cache_k.stride(2), self.cache_k.shape[1], xk.data_ptr(), xv.data_ptr(),
             pos_dev, pos_host, self.dram_kv_cache_size, out.data_ptr(), lse_ptr, buf.data_ptr(), nbytes,
             status.data_ptr(), self.n_kv_heads, rep, self.head_dim, _native.dtype_code(xq.dtype),
-            _native.stream_ptr()), "da_decode_attention")
+            _native.stream_ptr()), "da_decode_attention_tokens")
 
     def check_status(self) -> None:
         """Synchronises; raises if any kernel of this operator flagged a problem."""

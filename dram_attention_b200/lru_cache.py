@@ -115,17 +115,25 @@ class LRUCache(torch.nn.Module):
         # maintained by the LRU kernel, consumed by the attention kernel that fetches on the fly
         self.register_buffer("slot_source", torch.full((num_kv_heads, num_hbm_pages), -1, **i32),
                              persistent=False)
-        # Split of the slots used by the two-launch attention: the first n_evictable[h] entries
-        # of evict_order[h] are the slots the coming LRU update may evict.  "Everything" is always
-        # a valid split; the LRU kernel leaves a tighter one for the following step in *_next.
+        # Eviction front used by the two-launch attention: the first n_evictable[h] entries of
+        # evict_order[h] (copy evict_flip[h]) are the slots the first launch leaves out because the
+        # LRU update running beside it may evict them: the `split_cap` slots that come first in
+        # eviction order.  The update writes the other copy for the following step and sets
+        # evict_redo[h] when one of its victims lay outside the current front (the second launch
+        # then covers the whole head).  All of it lives on the device, so a captured step stays
+        # consistent whatever ran between two replays.  "Every slot" is the starting front.
         self.register_buffer("evict_order", torch.arange(num_hbm_pages, **i32).repeat(2, num_kv_heads, 1),
                              persistent=False)    # two copies; evict_flip[h] names the current one
         self.register_buffer("n_evictable", torch.full((2, num_kv_heads), num_hbm_pages, **i32),
                              persistent=False)
         self.register_buffer("evict_flip", torch.zeros(num_kv_heads, **i32), persistent=False)
-        self.split_valid = True    # evict_order / n_evictable describe the tables as they are now
+        self.register_buffer("evict_redo", torch.zeros(num_kv_heads, **i32), persistent=False)
+        self.split_cap = min(self.default_split_cap, max(1, num_hbm_pages // 4))
         self._miss = {}
         self._last_list_len = None
+
+    # slots per head in the eviction front (a steady decode step misses a handful of pages per head)
+    default_split_cap = 128
 
     @property
     def current_step(self) -> torch.Tensor:
@@ -140,12 +148,13 @@ class LRUCache(torch.nn.Module):
                                            mk(self.num_kv_heads))
         return bufs
 
-    def update_tables_(self, page_list: torch.Tensor, want_split: bool = False) -> None:
+    def update_tables_(self, page_list: torch.Tensor, advance_split: bool = True) -> None:
         """Enqueue the LRU table update for an int32 page list (Hk, list_len): step
-        counters, hit stamps, victim choice, both maps, and the device-side miss list.
-        With `want_split` the kernel also leaves, in the copy of evict_order / n_evictable that
-        evict_flip does not name, which slots the following update can evict (the two-launch
-        attention then flips to it)."""
+        counters, hit stamps, victim choice, both maps, the device-side miss list, and the
+        eviction front for the following step (written into the copy of evict_order /
+        n_evictable that evict_flip does not name).  `advance_split=False` when the two-launch
+        attention follows: its second launch makes the new front current when both are done;
+        otherwise the update does it itself."""
         list_len = page_list.shape[1]
         miss_pages, miss_slots, n_miss = self._miss_buffers(list_len)
         if self._last_list_len != list_len:
@@ -159,19 +168,9 @@ class LRUCache(torch.nn.Module):
             self.num_dram_pages, self.hbm_page_to_dram_page_mapping.data_ptr(),
             self.page_access_time.data_ptr(), self.num_hbm_pages, self.step_counters.data_ptr(),
             self.num_kv_heads, miss_pages.data_ptr(), miss_slots.data_ptr(), n_miss.data_ptr(),
-            self.slot_source.data_ptr(),
-            self.evict_order.data_ptr() if want_split else 0,
-            self.n_evictable.data_ptr() if want_split else 0,
-            self.evict_flip.data_ptr() if want_split else 0,
-            self.status.data_ptr(), _native.stream_ptr()), "da_lru_update")
-        self.split_valid = False   # until the attention's second launch installs the new split
-
-    def reset_split_(self) -> None:
-        """Make "every slot may be evicted" the current split (always correct)."""
-        self.evict_order.copy_(torch.arange(self.num_hbm_pages, dtype=torch.int32,
-                                            device=self.evict_order.device).expand_as(self.evict_order))
-        self.n_evictable.fill_(self.num_hbm_pages)
-        self.split_valid = True
+            self.slot_source.data_ptr(), self.evict_order.data_ptr(), self.n_evictable.data_ptr(),
+            self.evict_flip.data_ptr(), self.evict_redo.data_ptr(), int(self.split_cap),
+            1 if advance_split else 0, self.status.data_ptr(), _native.stream_ptr()), "da_lru_update")
 
     def fetch_(self, list_len: int) -> None:
         """Enqueue the gather-copy of the pages the last update_tables_ found missing."""

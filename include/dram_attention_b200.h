@@ -136,20 +136,26 @@ DA_API int da_topk_pages(const float *scores, int32_t *page_list,
  *             marks of the previous call using the previous miss list, so when it is used
  *             the array must start at -1, n_miss at 0, and the same miss buffers must be
  *             passed every time.  NULL when da_fetch_pages does the copy.
- * split_order, split_count, split_flip  optional, all or none, for da_decode_attention_phased:
- *             split_order is [2][n_kv_heads][n_slots] int32, split_count [2][n_kv_heads],
- *             split_flip [n_kv_heads].  The call writes copy 1 - split_flip[h] (it never
- *             touches the copy split_flip[h] names, which the attention of this step is
- *             using): afterwards the first split_count entries of that copy's split_order[h]
- *             are the only slots the NEXT call can evict, provided its list is not longer
- *             than this one; the other slots follow.  (Every list entry either hits, which
- *             takes a slot out of the eviction order's front, or misses, which consumes one,
- *             so victims come from the first list_len slots this call did not touch; when
- *             fewer than list_len slots were left untouched the count is n_slots.)
+ * split_order, split_count, split_flip, split_redo  optional, all or none: the "eviction front"
+ *             that da_decode_attention_phased works from.  split_order is
+ *             [2][n_kv_heads][n_slots] int32, split_count [2][n_kv_heads], split_flip and
+ *             split_redo [n_kv_heads].  Copy split_flip[h] is the CURRENT front of head h: its
+ *             first split_count entries are the slots an attention launch that runs beside this
+ *             update has left out because they may be evicted.  The call
+ *               - sets split_redo[h] = 1 if it evicted a slot outside the current front (the
+ *                 attention then has to redo the head), else 0;
+ *               - writes the other copy: the split_cap slots that are now first in eviction
+ *                 order ((time, slot) ascending among the slots this call did not touch), then
+ *                 every other slot; split_count = split_cap, or n_slots (every slot, in place)
+ *                 when fewer than split_cap slots were left untouched;
+ *               - with split_advance != 0 makes that copy current itself (callers that run no
+ *                 phased attention after the update); otherwise phase 2 of the attention does.
+ *             Before the first call: both copies any permutation of the slots with
+ *             split_count = n_slots, split_flip = 0.
  * status      (1) int32, bits or-ed in
  * Requires n_slots <= 8192, list_len <= 8192 and the shared-memory plan
- * (3*n_slots + 2*max(n_slots, T) + list_len + 8192 ints, T = power of two >= 2*list_len)
- * to fit 226 KiB: e.g. 8192 slots with lists up to 4096, or 4096 slots with lists up to 8192.
+ * (2*T + 2*n_slots + 3*list_len ints + n_slots bytes, T = power of two >= 2*list_len) to fit
+ * 222 KiB: e.g. 8192 slots with lists up to 4096.
  */
 DA_API int da_lru_update(const int32_t *page_list, int list_len,
                   int32_t *dram_to_slot, int n_dram_pages,
@@ -157,7 +163,8 @@ DA_API int da_lru_update(const int32_t *page_list, int list_len,
                   int32_t *step, int n_kv_heads,
                   int32_t *miss_pages, int32_t *miss_slots, int32_t *n_miss,
                   int32_t *slot_source, int32_t *split_order, int32_t *split_count,
-                  const int32_t *split_flip, int32_t *status, da_stream_t stream);
+                  int32_t *split_flip, int32_t *split_redo, int split_cap, int split_advance,
+                  int32_t *status, da_stream_t stream);
 
 /*
  * Miss-page fetch: gather-copy of the pages named by da_lru_update from DRAM into
@@ -207,10 +214,43 @@ DA_API size_t da_decode_attention_workspace_bytes(int n_kv_heads, int rep, int h
  *              first 1024 bytes hold counters that must be ZERO before the first
  *              call; each call leaves them zero again
  * status       (1) int32, bits or-ed in
- * Requires head_dim in {64, 128}, rep in {1, 2, 4, 8}; all bases and strides
+ * Requires head_dim in {64, 128}, rep <= 16 (8 for float32); all bases and strides
  * multiples of 16 bytes.
  */
 DA_API int da_decode_attention(const void *q,
+                        const void *prefix_kv, long long prefix_head_stride,
+                        int n_prefix_tokens,
+                        void *local_k, void *local_v,
+                        long long local_token_stride, long long local_head_stride,
+                        int local_capacity,
+                        const void *new_k, const void *new_v,
+                        const int32_t *start_pos_dev, int start_pos_host, int dram_tokens,
+                        void *out, float *lse_out,
+                        void *workspace, size_t workspace_bytes, int32_t *status,
+                        int n_kv_heads, int rep, int head_dim, int dtype,
+                        da_stream_t stream);
+
+/*
+ * da_decode_attention for several query tokens in one call: the generate stage with
+ * seq_len > 1 (dram_attention/dram_attention.py:144-177 with a (1, s, Hq, D) query; the
+ * evaluation harness feeds the unaligned tail of a prompt this way).
+ *
+ *   T = start_pos - dram_tokens; local[T + i] = new_k/new_v[i] for the s tokens;
+ *   query token i attends over the prefix tokens [0, n_prefix_tokens - (s - 1 - i)) and the
+ *   local tokens [0, T + i]: both parts carry the bottom-right aligned causal mask that
+ *   flash_attn_with_kvcache(causal=True) applies (dram_attention.py:195-205, :211-223) --
+ *   on the prefix it hides the LAST s - 1 - i tokens of the slot table from token i, as the
+ *   reference does.
+ *
+ * q, out       (n_q_tokens, n_kv_heads * rep, head_dim); new_k, new_v (n_q_tokens, n_kv_heads,
+ *              head_dim); lse_out optional (n_q_tokens, n_kv_heads * rep)
+ * workspace    da_decode_attention_tokens_workspace_bytes() bytes
+ * One launch covers 16 / rep tokens for 16-bit types (8 / rep for float32); longer calls are
+ * several launches on `stream`.  Requires rep <= 16 (8 for float32), n_q_tokens <= local_capacity.
+ */
+DA_API size_t da_decode_attention_tokens_workspace_bytes(int n_kv_heads, int rep, int head_dim,
+                        int n_q_tokens);
+DA_API int da_decode_attention_tokens(const void *q, int n_q_tokens,
                         const void *prefix_kv, long long prefix_head_stride,
                         int n_prefix_tokens,
                         void *local_k, void *local_v,
@@ -238,10 +278,8 @@ DA_API int da_decode_attention(const void *q,
  * dram_pages   (n_kv_heads, n_dram_pages, page_size, 2, head_dim): pinned, device-mapped
  *              host memory (or device memory), 16-byte aligned
  * slot_source  (n_kv_heads, n_slots) int32 as left by da_lru_update
- * Other arguments as da_decode_attention.  Requires page_size to be a multiple of 16 and
- * (slot tokens + local capacity) / 16 units to be at most 32 per warp of the launch
- * (4 * max(1, min(296 / n_kv_heads, 148)) warps per head); otherwise DA_ERR_UNSUPPORTED
- * (use da_fetch_pages + da_decode_attention).
+ * Other arguments as da_decode_attention.  Requires page_size to be a multiple of 16;
+ * otherwise DA_ERR_UNSUPPORTED (use da_fetch_pages + da_decode_attention).
  */
 DA_API int da_decode_attention_fetch(const void *q,
                         void *slots, long long slots_head_stride, int n_slots, int page_size,
@@ -257,33 +295,39 @@ DA_API int da_decode_attention_fetch(const void *q,
                         da_stream_t stream);
 
 /*
- * da_decode_attention_fetch as two launches, so that most of the attention runs BESIDE
- * the selection and the LRU update instead of after them (same reference lines as
- * da_decode_attention_fetch; the result is the same).
+ * da_decode_attention_fetch as two launches, so that nearly all of the attention runs BESIDE
+ * the scoring, the selection and the LRU update instead of after them (same reference lines
+ * as da_decode_attention_fetch; the result is the same).
  *
- *   phase 1  (may run concurrently with da_topk_pages / da_lru_update of the same step):
- *            appends the new key/value, attends over the local window and over the slots
- *            that this step's LRU update cannot evict, writes partials.  Uses at most 116
- *            CTAs that each fill an SM, so 32 SMs stay free for the selection kernels.
- *   phase 2  (after da_lru_update and after phase 1): attends over the evictable slots,
- *            reading freshly assigned ones from DRAM as da_decode_attention_fetch does,
- *            merges the partials of both phases, writes the output, and flips
- *            split_flip[h], which makes the split this step's da_lru_update wrote current.
+ *   phase 1  (may run concurrently with da_score_pages / da_topk_pages / da_lru_update of the
+ *            same step): appends the new key/value, attends over the local window and over
+ *            every slot outside the current eviction front, writes partials.  By default at
+ *            most 116 CTAs that each fill an SM, so 32 SMs stay free for the other kernels.
+ *   phase 2  (after da_lru_update; need NOT wait for phase 1): attends over the slots of the
+ *            front, reading freshly assigned ones from DRAM as da_decode_attention_fetch
+ *            does, and writes partials.  If the update set split_redo[h] (it had to evict a
+ *            slot outside the front, e.g. after a query that shares nothing with the last
+ *            one), phase 2 covers the whole head -- every slot and the local window -- and the
+ *            rows phase 1 wrote for that head are ignored.
+ *   The CTA of a head that finishes LAST, whichever launch it belongs to, merges the
+ *   partials, writes the output, and flips split_flip[h], which makes the front the update
+ *   wrote current.  Both launches of a step must have been enqueued before the next step's
+ *   first one; a step is complete when both have finished.
  *
- * split_order, split_count, split_flip   as for da_lru_update: copy split_flip[h] is the split
- *            both phases of one step use (first split_count entries of split_order[h] = the
- *            evictable slots).  Before the first step: both copies any permutation of the slots
- *            with split_count = n_slots (everything in phase 2), split_flip = 0.
+ * split_order, split_count, split_flip, split_redo   as for da_lru_update (called with
+ *            split_advance = 0 between the two launches).
+ * phase1_ctas, phase2_ctas  CTAs per KV head of the two launches, the same values in both
+ *            calls of a step; 0 = defaults (116 / n_kv_heads and 64 / n_kv_heads), at most 148.
  * workspace  da_decode_attention_phased_workspace_bytes() bytes, shared by both phases.
- * The list handed to da_lru_update must not be longer than in the step before.
  */
 DA_API size_t da_decode_attention_phased_workspace_bytes(int n_kv_heads, int rep, int head_dim);
-/* 1 if da_decode_attention_phased accepts this shape (page_size a multiple of 16, at most 64 units
- * per warp in either phase, the phase-1 CTA fits an SM's shared memory), else 0. */
+/* 1 if da_decode_attention_phased accepts this shape (page_size a multiple of 16, the phase-1
+ * CTA fits an SM's shared memory), else 0. */
 DA_API int da_decode_attention_phased_supported(int n_kv_heads, int rep, int head_dim, int dtype,
                         int n_slots, int page_size, int local_capacity);
 DA_API int da_decode_attention_phased(int phase, const int32_t *split_order, const int32_t *split_count,
-                        int32_t *split_flip,
+                        int32_t *split_flip, const int32_t *split_redo,
+                        int phase1_ctas, int phase2_ctas,
                         const void *q,
                         void *slots, long long slots_head_stride, int n_slots, int page_size,
                         const void *dram_pages, int n_dram_pages, const int32_t *slot_source,

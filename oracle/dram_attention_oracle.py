@@ -250,6 +250,27 @@ def attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> Tuple[torch.Ten
     return out.reshape(hq, d), lse.reshape(hq)
 
 
+def attend_tokens(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Softmax attention of S query tokens with the causal mask aligned to the bottom-right
+    corner: query i sees keys j <= T - S + i.
+
+    q (S, Hq, D); k, v (T, Hk, D).  Returns out (S, Hq, D) and lse (S, Hq), float64.  This is
+    what both flash_attn_with_kvcache(causal=True) calls of the reference compute when the
+    generate stage gets several tokens (dram_attention/dram_attention.py:195-205 with
+    cache_seqlens = all slot tokens, :211-223 with the S new rows appended first); the mask
+    alignment is the documented behaviour of flash-attn >= 2.1.  On the prefix part it hides the
+    last S-1-i tokens of the slot table from query i.
+    """
+    s_q, hq, d = q.shape
+    t = k.shape[0]
+    outs, lses = [], []
+    for i in range(s_q):
+        o, l = attend(q[i], k[:t - s_q + i + 1], v[:t - s_q + i + 1])
+        outs.append(o)
+        lses.append(l)
+    return torch.stack(outs), torch.stack(lses)
+
+
 def combine(prefix_out: torch.Tensor, suffix_out: torch.Tensor,
             prefix_lse: torch.Tensor, suffix_lse: torch.Tensor) -> torch.Tensor:
     """LSE-weighted merge, dram_attention/dram_attention.py:225-238."""
@@ -378,20 +399,26 @@ class OracleDRAMAttention:
 
     def generate(self, xq: torch.Tensor, xk: torch.Tensor, xv: torch.Tensor,
                  start_pos: int) -> StepTrace:
-        """dram_attention.py:144-177.  xq (1,1,Hq,D); xk, xv (1,1,Hk,D)."""
+        """dram_attention.py:144-177.  xq (1,S,Hq,D); xk, xv (1,S,Hk,D).  `out` of the trace
+        is (Hq, D) for one token and (S, Hq, D) for several."""
         assert xq.shape[0] == 1, "Only support batch size 1"
-        assert xq.shape[1] == 1
-        q = xq[0, 0]
+        s_q = xq.shape[1]
         if self.lru_cache is not None:
             scores, page_list, mp, ms, nm = self.lru_cache.get_kv_cache_(xq)
             pk, pv = self.lru_cache.kv_views()
         else:
             scores = page_list = mp = ms = nm = None
             pk, pv = self.static_k, self.static_v
-        po, plse = attend(q, pk.transpose(0, 1), pv.transpose(0, 1))
         t = int(start_pos) - self.dram_kv_cache_size
-        self.cache_k[t] = xk[0, 0]
-        self.cache_v[t] = xv[0, 0]
-        so, slse = attend(q, self.cache_k[:t + 1], self.cache_v[:t + 1])
-        out = combine(po, so, plse, slse)
+        self.cache_k[t:t + s_q] = xk[0]
+        self.cache_v[t:t + s_q] = xv[0]
+        if s_q == 1:
+            q = xq[0, 0]
+            po, plse = attend(q, pk.transpose(0, 1), pv.transpose(0, 1))
+            so, slse = attend(q, self.cache_k[:t + 1], self.cache_v[:t + 1])
+            out = combine(po, so, plse, slse)
+        else:
+            po, plse = attend_tokens(xq[0], pk.transpose(0, 1), pv.transpose(0, 1))
+            so, slse = attend_tokens(xq[0], self.cache_k[:t + s_q], self.cache_v[:t + s_q])
+            out = torch.stack([combine(po[i], so[i], plse[i], slse[i]) for i in range(s_q)])
         return StepTrace(scores, page_list, mp, ms, nm, out)

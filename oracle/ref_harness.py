@@ -28,19 +28,24 @@ import contextlib
 import os
 import sys
 
-REFERENCE_ROOT = os.environ.get("DRAM_ATTENTION_REFERENCE", "/root/reference")
+# where the reference project is checked out: the environment decides (nothing is assumed)
+REFERENCE_ROOT = os.environ.get("DRAM_ATTENTION_REFERENCE", "")
 
 
 def reference_available() -> bool:
-    return os.path.isdir(os.path.join(REFERENCE_ROOT, "dram_attention"))
+    return bool(REFERENCE_ROOT) and os.path.isdir(os.path.join(REFERENCE_ROOT, "dram_attention"))
 
 
 def _flash_attn_with_kvcache_cpu(q, k_cache, v_cache, k=None, v=None, rotary_cos=None,
                                  rotary_sin=None, causal=False, cache_seqlens=None,
                                  rotary_interleaved=True, return_softmax_lse=False, **_):
+    """Documented behaviour of flash_attn_with_kvcache (flash_attn_interface.py docstring of
+    flash-attn 2.8.3): k/v are written into the cache at cache_seqlens; attention runs over the
+    first cache_seqlens + s tokens; with causal=True the mask is aligned to the bottom-right
+    corner, i.e. query i of s sees keys j <= seqlen_k - s + i."""
     import torch
     b, s, hq, d = q.shape
-    assert b == 1 and s == 1
+    assert b == 1
     seqlen = int(cache_seqlens)
     if k is not None:
         k_cache[:, seqlen:seqlen + s] = k
@@ -48,16 +53,20 @@ def _flash_attn_with_kvcache_cpu(q, k_cache, v_cache, k=None, v=None, rotary_cos
         seqlen = seqlen + s
     hk = k_cache.shape[2]
     rep = hq // hk
-    qf = q[0, 0].double().reshape(hk, rep, d)
-    kf = k_cache[0, :seqlen].double().permute(1, 0, 2)
-    vf = v_cache[0, :seqlen].double().permute(1, 0, 2)
-    logits = torch.bmm(qf, kf.transpose(1, 2)) * (d ** -0.5)
-    lse = torch.logsumexp(logits, dim=-1)
-    out = torch.bmm(torch.exp(logits - lse[..., None]), vf).reshape(1, 1, hq, d)
+    qf = q[0].double().reshape(s, hk, rep, d).permute(1, 2, 0, 3)        # (Hk, rep, s, D)
+    kf = k_cache[0, :seqlen].double().permute(1, 0, 2)[:, None]          # (Hk, 1, T, D)
+    vf = v_cache[0, :seqlen].double().permute(1, 0, 2)[:, None]
+    logits = torch.matmul(qf, kf.transpose(-1, -2)) * (d ** -0.5)        # (Hk, rep, s, T)
+    if causal and s > 1:
+        j = torch.arange(seqlen)[None, :]
+        i = torch.arange(s)[:, None]
+        logits = logits.masked_fill(j > seqlen - s + i, float("-inf"))
+    lse = torch.logsumexp(logits, dim=-1)                                # (Hk, rep, s)
+    out = torch.matmul(torch.exp(logits - lse[..., None]), vf)           # (Hk, rep, s, D)
     # flash-attn returns the output in q's dtype and the lse in float32; the
     # arithmetic in between is float64 here so the fixture is accurate to float32
-    out = out.to(q.dtype)
-    lse = lse.reshape(1, hq, 1).float()
+    out = out.permute(2, 0, 1, 3).reshape(1, s, hq, d).to(q.dtype)
+    lse = lse.permute(0, 1, 2).reshape(1, hq, s).float()
     return (out, lse) if return_softmax_lse else out
 
 
@@ -83,6 +92,8 @@ def reference_on_cpu():
     as described in the module docstring.  Patches are undone on exit."""
     os.environ.setdefault("TRITON_INTERPRET", "1")
     import torch
+    if not reference_available():
+        raise RuntimeError("set DRAM_ATTENTION_REFERENCE to the checkout of long-context/dram-attention")
     if REFERENCE_ROOT not in sys.path:
         sys.path.insert(0, REFERENCE_ROOT)
     orig_empty = torch.empty

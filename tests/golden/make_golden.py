@@ -16,6 +16,11 @@ Outputs (all small .npz files, committed):
                       the seed and guarded by a checksum.
   mini_traj.npz       a smaller trajectory whose inputs are multiples of 1/8
                       stored as int8 (many exact score ties), inputs included.
+  multi_traj_*.npz    generate calls with several tokens each (2, 3, 1, 4, 2 tokens) on the
+                      same kind of inputs: outputs of every token, page lists, tables.  Two
+                      head layouts, the ones the reference's selector accepts with more than
+                      one token (its `view` after `swapaxes`, topk_selector.py:52-55, needs
+                      one KV head or a GQA group of one; anything else raises there).
 """
 
 from __future__ import annotations
@@ -166,12 +171,69 @@ def mini_traj(ref):
     print("mini trajectory: out", res["out"].shape)
 
 
+def multi_traj(ref, hq, hk):
+    """Generate calls that carry several tokens each (the reference's generate stage takes
+    seq_len > 1: dram_attention/topk_selector.py:48-61, lru_cache.py:260-264,
+    dram_attention.py:191-223)."""
+    g = torch.Generator().manual_seed(2 + hq)
+    d, p = 64, 16
+    local, lru, top_k, max_out = 64, 384, 64, 16
+    counts = [2, 3, 1, 4, 2]
+    s = 640 + local - p
+    k8 = torch.randint(-16, 17, (1, s, hk, d), generator=g, dtype=torch.int8)
+    v8 = torch.randint(-16, 17, (1, s, hk, d), generator=g, dtype=torch.int8)
+    n_tok = sum(counts)
+    q8 = torch.randint(-8, 9, (1, n_tok, hq, d), generator=g, dtype=torch.int8)
+    xk8 = torch.randint(-16, 17, (1, n_tok, hk, d), generator=g, dtype=torch.int8)
+    xv8 = torch.randint(-16, 17, (1, n_tok, hk, d), generator=g, dtype=torch.int8)
+    f = lambda t: t.float() / 8.0
+    ctor = dict(max_output_length=max_out, lru_hbm_cache_size=lru, local_cache_size=local,
+                page_size=p, top_k=top_k, n_kv_heads=hk, head_dim=d)
+    m = ref.DRAMAttention(device="cpu", dtype=torch.float32, **ctor)
+    m.init_cache(f(k8), f(v8))
+    lc = m.lru_cache
+    lists = []
+    orig_load = lc.load_
+
+    def spy(idx):
+        lists.append(idx.numpy().copy())
+        return orig_load(idx)
+
+    lc.load_ = spy
+    outs, h2ds, times = [], [], []
+    pos, a = s, 0
+    for c in counts:
+        out = m(f(q8[:, a:a + c]), f(xk8[:, a:a + c]), f(xv8[:, a:a + c]), start_pos=pos, stage="generate")
+        outs.append(out[0].float().numpy().copy())            # (c, Hq, D)
+        h2ds.append(lc.hbm_page_to_dram_page_mapping.numpy().copy())
+        times.append(lc.page_access_time.numpy().copy())
+        pos += c
+        a += c
+    res = dict(out=np.concatenate(outs), h2d=np.stack(h2ds), time=np.stack(times),
+               d2h_final=lc.dram_page_to_hbm_page_mapping.numpy().copy(),
+               cache_k=m.cache_k[0].numpy().copy(), counts=np.array(counts),
+               k8=k8.numpy(), v8=v8.numpy(), q8=q8.numpy(), xk8=xk8.numpy(), xv8=xv8.numpy(),
+               ctor=np.array([max_out, lru, local, p, top_k, hk, d]),
+               dram_tokens=np.array([m.dram_kv_cache_size]))
+    for i, l in enumerate(lists):
+        res[f"list{i}"] = l
+    res["heads"] = np.array([hq, hk])
+    np.savez_compressed(os.path.join(HERE, f"multi_traj_hq{hq}_hk{hk}.npz"), **res)
+    print("multi-token trajectory: out", res["out"].shape, "lists", [l.shape for l in lists])
+
+
 if __name__ == "__main__":
     with reference_on_cpu() as ref:
+        if "--only-multi" in sys.argv:
+            multi_traj(ref, 4, 1)
+            multi_traj(ref, 2, 2)
+            sys.exit(0)
         scorer_values(ref)
         lru_kernel_cases(ref)
         mini_traj(ref)
         plumbing_traj(ref)
+        multi_traj(ref, 4, 1)
+        multi_traj(ref, 2, 2)
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")

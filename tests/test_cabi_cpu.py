@@ -28,7 +28,8 @@ def test_header_declares_the_expected_entry_points():
     names = declared_symbols()
     for n in ["da_version", "da_error_string", "da_score_pages", "da_topk_pages", "da_lru_update",
               "da_fetch_pages", "da_decode_attention", "da_decode_attention_fetch",
-              "da_decode_attention_static", "da_decode_attention_workspace_bytes", "da_decode_attention_phased", "da_decode_attention_phased_supported",
+              "da_decode_attention_static", "da_decode_attention_workspace_bytes", "da_decode_attention_phased",
+              "da_decode_attention_phased_supported", "da_decode_attention_tokens",
               "da_build_pages"]:
         assert n in names
 
@@ -56,14 +57,18 @@ def test_host_side_argument_checks(native):
     assert lib.da_score_pages(16, 16, 16, 1, 1, 1, 1, 1, 7, 0, 0) == -3         # bad dtype
     assert lib.da_topk_pages(16, 16, 1, 1, 1, 8, 9, 0) == -2                 # k > pages
     assert lib.da_topk_pages(16, 16, 1, 1, 1, 10000, 5000, 0) == -5          # k too large
-    assert lib.da_lru_update(16, 4, 16, 8, 16, 16, 9000, 16, 1, 16, 16, 16, 0, 0, 0, 0, 16, 0) == -5
+    assert lib.da_lru_update(16, 4, 16, 8, 16, 16, 9000, 16, 1, 16, 16, 16, 0, 0, 0, 0, 0, 0, 0, 16, 0) == -5
+    # the four arrays of the eviction front come together or not at all
+    assert lib.da_lru_update(16, 4, 16, 8, 16, 16, 64, 16, 1, 16, 16, 16, 0, 16, 16, 16, 0, 8, 0, 16, 0) == -1
     assert lib.da_fetch_pages(0, 16, 16, 16, 16, 1, 1, 1, 1, 16, 0) == -1
     assert lib.da_decode_attention_phased_supported(8, 4, 128, 2, 2048, 16, 4160) == 1
     assert lib.da_decode_attention_phased_supported(8, 4, 128, 2, 2048, 8, 4160) == 0     # page < 16 tokens
     assert lib.da_decode_attention_phased_supported(8, 4, 128, 0, 2048, 16, 4160) == 0     # fp32, D 128: CTA too big
     ws = lib.da_decode_attention_workspace_bytes(8, 4, 128)
     assert ws == 1024 + 8 * 37 * 4 * 132 * 4
-    assert lib.da_decode_attention_phased_workspace_bytes(8, 4, 128) == 1024 + 8 * (14 + 37) * 4 * 132 * 4
+    assert lib.da_decode_attention_tokens_workspace_bytes(8, 4, 128, 3) == 1024 + 8 * 37 * 12 * 132 * 4
+    assert lib.da_decode_attention_tokens_workspace_bytes(8, 4, 128, 9) == 1024 + 8 * 37 * 16 * 132 * 4
+    assert lib.da_decode_attention_phased_workspace_bytes(8, 4, 128) == 1024 + 8 * (148 + 148) * 4 * 132 * 4
     args = [256, 256, 4096, 16, 256, 256, 1024, 128, 64, 256, 256, 0, 0, 0, 256, 0, 256, ws, 256,
             8, 4, 128, 2, 0]
     bad = list(args); bad[21] = 96
@@ -74,6 +79,8 @@ def test_host_side_argument_checks(native):
     assert lib.da_decode_attention(*bad) == -6                                # workspace
     bad = list(args); bad[22] = 9
     assert lib.da_decode_attention(*bad) == -3                                # dtype
+    bad = list(args); bad[20] = 17
+    assert lib.da_decode_attention(*bad) == -5                                # GQA group wider than a launch
 
 
 def test_operator_refuses_cpu_tensors(native):

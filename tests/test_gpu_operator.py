@@ -131,11 +131,17 @@ def _oracle_follow(w, steps, gpu_lists):
     return o, res
 
 
-def test_bf16_layer_trajectory_against_oracle(da, fused):
+@pytest.mark.parametrize("front", [None, 1, 100000])
+def test_bf16_layer_trajectory_against_oracle(da, fused, front, monkeypatch):
     """A reduced Llama-shaped bf16 layer (2 KV heads, 16K-token prefix): every step's
     selection equals the oracle's up to near-ties at the k-th score, LRU tables are
-    bit-exact given the same list, outputs within 2e-2."""
+    bit-exact given the same list, outputs within 2e-2.  The query is re-drawn every fourth
+    step, which evicts far more slots than the eviction front holds: those steps take the
+    redo path of the two-launch layout.  front = 1 makes nearly every step one (a front of a
+    single slot), a huge front keeps every slot in the second launch."""
     steps = 10
+    if front is not None:
+        monkeypatch.setattr(da.LRUCache, "default_split_cap", front)
     w = llama_layer_workload(seed=0, steps=steps, dram_tokens=16384, n_kv_heads=2, lru=4096, local=512,
                              top_k=1024, needles=4, redraw_every=4)
     m, outs, lists, h2ds, times = _run(da, w.ctor_kwargs(), torch.bfloat16, w.k, w.v, w.xq, w.xk, w.xv, True)
@@ -220,6 +226,134 @@ def test_generate_step_is_graph_capturable(da, fused):
     assert torch.equal(m.cache_k, e.cache_k)
     m.check_status()
     e.check_status()
+
+
+def test_captured_step_survives_an_eager_load(da):
+    """The eviction front lives on the device: a captured step replayed after an eager
+    LRUCache.load_() of another list (which evicts slots behind the graph's back) still
+    gives what an eager twin gives."""
+    steps = 6
+    w = llama_layer_workload(seed=2, steps=steps, dram_tokens=8192, n_kv_heads=2, lru=2048, local=256,
+                             top_k=512, needles=2)
+    m = da.DRAMAttention(device=DEV, dtype=torch.bfloat16, **w.ctor_kwargs())
+    m.init_cache(w.k.to(DEV), w.v.to(DEV))
+    e = da.DRAMAttention(device=DEV, dtype=torch.bfloat16, **w.ctor_kwargs())
+    e.init_cache(w.k.to(DEV), w.v.to(DEV))
+    s = w.k.shape[1]
+    xq, xk, xv = (t[0].to(DEV).clone() for t in (w.xq, w.xk, w.xv))
+    pos = torch.tensor([s], dtype=torch.int32, device=DEV)
+    out_static = torch.empty_like(xq)
+    m(xq, xk, xv, start_pos=pos, stage="generate")
+    e(xq, xk, xv, start_pos=s, stage="generate")
+    pos.add_(1)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out_static.copy_(m(xq, xk, xv, start_pos=pos, stage="generate"))
+    g = torch.Generator().manual_seed(7)
+    for i in range(1, steps):
+        if i in (2, 4):
+            # 60 pages per head that the query stream never asked for
+            other = torch.randint(0, m.lru_cache.num_dram_pages, (2, 60), generator=g).to(DEV)
+            m.lru_cache.load_(other)
+            e.lru_cache.load_(other)
+        xq.copy_(w.xq[i].to(DEV)); xk.copy_(w.xk[i].to(DEV)); xv.copy_(w.xv[i].to(DEV))
+        graph.replay()
+        pos.add_(1)
+        want = e(xq, xk, xv, start_pos=s + i, stage="generate")
+        assert torch.equal(out_static, want), i
+        lc = m.lru_cache
+        h2d = lc.hbm_page_to_dram_page_mapping.cpu().long()
+        for h in range(lc.num_kv_heads):
+            assert torch.equal(lc.hbm_kv_cache[h].cpu(), lc.dram_kv_cache[h, h2d[h]]), i
+    assert torch.equal(m.lru_cache.hbm_page_to_dram_page_mapping, e.lru_cache.hbm_page_to_dram_page_mapping)
+    m.check_status()
+    e.check_status()
+
+
+# ---- generate calls with several tokens --------------------------------------------------
+
+@pytest.mark.parametrize("heads", ["hq4_hk1", "hq2_hk2"])
+def test_multi_token_generate_matches_reference_run(da, golden_dir, heads):
+    """Generate calls with 2, 3, 1, 4, 2 tokens on exactly-tying inputs, against what the
+    reference's own classes produced (the two head layouts its selector accepts with more than
+    one token): page lists and tables bit-exact, the appended local rows, every token's output
+    within 1e-4."""
+    g = np.load(os.path.join(golden_dir, f"multi_traj_{heads}.npz"))
+    max_out, lru, local, p, top_k, hk, d = [int(x) for x in g["ctor"]]
+    ctor = dict(max_output_length=max_out, lru_hbm_cache_size=lru, local_cache_size=local, page_size=p,
+                top_k=top_k, n_kv_heads=hk, head_dim=d)
+    f = lambda a: (torch.from_numpy(a).float() / 8.0).to(DEV)
+    m = da.DRAMAttention(device=DEV, dtype=torch.float32, **ctor)
+    m.init_cache(f(g["k8"]), f(g["v8"]))
+    assert m.dram_kv_cache_size == int(g["dram_tokens"][0])
+    lists = _spy_lists(m)
+    q, xk, xv = f(g["q8"]), f(g["xk8"]), f(g["xv8"])
+    pos, a = g["k8"].shape[1], 0
+    for i, c in enumerate(g["counts"].tolist()):
+        out = m(q[:, a:a + c], xk[:, a:a + c], xv[:, a:a + c], start_pos=pos, stage="generate")
+        assert out.shape == (1, c, q.shape[2], d)
+        assert np.array_equal(lists[i].cpu().numpy(), g[f"list{i}"]), i
+        assert np.array_equal(m.lru_cache.hbm_page_to_dram_page_mapping.cpu().numpy(), g["h2d"][i]), i
+        assert np.array_equal(m.lru_cache.page_access_time.cpu().numpy(), g["time"][i]), i
+        assert np.abs(out[0].cpu().numpy() - g["out"][a:a + c]).max() <= 1e-4, i
+        pos += c
+        a += c
+    assert np.array_equal(m.lru_cache.dram_page_to_hbm_page_mapping.cpu().numpy(), g["d2h_final"])
+    assert np.array_equal(m.cache_k[0].cpu().numpy(), g["cache_k"])
+    m.check_status()
+
+
+@pytest.mark.parametrize("dtype,counts", [(torch.bfloat16, [2, 4, 5, 1, 8]), (torch.float32, [3, 2, 1])])
+def test_multi_token_generate_against_oracle(da, dtype, counts):
+    """Several tokens per call on a GQA layer (2 KV heads x 4 query heads, a shape the reference's
+    own selector cannot take with more than one token): the oracle follows the GPU's page
+    lists; tables bit-exact, outputs within the suite's tolerance.  5 and 8 tokens need two
+    attention launches per call."""
+    n_tok = sum(counts)
+    w = llama_layer_workload(seed=3, steps=n_tok, dram_tokens=8192, n_kv_heads=2, lru=4096, local=256,
+                             top_k=256, needles=2, dtype=dtype)
+    m = da.DRAMAttention(device=DEV, dtype=dtype, **w.ctor_kwargs())
+    m.init_cache(w.k.to(DEV), w.v.to(DEV))
+    lists = _spy_lists(m)
+    o = orc.OracleDRAMAttention(dtype=torch.float32, **w.ctor_kwargs())
+    o.init_cache(w.k.float(), w.v.float())
+    xq = w.xq[:, 0, 0][None]       # (1, n_tok, Hq, D)
+    xk = w.xk[:, 0, 0][None]
+    xv = w.xv[:, 0, 0][None]
+    pos, a = w.k.shape[1], 0
+    for i, c in enumerate(counts):
+        out = m(xq[:, a:a + c].to(DEV), xk[:, a:a + c].to(DEV), xv[:, a:a + c].to(DEV), start_pos=pos,
+                stage="generate")
+        lst = lists[i].cpu().numpy().astype(np.int64)
+        assert lst.shape == (2, c * 4 * 16)
+        lc = o.lru_cache
+        lc.load_(lst)
+        pk, pv = lc.kv_views()
+        t = pos - o.dram_kv_cache_size
+        o.cache_k[t:t + c], o.cache_v[t:t + c] = xk[0, a:a + c].float(), xv[0, a:a + c].float()
+        qf = xq[0, a:a + c].float()
+        po, pl = orc.attend_tokens(qf, pk.transpose(0, 1), pv.transpose(0, 1))
+        so, sl = orc.attend_tokens(qf, o.cache_k[:t + c], o.cache_v[:t + c])
+        for j in range(c):
+            assert_out_close(out[0, j].float().cpu(), orc.combine(po[j], so[j], pl[j], sl[j]), dtype, (i, j))
+        assert np.array_equal(m.lru_cache.hbm_page_to_dram_page_mapping.cpu().numpy(), lc.h2d), i
+        # every token's own selection is the oracle's (up to near-ties at the k-th score)
+        scores = orc.scores_by_query_head(qf[None], lc.chunk_min_max)      # (c, Hk, rep, L)
+        own = orc.build_page_list(orc.select_pages(scores, lc.top_k)).numpy()
+        if not np.array_equal(own, lst):
+            sc = scores.permute(1, 0, 2, 3).reshape(2, c * 4, -1)
+            for h in range(2):
+                for r in range(c * 4):
+                    got, want = set(lst[h, r * 16:(r + 1) * 16].tolist()), set(own[h, r * 16:(r + 1) * 16].tolist())
+                    kth = torch.sort(sc[h, r], descending=True).values[15].item()
+                    for pg in got ^ want:
+                        assert abs(sc[h, r, pg].item() - kth) <= 1e-3 * max(1.0, abs(kth)), (i, h, r, pg)
+        pos += c
+        a += c
+    assert torch.equal(m.cache_k[0, :pos - m.dram_kv_cache_size].cpu().float(),
+                       o.cache_k[:pos - o.dram_kv_cache_size])
+    m.check_status()
 
 
 # ---- the reference's operator API tests (dram_attention/dram_attention_test.py) ----

@@ -180,10 +180,12 @@ class Tables:
         self.g_dram = self.dram.clone().pin_memory()
         self.g_hbm = self.hbm.to(DEV)
         self.g_status = torch.zeros(1, dtype=torch.int32, device=DEV)
-        self.g_order = torch.full((2, self.hk, self.nh), -5, dtype=torch.int32, device=DEV)
-        self.g_nev = torch.full((2, self.hk), -5, dtype=torch.int32, device=DEV)
-        self.g_flip = torch.zeros(self.hk, dtype=torch.int32, device=DEV)   # copy 1 gets written
-        self.prev_split = None
+        # eviction front: both copies start as "every slot"; the update advances the flip itself
+        self.g_order = torch.arange(self.nh, dtype=torch.int32, device=DEV).repeat(2, self.hk, 1)
+        self.g_nev = torch.full((2, self.hk), self.nh, dtype=torch.int32, device=DEV)
+        self.g_flip = torch.zeros(self.hk, dtype=torch.int32, device=DEV)
+        self.g_redo = torch.full((self.hk,), -5, dtype=torch.int32, device=DEV)
+        self.split_cap = max(1, self.nh // 4)
         return self
 
     def gpu_step(self, lst):
@@ -194,29 +196,44 @@ class Tables:
         mp = torch.full((self.hk, kk), -9, dtype=torch.int32, device=DEV)
         ms = torch.full((self.hk, kk), -9, dtype=torch.int32, device=DEV)
         nm = torch.full((self.hk,), -9, dtype=torch.int32, device=DEV)
+        flip = self.g_flip.cpu().numpy()
+        cur_order = np.stack([self.g_order[flip[h], h].cpu().numpy() for h in range(self.hk)])
+        cur_nev = np.array([int(self.g_nev[flip[h], h]) for h in range(self.hk)])
+        before = (self.g_order.clone(), self.g_nev.clone())
         _native.check(lib.da_lru_update(gl.data_ptr(), kk, self.g_d2h.data_ptr(), self.ld,
                                         self.g_h2d.data_ptr(), self.g_time.data_ptr(), self.nh,
                                         self.g_step.data_ptr(), self.hk, mp.data_ptr(), ms.data_ptr(),
                                         nm.data_ptr(), 0, self.g_order.data_ptr(), self.g_nev.data_ptr(),
-                                        self.g_flip.data_ptr(), self.g_status.data_ptr(), s))
+                                        self.g_flip.data_ptr(), self.g_redo.data_ptr(), self.split_cap, 1,
+                                        self.g_status.data_ptr(), s))
         page_bytes = self.dram.shape[2] * self.dram.element_size()
         _native.check(lib.da_fetch_pages(self.g_dram.data_ptr(), self.g_hbm.data_ptr(), mp.data_ptr(),
                                          ms.data_ptr(), nm.data_ptr(), kk, self.hk, self.ld, self.nh,
                                          page_bytes, s))
         torch.cuda.synchronize()
         mp, ms, nm = mp.cpu().numpy(), ms.cpu().numpy(), nm.cpu().numpy()
-        # the split the previous call left must contain every slot this call evicted
-        if self.prev_split is not None and self.prev_split[2] >= kk:
-            order, nev, _ = self.prev_split
-            for h in range(self.hk):
-                assert set(ms[h, :nm[h]].tolist()) <= set(order[h, :nev[h]].tolist()), h
-        order, nev = self.g_order[1].cpu().numpy(), self.g_nev[1].cpu().numpy()
-        assert int(self.g_order[0].max()) == -5 and int(self.g_nev[0].max()) == -5   # current copy untouched
-        if not (int(self.g_status) & 2):
-            for h in range(self.hk):
-                assert sorted(order[h].tolist()) == list(range(self.nh)), h
-                assert nev[h] == self.nh or nev[h] == min(kk, self.nh), h
-        self.prev_split = (order, nev, kk)
+        # redo flag: exactly "a victim of this call lay outside the front that was current"
+        redo = self.g_redo.cpu().numpy()
+        new_flip = self.g_flip.cpu().numpy()
+        times = self.g_time.cpu().numpy()
+        step_now = int(self.g_step[0])
+        for h in range(self.hk):
+            outside = not (set(ms[h, :nm[h]].tolist()) <= set(cur_order[h, :cur_nev[h]].tolist()))
+            assert redo[h] == int(outside), (h, redo[h], outside)
+            assert new_flip[h] == 1 - flip[h], h          # split_advance = 1
+            # the copy that was current is untouched, the other one holds the new front
+            assert torch.equal(self.g_order[flip[h], h], before[0][flip[h], h])
+            assert int(self.g_nev[flip[h], h]) == int(before[1][flip[h], h])
+            order = self.g_order[new_flip[h], h].cpu().numpy()
+            nev = int(self.g_nev[new_flip[h], h])
+            assert sorted(order.tolist()) == list(range(self.nh)), h
+            assert nev == self.nh or nev == min(self.split_cap, self.nh), h
+            if nev < self.nh:
+                # the front = the nev slots that come first in (time, slot) order among the
+                # slots this call did not touch (listed in any order)
+                untouched = [s_ for s_ in range(self.nh) if times[h, s_] < step_now]
+                want = sorted(untouched, key=lambda s_: (times[h, s_], s_))[:nev]
+                assert sorted(order[:nev].tolist()) == sorted(want), h
         return mp, ms, nm
 
     def cpu_step(self, lst, fn=orc.lru_walk):
@@ -430,6 +447,61 @@ def test_decode_attention_matches_oracle(da, dtype, d, hk, rep, n_prefix, cap, t
     # tolerances (tests/conftest.py:out_tolerance): 1e-4 absolute in float32; 2e-2 absolute
     # plus half an ulp of the stored value in 16-bit types
     _attention_case(da, dtype, d, hk, rep, n_prefix, cap, t_new, n_prefix + t_new, device_pos)
+
+
+@pytest.mark.parametrize("dtype,d,hk,rep,n_prefix,cap,t0,s_q", [
+    (torch.bfloat16, 128, 2, 4, 512, 96, 40, 2),     # 8 rows: the half-tile kernel
+    (torch.bfloat16, 128, 2, 4, 512, 96, 40, 4),     # 16 rows: the full tile
+    (torch.bfloat16, 128, 1, 4, 1000, 64, 13, 7),    # two launches (4 + 3 tokens), ragged prefix
+    (torch.float16, 64, 3, 2, 300, 40, 5, 8),        # 16 rows with rep 2
+    (torch.bfloat16, 128, 2, 1, 200, 64, 0, 16),     # 16 tokens of one head each, empty local window before
+    (torch.float32, 64, 2, 4, 2048, 272, 240, 2),    # float32: 8 rows per launch
+    (torch.float32, 64, 2, 4, 520, 64, 30, 5),       # float32: three launches (2 + 2 + 1)
+    (torch.float32, 128, 1, 3, 100, 32, 7, 3),       # a GQA group of three
+])
+def test_decode_attention_tokens_matches_oracle(da, dtype, d, hk, rep, n_prefix, cap, t0, s_q):
+    """Several query tokens per call: each sees the slot table minus its last s-1-i tokens
+    and the local window up to its own position (bottom-right causal mask on both parts)."""
+    from dram_attention_b200 import _native
+    lib = _native.lib()
+    g = _g(n_prefix + s_q)
+    hq = hk * rep
+    prefix = torch.randn(hk, n_prefix, 2, d, generator=g).to(dtype)
+    local_k = torch.randn(cap, hk, d, generator=g).to(dtype)
+    local_v = torch.randn(cap, hk, d, generator=g).to(dtype)
+    q = (torch.randn(s_q, hq, d, generator=g) * 1.5).to(dtype)
+    nk = torch.randn(s_q, hk, d, generator=g).to(dtype)
+    nv = torch.randn(s_q, hk, d, generator=g).to(dtype)
+    dram_tokens = 4096
+    ws_bytes = lib.da_decode_attention_tokens_workspace_bytes(hk, rep, d, s_q)
+    ws = torch.zeros(ws_bytes, dtype=torch.uint8, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    g_prefix, g_lk, g_lv = prefix.to(DEV), local_k.to(DEV), local_v.to(DEV)
+    g_q, g_nk, g_nv = q.to(DEV), nk.to(DEV), nv.to(DEV)
+    out = torch.empty(s_q, hq, d, dtype=dtype, device=DEV)
+    lse = torch.empty(s_q, hq, dtype=torch.float32, device=DEV)
+    _native.check(lib.da_decode_attention_tokens(
+        g_q.data_ptr(), s_q, g_prefix.data_ptr(), g_prefix.stride(0), n_prefix, g_lk.data_ptr(),
+        g_lv.data_ptr(), g_lk.stride(0), g_lk.stride(1), cap, g_nk.data_ptr(), g_nv.data_ptr(),
+        0, dram_tokens + t0, dram_tokens, out.data_ptr(), lse.data_ptr(), ws.data_ptr(), ws_bytes,
+        status.data_ptr(), hk, rep, d, _native.dtype_code(dtype), _native.stream_ptr()))
+    torch.cuda.synchronize()
+    assert int(status) == 0
+    local_k[t0:t0 + s_q], local_v[t0:t0 + s_q] = nk, nv
+    po, pl = orc.attend_tokens(q, prefix[:, :, 0].transpose(0, 1), prefix[:, :, 1].transpose(0, 1))
+    so, sl = orc.attend_tokens(q, local_k[:t0 + s_q], local_v[:t0 + s_q])
+    for i in range(s_q):
+        assert_out_close(out[i].float().cpu(), orc.combine(po[i], so[i], pl[i], sl[i]), dtype, i)
+        assert torch.allclose(lse[i].cpu().double(), torch.logaddexp(pl[i], sl[i]), rtol=1e-4, atol=1e-4)
+    assert torch.equal(g_lk.cpu(), local_k) and torch.equal(g_lv.cpu(), local_v)
+    assert int(ws[:1024].view(torch.int32).abs().sum()) == 0
+    # more tokens than the local window can take, or a group wider than a launch: rejected on the host
+    rc = lib.da_decode_attention_tokens(
+        g_q.data_ptr(), cap + 1, g_prefix.data_ptr(), g_prefix.stride(0), n_prefix, g_lk.data_ptr(),
+        g_lv.data_ptr(), g_lk.stride(0), g_lk.stride(1), cap, g_nk.data_ptr(), g_nv.data_ptr(),
+        0, dram_tokens, dram_tokens, out.data_ptr(), 0, ws.data_ptr(), ws_bytes, status.data_ptr(), hk, rep, d,
+        _native.dtype_code(dtype), _native.stream_ptr())
+    assert rc == -2
 
 
 def test_decode_attention_bad_position_is_reported(da):

@@ -185,3 +185,31 @@ def test_plumbing_trajectory_matches_reference(golden_dir):
     assert np.array_equal(m.lru_cache.h2d, g["h2d"][-1])
     assert np.array_equal(m.lru_cache.d2h, g["d2h_final"])
     assert np.array_equal(m.lru_cache.page_access_time, g["time"][-1].astype(np.int64))
+
+
+@pytest.mark.parametrize("heads", ["hq4_hk1", "hq2_hk2"])
+def test_multi_token_generate_matches_reference(golden_dir, heads):
+    """Generate calls with several tokens each, run by the reference's own classes (the two
+    head layouts its selector accepts with more than one token): lists, tables, the appended
+    local rows and every token's output."""
+    g = _load(golden_dir, f"multi_traj_{heads}.npz")
+    max_out, lru, local, p, top_k, hk, d = [int(x) for x in g["ctor"]]
+    ctor = dict(max_output_length=max_out, lru_hbm_cache_size=lru, local_cache_size=local,
+                page_size=p, top_k=top_k, n_kv_heads=hk, head_dim=d)
+    f = lambda a: torch.from_numpy(a).float() / 8.0
+    m = orc.OracleDRAMAttention(dtype=torch.float32, **ctor)
+    m.init_cache(f(g["k8"]), f(g["v8"]))
+    assert m.dram_kv_cache_size == int(g["dram_tokens"][0])
+    q, xk, xv = f(g["q8"]), f(g["xk8"]), f(g["xv8"])
+    pos, a = g["k8"].shape[1], 0
+    for i, c in enumerate(g["counts"].tolist()):
+        t = m.generate(q[:, a:a + c], xk[:, a:a + c], xv[:, a:a + c], pos)
+        assert np.array_equal(t.page_list, g[f"list{i}"]), i
+        assert np.array_equal(m.lru_cache.h2d, g["h2d"][i]), i
+        assert np.array_equal(m.lru_cache.page_access_time, g["time"][i].astype(np.int64)), i
+        out = t.out if c > 1 else t.out[None]
+        assert np.allclose(out.numpy(), g["out"][a:a + c], rtol=1e-4, atol=1e-4), i
+        pos += c
+        a += c
+    assert np.array_equal(m.lru_cache.d2h, g["d2h_final"])
+    assert np.array_equal(m.cache_k.numpy(), g["cache_k"])

@@ -2,11 +2,14 @@
 allocate device memory while running (a frozen memory plan, a plugin without access
 to the allocator).  It keeps the kernel's scratch in a buffer built into the library.
 Checked here through the C ABI against da_decode_attention (caller-provided
-workspace) on two consecutive calls, which also exercises the reuse of the shared
-buffer.  The file name makes pytest collect it last."""
+workspace) and against the CPU oracle on two consecutive calls, which also exercises the
+reuse of the shared buffer.  The file name makes pytest collect it last."""
 
 import pytest
 import torch
+
+from oracle import dram_attention_oracle as orc
+from tests.conftest import assert_out_close
 
 pytestmark = pytest.mark.gpu
 
@@ -67,6 +70,13 @@ def test_static_scratch_matches_workspace_entry_point(native, dtype, hk, rep, d,
         assert torch.equal(out_a, out_b)
         assert torch.allclose(lse_a, lse_b, rtol=1e-4, atol=1e-4)
         assert torch.equal(lk_a, lk_b) and torch.equal(lv_a, lv_b)
+        # and against the CPU oracle on its own: prefix part, local part (new row appended), merge
+        t = t0 + call
+        prefix = x["prefix"].cpu()
+        po, pl = orc.attend(q.cpu(), prefix[:, :, 0].transpose(0, 1), prefix[:, :, 1].transpose(0, 1))
+        so, sl = orc.attend(q.cpu(), lk_b[:t + 1].cpu(), lv_b[:t + 1].cpu())
+        assert_out_close(out_b.float().cpu(), orc.combine(po, so, pl, sl), dtype, call)
+        assert torch.equal(lk_b[t].cpu(), nk.cpu()) and torch.equal(lv_b[t].cpu(), nv.cpu())
 
 
 def test_static_scratch_rejects_shapes_beyond_its_capacity(native):
