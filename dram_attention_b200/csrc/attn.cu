@@ -182,8 +182,10 @@ struct SimtMath {
 template <typename T, int D, int ROWS, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 2 : 1) decode_attention_kernel(const AttnParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
-    decode_attention_body<SimtMath<T, D, ROWS>, WARPS>(p, smem);
+    decode_attention_body<SimtMath<T, D, ROWS>, WARPS, SimtMath<T, D, ROWS>::kStages>(p, smem);
 }
+
+constexpr int kSimtPhase1Warps = 8;   // float32 stages are twice as large: 8 warps fill an SM
 
 template <typename T, int D, int ROWS, int WARPS>
 static cudaError_t launch_attn_w(const AttnParams &p, int n_kv_heads, int splits, cudaStream_t stream) {
@@ -207,7 +209,7 @@ static cudaError_t launch_attn_w(const AttnParams &p, int n_kv_heads, int splits
 
 template <typename T, int D, int ROWS>
 static cudaError_t launch_attn(const AttnParams &p, int n_kv_heads, int splits, cudaStream_t stream) {
-    if (p.phase == 1) return launch_attn_w<T, D, ROWS, kAttnPhase1Warps>(p, n_kv_heads, splits, stream);
+    if (p.phase == 1) return launch_attn_w<T, D, ROWS, kSimtPhase1Warps>(p, n_kv_heads, splits, stream);
     return launch_attn_w<T, D, ROWS, kAttnWarps>(p, n_kv_heads, splits, stream);
 }
 
@@ -334,6 +336,7 @@ static int run_attention(const AttnCall &c) {
     p.phase = c.phase;
     p.n_kv_heads = c.n_kv_heads;
     p.rep = c.rep;
+    p.head_dim = c.head_dim;
     p.s_total = c.n_q_tokens;
     p.part_rows = part_rows;
     p.part_offset = 0;
@@ -475,11 +478,12 @@ extern "C" int da_decode_attention_phased_supported(int n_kv_heads, int rep, int
     if (rep > da::max_rows_of(dtype)) return 0;
     if (n_kv_heads * 4 > da::kCounterBytes) return 0;
     if (page_size % da::kUnitTokens != 0 || (long long)n_slots * page_size > 0x7fffffffLL) return 0;
-    // shared memory of a phase-1 CTA: 8 warps x stages x stage bytes
+    // shared memory of a phase-1 CTA: warps x stages x stage bytes, plus the plan tables
     const size_t esz = dtype == DA_F32 ? 4 : 2;
     size_t stage = (size_t)da::kUnitTokens * (2 * head_dim * esz + (esz == 2 ? 16 : 0));
-    const int stages = esz == 2 ? (stage > 8192 ? 3 : 4) : (stage >= 16384 ? 2 : (stage >= 8192 ? 3 : 4));
-    const size_t smem = (size_t)da::kAttnPhase1Warps * stages * stage + 2048;
+    const int stages = esz == 2 ? 2 : (stage >= 16384 ? 2 : (stage >= 8192 ? 3 : 4));
+    const int warps = esz == 2 ? da::kAttnPhase1Warps : da::kSimtPhase1Warps;
+    const size_t smem = (size_t)warps * stages * stage + (size_t)warps * da::kRoundUnits * 16 + 2048;
     return smem <= 227 * 1024 ? 1 : 0;
 }
 

@@ -6,12 +6,12 @@
 //
 // Work unit = 16 consecutive tokens of one KV head.  A warp owns a private ring of stages with
 // one mbarrier each, so the main loop has no CTA-wide synchronisation.  Units are dealt
-// round-robin to the (CTA, warp) workers of a head; a warp plans 64 of its units at a time
-// (two per lane: where the unit lies, whether it has to come from DRAM) and walks a round with
-// the DRAM-sourced units first.
+// round-robin to the (CTA, warp) workers of a head; a warp plans 32 of its units at a time
+// (one per lane: where the unit lies, whether it has to come from DRAM) into a small table in
+// shared memory and walks a round with the DRAM-sourced units first.
 //
 // Math policy interface:
-//   Elem, kD, kPitch (bytes between two tokens of a stage), kStages, kPerTokenCopy
+//   Elem, kD, kPitch (bytes between two tokens of a stage), kPerTokenCopy
 //   struct State; init(State&, p, h, lane, rows); consume(State&, stage, avail, lane);
 //   publish(State&, red, lane, rows)   red = float [rows][D + 4] of this warp
 #pragma once
@@ -20,7 +20,7 @@
 
 namespace da {
 
-template <typename Math, int WARPS>
+template <typename Math, int WARPS, int STAGES>
 __device__ __forceinline__ void decode_attention_body(const AttnParams &p, unsigned char *smem) {
     using T = typename Math::Elem;
     constexpr int D = Math::kD;
@@ -29,15 +29,14 @@ __device__ __forceinline__ void decode_attention_body(const AttnParams &p, unsig
     constexpr int TOKB = 2 * ROWB;               // one token of the slot table: key row, value row
     constexpr int PITCH = Math::kPitch;          // the same token in a stage
     constexpr int STAGEB = kUnitTokens * PITCH;
-    constexpr int STAGES = Math::kStages;
     constexpr int PW = PartialRow<D>::kWidth;
     constexpr int THREADS = WARPS * 32;
     constexpr float NEG_INF = -INFINITY;
     static_assert(STAGES * STAGEB >= kAttnMaxRows * PW * (int)sizeof(float), "a warp's ring holds its partial");
 
     __shared__ __align__(8) uint64_t bars[WARPS][STAGES];
+    __shared__ __align__(16) uint4 plan_tab[WARPS][kRoundUnits];
     __shared__ int sh_last;
-    __shared__ unsigned char perm_s[WARPS][kRoundUnits];
 
     const int h = blockIdx.y;
     const int x = blockIdx.x;
@@ -61,11 +60,11 @@ __device__ __forceinline__ void decode_attention_body(const AttnParams &p, unsig
     const int n_workers = splits * WARPS;
     const int worker = x * WARPS + warp;
     const LaunchUnits lu = launch_units(p, h, n_local);
-    const int units_prefix = lu.units_slots;
     const int units = lu.units_slots + lu.units_local;
     const int total_my = units > worker ? (units - worker + n_workers - 1) / n_workers : 0;
 
     unsigned char *my_stages = smem + (size_t)warp * STAGES * STAGEB;
+    uint4 *tab = plan_tab[warp];
     if (lane == 0) {
 #pragma unroll
         for (int s = 0; s < STAGES; ++s) mbar_init(&bars[warp][s], 1);
@@ -93,71 +92,42 @@ __device__ __forceinline__ void decode_attention_body(const AttnParams &p, unsig
     Math::init(st, p, h, lane, rows);
 
     const uint64_t stream_policy = l2_policy_evict_first();   // the KV stream is read once per step
-    const bool planned = p.slot_source != nullptr || lu.order != nullptr;
     bool dead = false;
 
     for (int round = 0; round * kRoundUnits < total_my && !dead; ++round) {
-        UnitPlan plan;
-        int perm[2] = {0, 0};
-        if (planned) {
-            plan = plan_round(p, lu, h, worker, n_workers, lane, round, total_my);
-            plan_order(plan, lane, perm, perm_s[warp]);
-        } else {
-            plan.n_round = min(kRoundUnits, total_my - round * kRoundUnits);
-            plan.base[0] = plan.base[1] = plan.src[0] = plan.src[1] = -1;
-        }
-        const int n_round = plan.n_round;
+        const int n_round = plan_round(p, lu, h, worker, n_workers, lane, round, total_my, tab, (size_t)E);
         const int g0 = round * kRoundUnits;   // units this warp has consumed before this round
-
-        auto unit_index = [&](int it) -> int {
-            const int v = plan_lookup(perm, it);
-            return planned ? v : it;
-        };
-        // first slot-table token of the unit with index idx of this round
-        auto unit_base = [&](int u, int idx) -> int {
-            const int b = plan_lookup(plan.base, idx);
-            return planned ? b : u * kUnitTokens;
-        };
-        auto unit_src = [&](int idx) -> int {
-            const int v = plan_lookup(plan.src, idx);
-            return planned ? v : -1;
-        };
-        // tokens that exist from the unit's first token on (before any causal cut)
-        auto unit_avail = [&](int u, int base) -> int {
-            if (u < units_prefix) return n_prefix - base;
-            return n_local - (u - units_prefix) * kUnitTokens;
-        };
 
         // start the copies of the unit at position `it` of this round into stage s
         auto issue = [&](int s, int it) {
-            const int idx = unit_index(it);
-            const int u = worker + (g0 + idx) * n_workers;
+            const uint4 e = tab[it];
             uint64_t *bar = &bars[warp][s];
             unsigned char *dst = my_stages + (size_t)s * STAGEB;
-            const int base = unit_base(u, idx);
-            const int src_page = unit_src(idx);
-            const int ntok = min(kUnitTokens, unit_avail(u, base));
-            if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)ntok * TOKB);
-            __syncwarp();
-            if (u < units_prefix) {
-                const size_t tok = (size_t)base;
+            const int z = (int)e.z;
+            if (z >= 0) {
+                // slot-table unit (from its slot, or from the DRAM page that was just assigned to it)
+                const int ntok = min(kUnitTokens, n_prefix - z);
                 const unsigned char *src =
-                    src_page < 0 ? p.prefix + ((size_t)h * p.prefix_head_stride + tok * 2 * D) * E
-                                 : p.dram + ((size_t)h * p.dram_head_stride +
-                                             ((size_t)src_page * p.page_tokens + tok % p.page_tokens) * 2 * D) * E;
+                    reinterpret_cast<const unsigned char *>(((unsigned long long)e.y << 32) | e.x);
+                if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)ntok * TOKB);
+                __syncwarp();
                 if constexpr (Math::kPerTokenCopy) {
                     // a token's key and value rows are contiguous in HBM: one copy per token
-                    if (lane < ntok) bulk_copy_g2s_hint(dst + lane * PITCH, src + (size_t)lane * TOKB, TOKB, bar,
-                                                         stream_policy);
+                    if (lane < ntok)
+                        bulk_copy_g2s_hint(dst + lane * PITCH, src + (size_t)lane * TOKB, TOKB, bar, stream_policy);
                 } else {
                     if (lane == 0) bulk_copy_g2s_hint(dst, src, (uint32_t)ntok * TOKB, bar, stream_policy);
                 }
             } else {
                 // local window: one copy per row, key rows by lanes 0..15, value rows by lanes 16..31
+                const int tfirst = -1 - z;
+                const int ntok = min(kUnitTokens, n_local - tfirst);
+                if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)ntok * TOKB);
+                __syncwarp();
                 const int tl = lane & 15;
                 const int is_v = lane >> 4;
                 if (tl < ntok) {
-                    const int t = (u - units_prefix) * kUnitTokens + tl;
+                    const int t = tfirst + tl;
                     const unsigned char *src;
                     if (t >= t0) {   // one of this call's new tokens: straight from the inputs
                         src = (is_v ? p.new_v : p.new_k) + ((size_t)(t - t0) * p.n_kv_heads + h) * ROWB;
@@ -175,22 +145,22 @@ __device__ __forceinline__ void decode_attention_body(const AttnParams &p, unsig
         for (int it = 0; it < n_round; ++it) {
             const int g = g0 + it;
             const int s = g % STAGES;
+            const uint4 e = tab[it];
+            const int z = (int)e.z;
+            // tokens that exist from the unit's first token on (before any causal cut)
+            const int avail = z >= 0 ? n_prefix - z : n_local - (-1 - z);
+            const int ntok = min(kUnitTokens, avail);
+            unsigned char *sb = my_stages + (size_t)s * STAGEB;
             const bool arrived = mbar_wait_bounded(&bars[warp][s], (uint32_t)((g / STAGES) & 1));
             if (!__all_sync(DA_FULL_MASK, arrived)) {
                 if (lane == 0) atomicOr(p.status, DA_STATUS_WAIT_TIMEOUT);
                 dead = true;
                 break;
             }
-            const int idx = unit_index(it);
-            const int u = worker + (g0 + idx) * n_workers;
-            const int base = unit_base(u, idx);
-            const int avail = unit_avail(u, base);
-            const int ntok = min(kUnitTokens, avail);
-            unsigned char *sb = my_stages + (size_t)s * STAGEB;
-            if (u < units_prefix && unit_src(idx) >= 0) {
+            if (z >= 0 && (int)e.w >= 0) {
                 // this unit came from DRAM: write it through to its slot
                 unsigned char *slot = const_cast<unsigned char *>(p.prefix) +
-                                      ((size_t)h * p.prefix_head_stride + (size_t)base * 2 * D) * E;
+                                      ((size_t)h * p.prefix_head_stride + (size_t)z * 2 * D) * E;
                 for (int i = lane; i < ntok * (TOKB / 16); i += 32) {
                     const int t = i / (TOKB / 16), c = i % (TOKB / 16);
                     reinterpret_cast<uint4 *>(slot + (size_t)t * TOKB)[c] =
@@ -212,6 +182,7 @@ __device__ __forceinline__ void decode_attention_body(const AttnParams &p, unsig
             __syncwarp();
             if (it + STAGES < n_round) issue(s, it + STAGES);
         }
+        __syncwarp();   // the table is rewritten by the next round
     }
 
     // ---- this warp's partial into its own (now idle) ring ----------------------------------
@@ -260,7 +231,7 @@ __device__ __forceinline__ void decode_attention_body(const AttnParams &p, unsig
         first = p.splits1;                 // the head was redone by phase 2: leave phase 1's rows out
         n_rows = p.part_rows - p.splits1;
     }
-    merge_splits<T, D, THREADS>(p, h, first, n_rows, rows, reinterpret_cast<float *>(smem));
+    merge_splits<T, D, THREADS>(p, h, first, n_rows, rows, smem, WARPS * STAGES * STAGEB);
     // every CTA of this head is done with the eviction front: the one the LRU update left becomes current
     if (p.phase != 0 && tid == 0) p.flip[h] ^= 1;
     if (tid == 0) p.counters[h] = 0u;

@@ -11,17 +11,17 @@ constexpr int kAttnWarps = 4;          // warps per CTA of the single launch and
 constexpr int kAttnThreads = kAttnWarps * 32;
 constexpr int kUnitTokens = 16;
 constexpr int kCounterBytes = 1024;
-constexpr int kAttnTargetCtas = 296;   // 2 per SM on 148 SMs
+constexpr int kAttnTargetCtas = 444;   // 3 per SM on 148 SMs
 constexpr int kAttnMaxSplits = 148;
 constexpr int kAttnMaxRows = 16;       // query rows (tokens x GQA group) of one KV head per launch
-constexpr int kRoundUnits = 64;        // units a warp plans at a time (two per lane)
+constexpr int kRoundUnits = 32;        // units a warp plans at a time (one per lane)
 
 // Phase 1 runs beside the selection kernels, whose CTAs need a whole SM each.  Its CTAs are
-// therefore built to fill an SM on their own (8 warps, twice the shared memory), and by default
+// therefore built to fill an SM on their own (12 warps, all of the shared memory), and by default
 // there are at most 116 of them: wherever the hardware places them, 32 of the 148 SMs stay empty.
-// Phase 2 normally covers only the few slots the LRU update could evict; 64 CTAs (two per SM on
-// those 32 SMs) are plenty.
-constexpr int kAttnPhase1Warps = 8;
+// Phase 2 normally covers only the few slots the LRU update could evict; 64 CTAs on those 32 SMs
+// are plenty.
+constexpr int kAttnPhase1Warps = 12;
 constexpr int kAttnPhase1Ctas = 116;
 constexpr int kAttnPhase2Ctas = 64;
 
@@ -86,6 +86,7 @@ struct AttnParams {
     int splits1;                     // rows of phase 1 (first in the workspace)
     int n_kv_heads;
     int rep;
+    int head_dim;
     // query tokens: the call has s_total of them (appended at consecutive positions); this
     // launch computes tokens [q_tok0, q_tok0 + n_q), i.e. n_q * rep query rows per KV head
     int s_total, q_tok0, n_q;
@@ -128,163 +129,170 @@ __device__ __forceinline__ LaunchUnits launch_units(const AttnParams &p, int h, 
     return lu;
 }
 
-// Where each unit of one round of a warp comes from (two per lane).
-struct UnitPlan {
-    int n_round;       // units of this round: positions round * 64 .. round * 64 + n_round - 1 of the warp
-    int base[2];       // lane i: first token (inside the head's slot table) of unit i and 32 + i, or -1
-    int src[2];        // lane i: DRAM page to read that unit from instead, or -1
-};
-
-__device__ __forceinline__ UnitPlan plan_round(const AttnParams &p, const LaunchUnits &lu, int h, int worker,
-                                               int n_workers, int lane, int round, int total_my) {
-    UnitPlan pl;
-    pl.n_round = min(kRoundUnits, total_my - round * kRoundUnits);
-#pragma unroll
-    for (int k = 0; k < 2; ++k) {
-        pl.base[k] = -1;
-        pl.src[k] = -1;
-        const int i = 32 * k + lane;
-        const int u = worker + (round * kRoundUnits + i) * n_workers;
-        if (i < pl.n_round && u < lu.units_slots) {
-            int base = u * kUnitTokens;
-            if (lu.order) {
-                int slot = lu.order[lu.order_off + u / lu.ups];
-                slot = min(max(slot, 0), p.n_slots - 1);
-                base = slot * p.page_tokens + (u % lu.ups) * kUnitTokens;
-            }
-            pl.base[k] = base;
-            if (p.slot_source && p.phase != 1)
-                pl.src[k] = p.slot_source[(size_t)h * p.n_slots + base / p.page_tokens];
+// One entry of a warp's plan table (shared memory, in the order the warp visits its units):
+//   x, y  global address of the unit's first token (slot table, or the DRAM page to read instead)
+//   z     slot-table units: first token inside the head's slot table (>= 0);
+//         local-window units: -1 - first token of the unit in the local window
+//   w     DRAM page the unit is read from (it is then written through to its slot), or -1
+// A round covers the warp's units at positions round * 32 .. round * 32 + n_round - 1; lane i plans
+// unit i.  Units that have to come from DRAM are visited first, so that their host-link latency
+// overlaps everything else the warp does.  Returns n_round.
+__device__ __forceinline__ int plan_round(const AttnParams &p, const LaunchUnits &lu, int h, int worker,
+                                          int n_workers, int lane, int round, int total_my, uint4 *tab,
+                                          size_t elem_bytes) {
+    const int n_round = min(kRoundUnits, total_my - round * kRoundUnits);
+    const int u = worker + (round * kRoundUnits + lane) * n_workers;
+    const bool valid = lane < n_round;
+    int base = -1, src = -1;
+    if (valid && u < lu.units_slots) {
+        base = u * kUnitTokens;
+        if (lu.order) {
+            int slot = lu.order[lu.order_off + u / lu.ups];
+            slot = min(max(slot, 0), p.n_slots - 1);
+            base = slot * p.page_tokens + (u % lu.ups) * kUnitTokens;
         }
+        if (p.slot_source && p.phase != 1) src = p.slot_source[(size_t)h * p.n_slots + base / p.page_tokens];
     }
-    return pl;
-}
-
-// Order in which a warp walks the units of a round: the ones that have to come from DRAM first,
-// so that their host-link latency overlaps everything else the warp does.  perm = position ->
-// unit index (two per lane, like the plan); `scratch` is 64 bytes of shared memory of this warp.
-__device__ __forceinline__ void plan_order(const UnitPlan &pl, int lane, int (&perm)[2], unsigned char *scratch) {
-    const unsigned lt = (1u << lane) - 1;
-    const unsigned f0 = __ballot_sync(DA_FULL_MASK, pl.src[0] >= 0);
-    const unsigned f1 = __ballot_sync(DA_FULL_MASK, pl.src[1] >= 0);
-    const int nf = __popc(f0) + __popc(f1);
-#pragma unroll
-    for (int k = 0; k < 2; ++k) {
-        const int i = 32 * k + lane;
-        if (i < pl.n_round) {
-            const int fresh_before = k == 0 ? __popc(f0 & lt) : __popc(f0) + __popc(f1 & lt);
-            const bool fresh = pl.src[k] >= 0;
-            scratch[fresh ? fresh_before : nf + (i - fresh_before)] = (unsigned char)i;
+    const unsigned fresh = __ballot_sync(DA_FULL_MASK, valid && src >= 0);
+    if (valid) {
+        const int before = __popc(fresh & ((1u << lane) - 1));
+        const int pos = src >= 0 ? before : __popc(fresh) + (lane - before);
+        uint4 e;
+        unsigned long long addr = 0;
+        if (base >= 0) {
+            const size_t tok_bytes = (size_t)2 * p.head_dim * elem_bytes;
+            const unsigned char *a =
+                src < 0 ? p.prefix + (size_t)h * p.prefix_head_stride * elem_bytes + (size_t)base * tok_bytes
+                        : p.dram + (size_t)h * p.dram_head_stride * elem_bytes +
+                              ((size_t)src * p.page_tokens + base % p.page_tokens) * tok_bytes;
+            addr = (unsigned long long)a;
+            e.z = (unsigned)base;
+        } else {
+            e.z = (unsigned)(-1 - (u - lu.units_slots) * kUnitTokens);
         }
+        e.x = (unsigned)(addr & 0xffffffffull);
+        e.y = (unsigned)(addr >> 32);
+        e.w = (unsigned)src;
+        tab[pos] = e;
     }
     __syncwarp();
-#pragma unroll
-    for (int k = 0; k < 2; ++k) perm[k] = (32 * k + lane < pl.n_round) ? scratch[32 * k + lane] : 0;
-    __syncwarp();
+    return n_round;
 }
-
-// value of lane (it % 32)'s entry (it / 32) of a two-deep per-lane table
-__device__ __forceinline__ int plan_lookup(const int (&tab)[2], int it) {
-    const int v0 = __shfl_sync(DA_FULL_MASK, tab[0], it & 31);
-    const int v1 = __shfl_sync(DA_FULL_MASK, tab[1], it & 31);
-    return (it & 32) ? v1 : v0;
-}
-
 
 // Floats per partial row: acc[D], max, l, padded to a multiple of 4 so that rows can
 // be read with 128-bit loads.
 template <int D> struct PartialRow { static constexpr int kWidth = D + 4; };
 
+__device__ __forceinline__ void cp_async_16(void *dst_smem, const void *src_gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst_smem)), "l"(src_gmem) : "memory");
+}
+
+__device__ __forceinline__ void cp_async_wait_all() {
+    asm volatile("cp.async.wait_all;" ::: "memory");
+}
+
 // Final merge of the per-CTA partials of one head by one CTA of THREADS threads.  A CTA's
-// partial = `rows` rows of (acc[D] already weighted to the row's max, max, l).  `scratch` holds
-// at least 2 * splits * rows floats of shared memory (the idle stage buffers).  Loads bypass L1
-// (the rows were written by other SMs).  The first batch of accumulator rows is requested
-// together with the (max, l) pairs.
+// partial = `rows` rows of (acc[D] already weighted to the row's max, max, l); the partials of
+// consecutive CTAs are contiguous in the workspace.  They are brought into shared memory (the
+// idle stage buffers, `smem_bytes` of them) with 16-byte asynchronous copies that bypass L1 (the
+// rows were written by other SMs) and need no registers, as many CTAs' rows at a time as fit;
+// the first batch is requested before the (max, l) pairs are looked at.
 template <typename T, int D, int THREADS>
 __device__ __forceinline__ void merge_splits(const AttnParams &p, int h, int first_row, int splits, int rows,
-                                             float *scratch) {
+                                             unsigned char *smem, int smem_bytes) {
     constexpr int PW = PartialRow<D>::kWidth;
     constexpr int VPR = D / 4;          // float4 per accumulator row
-    constexpr int BATCH = 40;
     constexpr float NEG_INF = -INFINITY;
+    constexpr int MAXE = (kAttnMaxRows * VPR + THREADS - 1) / THREADS;   // output float4 per thread
     __shared__ float sh_m[kAttnMaxRows], sh_l[kAttnMaxRows];
     const int tid = threadIdx.x;
     const float *hp = p.partials + ((size_t)(h * p.part_rows + first_row) * rows) * PW;
     const int n = splits * rows;
-    const int RS = rows * PW / 4;  // float4 stride between the partials of two CTAs
-    float *wgt = scratch;        // [n] max, then weight
-    float *lsum = scratch + n;   // [n] l of every partial row
+    float *wgt = reinterpret_cast<float *>(smem);   // [n] max, then weight
+    float *lsum = wgt + n;                          // [n] l of every partial row
+    const int head_bytes = ((2 * n * (int)sizeof(float)) + 15) & ~15;
+    float4 *buf = reinterpret_cast<float4 *>(smem + head_bytes);
+    const int cta_f4 = rows * PW / 4;               // float4 per CTA's partial
+    int chunk = (smem_bytes - head_bytes) / (cta_f4 * 16);
+    chunk = min(max(chunk, 1), splits);
 
-    for (int e0 = 0; e0 < rows * VPR; e0 += THREADS) {
-        const int e = e0 + tid;
-        const bool live = e < rows * VPR;
-        const int r = live ? e / VPR : 0;
-        const int c4 = live ? e % VPR : 0;
-        const float4 *col = reinterpret_cast<const float4 *>(hp + (size_t)r * PW) + c4;
-        float4 v[BATCH];
-        // first batch of accumulator loads goes out before anything is waited on
+    auto request = [&](int s0) {
+        const int cnt = min(chunk, splits - s0);
+        const float4 *src = reinterpret_cast<const float4 *>(hp) + (size_t)s0 * cta_f4;
+        for (int i = tid; i < cnt * cta_f4; i += THREADS) cp_async_16(buf + i, src + i);
+    };
+    request(0);
+    for (int i = tid; i < n; i += THREADS) {
+        const float2 ml = __ldcg(reinterpret_cast<const float2 *>(hp + (size_t)i * PW + D));
+        wgt[i] = ml.x;
+        lsum[i] = ml.y;
+    }
+    __syncthreads();
+    {   // one warp per query row: common max, weights exp2(max_s - max), weighted row sum
+        const int lane = tid & 31;
+        for (int rr = tid >> 5; rr < rows; rr += THREADS / 32) {
+            float mn = NEG_INF;
+            for (int s = lane; s < splits; s += 32) mn = fmaxf(mn, wgt[s * rows + rr]);
 #pragma unroll
-        for (int u = 0; u < BATCH; ++u)
-            if (u < splits) v[u] = __ldcg(col + (size_t)u * RS);
-        if (e0 == 0) {
-            for (int i = tid; i < n; i += THREADS) {
-                const float2 ml = __ldcg(reinterpret_cast<const float2 *>(hp + (size_t)i * PW + D));
-                wgt[i] = ml.x;
-                lsum[i] = ml.y;
+            for (int off = 16; off >= 1; off >>= 1) mn = fmaxf(mn, __shfl_xor_sync(DA_FULL_MASK, mn, off));
+            const float ms = (mn == NEG_INF) ? 0.f : mn;
+            float ll = 0.f;
+            for (int s = lane; s < splits; s += 32) {
+                const float w = fast_exp2(wgt[s * rows + rr] - ms);
+                wgt[s * rows + rr] = w;
+                ll = fmaf(lsum[s * rows + rr], w, ll);
             }
-            __syncthreads();
-            // one warp per query row: common max, weights exp2(max_s - max), weighted row sum
-            const int lane = tid & 31;
-            for (int rr = tid >> 5; rr < rows; rr += THREADS / 32) {
-                float mn = NEG_INF;
-                for (int s = lane; s < splits; s += 32) mn = fmaxf(mn, wgt[s * rows + rr]);
 #pragma unroll
-                for (int off = 16; off >= 1; off >>= 1) mn = fmaxf(mn, __shfl_xor_sync(DA_FULL_MASK, mn, off));
-                const float ms = (mn == NEG_INF) ? 0.f : mn;
-                float ll = 0.f;
-                for (int s = lane; s < splits; s += 32) {
-                    const float w = fast_exp2(wgt[s * rows + rr] - ms);
-                    wgt[s * rows + rr] = w;
-                    ll = fmaf(lsum[s * rows + rr], w, ll);
-                }
-#pragma unroll
-                for (int off = 16; off >= 1; off >>= 1) ll += __shfl_xor_sync(DA_FULL_MASK, ll, off);
-                if (lane == 0) {
-                    sh_m[rr] = ms;
-                    sh_l[rr] = ll;
-                }
+            for (int off = 16; off >= 1; off >>= 1) ll += __shfl_xor_sync(DA_FULL_MASK, ll, off);
+            if (lane == 0) {
+                sh_m[rr] = ms;
+                sh_l[rr] = ll;
             }
-            __syncthreads();
         }
-        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int s0 = 0; s0 < splits; s0 += BATCH) {
-            if (s0 > 0) {
+    }
+    float4 a[MAXE];
 #pragma unroll
-                for (int u = 0; u < BATCH; ++u)
-                    if (s0 + u < splits) v[u] = __ldcg(col + (size_t)(s0 + u) * RS);
-            }
+    for (int k = 0; k < MAXE; ++k) a[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s0 = 0; s0 < splits; s0 += chunk) {
+        const int cnt = min(chunk, splits - s0);
+        cp_async_wait_all();
+        __syncthreads();      // the chunk and (first time round) the weights are in shared memory
 #pragma unroll
-            for (int u = 0; u < BATCH; ++u) {
-                if (s0 + u < splits) {
-                    const float w = wgt[(s0 + u) * rows + r];
-                    a.x = fmaf(v[u].x, w, a.x);
-                    a.y = fmaf(v[u].y, w, a.y);
-                    a.z = fmaf(v[u].z, w, a.z);
-                    a.w = fmaf(v[u].w, w, a.w);
+        for (int k = 0; k < MAXE; ++k) {
+            const int e = k * THREADS + tid;
+            if (e < rows * VPR) {
+                const int r = e / VPR, c4 = e % VPR;
+                const float4 *col = buf + r * (PW / 4) + c4;
+                for (int s = 0; s < cnt; ++s) {
+                    const float4 v = col[s * cta_f4];
+                    const float w = wgt[(s0 + s) * rows + r];
+                    a[k].x = fmaf(v.x, w, a[k].x);
+                    a[k].y = fmaf(v.y, w, a[k].y);
+                    a[k].z = fmaf(v.z, w, a[k].z);
+                    a[k].w = fmaf(v.w, w, a[k].w);
                 }
             }
         }
-        if (live) {
+        if (s0 + chunk < splits) {
+            __syncthreads();  // everybody is done with the buffer
+            request(s0 + chunk);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < MAXE; ++k) {
+        const int e = k * THREADS + tid;
+        if (e < rows * VPR) {
+            const int r = e / VPR, c4 = e % VPR;
             const float ll = sh_l[r];
             const float inv = ll > 0.f ? 1.f / ll : 0.f;
             // row r = (query token, head of the group)
             const int tok = p.q_tok0 + r / p.rep;
             const size_t orow = (size_t)tok * p.n_kv_heads * p.rep + (size_t)h * p.rep + r % p.rep;
             T *dst = reinterpret_cast<T *>(p.out) + orow * D + 4 * c4;
-            dst[0] = from_float<T>(a.x * inv);
-            dst[1] = from_float<T>(a.y * inv);
-            dst[2] = from_float<T>(a.z * inv);
-            dst[3] = from_float<T>(a.w * inv);
+            dst[0] = from_float<T>(a[k].x * inv);
+            dst[1] = from_float<T>(a[k].y * inv);
+            dst[2] = from_float<T>(a[k].z * inv);
+            dst[3] = from_float<T>(a[k].w * inv);
             if (c4 == 0 && p.lse_out) p.lse_out[orow] = (sh_m[r] + log2f(ll)) * 0.6931471805599453f;
         }
     }

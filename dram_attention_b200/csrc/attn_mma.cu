@@ -91,7 +91,6 @@ struct MmaMath {
     static constexpr int ROWB = kD * 2;                   // one key (or value) row in HBM
     static constexpr int kPitch = 2 * ROWB + 16;          // padded token (key row, value row) in shared memory
     static constexpr int STAGEB = kUnitTokens * kPitch;
-    static constexpr int kStages = STAGEB > 8192 ? 3 : 4;
     static constexpr bool kPerTokenCopy = true;
     static constexpr int KSTEPS = kD / 16;                // k-steps of the QK contraction
     static constexpr int NT = kD / 8;                     // n-tiles of the PV contraction
@@ -147,16 +146,23 @@ struct MmaMath {
         const int v_off = ROWB + ((lm & 1) * 8 + lr) * kPitch + (lm >> 1) * 16;    // value tile (transposed load)
 
         // ---- S = Q K^T for 16 tokens (two n-tiles of 8) --------------------------------
+        // four independent accumulation chains (even / odd k-steps of each n-tile), added at the end
         float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+        float s0b[4] = {0.f, 0.f, 0.f, 0.f}, s1b[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int kp = 0; kp < KSTEPS / 2; ++kp) {
-            uint32_t b[4];
+            uint32_t b[4], c[4];
             ldmatrix_x4(b, sb + k_off + kp * 64);                 // tokens 0..7, channels 32kp .. 32kp+31
+            ldmatrix_x4(c, sb + k_off + 8 * kPitch + kp * 64);    // tokens 8..15
             mma(s0, st, 2 * kp, b[0], b[1]);
-            mma(s0, st, 2 * kp + 1, b[2], b[3]);
-            ldmatrix_x4(b, sb + k_off + 8 * kPitch + kp * 64);    // tokens 8..15
-            mma(s1, st, 2 * kp, b[0], b[1]);
-            mma(s1, st, 2 * kp + 1, b[2], b[3]);
+            mma(s1, st, 2 * kp, c[0], c[1]);
+            mma(s0b, st, 2 * kp + 1, b[2], b[3]);
+            mma(s1b, st, 2 * kp + 1, c[2], c[3]);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            s0[i] += s0b[i];
+            s1[i] += s1b[i];
         }
         uint32_t pa[NR][2];
 #pragma unroll
@@ -183,10 +189,13 @@ struct MmaMath {
             v3 = fast_exp2(v3 - msafe);
             st.l_part[half] = st.l_part[half] * alpha + ((v0 + v1) + (v2 + v3));
             st.m_run[half] = mnew;
+            // once the running maxima have settled alpha is exactly 1 for every row: skip the rescale
+            if (__any_sync(DA_FULL_MASK, alpha != 1.f)) {
 #pragma unroll
-            for (int d = 0; d < NT; ++d) {
-                st.o[d][2 * half] *= alpha;
-                st.o[d][2 * half + 1] *= alpha;
+                for (int d = 0; d < NT; ++d) {
+                    st.o[d][2 * half] *= alpha;
+                    st.o[d][2 * half + 1] *= alpha;
+                }
             }
             pa[half][0] = MmaTraits<T>::pack(v0, v1);  // tokens 0..7 block of P
             pa[half][1] = MmaTraits<T>::pack(v2, v3);  // tokens 8..15 block of P
@@ -232,17 +241,18 @@ struct MmaMath {
     }
 };
 
-template <typename T, int D, bool FULL, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 2 : 1) decode_attention_mma_kernel(const AttnParams p) {
+// WARPS per CTA, STAGES per warp, at least MINB CTAs per SM.
+template <typename T, int D, bool FULL, int WARPS, int STAGES, int MINB>
+__global__ void __launch_bounds__(WARPS * 32, MINB) decode_attention_mma_kernel(const AttnParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
-    decode_attention_body<MmaMath<T, D, FULL>, WARPS>(p, smem);
+    decode_attention_body<MmaMath<T, D, FULL>, WARPS, STAGES>(p, smem);
 }
 
-template <typename T, int D, bool FULL, int WARPS>
+template <typename T, int D, bool FULL, int WARPS, int STAGES, int MINB>
 static cudaError_t launch_mma_w(const AttnParams &p, int n_kv_heads, int splits, cudaStream_t stream) {
     using M = MmaMath<T, D, FULL>;
-    constexpr int SMEM = WARPS * M::kStages * M::STAGEB;
-    auto kern = decode_attention_mma_kernel<T, D, FULL, WARPS>;
+    constexpr int SMEM = WARPS * STAGES * M::STAGEB;
+    auto kern = decode_attention_mma_kernel<T, D, FULL, WARPS, STAGES, MINB>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -258,21 +268,26 @@ static cudaError_t launch_mma_w(const AttnParams &p, int n_kv_heads, int splits,
     return cudaGetLastError();
 }
 
-template <typename T, int D>
+// Geometry.  The loop of a warp is a chain of dependent instructions (wait, ldmatrix, mma,
+// softmax, issue), so an SM needs many warps to keep its copies flowing: 12 warps with two
+// stages each (203 KB of stages per SM for head_dim 128).  The single launch and phase 2 use
+// three 4-warp CTAs per SM; phase 1 one 12-warp CTA that fills its SM.
+template <typename T, int D, bool FULL>
 static cudaError_t launch_mma(const AttnParams &p, int n_kv_heads, int splits, cudaStream_t stream) {
-    const int rows = p.n_q * p.rep;
-    if (rows > 8) {
-        if (p.phase == 1) return launch_mma_w<T, D, true, kAttnPhase1Warps>(p, n_kv_heads, splits, stream);
-        return launch_mma_w<T, D, true, kAttnWarps>(p, n_kv_heads, splits, stream);
-    }
-    if (p.phase == 1) return launch_mma_w<T, D, false, kAttnPhase1Warps>(p, n_kv_heads, splits, stream);
-    return launch_mma_w<T, D, false, kAttnWarps>(p, n_kv_heads, splits, stream);
+    if (p.phase == 1) return launch_mma_w<T, D, FULL, kAttnPhase1Warps, 2, 1>(p, n_kv_heads, splits, stream);
+    return launch_mma_w<T, D, FULL, kAttnWarps, 2, 3>(p, n_kv_heads, splits, stream);
+}
+
+template <typename T, int D>
+static cudaError_t launch_mma_d(const AttnParams &p, int n_kv_heads, int splits, cudaStream_t stream) {
+    if (p.n_q * p.rep > 8) return launch_mma<T, D, true>(p, n_kv_heads, splits, stream);
+    return launch_mma<T, D, false>(p, n_kv_heads, splits, stream);
 }
 
 template <typename T>
 static cudaError_t dispatch_mma(const AttnParams &p, int n_kv_heads, int head_dim, int splits, cudaStream_t s) {
-    if (head_dim == 128) return launch_mma<T, 128>(p, n_kv_heads, splits, s);
-    if (head_dim == 64) return launch_mma<T, 64>(p, n_kv_heads, splits, s);
+    if (head_dim == 128) return launch_mma_d<T, 128>(p, n_kv_heads, splits, s);
+    if (head_dim == 64) return launch_mma_d<T, 64>(p, n_kv_heads, splits, s);
     return cudaErrorInvalidValue;
 }
 

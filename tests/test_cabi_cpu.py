@@ -65,9 +65,9 @@ def test_host_side_argument_checks(native):
     assert lib.da_decode_attention_phased_supported(8, 4, 128, 2, 2048, 8, 4160) == 0     # page < 16 tokens
     assert lib.da_decode_attention_phased_supported(8, 4, 128, 0, 2048, 16, 4160) == 0     # fp32, D 128: CTA too big
     ws = lib.da_decode_attention_workspace_bytes(8, 4, 128)
-    assert ws == 1024 + 8 * 37 * 4 * 132 * 4
-    assert lib.da_decode_attention_tokens_workspace_bytes(8, 4, 128, 3) == 1024 + 8 * 37 * 12 * 132 * 4
-    assert lib.da_decode_attention_tokens_workspace_bytes(8, 4, 128, 9) == 1024 + 8 * 37 * 16 * 132 * 4
+    assert ws == 1024 + 8 * 55 * 4 * 132 * 4
+    assert lib.da_decode_attention_tokens_workspace_bytes(8, 4, 128, 3) == 1024 + 8 * 55 * 12 * 132 * 4
+    assert lib.da_decode_attention_tokens_workspace_bytes(8, 4, 128, 9) == 1024 + 8 * 55 * 16 * 132 * 4
     assert lib.da_decode_attention_phased_workspace_bytes(8, 4, 128) == 1024 + 8 * (148 + 148) * 4 * 132 * 4
     args = [256, 256, 4096, 16, 256, 256, 1024, 128, 64, 256, 256, 0, 0, 0, 256, 0, 256, ws, 256,
             8, 4, 128, 2, 0]
