@@ -32,7 +32,7 @@ _SIGNATURES = {
     "da_topk_pages": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "da_lru_update": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                              c_int, c_int, c_void_p, c_void_p]),
+                              c_int, c_int, c_void_p, c_void_p, c_size_t, c_int, c_void_p, c_void_p]),
     "da_prefill_attention_supported": (c_int, [c_int, c_int]),
     "da_prefill_attention": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                      c_longlong, c_longlong, c_int, c_void_p, c_void_p]),

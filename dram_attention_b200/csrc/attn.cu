@@ -203,6 +203,9 @@ static cudaError_t launch_attn_w(const AttnParams &p, int n_kv_heads, int splits
         attr_set[dev] = true;
     }
     dim3 grid(splits, n_kv_heads);
+    // phase 1 runs on a stream of its own beside the kernels of the step; the other launches follow
+    // the LRU update in their stream and may move onto the SMs while it is still running
+    if (p.phase != 1) return launch_dependent(kern, grid, dim3(WARPS * 32), (size_t)SMEM, stream, p);
     kern<<<grid, WARPS * 32, SMEM, stream>>>(p);
     return cudaGetLastError();
 }

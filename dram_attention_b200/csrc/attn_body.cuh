@@ -46,6 +46,19 @@ __device__ __forceinline__ void decode_attention_body(const AttnParams &p, unsig
     const int warp = tid >> 5;
     const int rows = p.n_q * p.rep;
 
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < STAGES; ++s) mbar_init(&bars[warp][s], 1);
+    }
+    mbar_fence_init();
+    __syncthreads();
+    // Launched as a dependent of the kernel before it in the stream, i.e. possibly while that kernel
+    // is still at work.  The single launch reads nothing in global memory before the wait.  The
+    // second launch of a step (phase 2) always follows the LRU update, whose results it needs only
+    // late: it reads its inputs, the eviction queue as it was before the update and its query rows
+    // first (all of them complete before the update began) and waits further down.
+    if (p.phase != 2) griddep_wait();
+
     // ---- position and unit range ------------------------------------------------
     const int pos = p.start_pos_dev ? *p.start_pos_dev : p.start_pos_host;
     int t0 = pos - p.dram_tokens;   // index of the first new token in the local window
@@ -59,18 +72,12 @@ __device__ __forceinline__ void decode_attention_body(const AttnParams &p, unsig
     const int n_prefix = p.n_prefix_tokens;
     const int n_workers = splits * WARPS;
     const int worker = x * WARPS + warp;
-    const LaunchUnits lu = launch_units(p, h, n_local);
-    const int units = lu.units_slots + lu.units_local;
-    const int total_my = units > worker ? (units - worker + n_workers - 1) / n_workers : 0;
+    LaunchUnits lu = launch_units(p, h, n_local, false);
+    int units = lu.units_slots + lu.units_local;
+    int total_my = units > worker ? (units - worker + n_workers - 1) / n_workers : 0;
 
     unsigned char *my_stages = smem + (size_t)warp * STAGES * STAGEB;
     uint4 *tab = plan_tab[warp];
-    if (lane == 0) {
-#pragma unroll
-        for (int s = 0; s < STAGES; ++s) mbar_init(&bars[warp][s], 1);
-    }
-    mbar_fence_init();
-    __syncthreads();
 
     // ---- append the new keys/values to the local window ----------------------------
     if (x == 0 && warp == 0 && pos_ok && p.phase != 2 && p.q_tok0 == 0) {
@@ -94,8 +101,21 @@ __device__ __forceinline__ void decode_attention_body(const AttnParams &p, unsig
     const uint64_t stream_policy = l2_policy_evict_first();   // the KV stream is read once per step
     bool dead = false;
 
+    int base0 = plan_base(p, lu, worker, n_workers, lane, 0, total_my);
+    if (p.phase == 2) {
+        griddep_wait();   // from here on the LRU update is complete
+        if (p.redo[h] != 0) {
+            // it evicted beyond the front: this launch covers the whole head
+            lu = launch_units(p, h, n_local, true);
+            units = lu.units_slots + lu.units_local;
+            total_my = units > worker ? (units - worker + n_workers - 1) / n_workers : 0;
+            base0 = plan_base(p, lu, worker, n_workers, lane, 0, total_my);
+        }
+    }
+
     for (int round = 0; round * kRoundUnits < total_my && !dead; ++round) {
-        const int n_round = plan_round(p, lu, h, worker, n_workers, lane, round, total_my, tab, (size_t)E);
+        const int base = round == 0 ? base0 : plan_base(p, lu, worker, n_workers, lane, round, total_my);
+        const int n_round = plan_commit(p, lu, h, worker, n_workers, lane, round, total_my, base, tab, (size_t)E);
         const int g0 = round * kRoundUnits;   // units this warp has consumed before this round
 
         // start the copies of the unit at position `it` of this round into stage s

@@ -101,7 +101,8 @@ struct LaunchUnits {
     int ups;              // units per slot page
 };
 
-__device__ __forceinline__ LaunchUnits launch_units(const AttnParams &p, int h, int n_local) {
+// `redo`: the LRU update had to evict beyond the front (second launch only).
+__device__ __forceinline__ LaunchUnits launch_units(const AttnParams &p, int h, int n_local, bool redo) {
     LaunchUnits lu;
     lu.order = nullptr;
     lu.order_off = 0;
@@ -117,7 +118,7 @@ __device__ __forceinline__ LaunchUnits launch_units(const AttnParams &p, int h, 
             lu.units_slots = (p.n_slots - n_ev) * lu.ups;
             lu.order = order;
             lu.order_off = n_ev;
-        } else if (p.redo[h] != 0) {
+        } else if (redo) {
             lu.units_slots = p.n_slots * lu.ups;   // the whole head, slots in place
         } else {
             lu.units_slots = n_ev * lu.ups;
@@ -135,24 +136,38 @@ __device__ __forceinline__ LaunchUnits launch_units(const AttnParams &p, int h, 
 //         local-window units: -1 - first token of the unit in the local window
 //   w     DRAM page the unit is read from (it is then written through to its slot), or -1
 // A round covers the warp's units at positions round * 32 .. round * 32 + n_round - 1; lane i plans
-// unit i.  Units that have to come from DRAM are visited first, so that their host-link latency
-// overlaps everything else the warp does.  Returns n_round.
-__device__ __forceinline__ int plan_round(const AttnParams &p, const LaunchUnits &lu, int h, int worker,
-                                          int n_workers, int lane, int round, int total_my, uint4 *tab,
-                                          size_t elem_bytes) {
+// unit i.  Planning has two halves, so that the second launch of a step can do the first before
+// the LRU update has finished: plan_base() needs only the eviction queue as it was BEFORE the
+// update, plan_commit() the marks the update leaves (which slots must be read from DRAM).
+
+// First slot-table token of lane's unit of this round, or -1 (a local-window unit, or none).
+__device__ __forceinline__ int plan_base(const AttnParams &p, const LaunchUnits &lu, int worker, int n_workers,
+                                         int lane, int round, int total_my) {
     const int n_round = min(kRoundUnits, total_my - round * kRoundUnits);
     const int u = worker + (round * kRoundUnits + lane) * n_workers;
-    const bool valid = lane < n_round;
-    int base = -1, src = -1;
-    if (valid && u < lu.units_slots) {
+    int base = -1;
+    if (lane < n_round && u < lu.units_slots) {
         base = u * kUnitTokens;
         if (lu.order) {
             int slot = lu.order[lu.order_off + u / lu.ups];
             slot = min(max(slot, 0), p.n_slots - 1);
             base = slot * p.page_tokens + (u % lu.ups) * kUnitTokens;
         }
-        if (p.slot_source && p.phase != 1) src = p.slot_source[(size_t)h * p.n_slots + base / p.page_tokens];
     }
+    return base;
+}
+
+// Writes the round's table.  Units that have to come from DRAM are visited first, so that their
+// host-link latency overlaps everything else the warp does.  Returns n_round.
+__device__ __forceinline__ int plan_commit(const AttnParams &p, const LaunchUnits &lu, int h, int worker,
+                                           int n_workers, int lane, int round, int total_my, int base,
+                                           uint4 *tab, size_t elem_bytes) {
+    const int n_round = min(kRoundUnits, total_my - round * kRoundUnits);
+    const int u = worker + (round * kRoundUnits + lane) * n_workers;
+    const bool valid = lane < n_round;
+    int src = -1;
+    if (base >= 0 && p.slot_source && p.phase != 1)
+        src = p.slot_source[(size_t)h * p.n_slots + base / p.page_tokens];
     const unsigned fresh = __ballot_sync(DA_FULL_MASK, valid && src >= 0);
     if (valid) {
         const int before = __popc(fresh & ((1u << lane) - 1));

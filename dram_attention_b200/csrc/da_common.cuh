@@ -92,6 +92,32 @@ template <typename T, int N> __device__ __forceinline__ void load_elems(const vo
     }
 }
 
+// ---- programmatic dependent launch ---------------------------------------------
+// The kernels of a generate step form a chain (scores -> page list -> tables -> attention).  A
+// kernel launched with launch_dependent() may be placed on the SMs while its predecessor in the
+// stream is still running; it must call griddep_wait() before it touches anything an earlier
+// kernel of the stream wrote (the call returns once those kernels have completed and their
+// writes are visible).  A predecessor lets its successor in early with
+// griddep_launch_dependents().  Both are no-ops for kernels launched the ordinary way.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                           cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ---- small math ------------------------------------------------------------
 
 __device__ __forceinline__ float fast_exp2(float x) {

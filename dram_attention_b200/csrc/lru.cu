@@ -5,17 +5,28 @@
 //   2. misses: the first appearance (in list order) of every non-resident page is
 //      found with a shared-memory hash table keyed by page id that keeps the
 //      smallest list index, and ranked by a block prefix sum.
-//   3. victims: the n_miss slots with the smallest (time, slot).  No sort: a radix
-//      select on the time finds the time T of the n_miss-th slot, every slot with
-//      time < T is a victim, and the slots with time == T fill the rest in slot order
-//      (an ordered block scan); the victims are then ranked among themselves by
-//      counting.  One 8-bit select pass per byte of the step counter.
+//   3. victims: the n_miss slots with the smallest (time, slot).
 //   4. the j-th miss takes the j-th victim; tables updated; (page, slot) pairs
 //      emitted for the payload copy.
-//   5. optionally (two-launch attention) the eviction FRONT: the same select, for position
-//      n_miss + split_cap, names the slots that are first in eviction order after this call;
-//      and the call reports whether one of its own victims lay outside the front that was
-//      current when it ran (the attention then redoes that head).
+//
+// Two kernels, which differ in step 3:
+//
+//   lru_queue_kernel   the caller keeps the slots of every head as a QUEUE in eviction order
+//       ((time, slot) ascending; two copies, the call reads one and writes the other).  Slots
+//       this call does not touch keep their relative order, and the touched ones (hits and
+//       victims) all get the newest stamp, i.e. go to the back in slot order.  So the victims are
+//       simply the first n_miss untouched slots of the queue, and the new queue is a stable
+//       partition: two rounds of block prefix sums, no sort, no select, and the timestamps are
+//       never read.  The front of the new queue is what the NEXT call will evict from: the
+//       two-launch attention leaves the first `split_cap` slots to its second launch, and this
+//       call reports (redo) when one of its own victims lay beyond the front that was current.
+//       When only a few pages miss, the kernel also copies them from DRAM (pinned host memory)
+//       into their slots itself; the loads are issued before the second round of prefix sums, so
+//       the host-link latency hides behind it.
+//   lru_update_kernel  no queue: an 8-bit radix select on the time finds the time T of the
+//       n_miss-th slot, every slot with time < T is a victim, the slots with time == T fill the
+//       rest in slot order (an ordered block scan), and the victims older than T are ranked
+//       among themselves by counting.
 
 #include "da_common.cuh"
 
@@ -137,15 +148,14 @@ __device__ __forceinline__ void select_time(const int (&tm)[SR], int need, int b
     less_out = less;
 }
 
-// SR = slots per thread (n_slots <= SR * 1024), LR = list entries per thread.
+// Without a queue.  SR = slots per thread (n_slots <= SR * 1024), LR = list entries per thread.
 template <int SR, int LR>
 __global__ void __launch_bounds__(kLruThreads)
 lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *dram_to_slot, int n_dram_pages,
                   int32_t *slot_to_dram, int32_t *access_time, int n_slots, int32_t *step_counters,
                   int32_t *__restrict__ miss_pages, int32_t *__restrict__ miss_slots,
-                  int32_t *__restrict__ n_miss_out, int32_t *slot_source, int32_t *order_out,
-                  int32_t *n_evictable_out, int32_t *split_flip, int32_t *split_redo, int split_cap,
-                  int split_advance, int32_t *status) {
+                  int32_t *__restrict__ n_miss_out, int32_t *slot_source, int32_t *status) {
+    griddep_wait();   // the page list comes from the kernel before this one
     extern __shared__ __align__(16) int smem_i[];
     const int table = lru_table_size(list_len);
     int *tkey = smem_i;                  // [table] page id or -1; later: victim slots by rank
@@ -155,12 +165,10 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
     int *mpage = s2d_s + n_slots;        // [list_len] miss pages in list order
     int *vtime = mpage + list_len;       // [list_len] victims: time
     int *vslot = vtime + list_len;       // [list_len] victims: slot
-    unsigned char *in_front = reinterpret_cast<unsigned char *>(vslot + list_len);   // [n_slots] slot is in the current front
     __shared__ int wsum[kLruWarps];
     __shared__ int hist[512];
     __shared__ int res[2];
     __shared__ int sh_max;
-    __shared__ int sh_redo;
 
     const int h = blockIdx.x;
     const int tid = threadIdx.x;
@@ -196,23 +204,15 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
         }
     }
     const int step = step_counters[h] + 1;
-    const int prev_miss = min(n_miss_out[h], list_len);
-    // the eviction front the attention launch beside this update works from
-    const bool want_order = order_out != nullptr;
-    const int cur = want_order ? (split_flip[h] & 1) : 0;
-    const int32_t *front_cur = want_order ? order_out + ((size_t)cur * gridDim.x + h) * n_slots : nullptr;
-    const int n_front = want_order ? min(max(n_evictable_out[(size_t)cur * gridDim.x + h], 0), n_slots) : n_slots;
 #pragma unroll
     for (int r = 0; r < LR; ++r) sl[r] = pg[r] >= 0 ? d2s[pg[r]] : 0;
 
     // slot_source[slot] = DRAM page whose payload still has to be brought into the slot, -1
-    // otherwise: forget the marks of the previous call (its miss list is still in ms_out)
+    // otherwise.  Rewritten by every call: -1 everywhere, then (after several barriers) the marks
+    // of this call's misses.
     int32_t *src_map = slot_source ? slot_source + (size_t)h * n_slots : nullptr;
     if (src_map) {
-        for (int j = tid; j < prev_miss; j += kLruThreads) {
-            const int v = ms_out[j];
-            if (v >= 0 && v < n_slots) src_map[v] = -1;
-        }
+        for (int x = tid; x < n_slots; x += kLruThreads) src_map[x] = -1;
     }
 #pragma unroll
     for (int r = 0; r < SR; ++r) {
@@ -226,19 +226,9 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
         tkey[x] = -1;
         tval[x] = 0x7fffffff;
     }
-    for (int x = tid; x < n_slots; x += kLruThreads) in_front[x] = n_front >= n_slots;
-    if (tid == 0) {
-        sh_max = step;
-        sh_redo = 0;
-    }
+    if (tid == 0) sh_max = step;
     if (bad) atomicOr(status, DA_STATUS_BAD_PAGE_ID);
     __syncthreads();
-    if (n_front < n_slots) {
-        for (int x = tid; x < n_front; x += kLruThreads) {
-            const int v = front_cur[x];
-            if (v >= 0 && v < n_slots) in_front[v] = 1;
-        }
-    }
 
     // ---- 1. hits get the step; non-resident pages go into the hash table -------------
     const int tmask = table - 1;
@@ -297,7 +287,6 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
         hits = total;
     }
     const int bits = 32 - __clz(sh_max | 1);
-    const int n_found = n_miss;
 
     // ---- 3. victims ------------------------------------------------------------------------
     bool victim[SR];
@@ -359,74 +348,267 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
                 mp_out[j] = p;
                 ms_out[j] = v;
                 if (src_map) src_map[v] = p;
-                if (!in_front[v]) sh_redo = 1;   // evicted a slot the attention beside us is reading
             }
         }
     }
 
-    // ---- 5. the eviction front after this call -------------------------------------------------
-    // In (time, slot) order the slots are now [victims | untouched | hit by this call].  After
-    // this call victims and hits carry the newest stamp, so the next call's victims come from the
-    // front of the untouched run: how far in depends on how many of those slots it hits and how
-    // many pages it misses.  The first split_cap slots of the run are written as the new front
-    // (order_out = those first, every other slot after them); the next call checks its victims
-    // against it (sh_redo above).  With fewer than split_cap untouched slots every slot is in the front.
-    if (want_order) {
-        // two buffers, [2][n_kv_heads][...]: the one split_flip[h] does NOT name is written
-        const int wbuf = 1 - cur;
-        int32_t *ord = order_out + ((size_t)wbuf * gridDim.x + h) * n_slots;
-        const int cap = min(max(split_cap, 0), n_slots);
-        const int untouched = n_slots - hits - n_miss;
-        const bool bounded = !overflow && n_found == n_miss && untouched >= cap && cap > 0 && cap < n_slots;
-        if (bounded) {
-            int t2, less2;
-            select_time<SR>(tm, n_miss + cap, bits, hist, res, t2, less2);   // tm: times before assignment
-            int run_eq = 0, run_e = 0;
-#pragma unroll
-            for (int r = 0; r < SR; ++r) {
-                if (r * kLruThreads < n_slots) {
-                    const int s = r * kLruThreads + tid;
-                    const int eq = tm[r] == t2;
-                    int total;
-                    const int eq_rank = run_eq + block_exclusive_scan(eq, wsum, &total);
-                    run_eq += total;
-                    const bool front = tm[r] >= 0 && (tm[r] < t2 || (eq && less2 + eq_rank < n_miss + cap));
-                    const int e = front && !victim[r];
-                    const int e_before = run_e + block_exclusive_scan(e, wsum, &total);
-                    run_e += total;
-                    if (s < n_slots) ord[e ? e_before : cap + (s - e_before)] = s;
-                }
-            }
-        } else {
-            for (int s = tid; s < n_slots; s += kLruThreads) ord[s] = s;
-        }
-        if (tid == 0) n_evictable_out[(size_t)wbuf * gridDim.x + h] = bounded ? cap : n_slots;
-    }
-    __syncthreads();   // sh_redo
     if (tid == 0) {
         n_miss_out[h] = n_miss;
         step_counters[h] = step;
-        if (want_order) {
-            split_redo[h] = sh_redo;
-            if (split_advance) split_flip[h] = 1 - cur;
+    }
+}
+
+
+// 16-byte load that bypasses L1 (page payloads in pinned host memory are read once)
+__device__ __forceinline__ uint4 ld_stream_16(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+constexpr int kLruInlineBatch = 4;   // 16-byte loads a thread keeps in flight while it copies pages
+
+// With the eviction queue.  SR = slots per thread (n_slots <= SR * 1024), LR = list entries per thread.
+//   queue      [2][n_kv_heads][n_slots]: copy flip[h] is read (slots in eviction order), the other written
+//   n_front    [2][n_kv_heads]: how many slots at the head of the queue the attention leaves to its
+//              second launch; written for the new queue
+template <int SR, int LR>
+__global__ void __launch_bounds__(kLruThreads)
+lru_queue_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *dram_to_slot, int n_dram_pages,
+                 int32_t *slot_to_dram, int32_t *access_time, int n_slots, int32_t *step_counters,
+                 int32_t *__restrict__ miss_pages, int32_t *__restrict__ miss_slots,
+                 int32_t *__restrict__ n_miss_out, int32_t *slot_source, int32_t *queue, int32_t *n_front_io,
+                 int32_t *split_flip, int32_t *split_redo, int split_cap, int split_advance,
+                 const unsigned char *dram_pages, unsigned char *slots, unsigned long long page_bytes,
+                 int inline_max, int32_t *status) {
+    griddep_wait();   // the page list comes from the kernel before this one
+    extern __shared__ __align__(16) int smem_i[];
+    const int table = lru_table_size(list_len);
+    int *tkey = smem_i;                  // [table] page id or -1
+    int *tval = tkey + table;            // [table] smallest list index of that page
+    int *mpage = tval + table;           // [list_len] miss pages in list order
+    int *vslot = mpage + list_len;       // [list_len] victims in queue order
+    unsigned char *touched = reinterpret_cast<unsigned char *>(vslot + list_len);   // [n_slots] hit or victim
+    __shared__ int wsum[kLruWarps];
+    __shared__ int sh_redo;
+
+    const int h = blockIdx.x;
+    const int tid = threadIdx.x;
+    const int32_t *list = page_list + (size_t)h * list_len;
+    int32_t *d2s = dram_to_slot + (size_t)h * n_dram_pages;
+    int32_t *s2d = slot_to_dram + (size_t)h * n_slots;
+    int32_t *tim = access_time + (size_t)h * n_slots;
+    int32_t *mp_out = miss_pages + (size_t)h * list_len;
+    int32_t *ms_out = miss_slots + (size_t)h * list_len;
+
+    // ---- all independent global reads first ---------------------------------------------
+    const int cur = split_flip[h] & 1;
+    const int32_t *q_in = queue + ((size_t)cur * gridDim.x + h) * n_slots;
+    int32_t *q_out = queue + ((size_t)(1 - cur) * gridDim.x + h) * n_slots;
+    int qs[SR];
+#pragma unroll
+    for (int r = 0; r < SR; ++r) {
+        const int i = r * kLruThreads + tid;
+        qs[r] = i < n_slots ? min(max(q_in[i], 0), n_slots - 1) : -1;
+    }
+    int pg[LR], sl[LR];
+    int bad = 0;
+#pragma unroll
+    for (int r = 0; r < LR; ++r) {
+        const int i = r * kLruThreads + tid;
+        pg[r] = -1;
+        if (i < list_len) {
+            const int p = list[i];
+            if (p < 0 || p >= n_dram_pages) bad = 1; else pg[r] = p;
         }
+    }
+    const int step = step_counters[h] + 1;
+    const int n_front = min(max(n_front_io[(size_t)cur * gridDim.x + h], 0), n_slots);
+#pragma unroll
+    for (int r = 0; r < LR; ++r) sl[r] = pg[r] >= 0 ? d2s[pg[r]] : 0;
+
+    // slot_source is rewritten by every call: -1 everywhere, then (after several barriers) the
+    // marks of this call's misses
+    int32_t *src_map = slot_source ? slot_source + (size_t)h * n_slots : nullptr;
+    if (src_map) {
+        for (int x = tid; x < n_slots; x += kLruThreads) src_map[x] = -1;
+    }
+    for (int x = tid; x < table; x += kLruThreads) {
+        tkey[x] = -1;
+        tval[x] = 0x7fffffff;
+    }
+    for (int x = tid; x < n_slots; x += kLruThreads) touched[x] = 0;
+    if (tid == 0) sh_redo = 0;
+    if (bad) atomicOr(status, DA_STATUS_BAD_PAGE_ID);
+    __syncthreads();
+    griddep_launch_dependents();   // the kernel after this one may move onto the SMs and wait there
+
+    // ---- 1. hits get the step; non-resident pages go into the hash table -------------
+    const int tmask = table - 1;
+    const int tshift = 32 - (__ffs(table) - 1);
+#pragma unroll
+    for (int r = 0; r < LR; ++r) {
+        const int p = pg[r];
+        if (p < 0) { sl[r] = -1; continue; }   // sl[r] becomes the table position of a miss, -1 otherwise
+        const int s = sl[r];
+        sl[r] = -1;
+        if (s >= 0) {
+            if (s < n_slots) { touched[s] = 1; tim[s] = step; }
+        } else {
+            int pos = (int)(((uint32_t)p * 2654435761u) >> tshift) & tmask;
+            for (int probe = 0; probe < table; ++probe) {
+                const int prev = atomicCAS(&tkey[pos], -1, p);
+                if (prev == -1 || prev == p) {
+                    atomicMin(&tval[pos], r * kLruThreads + tid);
+                    sl[r] = pos;
+                    break;
+                }
+                pos = (pos + 1) & tmask;
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---- 2. first appearances, ranked in list order ----------------------------------------
+    int n_miss = 0;
+#pragma unroll
+    for (int r = 0; r < LR; ++r) {
+        if (r * kLruThreads < list_len) {
+            const int f = (sl[r] >= 0) && (tval[sl[r]] == r * kLruThreads + tid);
+            int total;
+            const int j = n_miss + block_exclusive_scan(f, wsum, &total);
+            if (f) mpage[j] = pg[r];
+            n_miss += total;
+        }
+    }
+
+    // ---- 3. victims = the first n_miss slots of the queue that no hit touched ------------------
+    int urank[SR];        // rank of this queue position among the untouched ones, or -1
+    int n_untouched = 0;
+#pragma unroll
+    for (int r = 0; r < SR; ++r) {
+        urank[r] = -1;
+        if (r * kLruThreads < n_slots) {
+            const int u = qs[r] >= 0 && !touched[qs[r]];
+            int total;
+            const int ex = n_untouched + block_exclusive_scan(u, wsum, &total);
+            if (u) urank[r] = ex;
+            n_untouched += total;
+        }
+    }
+    if (n_miss > n_untouched) {
+        // more distinct non-resident pages than slots this call may evict: tables stay as after the hits
+        if (tid == 0) atomicOr(status, DA_STATUS_LRU_OVERFLOW);
+        n_miss = 0;
+    }
+#pragma unroll
+    for (int r = 0; r < SR; ++r) {
+        if (urank[r] >= 0) {
+            if (urank[r] < n_miss) {
+                vslot[urank[r]] = qs[r];
+                touched[qs[r]] = 1;
+                if (r * kLruThreads + tid >= n_front) sh_redo = 1;   // beyond the front the attention left out
+            } else {
+                q_out[urank[r] - n_miss] = qs[r];                    // survivors keep their order
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---- 4. the j-th miss takes the j-th victim ---------------------------------------------
+    const bool copy_here = dram_pages != nullptr && n_miss <= inline_max;
+    for (int j = tid; j < n_miss; j += kLruThreads) {
+        const int p = mpage[j];
+        const int v = vslot[j];
+        const int old = s2d[v];
+        if (old >= 0 && old < n_dram_pages) d2s[old] = -1;
+        s2d[v] = p;
+        d2s[p] = v;
+        tim[v] = step;
+        mp_out[j] = p;
+        ms_out[j] = v;
+        if (src_map && !copy_here) src_map[v] = p;   // the attention kernel brings the page in
+    }
+    // Few misses: copy the pages here.  The first loads go out now and are stored after the
+    // second round of prefix sums.
+    const int vec_per_page = (int)(page_bytes / 16);
+    const int n_vec = copy_here ? n_miss * vec_per_page : 0;
+    const unsigned char *src_h = dram_pages + (size_t)h * n_dram_pages * page_bytes;
+    unsigned char *dst_h = slots + (size_t)h * n_slots * page_bytes;
+    uint4 first[kLruInlineBatch];
+#pragma unroll
+    for (int b = 0; b < kLruInlineBatch; ++b) {
+        const int i = b * kLruThreads + tid;
+        if (i < n_vec) first[b] = ld_stream_16(src_h + (size_t)mpage[i / vec_per_page] * page_bytes + (size_t)(i % vec_per_page) * 16);
+    }
+
+    // ---- 5. the touched slots go to the back of the queue, in slot order ------------------------
+    int run = n_untouched - n_miss;
+#pragma unroll
+    for (int r = 0; r < SR; ++r) {
+        if (r * kLruThreads < n_slots) {
+            const int s = r * kLruThreads + tid;
+            const int t = s < n_slots && touched[s];
+            int total;
+            const int ex = run + block_exclusive_scan(t, wsum, &total);
+            if (t) q_out[ex] = s;
+            run += total;
+        }
+    }
+
+#pragma unroll
+    for (int b = 0; b < kLruInlineBatch; ++b) {
+        const int i = b * kLruThreads + tid;
+        if (i < n_vec)
+            *reinterpret_cast<uint4 *>(dst_h + (size_t)vslot[i / vec_per_page] * page_bytes + (size_t)(i % vec_per_page) * 16) = first[b];
+    }
+    for (int i0 = kLruInlineBatch * kLruThreads; i0 < n_vec; i0 += kLruInlineBatch * kLruThreads) {
+        uint4 v[kLruInlineBatch];
+#pragma unroll
+        for (int b = 0; b < kLruInlineBatch; ++b) {
+            const int i = i0 + b * kLruThreads + tid;
+            if (i < n_vec) v[b] = ld_stream_16(src_h + (size_t)mpage[i / vec_per_page] * page_bytes + (size_t)(i % vec_per_page) * 16);
+        }
+#pragma unroll
+        for (int b = 0; b < kLruInlineBatch; ++b) {
+            const int i = i0 + b * kLruThreads + tid;
+            if (i < n_vec)
+                *reinterpret_cast<uint4 *>(dst_h + (size_t)vslot[i / vec_per_page] * page_bytes + (size_t)(i % vec_per_page) * 16) = v[b];
+        }
+    }
+    if (tid == 0) {
+        n_miss_out[h] = n_miss;
+        step_counters[h] = step;
+        const int cap = split_cap > 0 ? min(split_cap, n_slots) : n_slots;
+        n_front_io[(size_t)(1 - cur) * gridDim.x + h] = cap;
+        split_redo[h] = sh_redo;     // (the barriers of round 5 order the writes of round 3 before this read)
+        if (split_advance) split_flip[h] = 1 - cur;
     }
 }
 
 static size_t lru_smem_bytes(int n_slots, int list_len) {
-    return ((size_t)2 * lru_table_size(list_len) + 2 * (size_t)n_slots + 3 * (size_t)list_len) * sizeof(int) +
+    return ((size_t)2 * lru_table_size(list_len) + 2 * (size_t)n_slots + 3 * (size_t)list_len) * sizeof(int);
+}
+
+static size_t lru_queue_smem_bytes(int n_slots, int list_len) {
+    return ((size_t)2 * lru_table_size(list_len) + 2 * (size_t)list_len) * sizeof(int) +
            (((size_t)n_slots + 15) & ~(size_t)15);
 }
 
 constexpr size_t kLruMaxSmem = 227 * 1024 - 4096;
 
+struct LruArgs {
+    const int32_t *page_list; int list_len; int32_t *dram_to_slot; int n_dram_pages; int32_t *slot_to_dram;
+    int32_t *access_time; int n_slots; int32_t *step; int n_kv_heads; int32_t *miss_pages; int32_t *miss_slots;
+    int32_t *n_miss; int32_t *slot_source; int32_t *queue; int32_t *n_front; int32_t *split_flip;
+    int32_t *split_redo; int split_cap; int split_advance; const unsigned char *dram_pages; unsigned char *slots;
+    unsigned long long page_bytes; int inline_max; int32_t *status;
+};
+
 template <int SR, int LR>
-static cudaError_t launch_lru(const int32_t *page_list, int list_len, int32_t *dram_to_slot, int n_dram_pages,
-                              int32_t *slot_to_dram, int32_t *access_time, int n_slots, int32_t *step,
-                              int n_kv_heads, int32_t *miss_pages, int32_t *miss_slots, int32_t *n_miss,
-                              int32_t *slot_source, int32_t *order_out, int32_t *n_evictable_out,
-                              int32_t *split_flip, int32_t *split_redo, int split_cap, int split_advance,
-                              int32_t *status, size_t smem, cudaStream_t stream) {
+static cudaError_t launch_lru(const LruArgs &a, cudaStream_t stream) {
     static bool attr_set[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -436,13 +618,23 @@ static cudaError_t launch_lru(const int32_t *page_list, int list_len, int32_t *d
         e = cudaFuncSetAttribute(lru_update_kernel<SR, LR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)kLruMaxSmem);
         if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(lru_queue_kernel<SR, LR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)kLruMaxSmem);
+        if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    lru_update_kernel<SR, LR><<<n_kv_heads, kLruThreads, smem, stream>>>(
-        page_list, list_len, dram_to_slot, n_dram_pages, slot_to_dram, access_time, n_slots, step, miss_pages,
-        miss_slots, n_miss, slot_source, order_out, n_evictable_out, split_flip, split_redo, split_cap,
-        split_advance, status);
-    return cudaGetLastError();
+    if (a.queue) {
+        return launch_dependent(lru_queue_kernel<SR, LR>, dim3(a.n_kv_heads), dim3(kLruThreads),
+                                lru_queue_smem_bytes(a.n_slots, a.list_len), stream, a.page_list, a.list_len,
+                                a.dram_to_slot, a.n_dram_pages, a.slot_to_dram, a.access_time, a.n_slots, a.step,
+                                a.miss_pages, a.miss_slots, a.n_miss, a.slot_source, a.queue, a.n_front,
+                                a.split_flip, a.split_redo, a.split_cap, a.split_advance, a.dram_pages, a.slots,
+                                a.page_bytes, a.inline_max, a.status);
+    }
+    return launch_dependent(lru_update_kernel<SR, LR>, dim3(a.n_kv_heads), dim3(kLruThreads),
+                            lru_smem_bytes(a.n_slots, a.list_len), stream, a.page_list, a.list_len,
+                            a.dram_to_slot, a.n_dram_pages, a.slot_to_dram, a.access_time, a.n_slots, a.step,
+                            a.miss_pages, a.miss_slots, a.n_miss, a.slot_source, a.status);
 }
 
 }  // namespace da
@@ -450,27 +642,33 @@ static cudaError_t launch_lru(const int32_t *page_list, int list_len, int32_t *d
 extern "C" int da_lru_update(const int32_t *page_list, int list_len, int32_t *dram_to_slot, int n_dram_pages,
                              int32_t *slot_to_dram, int32_t *access_time, int n_slots, int32_t *step,
                              int n_kv_heads, int32_t *miss_pages, int32_t *miss_slots, int32_t *n_miss,
-                             int32_t *slot_source, int32_t *order_out, int32_t *n_evictable_out,
+                             int32_t *slot_source, int32_t *evict_queue, int32_t *front_count,
                              int32_t *split_flip, int32_t *split_redo, int split_cap, int split_advance,
+                             const void *dram_pages, void *slots, size_t page_bytes, int inline_fetch_max,
                              int32_t *status, da_stream_t stream) {
     if (!page_list || !dram_to_slot || !slot_to_dram || !access_time || !step || !miss_pages || !miss_slots ||
         !n_miss || !status)
         return DA_ERR_NULL;
     if (list_len < 1 || n_dram_pages < 1 || n_slots < 1 || n_kv_heads < 1) return DA_ERR_SHAPE;
-    if ((order_out == nullptr) != (n_evictable_out == nullptr) || (order_out == nullptr) != (split_flip == nullptr) ||
-        (order_out == nullptr) != (split_redo == nullptr))
+    if ((evict_queue == nullptr) != (front_count == nullptr) || (evict_queue == nullptr) != (split_flip == nullptr) ||
+        (evict_queue == nullptr) != (split_redo == nullptr))
         return DA_ERR_NULL;
     if (n_slots > da::kLruMaxSlots || list_len > da::kLruMaxList) return DA_ERR_UNSUPPORTED;
-    const size_t smem = da::lru_smem_bytes(n_slots, list_len);
+    const size_t smem = evict_queue ? da::lru_queue_smem_bytes(n_slots, list_len) : da::lru_smem_bytes(n_slots, list_len);
     if (smem > da::kLruMaxSmem) return DA_ERR_UNSUPPORTED;
+    // pages are copied by the update itself only with a queue, 16-byte granularity and both ends given
+    const bool can_copy = evict_queue && dram_pages && slots && inline_fetch_max > 0 && page_bytes >= 16 &&
+                          page_bytes % 16 == 0 && (((uintptr_t)dram_pages | (uintptr_t)slots) & 15) == 0;
+    da::LruArgs a{page_list, list_len, dram_to_slot, n_dram_pages, slot_to_dram, access_time, n_slots, step,
+                  n_kv_heads, miss_pages, miss_slots, n_miss, slot_source, evict_queue, front_count, split_flip,
+                  split_redo, split_cap, split_advance,
+                  can_copy ? static_cast<const unsigned char *>(dram_pages) : nullptr,
+                  can_copy ? static_cast<unsigned char *>(slots) : nullptr, (unsigned long long)page_bytes,
+                  can_copy ? inline_fetch_max : 0, status};
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     cudaError_t e;
-#define DA_LRU_ARGS page_list, list_len, dram_to_slot, n_dram_pages, slot_to_dram, access_time, n_slots, step, \
-                    n_kv_heads, miss_pages, miss_slots, n_miss, slot_source, order_out, n_evictable_out, split_flip, \
-                    split_redo, split_cap, split_advance, status, smem, s
-    if (n_slots <= 2048 && list_len <= 1024) e = da::launch_lru<2, 1>(DA_LRU_ARGS);
-    else if (n_slots <= 4096 && list_len <= 2048) e = da::launch_lru<4, 2>(DA_LRU_ARGS);
-    else e = da::launch_lru<8, 8>(DA_LRU_ARGS);
-#undef DA_LRU_ARGS
+    if (n_slots <= 2048 && list_len <= 1024) e = da::launch_lru<2, 1>(a, s);
+    else if (n_slots <= 4096 && list_len <= 2048) e = da::launch_lru<4, 2>(a, s);
+    else e = da::launch_lru<8, 8>(a, s);
     return (int)e;
 }

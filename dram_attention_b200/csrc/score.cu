@@ -24,6 +24,7 @@ template <typename T, int VEC, int REP>
 __global__ void __launch_bounds__(kScoreThreads, 2)
 score_pages_kernel(const T *__restrict__ q, const T *__restrict__ summaries, float *__restrict__ scores,
                    int n_kv_heads, int n_pages) {
+    griddep_launch_dependents();   // the selection kernel may move onto free SMs and wait there
     constexpr int D = 16 * VEC;
     constexpr int kWords = VEC * (int)sizeof(T) / 4;
     const int hk = blockIdx.y;
@@ -102,6 +103,7 @@ template <typename T>
 __global__ void __launch_bounds__(kScoreThreads)
 score_pages_generic_kernel(const T *__restrict__ q, const T *__restrict__ summaries,
                            float *__restrict__ scores, int n_kv_heads, int rep, int n_pages, int head_dim) {
+    griddep_launch_dependents();   // the selection kernel may move onto free SMs and wait there
     const int hk = blockIdx.y;
     const int tok = blockIdx.z;
     const int lane = threadIdx.x & 31;
@@ -172,6 +174,7 @@ template <typename T, int D, int REP>
 __global__ void __launch_bounds__(kScoreThreads, 2)
 score_pages_mma_kernel(const T *__restrict__ q, const T *__restrict__ summaries, float *__restrict__ scores,
                        int n_kv_heads, int n_pages) {
+    griddep_launch_dependents();   // the selection kernel may move onto free SMs and wait there
     static_assert(sizeof(T) == 2 && REP <= 8 && (2 * D) % 32 == 0, "16-bit types, at most 8 query rows");
     constexpr int CHUNKS = 2 * D / 8;   // 16-byte chunks per page summary
     constexpr int NI = CHUNKS / 4;      // chunks per lane = pairs of k-steps

@@ -119,6 +119,8 @@ template <int IPT>
 __global__ void __launch_bounds__(kTopkThreads)
 topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_list, int n_kv_heads, int rep,
                   int n_pages, int k) {
+    griddep_wait();                // the scores come from the kernel before this one
+    griddep_launch_dependents();   // the LRU update may move onto the SMs and wait there
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int cap = topk_candidate_capacity(k);
     unsigned long long *cand = reinterpret_cast<unsigned long long *>(smem_raw);  // [cap + 2]
@@ -427,7 +429,9 @@ static cudaError_t launch_topk(const float *scores, int32_t *page_list, int rows
     }
     const int cap = topk_candidate_capacity(k);
     const size_t smem = (size_t)(cap + 2) * sizeof(unsigned long long) + (size_t)cap * sizeof(int);
-    topk_pages_kernel<IPT><<<rows, kTopkThreads, smem, stream>>>(scores, page_list, n_kv_heads, rep, n_pages, k);
+    const cudaError_t le = launch_dependent(topk_pages_kernel<IPT>, dim3(rows), dim3(kTopkThreads), (size_t)smem, stream,
+                                            scores, page_list, n_kv_heads, rep, n_pages, k);
+    if (le != cudaSuccess) return le;
     return cudaGetLastError();
 }
 

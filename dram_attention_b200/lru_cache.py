@@ -115,25 +115,27 @@ class LRUCache(torch.nn.Module):
         # maintained by the LRU kernel, consumed by the attention kernel that fetches on the fly
         self.register_buffer("slot_source", torch.full((num_kv_heads, num_hbm_pages), -1, **i32),
                              persistent=False)
-        # Eviction front used by the two-launch attention: the first n_evictable[h] entries of
-        # evict_order[h] (copy evict_flip[h]) are the slots the first launch leaves out because the
-        # LRU update running beside it may evict them: the `split_cap` slots that come first in
-        # eviction order.  The update writes the other copy for the following step and sets
-        # evict_redo[h] when one of its victims lay outside the current front (the second launch
-        # then covers the whole head).  All of it lives on the device, so a captured step stays
-        # consistent whatever ran between two replays.  "Every slot" is the starting front.
+        # Eviction queue: evict_order[h] (copy evict_flip[h]) lists the slots of head h in eviction
+        # order ((time, slot) ascending; after the warm start every time is 0, so the identity).  The
+        # LRU update takes its victims from the head of the queue and writes the other copy for the
+        # following step.  The first n_evictable[h] entries are the FRONT: the slots the first
+        # launch of the two-launch attention leaves out because the update running beside it may
+        # evict them (`split_cap` of them); evict_redo[h] is set when a victim lay beyond the front
+        # (the second launch then covers the whole head).  All of it lives on the device, so a
+        # captured step stays consistent whatever ran between two replays.
+        self.split_cap = min(self.default_split_cap, max(1, num_hbm_pages // 4))
         self.register_buffer("evict_order", torch.arange(num_hbm_pages, **i32).repeat(2, num_kv_heads, 1),
                              persistent=False)    # two copies; evict_flip[h] names the current one
-        self.register_buffer("n_evictable", torch.full((2, num_kv_heads), num_hbm_pages, **i32),
+        self.register_buffer("n_evictable", torch.full((2, num_kv_heads), self.split_cap, **i32),
                              persistent=False)
         self.register_buffer("evict_flip", torch.zeros(num_kv_heads, **i32), persistent=False)
         self.register_buffer("evict_redo", torch.zeros(num_kv_heads, **i32), persistent=False)
-        self.split_cap = min(self.default_split_cap, max(1, num_hbm_pages // 4))
         self._miss = {}
-        self._last_list_len = None
 
     # slots per head in the eviction front (a steady decode step misses a handful of pages per head)
-    default_split_cap = 128
+    default_split_cap = 64
+    # a head that misses at most this many pages in a step has them copied by the LRU kernel itself
+    inline_fetch_max = 16
 
     @property
     def current_step(self) -> torch.Tensor:
@@ -148,21 +150,18 @@ class LRUCache(torch.nn.Module):
                                            mk(self.num_kv_heads))
         return bufs
 
-    def update_tables_(self, page_list: torch.Tensor, advance_split: bool = True) -> None:
+    def update_tables_(self, page_list: torch.Tensor, advance_split: bool = True,
+                       inline_fetch: bool = False) -> None:
         """Enqueue the LRU table update for an int32 page list (Hk, list_len): step
         counters, hit stamps, victim choice, both maps, the device-side miss list, and the
         eviction front for the following step (written into the copy of evict_order /
         n_evictable that evict_flip does not name).  `advance_split=False` when the two-launch
         attention follows: its second launch makes the new front current when both are done;
-        otherwise the update does it itself."""
+        otherwise the update does it itself.  With `inline_fetch` the kernel also copies the
+        pages of heads that miss only a few (at most `inline_fetch_max`) into their slots; the
+        others are marked in slot_source for the attention kernel that fetches on the fly."""
         list_len = page_list.shape[1]
         miss_pages, miss_slots, n_miss = self._miss_buffers(list_len)
-        if self._last_list_len != list_len:
-            # the kernel clears last call's marks from last call's miss list: start clean when
-            # another set of miss buffers comes into use
-            self.slot_source.fill_(-1)
-            n_miss.zero_()
-            self._last_list_len = list_len
         _native.check(_native.lib().da_lru_update(
             page_list.data_ptr(), list_len, self.dram_page_to_hbm_page_mapping.data_ptr(),
             self.num_dram_pages, self.hbm_page_to_dram_page_mapping.data_ptr(),
@@ -170,7 +169,12 @@ class LRUCache(torch.nn.Module):
             self.num_kv_heads, miss_pages.data_ptr(), miss_slots.data_ptr(), n_miss.data_ptr(),
             self.slot_source.data_ptr(), self.evict_order.data_ptr(), self.n_evictable.data_ptr(),
             self.evict_flip.data_ptr(), self.evict_redo.data_ptr(), int(self.split_cap),
-            1 if advance_split else 0, self.status.data_ptr(), _native.stream_ptr()), "da_lru_update")
+            1 if advance_split else 0,
+            self.dram_kv_cache.data_ptr() if inline_fetch else 0,
+            self.hbm_kv_cache.data_ptr() if inline_fetch else 0,
+            self.dram_kv_cache.shape[2] * self.dram_kv_cache.element_size(),
+            int(self.inline_fetch_max) if inline_fetch else 0,
+            self.status.data_ptr(), _native.stream_ptr()), "da_lru_update")
 
     def fetch_(self, list_len: int) -> None:
         """Enqueue the gather-copy of the pages the last update_tables_ found missing."""

@@ -130,40 +130,52 @@ DA_API int da_topk_pages(const float *scores, int32_t *page_list,
  * miss_pages, miss_slots (n_kv_heads, list_len) int32, written: the (page, slot)
  *             pairs whose payload has to be copied, in list order
  * n_miss      (n_kv_heads) int32, written
- * slot_source optional (n_kv_heads, n_slots) int32 for da_decode_attention_fetch: on return
- *             slot_source[h][s] = the DRAM page that slot s was just given and whose payload
- *             is not in the slot yet, -1 for every other slot.  The call first clears the
- *             marks of the previous call using the previous miss list, so when it is used
- *             the array must start at -1, n_miss at 0, and the same miss buffers must be
- *             passed every time.  NULL when da_fetch_pages does the copy.
- * split_order, split_count, split_flip, split_redo  optional, all or none: the "eviction front"
- *             that da_decode_attention_phased works from.  split_order is
- *             [2][n_kv_heads][n_slots] int32, split_count [2][n_kv_heads], split_flip and
- *             split_redo [n_kv_heads].  Copy split_flip[h] is the CURRENT front of head h: its
- *             first split_count entries are the slots an attention launch that runs beside this
- *             update has left out because they may be evicted.  The call
- *               - sets split_redo[h] = 1 if it evicted a slot outside the current front (the
- *                 attention then has to redo the head), else 0;
- *               - writes the other copy: the split_cap slots that are now first in eviction
- *                 order ((time, slot) ascending among the slots this call did not touch), then
- *                 every other slot; split_count = split_cap, or n_slots (every slot, in place)
- *                 when fewer than split_cap slots were left untouched;
+ * slot_source optional (n_kv_heads, n_slots) int32 for da_decode_attention_fetch, rewritten by
+ *             every call: slot_source[h][s] = the DRAM page that slot s was just given and
+ *             whose payload is not in the slot yet, -1 for every other slot.  NULL when
+ *             da_fetch_pages does the copy.
+ * evict_queue, front_count, split_flip, split_redo  optional, all or none: the eviction queue that
+ *             makes the update cheap and that da_decode_attention_phased works from.
+ *             evict_queue is [2][n_kv_heads][n_slots] int32, front_count [2][n_kv_heads],
+ *             split_flip and split_redo [n_kv_heads].  Copy split_flip[h] of evict_queue[.][h] is
+ *             the CURRENT queue of head h: all its slots in eviction order, i.e. sorted by
+ *             (access_time, slot) ascending; the first front_count entries are the FRONT, the
+ *             slots an attention launch that runs beside this update has left out because they
+ *             may be evicted.  The call
+ *               - takes its victims from the head of the current queue (the first slots no listed
+ *                 page hit), without reading access_time;
+ *               - sets split_redo[h] = 1 if a victim lay beyond the current front (the attention
+ *                 then has to redo the head), else 0;
+ *               - writes the other copy: the untouched slots in their old order, then the slots
+ *                 this call touched in slot order, with front_count = split_cap (n_slots when
+ *                 split_cap <= 0);
  *               - with split_advance != 0 makes that copy current itself (callers that run no
  *                 phased attention after the update); otherwise phase 2 of the attention does.
- *             Before the first call: both copies any permutation of the slots with
- *             split_count = n_slots, split_flip = 0.
+ *             Before the first call: both copies = the slots sorted by (access_time, slot) (the
+ *             identity when every time is zero), split_flip = 0, front_count at most n_slots.
+ *             Without a queue the victims are found by a radix select on access_time.
+ * dram_pages, slots, page_bytes, inline_fetch_max  optional (queue only): when a head misses at
+ *             most inline_fetch_max pages, the call copies them from dram_pages (n_kv_heads,
+ *             n_dram_pages, page_bytes; pinned, device-mapped host memory) into slots
+ *             (n_kv_heads, n_slots, page_bytes) itself -- the loads overlap the rest of the update
+ *             -- and leaves their slot_source entries at -1.  page_bytes a multiple of 16, both
+ *             bases 16-byte aligned.  NULL / 0: the pages are left to da_fetch_pages or to the
+ *             attention kernel.
  * status      (1) int32, bits or-ed in
- * Requires n_slots <= 8192, list_len <= 8192 and the shared-memory plan
- * (2*T + 2*n_slots + 3*list_len ints + n_slots bytes, T = power of two >= 2*list_len) to fit
- * 222 KiB: e.g. 8192 slots with lists up to 4096.
+ * Requires n_slots <= 8192, list_len <= 8192 and the shared-memory plan to fit 222 KiB: with a
+ * queue 2*T + 2*list_len ints + n_slots bytes, without 2*T + 2*n_slots + 3*list_len ints
+ * (T = power of two >= 2*list_len); e.g. 8192 slots with lists up to 4096.
+ * The kernel is launched so that it may move onto the SMs while the kernel before it in `stream`
+ * is still running (it waits for that kernel's results before it reads anything).
  */
 DA_API int da_lru_update(const int32_t *page_list, int list_len,
                   int32_t *dram_to_slot, int n_dram_pages,
                   int32_t *slot_to_dram, int32_t *access_time, int n_slots,
                   int32_t *step, int n_kv_heads,
                   int32_t *miss_pages, int32_t *miss_slots, int32_t *n_miss,
-                  int32_t *slot_source, int32_t *split_order, int32_t *split_count,
+                  int32_t *slot_source, int32_t *evict_queue, int32_t *front_count,
                   int32_t *split_flip, int32_t *split_redo, int split_cap, int split_advance,
+                  const void *dram_pages, void *slots, size_t page_bytes, int inline_fetch_max,
                   int32_t *status, da_stream_t stream);
 
 /*
@@ -303,7 +315,9 @@ DA_API int da_decode_attention_fetch(const void *q,
  *            same step): appends the new key/value, attends over the local window and over
  *            every slot outside the current eviction front, writes partials.  By default at
  *            most 116 CTAs that each fill an SM, so 32 SMs stay free for the other kernels.
- *   phase 2  (after da_lru_update; need NOT wait for phase 1): attends over the slots of the
+ *   phase 2  (directly after da_lru_update in the same stream; need NOT wait for phase 1; q,
+ *            new_k, new_v and start_pos_dev must have been complete before that update was
+ *            enqueued -- the launch overlaps it and reads them early): attends over the slots of the
  *            front, reading freshly assigned ones from DRAM as da_decode_attention_fetch
  *            does, and writes partials.  If the update set split_redo[h] (it had to evict a
  *            slot outside the front, e.g. after a query that shares nothing with the last
@@ -314,8 +328,8 @@ DA_API int da_decode_attention_fetch(const void *q,
  *   wrote current.  Both launches of a step must have been enqueued before the next step's
  *   first one; a step is complete when both have finished.
  *
- * split_order, split_count, split_flip, split_redo   as for da_lru_update (called with
- *            split_advance = 0 between the two launches).
+ * split_order, split_count, split_flip, split_redo   the evict_queue, front_count, split_flip and
+ *            split_redo of da_lru_update (called with split_advance = 0 between the two launches).
  * phase1_ctas, phase2_ctas  CTAs per KV head of the two launches, the same values in both
  *            calls of a step; 0 = defaults (116 / n_kv_heads and 64 / n_kv_heads), at most 148.
  * workspace  da_decode_attention_phased_workspace_bytes() bytes, shared by both phases.

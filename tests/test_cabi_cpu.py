@@ -57,9 +57,9 @@ def test_host_side_argument_checks(native):
     assert lib.da_score_pages(16, 16, 16, 1, 1, 1, 1, 1, 7, 0, 0) == -3         # bad dtype
     assert lib.da_topk_pages(16, 16, 1, 1, 1, 8, 9, 0) == -2                 # k > pages
     assert lib.da_topk_pages(16, 16, 1, 1, 1, 10000, 5000, 0) == -5          # k too large
-    assert lib.da_lru_update(16, 4, 16, 8, 16, 16, 9000, 16, 1, 16, 16, 16, 0, 0, 0, 0, 0, 0, 0, 16, 0) == -5
-    # the four arrays of the eviction front come together or not at all
-    assert lib.da_lru_update(16, 4, 16, 8, 16, 16, 64, 16, 1, 16, 16, 16, 0, 16, 16, 16, 0, 8, 0, 16, 0) == -1
+    assert lib.da_lru_update(16, 4, 16, 8, 16, 16, 9000, 16, 1, 16, 16, 16, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 16, 0) == -5
+    # the four arrays of the eviction queue come together or not at all
+    assert lib.da_lru_update(16, 4, 16, 8, 16, 16, 64, 16, 1, 16, 16, 16, 0, 16, 16, 16, 0, 8, 0, 0, 0, 0, 0, 16, 0) == -1
     assert lib.da_fetch_pages(0, 16, 16, 16, 16, 1, 1, 1, 1, 16, 0) == -1
     assert lib.da_decode_attention_phased_supported(8, 4, 128, 2, 2048, 16, 4160) == 1
     assert lib.da_decode_attention_phased_supported(8, 4, 128, 2, 2048, 8, 4160) == 0     # page < 16 tokens

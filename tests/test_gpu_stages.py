@@ -180,61 +180,78 @@ class Tables:
         self.g_dram = self.dram.clone().pin_memory()
         self.g_hbm = self.hbm.to(DEV)
         self.g_status = torch.zeros(1, dtype=torch.int32, device=DEV)
-        # eviction front: both copies start as "every slot"; the update advances the flip itself
-        self.g_order = torch.arange(self.nh, dtype=torch.int32, device=DEV).repeat(2, self.hk, 1)
-        self.g_nev = torch.full((2, self.hk), self.nh, dtype=torch.int32, device=DEV)
+        # eviction queue: the slots sorted by (time, slot); the update advances the flip itself.
+        # use_queue = False exercises the kernel that selects its victims on the timestamps.
+        order = np.stack([np.argsort(self.time[h], kind="stable") for h in range(self.hk)])
+        self.g_order = torch.from_numpy(np.stack([order, order]).astype(np.int32)).to(DEV)
+        self.split_cap = max(1, self.nh // 4)
+        self.g_nev = torch.full((2, self.hk), self.split_cap, dtype=torch.int32, device=DEV)
         self.g_flip = torch.zeros(self.hk, dtype=torch.int32, device=DEV)
         self.g_redo = torch.full((self.hk,), -5, dtype=torch.int32, device=DEV)
-        self.split_cap = max(1, self.nh // 4)
+        self.g_src = torch.full((self.hk, self.nh), -1, dtype=torch.int32, device=DEV)
+        self.g_prev = None
         return self
 
-    def gpu_step(self, lst):
+    def gpu_step(self, lst, use_queue=True, inline=0):
+        """One da_lru_update (+ da_fetch_pages for what the update did not copy itself)."""
         from dram_attention_b200 import _native
         lib, s = _native.lib(), _native.stream_ptr()
         kk = lst.shape[1]
         gl = torch.from_numpy(lst.astype(np.int32)).to(DEV)
-        mp = torch.full((self.hk, kk), -9, dtype=torch.int32, device=DEV)
-        ms = torch.full((self.hk, kk), -9, dtype=torch.int32, device=DEV)
-        nm = torch.full((self.hk,), -9, dtype=torch.int32, device=DEV)
-        flip = self.g_flip.cpu().numpy()
-        cur_order = np.stack([self.g_order[flip[h], h].cpu().numpy() for h in range(self.hk)])
-        cur_nev = np.array([int(self.g_nev[flip[h], h]) for h in range(self.hk)])
-        before = (self.g_order.clone(), self.g_nev.clone())
+        if self.g_prev is None or self.g_prev[0].shape[1] != kk:
+            self.g_prev = (torch.full((self.hk, kk), -9, dtype=torch.int32, device=DEV),
+                           torch.full((self.hk, kk), -9, dtype=torch.int32, device=DEV),
+                           torch.zeros(self.hk, dtype=torch.int32, device=DEV))
+            self.g_src.fill_(-1)
+        mp, ms, nm = self.g_prev
+        page_bytes = self.dram.shape[2] * self.dram.element_size()
+        if use_queue:
+            flip = self.g_flip.cpu().numpy()
+            cur_order = np.stack([self.g_order[flip[h], h].cpu().numpy() for h in range(self.hk)])
+            cur_nev = np.array([int(self.g_nev[flip[h], h]) for h in range(self.hk)])
+            before = self.g_order.clone()
+        q = (self.g_order.data_ptr(), self.g_nev.data_ptr(), self.g_flip.data_ptr(), self.g_redo.data_ptr()) \
+            if use_queue else (0, 0, 0, 0)
         _native.check(lib.da_lru_update(gl.data_ptr(), kk, self.g_d2h.data_ptr(), self.ld,
                                         self.g_h2d.data_ptr(), self.g_time.data_ptr(), self.nh,
                                         self.g_step.data_ptr(), self.hk, mp.data_ptr(), ms.data_ptr(),
-                                        nm.data_ptr(), 0, self.g_order.data_ptr(), self.g_nev.data_ptr(),
-                                        self.g_flip.data_ptr(), self.g_redo.data_ptr(), self.split_cap, 1,
+                                        nm.data_ptr(), self.g_src.data_ptr(), *q, self.split_cap, 1,
+                                        self.g_dram.data_ptr() if inline else 0,
+                                        self.g_hbm.data_ptr() if inline else 0, page_bytes, inline,
                                         self.g_status.data_ptr(), s))
-        page_bytes = self.dram.shape[2] * self.dram.element_size()
+        torch.cuda.synchronize()
+        mp_h, ms_h, nm_h = mp.cpu().numpy(), ms.cpu().numpy(), nm.cpu().numpy()
+        src = self.g_src.cpu().numpy()
+        copies_here = bool(inline) and use_queue and page_bytes % 16 == 0
+        for h in range(self.hk):
+            # slot_source marks exactly the pages the update left to somebody else
+            want = np.full(self.nh, -1)
+            if not (copies_here and nm_h[h] <= inline):
+                want[ms_h[h, :nm_h[h]]] = mp_h[h, :nm_h[h]]
+            assert np.array_equal(src[h], want), h
+            if copies_here and nm_h[h] <= inline and nm_h[h] > 0:
+                # ... and has already brought its own pages in
+                got = self.g_hbm[h, torch.from_numpy(ms_h[h, :nm_h[h]]).long().to(DEV)].cpu()
+                assert torch.equal(got, self.dram[h, torch.from_numpy(mp_h[h, :nm_h[h]]).long()]), h
         _native.check(lib.da_fetch_pages(self.g_dram.data_ptr(), self.g_hbm.data_ptr(), mp.data_ptr(),
                                          ms.data_ptr(), nm.data_ptr(), kk, self.hk, self.ld, self.nh,
                                          page_bytes, s))
         torch.cuda.synchronize()
-        mp, ms, nm = mp.cpu().numpy(), ms.cpu().numpy(), nm.cpu().numpy()
-        # redo flag: exactly "a victim of this call lay outside the front that was current"
-        redo = self.g_redo.cpu().numpy()
-        new_flip = self.g_flip.cpu().numpy()
-        times = self.g_time.cpu().numpy()
-        step_now = int(self.g_step[0])
-        for h in range(self.hk):
-            outside = not (set(ms[h, :nm[h]].tolist()) <= set(cur_order[h, :cur_nev[h]].tolist()))
-            assert redo[h] == int(outside), (h, redo[h], outside)
-            assert new_flip[h] == 1 - flip[h], h          # split_advance = 1
-            # the copy that was current is untouched, the other one holds the new front
-            assert torch.equal(self.g_order[flip[h], h], before[0][flip[h], h])
-            assert int(self.g_nev[flip[h], h]) == int(before[1][flip[h], h])
-            order = self.g_order[new_flip[h], h].cpu().numpy()
-            nev = int(self.g_nev[new_flip[h], h])
-            assert sorted(order.tolist()) == list(range(self.nh)), h
-            assert nev == self.nh or nev == min(self.split_cap, self.nh), h
-            if nev < self.nh:
-                # the front = the nev slots that come first in (time, slot) order among the
-                # slots this call did not touch (listed in any order)
-                untouched = [s_ for s_ in range(self.nh) if times[h, s_] < step_now]
-                want = sorted(untouched, key=lambda s_: (times[h, s_], s_))[:nev]
-                assert sorted(order[:nev].tolist()) == sorted(want), h
-        return mp, ms, nm
+        if use_queue and not (int(self.g_status) & 2):
+            redo = self.g_redo.cpu().numpy()
+            new_flip = self.g_flip.cpu().numpy()
+            times = self.g_time.cpu().numpy()
+            for h in range(self.hk):
+                # redo flag: exactly "a victim of this call lay beyond the front that was current"
+                outside = not (set(ms_h[h, :nm_h[h]].tolist()) <= set(cur_order[h, :cur_nev[h]].tolist()))
+                assert redo[h] == int(outside), (h, redo[h], outside)
+                assert new_flip[h] == 1 - flip[h], h          # split_advance = 1
+                # the copy that was current is untouched; the other one is the new eviction order
+                assert torch.equal(self.g_order[flip[h], h], before[flip[h], h])
+                order = self.g_order[new_flip[h], h].cpu().numpy()
+                assert np.array_equal(order, np.argsort(times[h], kind="stable")), h
+                assert int(self.g_nev[new_flip[h], h]) == min(self.split_cap, self.nh), h
+        return mp_h, ms_h, nm_h
 
     def cpu_step(self, lst, fn=orc.lru_walk):
         self.step += 1
@@ -310,16 +327,20 @@ def test_lru_matches_reference_kernel_runs(da, golden_dir):
     (2, 5000, 4096, 2048, 5, 64, torch.bfloat16),     # 1M-context layer geometry (per-head)
     (2, 600, 300, 300, 300, 8, torch.float32),        # many steps: > 8 bits of time
 ])
-def test_lru_random_trajectories_bit_exact(da, hk, ld, nh, kk, steps, page_dim, dtype):
+@pytest.mark.parametrize("mode", ["queue", "queue+copy", "select"])
+def test_lru_random_trajectories_bit_exact(da, hk, ld, nh, kk, steps, page_dim, dtype, mode):
+    """queue: victims from the eviction queue; queue+copy: the update also copies the pages of
+    heads that miss at most 6; select: no queue, victims by a select on the timestamps."""
     rng = np.random.default_rng(hk * 1000 + ld)
     t = Tables(hk, ld, nh, page_dim=page_dim, dtype=dtype, seed=ld).to_device()
+    kw = dict(use_queue=mode != "select", inline=6 if mode == "queue+copy" else 0)
     for s in range(steps):
         # a hot set that drifts (hits), fresh pages (misses) and duplicates inside the list
         distinct = int(rng.integers(1, min(kk, nh) + 1))
         pool = rng.choice(ld, size=distinct, replace=False)
         lst = rng.choice(pool, size=(hk, kk))
         mp_c, ms_c, nm_c = t.cpu_step(lst)
-        mp_g, ms_g, nm_g = t.gpu_step(lst)
+        mp_g, ms_g, nm_g = t.gpu_step(lst, **kw)
         assert np.array_equal(nm_g, nm_c), s
         for h in range(hk):
             assert np.array_equal(mp_g[h, :nm_c[h]], mp_c[h, :nm_c[h]]), (s, h)
