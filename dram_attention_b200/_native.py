@@ -27,6 +27,8 @@ _DTYPES = {torch.float32: DA_F32, torch.float16: DA_F16, torch.bfloat16: DA_BF16
 _SIGNATURES = {
     "da_version": (c_int, []),
     "da_error_string": (c_char_p, [c_int]),
+    "da_trace_bytes": (c_size_t, []),
+    "da_trace_set": (c_int, [c_void_p]),
     "da_score_pages": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                c_int, c_void_p]),
     "da_topk_pages": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
@@ -37,7 +39,8 @@ _SIGNATURES = {
     "da_prefill_attention": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                      c_longlong, c_longlong, c_int, c_void_p, c_void_p]),
     "da_gather_heads_buffer_bytes": (c_size_t, [c_int, c_int]),
-    "da_gather_heads": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "da_gather_heads": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,
+                                c_void_p]),
     "da_decode_attention_fetch": (c_int, [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_void_p,
                                           c_void_p, c_void_p, c_longlong, c_longlong, c_int, c_void_p, c_void_p,
                                           c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p,

@@ -1,4 +1,4 @@
-// Version and error text of the C ABI.
+// Version, error text and the profiling switch of the C ABI.
 
 #include "da_common.cuh"
 
@@ -18,4 +18,18 @@ extern "C" const char *da_error_string(int code) {
     }
     if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
     return "unknown error code";
+}
+
+extern "C" size_t da_trace_bytes(void) {
+    return (size_t)da::kTraceKernels * da::kTraceCtas * da::kTraceEvents * sizeof(unsigned long long);
+}
+
+extern "C" int da_trace_set(void *buffer) {
+    cudaError_t e;
+    if ((e = da::trace_set_score(buffer)) != cudaSuccess) return (int)e;
+    if ((e = da::trace_set_topk(buffer)) != cudaSuccess) return (int)e;
+    if ((e = da::trace_set_lru(buffer)) != cudaSuccess) return (int)e;
+    if ((e = da::trace_set_attn(buffer)) != cudaSuccess) return (int)e;
+    if ((e = da::trace_set_attn_mma(buffer)) != cudaSuccess) return (int)e;
+    return 0;
 }

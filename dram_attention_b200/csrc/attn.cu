@@ -530,6 +530,8 @@ extern "C" int da_decode_attention_phased(int phase, const int32_t *order, const
     return da::run_attention(c);
 }
 
+DA_DEFINE_TRACE_SETTER(trace_set_attn)
+
 // ---- entry point with built-in scratch ------------------------------------------------
 
 namespace da {

@@ -57,6 +57,9 @@ __device__ __forceinline__ void decode_attention_body(const AttnParams &p, unsig
     // second launch of a step (phase 2) always follows the LRU update, whose results it needs only
     // late: it reads its inputs, the eviction queue as it was before the update and its query rows
     // first (all of them complete before the update began) and waits further down.
+    const int trace_kernel = p.phase == 2 ? 4 : 3;
+    const int trace_cta = h * splits + x;
+    if (tid == 0) trace_stamp(trace_kernel, trace_cta, 0);
     if (p.phase != 2) griddep_wait();
 
     // ---- position and unit range ------------------------------------------------
@@ -209,6 +212,7 @@ __device__ __forceinline__ void decode_attention_body(const AttnParams &p, unsig
     float *red = reinterpret_cast<float *>(my_stages);
     Math::publish(st, red, lane, rows);
     __syncthreads();
+    if (tid == 0) trace_stamp(trace_kernel, trace_cta, 2);
 
     // ---- merge the warps, write this CTA's partial ------------------------------------
     float *part = p.partials + ((size_t)(h * p.part_rows + p.part_offset + x) * rows) * PW;
@@ -235,26 +239,28 @@ __device__ __forceinline__ void decode_attention_body(const AttnParams &p, unsig
         }
         part[e] = outv;  // c < D: weighted acc; c == D: max; c == D + 1: weighted l
     }
-    __threadfence();
     __syncthreads();
     if (tid == 0) {
+        __threadfence();   // the CTA's rows (ordered before this thread by the barrier) before its ticket
         const unsigned int ticket = atomicAdd(&p.counters[h], 1u);
         sh_last = (ticket == (unsigned int)(p.ticket_target - 1));
     }
     __syncthreads();
+    if (tid == 0) {
+        trace_stamp(trace_kernel, trace_cta, 3);
+        if (!sh_last) trace_stamp(trace_kernel, trace_cta, 1);
+    }
     if (!sh_last) return;
 
     // ---- the CTA of this head that finished last (of both launches, when there are two) --------
     __threadfence();   // the other CTAs fenced their rows before their tickets: pair that here
-    int first = 0, n_rows = p.part_rows;
-    if (p.phase != 0 && __ldcg(p.redo + h) != 0) {
-        first = p.splits1;                 // the head was redone by phase 2: leave phase 1's rows out
-        n_rows = p.part_rows - p.splits1;
-    }
-    merge_splits<T, D, THREADS>(p, h, first, n_rows, rows, smem, WARPS * STAGES * STAGEB);
+    // a head that phase 2 redid: phase 1's rows (the first in the workspace) are left out
+    merge_splits<T, D, THREADS>(p, h, p.part_rows, rows, p.phase != 0 ? p.redo + h : nullptr, p.splits1, smem,
+                                WARPS * STAGES * STAGEB);
     // every CTA of this head is done with the eviction front: the one the LRU update left becomes current
     if (p.phase != 0 && tid == 0) p.flip[h] ^= 1;
     if (tid == 0) p.counters[h] = 0u;
+    if (tid == 0) trace_stamp(trace_kernel, trace_cta, 1);
 }
 
 }  // namespace da

@@ -211,17 +211,19 @@ __device__ __forceinline__ void cp_async_wait_all() {
 // consecutive CTAs are contiguous in the workspace.  They are brought into shared memory (the
 // idle stage buffers, `smem_bytes` of them) with 16-byte asynchronous copies that bypass L1 (the
 // rows were written by other SMs) and need no registers, as many CTAs' rows at a time as fit;
-// the first batch is requested before the (max, l) pairs are looked at.
+// the first batch is requested before anything else is looked at.  `skip_flag` (may be null):
+// when the word it points to is non-zero the first `skip` CTAs' rows are left out (they get
+// weight zero); it is read together with the (max, l) pairs, so it costs no round trip.
 template <typename T, int D, int THREADS>
-__device__ __forceinline__ void merge_splits(const AttnParams &p, int h, int first_row, int splits, int rows,
-                                             unsigned char *smem, int smem_bytes) {
+__device__ __forceinline__ void merge_splits(const AttnParams &p, int h, int splits, int rows, const int32_t *skip_flag,
+                                             int skip, unsigned char *smem, int smem_bytes) {
     constexpr int PW = PartialRow<D>::kWidth;
     constexpr int VPR = D / 4;          // float4 per accumulator row
     constexpr float NEG_INF = -INFINITY;
     constexpr int MAXE = (kAttnMaxRows * VPR + THREADS - 1) / THREADS;   // output float4 per thread
     __shared__ float sh_m[kAttnMaxRows], sh_l[kAttnMaxRows];
     const int tid = threadIdx.x;
-    const float *hp = p.partials + ((size_t)(h * p.part_rows + first_row) * rows) * PW;
+    const float *hp = p.partials + ((size_t)h * p.part_rows * rows) * PW;
     const int n = splits * rows;
     float *wgt = reinterpret_cast<float *>(smem);   // [n] max, then weight
     float *lsum = wgt + n;                          // [n] l of every partial row
@@ -237,9 +239,10 @@ __device__ __forceinline__ void merge_splits(const AttnParams &p, int h, int fir
         for (int i = tid; i < cnt * cta_f4; i += THREADS) cp_async_16(buf + i, src + i);
     };
     request(0);
+    const int n_skip = (skip_flag != nullptr && __ldcg(skip_flag) != 0) ? skip * rows : 0;
     for (int i = tid; i < n; i += THREADS) {
         const float2 ml = __ldcg(reinterpret_cast<const float2 *>(hp + (size_t)i * PW + D));
-        wgt[i] = ml.x;
+        wgt[i] = i < n_skip ? NEG_INF : ml.x;
         lsum[i] = ml.y;
     }
     __syncthreads();

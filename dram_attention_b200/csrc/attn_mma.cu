@@ -302,3 +302,5 @@ cudaError_t launch_attention_mma(const AttnParams &p, int n_kv_heads, int head_d
 }
 
 }  // namespace da
+
+DA_DEFINE_TRACE_SETTER(trace_set_attn_mma)

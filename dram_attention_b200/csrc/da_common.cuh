@@ -92,6 +92,42 @@ template <typename T, int N> __device__ __forceinline__ void load_elems(const vo
     }
 }
 
+// ---- optional device-side time stamps (profiling) ----------------------------------
+// da_trace_set() hands every kernel file a buffer of kTraceKernels x kTraceCtas x kTraceEvents
+// 64-bit words.  While it is set, thread 0 of every CTA writes the global nanosecond timer at a
+// few points of the kernel (event 0 = the CTA runs, event 1 = it is done; the attention kernel
+// also 2 = its warps are through their units, 3 = its ticket is taken), so that the host can
+// read where a step's time goes while the kernels overlap on several streams, which events on a
+// stream cannot show.  A launch overwrites the stamps of the launch before it.  Unset (the
+// default) a stamp site costs one load of the pointer.
+constexpr int kTraceKernels = 5;   // 0 scorer, 1 selection, 2 LRU update, 3 attention (single launch or phase 1), 4 phase 2
+constexpr int kTraceCtas = 1024;   // CTA index modulo this
+constexpr int kTraceEvents = 4;
+static __device__ unsigned long long *g_trace_buf;   // one copy per kernel file, all set together
+
+__device__ __forceinline__ void trace_stamp(int kernel, int cta, int event) {
+    unsigned long long *buf = g_trace_buf;
+    if (buf != nullptr) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        buf[((size_t)kernel * kTraceCtas + (cta % kTraceCtas)) * kTraceEvents + event] = t;
+    }
+}
+
+// Each kernel file defines its setter with this; api.cu calls them all.
+#define DA_DEFINE_TRACE_SETTER(name)                                                      \
+    namespace da {                                                                        \
+    cudaError_t name(void *buffer) {                                                      \
+        unsigned long long *b = static_cast<unsigned long long *>(buffer);                \
+        return cudaMemcpyToSymbol(g_trace_buf, &b, sizeof(b));                            \
+    }                                                                                     \
+    }
+cudaError_t trace_set_score(void *buffer);
+cudaError_t trace_set_topk(void *buffer);
+cudaError_t trace_set_lru(void *buffer);
+cudaError_t trace_set_attn(void *buffer);
+cudaError_t trace_set_attn_mma(void *buffer);
+
 // ---- programmatic dependent launch ---------------------------------------------
 // The kernels of a generate step form a chain (scores -> page list -> tables -> attention).  A
 // kernel launched with launch_dependent() may be placed on the SMs while its predecessor in the

@@ -65,6 +65,26 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int *wsum, int *total
     return before + incl - v;
 }
 
+// Exclusive ranks of SR flags per thread, flags ordered r-major (all of r = 0 across the block, then
+// r = 1, ...), two r at a time packed into one scan (counts stay below 2^16: at most 8192 slots).
+template <int SR>
+__device__ __forceinline__ void block_scan_flags(const int (&flag)[SR], int (&ex)[SR], int *wsum, int &total_all) {
+    int run = 0;
+#pragma unroll
+    for (int r = 0; r < SR; r += 2) {
+        const int f1 = r + 1 < SR ? flag[r + 1] : 0;
+        int total;
+        const int e = block_exclusive_scan(flag[r] | (f1 << 16), wsum, &total);
+        ex[r] = run + (e & 0xffff);
+        run += total & 0xffff;
+        if (r + 1 < SR) {
+            ex[r + 1] = run + (e >> 16);
+            run += total >> 16;
+        }
+    }
+    total_all = run;
+}
+
 __host__ __device__ inline int lru_table_size(int list_len) {
     int t = 64;
     while (t < 2 * list_len) t <<= 1;
@@ -383,7 +403,9 @@ lru_queue_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *d
                  int32_t *split_flip, int32_t *split_redo, int split_cap, int split_advance,
                  const unsigned char *dram_pages, unsigned char *slots, unsigned long long page_bytes,
                  int inline_max, int32_t *status) {
+    if (threadIdx.x == 0) trace_stamp(2, blockIdx.x, 0);
     griddep_wait();   // the page list comes from the kernel before this one
+    if (threadIdx.x == 0) trace_stamp(2, blockIdx.x, 2);
     extern __shared__ __align__(16) int smem_i[];
     const int table = lru_table_size(list_len);
     int *tkey = smem_i;                  // [table] page id or -1
@@ -403,16 +425,19 @@ lru_queue_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *d
     int32_t *mp_out = miss_pages + (size_t)h * list_len;
     int32_t *ms_out = miss_slots + (size_t)h * list_len;
 
-    // ---- all independent global reads first ---------------------------------------------
-    const int cur = split_flip[h] & 1;
-    const int32_t *q_in = queue + ((size_t)cur * gridDim.x + h) * n_slots;
-    int32_t *q_out = queue + ((size_t)(1 - cur) * gridDim.x + h) * n_slots;
-    int qs[SR];
+    // ---- all independent global reads first (both copies of the queue, so that nothing waits for
+    // the flip word) --------------------------------------------------------------------------
+    const int32_t *q_a = queue + (size_t)h * n_slots;
+    const int32_t *q_b = queue + ((size_t)gridDim.x + h) * n_slots;
+    int qa[SR], qb[SR];
 #pragma unroll
     for (int r = 0; r < SR; ++r) {
         const int i = r * kLruThreads + tid;
-        qs[r] = i < n_slots ? min(max(q_in[i], 0), n_slots - 1) : -1;
+        qa[r] = i < n_slots ? q_a[i] : -1;
+        qb[r] = i < n_slots ? q_b[i] : -1;
     }
+    const int nf_a = n_front_io[h], nf_b = n_front_io[(size_t)gridDim.x + h];
+    const int cur = split_flip[h] & 1;
     int pg[LR], sl[LR];
     int bad = 0;
 #pragma unroll
@@ -425,9 +450,18 @@ lru_queue_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *d
         }
     }
     const int step = step_counters[h] + 1;
-    const int n_front = min(max(n_front_io[(size_t)cur * gridDim.x + h], 0), n_slots);
 #pragma unroll
     for (int r = 0; r < LR; ++r) sl[r] = pg[r] >= 0 ? d2s[pg[r]] : 0;
+    int32_t *q_out = queue + ((size_t)(1 - cur) * gridDim.x + h) * n_slots;
+    const int n_front = min(max(cur ? nf_b : nf_a, 0), n_slots);
+    int qs[SR];
+#pragma unroll
+    for (int r = 0; r < SR; ++r) {
+        const int v = cur ? qb[r] : qa[r];
+        qs[r] = r * kLruThreads + tid < n_slots ? min(max(v, 0), n_slots - 1) : -1;
+    }
+    // the page held by the slots at the head of the queue, where the victims come from
+    const int sd0 = qs[0] >= 0 ? s2d[qs[0]] : -1;
 
     // slot_source is rewritten by every call: -1 everywhere, then (after several barriers) the
     // marks of this call's misses
@@ -487,52 +521,18 @@ lru_queue_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *d
     // ---- 3. victims = the first n_miss slots of the queue that no hit touched ------------------
     int urank[SR];        // rank of this queue position among the untouched ones, or -1
     int n_untouched = 0;
+    {
+        int flag[SR];
 #pragma unroll
-    for (int r = 0; r < SR; ++r) {
-        urank[r] = -1;
-        if (r * kLruThreads < n_slots) {
-            const int u = qs[r] >= 0 && !touched[qs[r]];
-            int total;
-            const int ex = n_untouched + block_exclusive_scan(u, wsum, &total);
-            if (u) urank[r] = ex;
-            n_untouched += total;
-        }
-    }
-    if (n_miss > n_untouched) {
-        // more distinct non-resident pages than slots this call may evict: tables stay as after the hits
-        if (tid == 0) atomicOr(status, DA_STATUS_LRU_OVERFLOW);
-        n_miss = 0;
-    }
+        for (int r = 0; r < SR; ++r) flag[r] = qs[r] >= 0 && !touched[qs[r]];
+        block_scan_flags<SR>(flag, urank, wsum, n_untouched);   // (its barriers also publish mpage)
 #pragma unroll
-    for (int r = 0; r < SR; ++r) {
-        if (urank[r] >= 0) {
-            if (urank[r] < n_miss) {
-                vslot[urank[r]] = qs[r];
-                touched[qs[r]] = 1;
-                if (r * kLruThreads + tid >= n_front) sh_redo = 1;   // beyond the front the attention left out
-            } else {
-                q_out[urank[r] - n_miss] = qs[r];                    // survivors keep their order
-            }
-        }
+        for (int r = 0; r < SR; ++r)
+            if (!flag[r]) urank[r] = -1;
     }
-    __syncthreads();
-
-    // ---- 4. the j-th miss takes the j-th victim ---------------------------------------------
-    const bool copy_here = dram_pages != nullptr && n_miss <= inline_max;
-    for (int j = tid; j < n_miss; j += kLruThreads) {
-        const int p = mpage[j];
-        const int v = vslot[j];
-        const int old = s2d[v];
-        if (old >= 0 && old < n_dram_pages) d2s[old] = -1;
-        s2d[v] = p;
-        d2s[p] = v;
-        tim[v] = step;
-        mp_out[j] = p;
-        ms_out[j] = v;
-        if (src_map && !copy_here) src_map[v] = p;   // the attention kernel brings the page in
-    }
-    // Few misses: copy the pages here.  The first loads go out now and are stored after the
-    // second round of prefix sums.
+    // Few misses: the update copies the pages itself.  The pages are known now, so the loads from
+    // DRAM go out here and are stored at the very end: the host-link latency hides behind the rest.
+    const bool copy_here = dram_pages != nullptr && n_miss <= inline_max && n_miss <= n_untouched;
     const int vec_per_page = (int)(page_bytes / 16);
     const int n_vec = copy_here ? n_miss * vec_per_page : 0;
     const unsigned char *src_h = dram_pages + (size_t)h * n_dram_pages * page_bytes;
@@ -543,39 +543,73 @@ lru_queue_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *d
         const int i = b * kLruThreads + tid;
         if (i < n_vec) first[b] = ld_stream_16(src_h + (size_t)mpage[i / vec_per_page] * page_bytes + (size_t)(i % vec_per_page) * 16);
     }
+    if (n_miss > n_untouched) {
+        // more distinct non-resident pages than slots this call may evict: tables stay as after the hits
+        if (tid == 0) atomicOr(status, DA_STATUS_LRU_OVERFLOW);
+        n_miss = 0;
+    }
 
-    // ---- 5. the touched slots go to the back of the queue, in slot order ------------------------
-    int run = n_untouched - n_miss;
+    // ---- 4. the j-th miss takes the j-th victim; the other untouched slots keep their order ------
 #pragma unroll
     for (int r = 0; r < SR; ++r) {
-        if (r * kLruThreads < n_slots) {
-            const int s = r * kLruThreads + tid;
-            const int t = s < n_slots && touched[s];
-            int total;
-            const int ex = run + block_exclusive_scan(t, wsum, &total);
-            if (t) q_out[ex] = s;
-            run += total;
+        if (urank[r] >= 0) {
+            if (urank[r] < n_miss) {
+                const int j = urank[r];
+                const int v = qs[r];
+                const int p = mpage[j];
+                const int old = r == 0 ? sd0 : s2d[v];
+                if (old >= 0 && old < n_dram_pages) d2s[old] = -1;
+                s2d[v] = p;
+                d2s[p] = v;
+                tim[v] = step;
+                mp_out[j] = p;
+                ms_out[j] = v;
+                vslot[j] = v;
+                touched[v] = 1;
+                if (src_map && !copy_here) src_map[v] = p;           // the attention kernel brings the page in
+                if (r * kLruThreads + tid >= n_front) sh_redo = 1;   // beyond the front the attention left out
+            } else {
+                q_out[urank[r] - n_miss] = qs[r];
+            }
         }
+    }
+    __syncthreads();
+
+    // ---- 5. the touched slots go to the back of the queue, in slot order ------------------------
+    {
+        int flag[SR], pos[SR], n_touched;
+#pragma unroll
+        for (int r = 0; r < SR; ++r) {
+            const int s = r * kLruThreads + tid;
+            flag[r] = s < n_slots && touched[s];
+        }
+        block_scan_flags<SR>(flag, pos, wsum, n_touched);
+#pragma unroll
+        for (int r = 0; r < SR; ++r)
+            if (flag[r]) q_out[n_untouched - n_miss + pos[r]] = r * kLruThreads + tid;
     }
 
-#pragma unroll
-    for (int b = 0; b < kLruInlineBatch; ++b) {
-        const int i = b * kLruThreads + tid;
-        if (i < n_vec)
-            *reinterpret_cast<uint4 *>(dst_h + (size_t)vslot[i / vec_per_page] * page_bytes + (size_t)(i % vec_per_page) * 16) = first[b];
-    }
-    for (int i0 = kLruInlineBatch * kLruThreads; i0 < n_vec; i0 += kLruInlineBatch * kLruThreads) {
-        uint4 v[kLruInlineBatch];
+    // ---- 6. store the copied pages --------------------------------------------------------------
+    if (n_miss > 0) {   // (not after an overflow)
 #pragma unroll
         for (int b = 0; b < kLruInlineBatch; ++b) {
-            const int i = i0 + b * kLruThreads + tid;
-            if (i < n_vec) v[b] = ld_stream_16(src_h + (size_t)mpage[i / vec_per_page] * page_bytes + (size_t)(i % vec_per_page) * 16);
-        }
-#pragma unroll
-        for (int b = 0; b < kLruInlineBatch; ++b) {
-            const int i = i0 + b * kLruThreads + tid;
+            const int i = b * kLruThreads + tid;
             if (i < n_vec)
-                *reinterpret_cast<uint4 *>(dst_h + (size_t)vslot[i / vec_per_page] * page_bytes + (size_t)(i % vec_per_page) * 16) = v[b];
+                *reinterpret_cast<uint4 *>(dst_h + (size_t)vslot[i / vec_per_page] * page_bytes + (size_t)(i % vec_per_page) * 16) = first[b];
+        }
+        for (int i0 = kLruInlineBatch * kLruThreads; i0 < n_vec; i0 += kLruInlineBatch * kLruThreads) {
+            uint4 v[kLruInlineBatch];
+#pragma unroll
+            for (int b = 0; b < kLruInlineBatch; ++b) {
+                const int i = i0 + b * kLruThreads + tid;
+                if (i < n_vec) v[b] = ld_stream_16(src_h + (size_t)mpage[i / vec_per_page] * page_bytes + (size_t)(i % vec_per_page) * 16);
+            }
+#pragma unroll
+            for (int b = 0; b < kLruInlineBatch; ++b) {
+                const int i = i0 + b * kLruThreads + tid;
+                if (i < n_vec)
+                    *reinterpret_cast<uint4 *>(dst_h + (size_t)vslot[i / vec_per_page] * page_bytes + (size_t)(i % vec_per_page) * 16) = v[b];
+            }
         }
     }
     if (tid == 0) {
@@ -583,8 +617,14 @@ lru_queue_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *d
         step_counters[h] = step;
         const int cap = split_cap > 0 ? min(split_cap, n_slots) : n_slots;
         n_front_io[(size_t)(1 - cur) * gridDim.x + h] = cap;
-        split_redo[h] = sh_redo;     // (the barriers of round 5 order the writes of round 3 before this read)
+        split_redo[h] = sh_redo;     // (the barrier after round 4 orders its writes before this read)
+        split_redo[gridDim.x + h] += n_miss;        // running totals, for whoever wants to watch the cache
+        split_redo[2 * gridDim.x + h] += sh_redo;
         if (split_advance) split_flip[h] = 1 - cur;
+    }
+    if (g_trace_buf != nullptr) {
+        __syncthreads();
+        if (tid == 0) trace_stamp(2, blockIdx.x, 1);
     }
 }
 
@@ -638,6 +678,8 @@ static cudaError_t launch_lru(const LruArgs &a, cudaStream_t stream) {
 }
 
 }  // namespace da
+
+DA_DEFINE_TRACE_SETTER(trace_set_lru)
 
 extern "C" int da_lru_update(const int32_t *page_list, int list_len, int32_t *dram_to_slot, int n_dram_pages,
                              int32_t *slot_to_dram, int32_t *access_time, int n_slots, int32_t *step,

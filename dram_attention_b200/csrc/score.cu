@@ -24,6 +24,7 @@ template <typename T, int VEC, int REP>
 __global__ void __launch_bounds__(kScoreThreads, 2)
 score_pages_kernel(const T *__restrict__ q, const T *__restrict__ summaries, float *__restrict__ scores,
                    int n_kv_heads, int n_pages) {
+    if (threadIdx.x == 0) trace_stamp(0, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, 0);
     griddep_launch_dependents();   // the selection kernel may move onto free SMs and wait there
     constexpr int D = 16 * VEC;
     constexpr int kWords = VEC * (int)sizeof(T) / 4;
@@ -103,6 +104,7 @@ template <typename T>
 __global__ void __launch_bounds__(kScoreThreads)
 score_pages_generic_kernel(const T *__restrict__ q, const T *__restrict__ summaries,
                            float *__restrict__ scores, int n_kv_heads, int rep, int n_pages, int head_dim) {
+    if (threadIdx.x == 0) trace_stamp(0, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, 0);
     griddep_launch_dependents();   // the selection kernel may move onto free SMs and wait there
     const int hk = blockIdx.y;
     const int tok = blockIdx.z;
@@ -174,6 +176,7 @@ template <typename T, int D, int REP>
 __global__ void __launch_bounds__(kScoreThreads, 2)
 score_pages_mma_kernel(const T *__restrict__ q, const T *__restrict__ summaries, float *__restrict__ scores,
                        int n_kv_heads, int n_pages) {
+    if (threadIdx.x == 0) trace_stamp(0, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, 0);
     griddep_launch_dependents();   // the selection kernel may move onto free SMs and wait there
     static_assert(sizeof(T) == 2 && REP <= 8 && (2 * D) % 32 == 0, "16-bit types, at most 8 query rows");
     constexpr int CHUNKS = 2 * D / 8;   // 16-byte chunks per page summary
@@ -242,6 +245,10 @@ score_pages_mma_kernel(const T *__restrict__ q, const T *__restrict__ summaries,
                 if (pg + 1 < n_pages) out[(size_t)row * n_pages + pg + 1] = c[1];
             }
         }
+    }
+    if (g_trace_buf != nullptr) {
+        __syncthreads();
+        if (threadIdx.x == 0) trace_stamp(0, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, 1);
     }
 }
 
@@ -335,3 +342,5 @@ extern "C" int da_score_pages(const void *q, const void *summaries, float *score
     }
     return (int)e;
 }
+
+DA_DEFINE_TRACE_SETTER(trace_set_score)

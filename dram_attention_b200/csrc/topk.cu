@@ -119,7 +119,15 @@ template <int IPT>
 __global__ void __launch_bounds__(kTopkThreads)
 topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_list, int n_kv_heads, int rep,
                   int n_pages, int k) {
+    if (threadIdx.x == 0) trace_stamp(1, blockIdx.x, 0);
+    // on whichever path the kernel leaves: thread 0's end stamp
+    struct EndStamp {
+        __device__ ~EndStamp() {
+            if (threadIdx.x == 0) trace_stamp(1, blockIdx.x, 1);
+        }
+    } end_stamp;
     griddep_wait();                // the scores come from the kernel before this one
+    if (threadIdx.x == 0) trace_stamp(1, blockIdx.x, 2);
     griddep_launch_dependents();   // the LRU update may move onto the SMs and wait there
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int cap = topk_candidate_capacity(k);
@@ -451,3 +459,5 @@ extern "C" int da_topk_pages(const float *scores, int32_t *page_list, int n_toke
     else e = da::launch_topk<0>(scores, page_list, rows, n_kv_heads, rep, n_pages, k, s);
     return (int)e;
 }
+
+DA_DEFINE_TRACE_SETTER(trace_set_topk)

@@ -105,6 +105,24 @@ class DRAMAttention(torch.nn.Module):
                 k_cache=dram_k_cache[0].transpose(0, 1), v_cache=dram_v_cache[0].transpose(0, 1),
                 device=self.device, page_size=self.page_size)
 
+    def init_cache_sharing(self, other: "DRAMAttention") -> None:
+        """Initialise this operator as `init_cache` would with the prefill KV `other` was given,
+        WITHOUT a second copy of the DRAM prefix: the pinned pages and their summaries are shared
+        with `other`, while the slot table, the LRU state and the local window are this operator's
+        own (in the state right after cache construction).  For synthetic stacks in which several
+        layers are fed the same prefix."""
+        assert isinstance(other.lru_cache, LRUCache), "the other operator has no DRAM-backed cache"
+        assert (self.page_size, self.n_kv_heads, self.head_dim, self.lru_hbm_cache_size, self.local_cache_size) == \
+            (other.page_size, other.n_kv_heads, other.head_dim, other.lru_hbm_cache_size, other.local_cache_size)
+        self.dram_kv_cache_size = other.dram_kv_cache_size
+        n = min(self.cache_k.shape[1], other.cache_k.shape[1], other.local_cache_size)
+        self.cache_k[:, :n].copy_(other.cache_k[:, :n])
+        self.cache_v[:, :n].copy_(other.cache_v[:, :n])
+        self.lru_cache = LRUCache.sharing_dram_of(other.lru_cache, top_k=self.top_k // self.page_size)
+        self._can_fuse = self.page_size % 16 == 0
+        self._can_overlap = self._can_fuse
+        self._overlap_ok = {}
+
     # ---- forward ------------------------------------------------------------------
     def forward(self, xq: torch.Tensor, xk: torch.Tensor, xv: torch.Tensor, *, start_pos, stage: str):
         """xq (1, s, Hq, D), xk/xv (1, s, Hk, D).  `stage` is "prefill" (dense causal

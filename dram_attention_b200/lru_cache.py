@@ -64,8 +64,11 @@ class LRUCache(torch.nn.Module):
 
     def __init__(self, k_cache: torch.Tensor, v_cache: torch.Tensor, page_size: int, top_k: int,
                  lru_hbm_cache_size: Optional[int] = None, hbm_kv_cache_fraction: float = 0.2,
-                 device: str = "cuda"):
+                 device: str = "cuda", _share: Optional["LRUCache"] = None):
         super().__init__()
+        if _share is not None:
+            self._init_shared(_share, top_k)
+            return
         assert k_cache.shape == v_cache.shape, "Key and value cache shapes must match."
         num_kv_heads, dram_kv_cache_size, head_dim = k_cache.shape
         dtype = k_cache.dtype
@@ -110,6 +113,39 @@ class LRUCache(torch.nn.Module):
             torch.cuda.current_stream().synchronize()  # k_dev/v_dev may be temporaries
         self.top_k_selector = IPUpperboundTopKSelector(k_cache, num_dram_pages, device=dev,
                                                        _summaries=summaries)
+        self._init_tables(dev)
+
+    @classmethod
+    def sharing_dram_of(cls, other: "LRUCache", top_k: Optional[int] = None) -> "LRUCache":
+        """A second cache over the SAME pinned DRAM pages and page summaries as `other` (neither is
+        copied), with a slot table, LRU tables and queue of its own in the warm-start state.  For
+        stacks of layers that are fed the same synthetic prefix: the host memory is paid once,
+        everything a decode step reads or writes on the device is per layer."""
+        return cls(None, None, other.page_size, other.top_k if top_k is None else top_k, _share=other)
+
+    def _init_shared(self, other: "LRUCache", top_k: int) -> None:
+        self.page_size, self.num_kv_heads, self.head_dim = other.page_size, other.num_kv_heads, other.head_dim
+        self.num_dram_pages, self.num_hbm_pages, self.top_k = other.num_dram_pages, other.num_hbm_pages, top_k
+        dev = other.hbm_kv_cache.device
+        i32 = dict(dtype=torch.int32, device=dev)
+        hk, ld, nh = self.num_kv_heads, self.num_dram_pages, self.num_hbm_pages
+        self.register_buffer("step_counters", torch.zeros(hk, **i32))
+        self.register_buffer("dram_kv_cache", other.dram_kv_cache, persistent=False)
+        self.register_buffer("hbm_kv_cache", torch.empty_like(other.hbm_kv_cache))
+        # warm start: the rightmost pages, read back from the shared DRAM pages
+        self.hbm_kv_cache.copy_(other.dram_kv_cache[:, ld - nh:], non_blocking=True)
+        self.register_buffer("page_access_time", torch.zeros(hk, nh, **i32))
+        self.register_buffer("dram_page_to_hbm_page_mapping", torch.full((hk, ld), -1, **i32))
+        self.register_buffer("hbm_page_to_dram_page_mapping", torch.arange(ld - nh, ld, **i32).repeat(hk, 1))
+        self.dram_page_to_hbm_page_mapping[:, ld - nh:] = torch.arange(nh, **i32)[None]
+        self.top_k_selector = IPUpperboundTopKSelector(
+            torch.empty(hk, ld * self.page_size, self.head_dim, dtype=other.hbm_kv_cache.dtype, device="meta"),
+            ld, device=dev, _summaries=other.top_k_selector.chunk_min_max)
+        self._init_tables(dev)
+
+    def _init_tables(self, dev) -> None:
+        num_kv_heads, num_hbm_pages = self.num_kv_heads, self.num_hbm_pages
+        i32 = dict(dtype=torch.int32, device=dev)
         self.register_buffer("status", torch.zeros(1, **i32), persistent=False)
         # slot -> DRAM page whose payload is still to be brought in (-1: slot is up to date);
         # maintained by the LRU kernel, consumed by the attention kernel that fetches on the fly
@@ -129,7 +165,8 @@ class LRUCache(torch.nn.Module):
         self.register_buffer("n_evictable", torch.full((2, num_kv_heads), self.split_cap, **i32),
                              persistent=False)
         self.register_buffer("evict_flip", torch.zeros(num_kv_heads, **i32), persistent=False)
-        self.register_buffer("evict_redo", torch.zeros(num_kv_heads, **i32), persistent=False)
+        # row 0: redo flag of the last update; row 1: pages missed so far; row 2: updates that set the flag
+        self.register_buffer("evict_redo", torch.zeros(3, num_kv_heads, **i32), persistent=False)
         self._miss = {}
 
     # slots per head in the eviction front (a steady decode step misses a handful of pages per head)

@@ -39,7 +39,15 @@ class KVHeadShardedDRAMAttention(torch.nn.Module):
     its own projections) or, with `presliced=True`, only this rank's heads.
 
     `operator_factory(n_kv_heads=..., **ctor_kwargs)` builds the per-rank operator
-    (DRAMAttention by default; tests inject a stand-in)."""
+    (DRAMAttention by default; tests inject a stand-in).
+
+    The first decode call sets the peer-memory gather up (an allocation, a rendezvous and a
+    barrier): make it eagerly, before any CUDA-graph capture.  The gather kernel never hangs: a
+    rank that waits longer than `gather_timeout_us` for a peer gives up, marks the peer's rows
+    of its output with NaN and sets a status bit.  `check_status()` reads that bit (it
+    synchronises): call it between steps, or at the latest before the outputs are trusted."""
+
+    gather_timeout_us = 0   # 0: the library's default (0.2 s)
 
     def __init__(self, *, n_kv_heads: int, rank: Optional[int] = None, world_size: Optional[int] = None,
                  process_group=None, operator_factory: Optional[Callable] = None, presliced: bool = False,
@@ -91,7 +99,8 @@ class KVHeadShardedDRAMAttention(torch.nn.Module):
         with torch.cuda.device(local.device):
             _native.check(_native.lib().da_gather_heads(
                 src.data_ptr(), nbytes, handle.buffer_ptrs_dev, seq.data_ptr(), self.rank, self.world_size,
-                out.data_ptr(), status.data_ptr(), _native.stream_ptr()), "da_gather_heads")
+                out.data_ptr(), int(self.gather_timeout_us), status.data_ptr(), _native.stream_ptr()),
+                "da_gather_heads")
         return out
 
     def check_status(self) -> None:

@@ -153,3 +153,64 @@ def scorer_workload(seed: int = 0, pages: int = 65536, n_kv_heads: int = 8, rep:
             mm[h, a:b, 1] = mx
     q = torch.randn(1, 1, n_kv_heads * rep, head_dim, generator=g).to(dtype)
     return q, mm
+
+
+def device_layer_inputs(device, seed: int, steps: int, dram_tokens: int, n_kv_heads: int = 8, rep: int = 4,
+                        local: int = 4096, page_size: int = 16, needles: int = 16, redraw_every: int = 0,
+                        dtype: torch.dtype = torch.bfloat16):
+    """The same kind of layer as `llama_layer_workload` (head_dim 128; N(0,1) keys/values with 8
+    outlier channels x10; `needles` pages along a shared direction u; queries u + N(0,1) drifting by
+    N(0, 0.05^2), re-drawn from N(0,1) every `redraw_every` steps), generated ON THE DEVICE from a
+    device generator seeded with `seed`: for the large benchmark workloads (a million-token prefix,
+    many sequences) that take minutes to draw on the host.  Not bit-identical to the host version.
+
+    Returns (k, v, xq, xk, xv, u, outlier_channels): k, v (1, S, Hk, D) with S = dram_tokens +
+    local - page_size; xq (steps, 1, 1, Hq, D); xk, xv (steps, 1, 1, Hk, D); the needle direction
+    and the outlier channels (for `device_decode_inputs` of further layers over the same prefix)."""
+    d, hk, hq = 128, n_kv_heads, n_kv_heads * rep
+    s = dram_tokens + local - page_size
+    g = torch.Generator(device=device).manual_seed(seed)
+    ch = torch.randperm(d, generator=g, device=device)[:8]
+    k = torch.empty(1, s, hk, d, dtype=dtype, device=device)
+    v = torch.empty(1, s, hk, d, dtype=dtype, device=device)
+    chunk = 65536
+    for t in (k, v):
+        for a in range(0, s, chunk):
+            b = min(s, a + chunk)
+            x = torch.randn(b - a, hk, d, generator=g, device=device)
+            x[..., ch] *= 10.0
+            t[0, a:b] = x.to(dtype)
+    u = torch.randn(d, generator=g, device=device)
+    u = u / u.norm() * (d ** 0.5)
+    if needles:
+        pages = torch.randperm(dram_tokens // page_size, generator=g, device=device)[:needles]
+        for pg in pages.tolist():
+            k[0, pg * page_size:(pg + 1) * page_size] = \
+                (u + 0.3 * torch.randn(page_size, hk, d, generator=g, device=device)).to(dtype)
+    xq, xk, xv = device_decode_inputs(device, seed + 1, steps, u, ch, hk, rep, redraw_every, dtype)
+    return k, v, xq, xk, xv, u, ch
+
+
+def device_decode_inputs(device, seed: int, steps: int, u: torch.Tensor, outlier_channels: torch.Tensor,
+                         n_kv_heads: int, rep: int, redraw_every: int = 0,
+                         dtype: torch.dtype = torch.bfloat16):
+    """Per-step decode inputs of one layer on the device: queries u + N(0,1) that drift by
+    N(0, 0.05^2) per step (re-drawn from N(0,1) every `redraw_every` steps), new keys/values
+    N(0,1) with the outlier channels x10."""
+    d, hk, hq = u.shape[0], n_kv_heads, n_kv_heads * rep
+    g = torch.Generator(device=device).manual_seed(seed)
+    q = u[None] + torch.randn(hq, d, generator=g, device=device)
+    noise = 0.05 * torch.randn(steps, hq, d, generator=g, device=device)
+    xq = torch.empty(steps, 1, 1, hq, d, dtype=dtype, device=device)
+    for i in range(steps):
+        if i:
+            if redraw_every and i % redraw_every == 0:
+                q = torch.randn(hq, d, generator=g, device=device)
+            else:
+                q = q + noise[i]
+        xq[i, 0, 0] = q.to(dtype)
+    xk = torch.randn(steps, 1, 1, hk, d, generator=g, device=device)
+    xv = torch.randn(steps, 1, 1, hk, d, generator=g, device=device)
+    xk[..., outlier_channels] *= 10.0
+    xv[..., outlier_channels] *= 10.0
+    return xq, xk.to(dtype), xv.to(dtype)

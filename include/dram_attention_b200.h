@@ -68,6 +68,22 @@ DA_API int da_version(void);
 DA_API const char *da_error_string(int code);
 
 /*
+ * Profiling switch (no counterpart in the reference).  While a buffer of da_trace_bytes() bytes
+ * of device memory is set, thread 0 of every CTA of every kernel of this library writes the
+ * GPU's global nanosecond timer into it at a few points: the buffer is
+ * [5 kernels][1024 CTAs (index modulo)][4 events] of uint64, kernels 0 = page scorer,
+ * 1 = selection, 2 = LRU update, 3 = attention (single launch or phase 1), 4 = attention phase 2;
+ * events 0 = the CTA is on its SM, 1 = it is done, and for selection and LRU update 2 = the
+ * kernel before it in the stream has finished (they are launched early and wait), for the
+ * attention 2 = its warps are through their units, 3 = its ticket is taken.  A launch overwrites
+ * the stamps of the launch before it, so after a step the buffer holds that step's time line,
+ * including the kernels that ran side by side on different streams.  da_trace_set(NULL)
+ * switches it off (the default).  Applies to the current device; call it outside stream capture.
+ */
+DA_API size_t da_trace_bytes(void);
+DA_API int da_trace_set(void *buffer);
+
+/*
  * Page scorer.  Replaces max_inner_product()
  * (dram_attention/max_ip_triton_kernel.py:95-124, formula :72-80 and :127-133)
  * together with the GQA reshapes around it (dram_attention/topk_selector.py:48-59).
@@ -137,7 +153,9 @@ DA_API int da_topk_pages(const float *scores, int32_t *page_list,
  * evict_queue, front_count, split_flip, split_redo  optional, all or none: the eviction queue that
  *             makes the update cheap and that da_decode_attention_phased works from.
  *             evict_queue is [2][n_kv_heads][n_slots] int32, front_count [2][n_kv_heads],
- *             split_flip and split_redo [n_kv_heads].  Copy split_flip[h] of evict_queue[.][h] is
+ *             split_flip [n_kv_heads], split_redo [3][n_kv_heads] (row 0 the flag described
+ *             below; rows 1 and 2 running totals the call adds to: pages missed, calls that
+ *             set the flag).  Copy split_flip[h] of evict_queue[.][h] is
  *             the CURRENT queue of head h: all its slots in eviction order, i.e. sorted by
  *             (access_time, slot) ascending; the first front_count entries are the FRONT, the
  *             slots an attention launch that runs beside this update has left out because they
@@ -439,9 +457,13 @@ DA_API int da_prefill_attention(const void *q, const void *k, const void *v, voi
  * sharding on the GPUs of one node (no counterpart in the reference, which runs on one
  * GPU; it replaces the library all-gather that would otherwise follow the attention
  * launch).  One launch of one CTA: the rank's rows are stored into every rank's gather
- * buffer, one flag per peer is released, the CTA waits (bounded: DA_STATUS_WAIT_TIMEOUT
- * after ~2^22 polls) until every source rank's flag for this step is set in its own
- * buffer, copies the assembled block to `out` and advances *seq.
+ * buffer, one flag per peer is released, the CTA waits until every source rank's flag for
+ * this step is set in its own buffer, copies the assembled block to `out` and advances *seq.
+ * The wait is bounded by the GPU's timer: after timeout_us microseconds (0 = the default,
+ * 200 000) the kernel sets DA_STATUS_WAIT_TIMEOUT in *status, fills the rows of every rank
+ * whose flag did not come with 0xFF bytes (NaN in every floating-point format) and returns:
+ * nothing hangs, and a gather that timed out cannot be mistaken for a result.  The caller
+ * has to look at *status (between steps; it is sticky).
  *
  * local         bytes_per_rank bytes, device memory, 16-byte aligned (this rank's rows)
  * peer_buffers  DEVICE array of `world` pointers; entry g = rank g's gather buffer of
@@ -454,7 +476,7 @@ DA_API int da_prefill_attention(const void *q, const void *k, const void *v, voi
  */
 DA_API size_t da_gather_heads_buffer_bytes(int bytes_per_rank, int world);
 DA_API int da_gather_heads(const void *local, int bytes_per_rank, void *const *peer_buffers,
-                    int32_t *seq, int rank, int world, void *out, int32_t *status,
+                    int32_t *seq, int rank, int world, void *out, int timeout_us, int32_t *status,
                     da_stream_t stream);
 
 #ifdef __cplusplus

@@ -225,7 +225,8 @@ def lru_vectorised(page_list: np.ndarray, d2h: np.ndarray, h2d: np.ndarray,
 # Attention over the slot table and the local window, and the LSE merge
 # --------------------------------------------------------------------------
 
-def attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+def attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+           dtype: torch.dtype = torch.float64) -> Tuple[torch.Tensor, torch.Tensor]:
     """Exact softmax attention of one query token, GQA by contiguous groups.
 
     q (Hq, D); k, v (T, Hk, D); scale D**-0.5.  Returns out (Hq, D) and
@@ -235,14 +236,16 @@ def attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> Tuple[torch.Ten
     and a float32 dot product alone is uncertain by ~1e-5 relative).  This is what the
     reference obtains from flash_attn_with_kvcache(..., return_softmax_lse=True)
     at dram_attention/dram_attention.py:195-205 and :211-223 (for a single
-    query row the causal flag changes nothing).
+    query row the causal flag changes nothing).  `dtype` = float32 gives the
+    arithmetic a pure-PyTorch float32 path would use; only the timed CPU
+    baseline asks for it, every check uses float64.
     """
     hq, d = q.shape
     t, hk, _ = k.shape
     rep = hq // hk
-    qf = q.to(torch.float64).reshape(hk, rep, d)
-    kf = k.to(torch.float64).permute(1, 0, 2)  # (Hk, T, D)
-    vf = v.to(torch.float64).permute(1, 0, 2)
+    qf = q.to(dtype).reshape(hk, rep, d)
+    kf = k.to(dtype).permute(1, 0, 2)  # (Hk, T, D)
+    vf = v.to(dtype).permute(1, 0, 2)
     logits = torch.bmm(qf, kf.transpose(1, 2)) * (d ** -0.5)  # (Hk, rep, T)
     lse = torch.logsumexp(logits, dim=-1)
     p = torch.exp(logits - lse[..., None])
@@ -377,6 +380,7 @@ class OracleDRAMAttention:
         self.cache_v = torch.zeros(shape, dtype=dtype)
         self.lru_cache: Optional[OracleLRUCache] = None
         self.static_k = self.static_v = None
+        self.attn_dtype = torch.float64   # float32 only for the timed CPU baseline
 
     def init_cache(self, k_cache: torch.Tensor, v_cache: torch.Tensor):
         """dram_attention.py:65-105.  k_cache, v_cache are (1, S, Hk, D)."""
@@ -414,8 +418,8 @@ class OracleDRAMAttention:
         self.cache_v[t:t + s_q] = xv[0]
         if s_q == 1:
             q = xq[0, 0]
-            po, plse = attend(q, pk.transpose(0, 1), pv.transpose(0, 1))
-            so, slse = attend(q, self.cache_k[:t + 1], self.cache_v[:t + 1])
+            po, plse = attend(q, pk.transpose(0, 1), pv.transpose(0, 1), self.attn_dtype)
+            so, slse = attend(q, self.cache_k[:t + 1], self.cache_v[:t + 1], self.attn_dtype)
             out = combine(po, so, plse, slse)
         else:
             po, plse = attend_tokens(xq[0], pk.transpose(0, 1), pv.transpose(0, 1))

@@ -31,6 +31,8 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")        # nothing bound to an NVLink multicast object at exit
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
     dist.init_process_group("nccl", device_id=dev)
 
     steps = 6

@@ -187,7 +187,9 @@ class Tables:
         self.split_cap = max(1, self.nh // 4)
         self.g_nev = torch.full((2, self.hk), self.split_cap, dtype=torch.int32, device=DEV)
         self.g_flip = torch.zeros(self.hk, dtype=torch.int32, device=DEV)
-        self.g_redo = torch.full((self.hk,), -5, dtype=torch.int32, device=DEV)
+        self.g_redo = torch.zeros(3, self.hk, dtype=torch.int32, device=DEV)
+        self.g_redo[0] = -5
+        self.miss_total = np.zeros(self.hk, np.int64)
         self.g_src = torch.full((self.hk, self.nh), -1, dtype=torch.int32, device=DEV)
         self.g_prev = None
         return self
@@ -238,7 +240,9 @@ class Tables:
                                          page_bytes, s))
         torch.cuda.synchronize()
         if use_queue and not (int(self.g_status) & 2):
-            redo = self.g_redo.cpu().numpy()
+            redo = self.g_redo[0].cpu().numpy()
+            self.miss_total += nm_h
+            assert np.array_equal(self.g_redo[1].cpu().numpy(), self.miss_total)
             new_flip = self.g_flip.cpu().numpy()
             times = self.g_time.cpu().numpy()
             for h in range(self.hk):
