@@ -89,6 +89,9 @@ def parse_args():
                          "the warm-up, inside the 64 steps the configuration names)")
     ap.add_argument("--clock-period-ms", type=float, default=2.0,
                     help="NVML polling period while the GPU works alone; the end-to-end loop is polled 10x slower")
+    ap.add_argument("--reference-gpu", action="store_true",
+                    help="also time the UNMODIFIED reference package on this GPU (its Triton kernels and flash-attn), "
+                         "if a copy of it lies under the git-ignored baseline/_ref/; one data point, off by default")
     ap.add_argument("--cfg4-sequences", type=int, default=8)
     ap.add_argument("--cfg4-steps", type=int, default=128)
     ap.add_argument("--cfg4-redraw", type=int, default=32)
@@ -426,7 +429,7 @@ def bench_cfg2(args, ctx):
     K, W = args.steps, max(args.warmup, 3)
     NW = max(1, args.windows)
     settle = max(0, args.settle_steps)
-    total = settle + W + (NW + 1) * K + (W + K) + K + 8
+    total = settle + W + (NW + 1) * K + (W + K) + K + 8 + (W + 2 * K + 4 if args.reference_gpu else 0)
     by_seq = world > 1 and args.shard == "sequence"
     n_seq = world if by_seq else 1
     w = llama_layer_workload(seed=(rank if by_seq else 0), steps=total, dram_tokens=args.dram_tokens, max_out=total)
@@ -785,6 +788,68 @@ def cfg2_extras(args, ctx, r):
     return out
 
 
+def bench_reference_gpu(args, ctx, w):
+    """One data point for the unmodified reference on this GPU: its DRAMAttention (Triton scorer and LRU
+    kernels, flash-attn for the two attention calls, torch for the rest) on the same layer, eager steps
+    after a warm start; nothing of this package is on that path.  Any failure is reported as text."""
+    torch, dev = ctx.torch, ctx.dev
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "dram_attention")):
+        return {"unavailable": "no copy of the reference package under baseline/_ref/"}
+    try:
+        if ref_root not in sys.path:
+            sys.path.insert(0, ref_root)
+        import dram_attention as ref
+        K, W = args.steps, max(args.warmup, 3)
+        m = ref.DRAMAttention(device=dev, dtype=w.dtype, **w.ctor_kwargs())
+        m.init_cache(w.k.to(dev), w.v.to(dev))
+        S = w.prefill_len
+        dq, dk, dv = w.xq.to(dev), w.xk.to(dev), w.xv.to(dev)
+        for i in range(W):      # Triton compiles and autotunes here
+            out = m(dq[i], dk[i], dv[i], start_pos=S + i, stage="generate")
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for i in range(W, W + K):
+            out = m(dq[i], dk[i], dv[i], start_pos=S + i, stage="generate")
+        ev1.record()
+        torch.cuda.synchronize()
+        ms = ev0.elapsed_time(ev1) / K
+        res = {"what": "unmodified reference DRAMAttention on this GPU, generate steps after a warm start", "steps": K,
+               "eager_ms_per_step": ms, "eager_tok_s": 1e3 / ms, "finite": bool(torch.isfinite(out.float()).all())}
+        # the way its chat example decodes: ONE step captured in a CUDA graph with a device-side position,
+        # replayed per token (examples/long-qa-chat/chat.py:238-249, :272)
+        try:
+            first = W + K
+            xq, xk, xv = dq[first].clone(), dk[first].clone(), dv[first].clone()
+            pos = torch.tensor([S + first], dtype=torch.int32, device=dev)
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                m(xq, xk, xv, start_pos=pos, stage="generate")
+            torch.cuda.current_stream().wait_stream(side)
+            pos.add_(1)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                out_g = m(xq, xk, xv, start_pos=pos, stage="generate")
+            torch.cuda.synchronize()
+            ev0.record()
+            for i in range(K):
+                xq.copy_(dq[first + 1 + i]); xk.copy_(dk[first + 1 + i]); xv.copy_(dv[first + 1 + i])
+                g.replay()
+                pos.add_(1)
+            ev1.record()
+            torch.cuda.synchronize()
+            gms = ev0.elapsed_time(ev1) / K
+            res.update(graph_ms_per_step=gms, graph_tok_s=1e3 / gms, graph_finite=bool(torch.isfinite(out_g.float()).all()))
+        except Exception as e:
+            res["graph_error"] = repr(e)[:400]
+            torch.cuda.synchronize()
+        return res
+    except Exception as e:
+        return {"error": repr(e)[:600]}
+
+
 def bench_kv_head_sharded(args, ctx, one_gpu_ms_per_step):
     """ONE 128K sequence, its KV heads sharded over the ranks, outputs all-gathered (N > 1)."""
     torch = ctx.torch
@@ -1129,6 +1194,8 @@ def run_b200(args):
         more = {}
         if extras and world == 1:
             more.update(cfg2_extras(args, ctx, r))
+        if args.reference_gpu and world == 1:
+            more["reference_gpu"] = bench_reference_gpu(args, ctx, w)
         # free the 128K layer before the other configurations are built
         for key in ("op", "inner", "dq", "dk", "dv", "launch_us"):
             r.pop(key, None)

@@ -271,6 +271,84 @@ def test_captured_step_survives_an_eager_load(da):
     e.check_status()
 
 
+# ---- several operators side by side: a stack of layers, a batch of sequences ----------------
+
+def _step_interleaved(da, modules, workloads, steps):
+    """Steps the operators round-robin (token step i of every operator, then i + 1, ...), checks the
+    slot payloads after every call, and returns per operator (outputs, page lists, h2d, times)."""
+    logs = [dict(out=[], h2d=[], time=[], lists=_spy_lists(m)) for m in modules]
+    for i in range(steps):
+        for m, w, log in zip(modules, workloads, logs):
+            s = w.k.shape[1]
+            out = m(w.xq[i].to(DEV), w.xk[i].to(DEV), w.xv[i].to(DEV), start_pos=s + i, stage="generate")
+            log["out"].append(out[0, 0].float().cpu())
+            lc = m.lru_cache
+            h2d = lc.hbm_page_to_dram_page_mapping.cpu().numpy().astype(np.int64)
+            for h in range(lc.num_kv_heads):
+                assert torch.equal(lc.hbm_kv_cache[h].cpu(), lc.dram_kv_cache[h, torch.from_numpy(h2d[h])]), i
+            log["h2d"].append(h2d)
+            log["time"].append(lc.page_access_time.cpu().numpy().astype(np.int64))
+    for m in modules:
+        m.check_status()
+    return logs
+
+
+def _assert_follows_oracle(w, steps, log):
+    lists = [l.cpu().numpy().astype(np.int64) for l in log["lists"]]
+    o, res = _oracle_follow(w, steps, lists)
+    for i, (scores, own, out, h2d, tim) in enumerate(res):
+        assert np.array_equal(log["h2d"][i], h2d), i
+        assert np.array_equal(log["time"][i], tim), i
+        assert_out_close(log["out"][i], out, torch.bfloat16, i)
+
+
+def test_two_layers_share_one_dram_prefix(da):
+    """A two-layer stack over ONE synthetic prefix (the shape of the 32-layer, million-token
+    configuration, reduced): the second layer is set up with init_cache_sharing, so both read the same
+    pinned pages and summaries, while slots, LRU state, local window and queries are each layer's own.
+    Stepped alternately, each layer follows its oracle (tables bit-exact, outputs within 2e-2)."""
+    import dataclasses
+    steps = 6
+    kw = dict(steps=steps, dram_tokens=16384, n_kv_heads=2, lru=4096, local=512, top_k=1024, needles=4)
+    w0 = llama_layer_workload(seed=4, **kw)
+    other = llama_layer_workload(seed=5, **kw)
+    w1 = dataclasses.replace(w0, xq=other.xq, xk=other.xk, xv=other.xv)
+    m0 = da.DRAMAttention(device=DEV, dtype=torch.bfloat16, **w0.ctor_kwargs())
+    m0.init_cache(w0.k.to(DEV), w0.v.to(DEV))
+    m1 = da.DRAMAttention(device=DEV, dtype=torch.bfloat16, **w0.ctor_kwargs())
+    m1.init_cache_sharing(m0)
+    assert m1.lru_cache.dram_kv_cache.data_ptr() == m0.lru_cache.dram_kv_cache.data_ptr()
+    assert m1.lru_cache.top_k_selector.chunk_min_max.data_ptr() == m0.lru_cache.top_k_selector.chunk_min_max.data_ptr()
+    assert m1.lru_cache.hbm_kv_cache.data_ptr() != m0.lru_cache.hbm_kv_cache.data_ptr()
+    assert m1.dram_kv_cache_size == m0.dram_kv_cache_size
+    logs = _step_interleaved(da, [m0, m1], [w0, w1], steps)
+    _assert_follows_oracle(w0, steps, logs[0])
+    _assert_follows_oracle(w1, steps, logs[1])
+    # the two layers really went their own ways
+    assert not torch.equal(m0.lru_cache.hbm_page_to_dram_page_mapping, m1.lru_cache.hbm_page_to_dram_page_mapping)
+
+
+def test_two_sequences_with_a_query_redraw(da):
+    """Two independent sequences stepped round-robin on one GPU (the batched configuration, reduced),
+    each with a query re-draw in the middle that evicts far more slots than the eviction front holds:
+    both follow their oracles through it."""
+    steps = 7
+    ws = [llama_layer_workload(seed=sd, steps=steps, dram_tokens=16384, n_kv_heads=2, lru=4096, local=512,
+                               top_k=1024, needles=0, redraw_every=3) for sd in (6, 7)]
+    ms = []
+    for w in ws:
+        m = da.DRAMAttention(device=DEV, dtype=torch.bfloat16, **w.ctor_kwargs())
+        m.init_cache(w.k.to(DEV), w.v.to(DEV))
+        ms.append(m)
+    logs = _step_interleaved(da, ms, ws, steps)
+    for w, m, log in zip(ws, ms, logs):
+        _assert_follows_oracle(w, steps, log)
+        assert int(m.lru_cache.evict_redo[2].sum()) >= 1       # the re-draw took the redo path
+        assert int(m.lru_cache.evict_redo[1].sum()) == sum(
+            int((np.diff(np.stack([log["h2d"][i - 1], log["h2d"][i]]), axis=0) != 0).sum()) for i in range(1, steps)) + \
+            int((log["h2d"][0] != np.arange(1024 - 256, 1024)[None]).sum())
+
+
 # ---- generate calls with several tokens --------------------------------------------------
 
 @pytest.mark.parametrize("heads", ["hq4_hk1", "hq2_hk2"])

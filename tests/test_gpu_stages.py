@@ -546,3 +546,57 @@ def test_decode_attention_bad_position_is_reported(da):
     torch.cuda.synchronize()
     assert int(status) & 4
     assert float(lk.abs().sum()) == 0  # nothing appended outside the window
+
+
+# ------------------------------------------------------------------ gather ----
+
+def test_gather_wait_runs_out_and_is_reported(da):
+    """The all-gather kernel of the KV-head sharding with a peer that never shows up (rank 0 of 2
+    on one GPU, nothing sets rank 1's flag): the kernel returns after its time budget, reports
+    DA_STATUS_WAIT_TIMEOUT, marks the missing rank's rows with NaN, and the context stays usable;
+    when the peer's rows and flag are there (written by hand, as its stores would) the next call
+    succeeds."""
+    from dram_attention_b200 import _native
+    lib = _native.lib()
+    world, nbytes = 2, 4 * 128 * 2
+    total = lib.da_gather_heads_buffer_bytes(nbytes, world)
+    assert total == 2 * world * nbytes + 2 * world * 4
+    bufs = [torch.zeros(total, dtype=torch.uint8, device=DEV) for _ in range(world)]
+    ptrs = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device=DEV)
+    seq = torch.zeros(1, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    g = _g(11)
+    local = torch.randn(4, 128, generator=g).bfloat16().to(DEV)
+    out = torch.zeros(world * 4, 128, dtype=torch.bfloat16, device=DEV)
+    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    _native.check(lib.da_gather_heads(local.data_ptr(), nbytes, ptrs.data_ptr(), seq.data_ptr(), 0, world,
+                                      out.data_ptr(), 2000, status.data_ptr(), _native.stream_ptr()))
+    t1.record()
+    torch.cuda.synchronize()
+    assert int(status) == _native.STATUS_WAIT_TIMEOUT
+    assert 1.5 <= t0.elapsed_time(t1) <= 50.0          # about the 2 ms it was given
+    assert torch.equal(out[:4], local)
+    assert bool(torch.isnan(out[4:].float()).all())     # nobody can take these rows for a result
+    assert int(seq) == 1
+    # rank 0's own rows went into both buffers, its flag (step 1 -> tag 1, slot 0) into both
+    flags1 = bufs[1][2 * world * nbytes:].view(torch.int32)
+    assert int(flags1[0 * world + 0]) == 1
+    assert torch.equal(bufs[1][:nbytes].view(torch.bfloat16).view(4, 128), local)
+    # the peer shows up for the next step (seq 1 -> slot 1, tag 2)
+    status.zero_()
+    peer_rows = torch.randn(4, 128, generator=g).bfloat16().to(DEV)
+    slot_bytes = world * nbytes
+    bufs[0][1 * slot_bytes + 1 * nbytes:1 * slot_bytes + 2 * nbytes] = peer_rows.view(torch.uint8).view(-1)
+    bufs[0][2 * world * nbytes:].view(torch.int32)[1 * world + 1] = 2
+    local2 = torch.randn(4, 128, generator=g).bfloat16().to(DEV)
+    _native.check(lib.da_gather_heads(local2.data_ptr(), nbytes, ptrs.data_ptr(), seq.data_ptr(), 0, world,
+                                      out.data_ptr(), 2000, status.data_ptr(), _native.stream_ptr()))
+    torch.cuda.synchronize()
+    assert int(status) == 0 and int(seq) == 2
+    assert torch.equal(out[:4], local2) and torch.equal(out[4:], peer_rows)
+    # bad arguments are refused on the host
+    assert lib.da_gather_heads(local.data_ptr(), nbytes, ptrs.data_ptr(), seq.data_ptr(), 2, world, out.data_ptr(),
+                               0, status.data_ptr(), _native.stream_ptr()) == -2
+    assert lib.da_gather_heads(local.data_ptr(), 24, ptrs.data_ptr(), seq.data_ptr(), 0, world, out.data_ptr(),
+                               0, status.data_ptr(), _native.stream_ptr()) == -2

@@ -1,8 +1,11 @@
 """Host-side logic of the KV-head sharding, on two gloo ranks (no GPU): head
-ranges, input slicing, and the all-gather that reassembles (1, s, Hq, D)."""
+ranges, input slicing, the all-gather that reassembles (1, s, Hq, D), and a rank that
+leaves between two steps."""
 
+import datetime
 import os
 import socket
+import time
 
 import pytest
 import torch
@@ -70,3 +73,39 @@ def test_two_rank_gather_reassembles_heads(seq):
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     mp.spawn(_worker, args=(2, port, seq), nprocs=2, join=True)
+
+
+def _leaver(rank, world, port, result_dir):
+    """Rank 1 leaves after the first step (between steps, nothing of its own in flight); rank 0's
+    next step must come back with an error within the process group's time-out, not wait for ever."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    hk, rep, d = 4, 2, 8
+    g = torch.Generator().manual_seed(1)
+    xq, xk, xv = torch.randn(1, 1, hk * rep, d, generator=g), torch.randn(1, 1, hk, d, generator=g), \
+        torch.randn(1, 1, hk, d, generator=g)
+    op = KVHeadShardedDRAMAttention(n_kv_heads=hk, operator_factory=FakeOperator)
+    out = op(xq, xk, xv, start_pos=1, stage="generate")
+    assert torch.equal(out, FakeOperator(hk)(xq, xk, xv, start_pos=1, stage="generate"))
+    if rank == 1:
+        os._exit(0)          # gone: no further call, no goodbye
+    t0 = time.monotonic()
+    try:
+        op(xq, xk, xv, start_pos=2, stage="generate")
+        verdict = "no error"
+    except Exception as e:   # a closed connection or the group's time-out, depending on who notices first
+        verdict = "error after %.1f s: %s" % (time.monotonic() - t0, type(e).__name__)
+    with open(os.path.join(result_dir, "rank0.txt"), "w") as f:
+        f.write(verdict)
+    os._exit(0)
+
+
+def test_rank_that_leaves_between_steps_is_an_error_not_a_hang(tmp_path):
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    t0 = time.monotonic()
+    mp.spawn(_leaver, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    assert time.monotonic() - t0 < 60
+    verdict = (tmp_path / "rank0.txt").read_text()
+    assert verdict.startswith("error after"), verdict
