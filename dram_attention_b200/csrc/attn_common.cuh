@@ -24,6 +24,7 @@ constexpr int kRoundUnits = 32;        // units a warp plans at a time (one per 
 constexpr int kAttnPhase1Warps = 12;
 constexpr int kAttnPhase1Ctas = 116;
 constexpr int kAttnPhase2Ctas = 64;
+constexpr int kAttnPhase2MaxPerHead = 8;   // the front is small: more CTAs only lengthen the merge
 
 __host__ __device__ inline int attn_splits(int n_kv_heads) {
     int s = kAttnTargetCtas / n_kv_heads;
@@ -40,6 +41,7 @@ __host__ __device__ inline int attn_splits_phase1(int n_kv_heads) {
 
 __host__ __device__ inline int attn_splits_phase2(int n_kv_heads) {
     int s = kAttnPhase2Ctas / n_kv_heads;
+    if (s > kAttnPhase2MaxPerHead) s = kAttnPhase2MaxPerHead;
     if (s < 1) s = 1;
     return s;
 }
@@ -202,16 +204,19 @@ __device__ __forceinline__ void cp_async_16(void *dst_smem, const void *src_gmem
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst_smem)), "l"(src_gmem) : "memory");
 }
 
-__device__ __forceinline__ void cp_async_wait_all() {
-    asm volatile("cp.async.wait_all;" ::: "memory");
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// waits until at most N of this thread's committed groups are still in flight
+template <int N> __device__ __forceinline__ void cp_async_wait_group() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
 // Final merge of the per-CTA partials of one head by one CTA of THREADS threads.  A CTA's
 // partial = `rows` rows of (acc[D] already weighted to the row's max, max, l); the partials of
 // consecutive CTAs are contiguous in the workspace.  They are brought into shared memory (the
 // idle stage buffers, `smem_bytes` of them) with 16-byte asynchronous copies that bypass L1 (the
-// rows were written by other SMs) and need no registers, as many CTAs' rows at a time as fit;
-// the first batch is requested before anything else is looked at.  `skip_flag` (may be null):
+// rows were written by other SMs) and need no registers.  When they do not all fit, the buffer
+// is used as two halves: the next batch is on its way while the current one is added up.  The
+// first batch is requested before anything else is looked at.  `skip_flag` (may be null):
 // when the word it points to is non-zero the first `skip` CTAs' rows are left out (they get
 // weight zero); it is read together with the (max, l) pairs, so it costs no round trip.
 template <typename T, int D, int THREADS>
@@ -228,17 +233,22 @@ __device__ __forceinline__ void merge_splits(const AttnParams &p, int h, int spl
     float *wgt = reinterpret_cast<float *>(smem);   // [n] max, then weight
     float *lsum = wgt + n;                          // [n] l of every partial row
     const int head_bytes = ((2 * n * (int)sizeof(float)) + 15) & ~15;
-    float4 *buf = reinterpret_cast<float4 *>(smem + head_bytes);
+    float4 *buf0 = reinterpret_cast<float4 *>(smem + head_bytes);
     const int cta_f4 = rows * PW / 4;               // float4 per CTA's partial
     int chunk = (smem_bytes - head_bytes) / (cta_f4 * 16);
-    chunk = min(max(chunk, 1), splits);
+    if (chunk < splits) chunk = max(chunk / 2, 1);  // two halves in flight
+    chunk = min(chunk, splits);
+    float4 *buf1 = buf0 + (size_t)chunk * cta_f4;
 
-    auto request = [&](int s0) {
+    // one commit group per batch (also when this thread has nothing to copy in it)
+    auto request = [&](int s0, float4 *buf) {
         const int cnt = min(chunk, splits - s0);
         const float4 *src = reinterpret_cast<const float4 *>(hp) + (size_t)s0 * cta_f4;
         for (int i = tid; i < cnt * cta_f4; i += THREADS) cp_async_16(buf + i, src + i);
+        cp_async_commit();
     };
-    request(0);
+    request(0, buf0);
+    if (chunk < splits) request(chunk, buf1);
     const int n_skip = (skip_flag != nullptr && __ldcg(skip_flag) != 0) ? skip * rows : 0;
     for (int i = tid; i < n; i += THREADS) {
         const float2 ml = __ldcg(reinterpret_cast<const float2 *>(hp + (size_t)i * PW + D));
@@ -271,10 +281,12 @@ __device__ __forceinline__ void merge_splits(const AttnParams &p, int h, int spl
     float4 a[MAXE];
 #pragma unroll
     for (int k = 0; k < MAXE; ++k) a[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s0 = 0; s0 < splits; s0 += chunk) {
+    int which = 0;
+    for (int s0 = 0; s0 < splits; s0 += chunk, which ^= 1) {
         const int cnt = min(chunk, splits - s0);
-        cp_async_wait_all();
-        __syncthreads();      // the chunk and (first time round) the weights are in shared memory
+        const float4 *buf = which ? buf1 : buf0;
+        if (s0 + chunk < splits) cp_async_wait_group<1>(); else cp_async_wait_group<0>();   // this batch has landed
+        __syncthreads();      // the batch and (first time round) the weights are in shared memory
 #pragma unroll
         for (int k = 0; k < MAXE; ++k) {
             const int e = k * THREADS + tid;
@@ -291,9 +303,9 @@ __device__ __forceinline__ void merge_splits(const AttnParams &p, int h, int spl
                 }
             }
         }
-        if (s0 + chunk < splits) {
-            __syncthreads();  // everybody is done with the buffer
-            request(s0 + chunk);
+        if (s0 + 2 * chunk < splits) {
+            __syncthreads();  // everybody is done with this half: the batch after the next goes into it
+            request(s0 + 2 * chunk, which ? buf1 : buf0);
         }
     }
 #pragma unroll
