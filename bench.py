@@ -61,6 +61,8 @@ NOMINAL_HBM_GBS = 8000.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one single-launch attention at the default workload, from
 # the ncu capture summarised in profiles/decode_attention_mma_llama128k.md
 ATTN_TRAFFIC_BYTES_128K = 154.4e6
+# the same counters for the phase-1 launch form of the default step (same profile file)
+PHASE1_TRAFFIC_BYTES_128K = 150.9e6
 
 
 def parse_args():
@@ -567,8 +569,9 @@ def bench_cfg2(args, ctx):
                 "decode_attention_mma_kernel, phase 1 of the default two-launch step", b_phase1,
                 p1["end"] - p1["first_cta_on_sm"], timing=stamp_note,
                 streaming_us=p1["units_done_median"] - p1["first_cta_on_sm"],
-                traffic=None, traffic_note="no ncu capture of this launch form; the single launch of the same kernel "
-                                           "over the same slots moves 1.02 x its algorithmic bytes (roofline_single_launch)")
+                traffic=(PHASE1_TRAFFIC_BYTES_128K if (hk == 8 and args.dram_tokens == 131072) else None),
+                traffic_note="dram__bytes_read.sum + dram__bytes_write.sum of one phase-1 launch of this workload "
+                             "(ncu capture summarised in profiles/decode_attention_mma_llama128k.md)")
         if p2:
             roof["roofline_phase2"] = roofline_obj("decode_attention_mma_kernel, phase 2 (eviction front + merge of both)",
                                                    b_phase2, p2["end"] - p2["first_cta_on_sm"], timing=stamp_note,
