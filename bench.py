@@ -296,7 +296,7 @@ def time_graph(ctx, capture_fn):
 # --------------------------------------------------------------------------------
 
 class StepTrace:
-    KERNELS = ["score", "topk", "lru", "attention_phase1", "attention_phase2"]
+    KERNELS = ["score", "topk", "lru", "attention_phase1", "attention_phase2", "gather"]
 
     def __init__(self, ctx):
         from dram_attention_b200 import _native
@@ -319,9 +319,11 @@ class StepTrace:
         """Start / end of every kernel of the last step that ran, in microseconds after the first
         CTA of the step got onto an SM."""
         import numpy as np
-        t = self.buf.cpu().numpy().reshape(5, 1024, 4)
-        live = [t[k][:, 0] > 0 for k in range(5)]
-        starts = [t[k][live[k], 0] for k in range(5) if live[k].any()]
+        n = len(self.KERNELS)
+        t = self.buf.cpu().numpy().reshape(n, 1024, 4)
+        live = [t[k][:, 0] > 0 for k in range(n)]
+        starts = [t[k][live[k], 0] for k in range(n - 1) if live[k].any()]   # the gather's CTA may sit on its SM from
+                                                                             # before the step's first kernel
         if not starts:
             return None
         t0 = min(int(s.min()) for s in starts)
@@ -341,6 +343,9 @@ class StepTrace:
                 e["units_done_min"], e["units_done_median"], e["units_done_max"] = \
                     us(le.min()), us(np.median(le)), us(le.max())
                 e["last_ticket"] = us(t[k][m, 3].max())
+            if k == 5:
+                e = {"on_sm": us(t[k][0, 0]), "rows_ready": us(t[k][0, 2]), "sent": us(t[k][0, 3]),
+                     "all_ranks_there_and_copied": us(t[k][0, 1]), "end": us(t[k][0, 1])}
             out[name] = e
         out["step_end"] = max(v["end"] for v in out.values())
         return out

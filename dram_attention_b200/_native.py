@@ -38,6 +38,8 @@ _SIGNATURES = {
     "da_prefill_attention_supported": (c_int, [c_int, c_int]),
     "da_prefill_attention": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                      c_longlong, c_longlong, c_int, c_void_p, c_void_p]),
+    "da_rope_qk": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                           c_void_p]),
     "da_gather_heads_buffer_bytes": (c_size_t, [c_int, c_int]),
     "da_gather_heads": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,
                                 c_void_p]),

@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_NAME = "libdram_attention_b200.so"
 LIB_PATH = os.path.join(HERE, LIB_NAME)
-SOURCES = ["api.cu", "score.cu", "topk.cu", "lru.cu", "fetch.cu", "gather.cu", "prefill.cu", "attn.cu", "attn_mma.cu"]
+SOURCES = ["api.cu", "score.cu", "topk.cu", "lru.cu", "fetch.cu", "gather.cu", "rope.cu", "prefill.cu", "attn.cu", "attn_mma.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 

@@ -31,5 +31,6 @@ extern "C" int da_trace_set(void *buffer) {
     if ((e = da::trace_set_lru(buffer)) != cudaSuccess) return (int)e;
     if ((e = da::trace_set_attn(buffer)) != cudaSuccess) return (int)e;
     if ((e = da::trace_set_attn_mma(buffer)) != cudaSuccess) return (int)e;
+    if ((e = da::trace_set_gather(buffer)) != cudaSuccess) return (int)e;
     return 0;
 }

@@ -60,7 +60,10 @@ __device__ __forceinline__ void decode_attention_body(const AttnParams &p, unsig
     const int trace_kernel = p.phase == 2 ? 4 : 3;
     const int trace_cta = h * splits + x;
     if (tid == 0) trace_stamp(trace_kernel, trace_cta, 0);
-    if (p.phase != 2) griddep_wait();
+    if (p.phase != 2) {
+        griddep_wait();
+        griddep_launch_dependents();   // a dependent launch after this one (the gather of the head shards) may move in
+    }
 
     // ---- position and unit range ------------------------------------------------
     const int pos = p.start_pos_dev ? *p.start_pos_dev : p.start_pos_host;
@@ -107,6 +110,7 @@ __device__ __forceinline__ void decode_attention_body(const AttnParams &p, unsig
     int base0 = plan_base(p, lu, worker, n_workers, lane, 0, total_my);
     if (p.phase == 2) {
         griddep_wait();   // from here on the LRU update is complete
+        griddep_launch_dependents();
         if (p.redo[h] != 0) {
             // it evicted beyond the front: this launch covers the whole head
             lu = launch_units(p, h, n_local, true);

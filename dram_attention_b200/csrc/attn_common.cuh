@@ -23,6 +23,9 @@ constexpr int kRoundUnits = 32;        // units a warp plans at a time (one per 
 // are plenty.
 constexpr int kAttnPhase1Warps = 12;
 constexpr int kAttnPhase1Ctas = 116;
+constexpr int kAttnPhase1MaxPerHead = 20;  // a shard of 1 to 4 KV heads: beyond 20 CTAs a head, every further partial
+                                           // row costs the final merge (which is on the step's critical path) more
+                                           // than the CTA adds in bandwidth (phase 1 is not on that path)
 constexpr int kAttnPhase2Ctas = 64;
 constexpr int kAttnPhase2MaxPerHead = 8;   // the front is small: more CTAs only lengthen the merge
 
@@ -35,6 +38,7 @@ __host__ __device__ inline int attn_splits(int n_kv_heads) {
 
 __host__ __device__ inline int attn_splits_phase1(int n_kv_heads) {
     int s = kAttnPhase1Ctas / n_kv_heads;
+    if (s > kAttnPhase1MaxPerHead) s = kAttnPhase1MaxPerHead;
     if (s < 1) s = 1;
     return s;
 }

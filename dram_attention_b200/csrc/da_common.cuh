@@ -100,7 +100,9 @@ template <typename T, int N> __device__ __forceinline__ void load_elems(const vo
 // read where a step's time goes while the kernels overlap on several streams, which events on a
 // stream cannot show.  A launch overwrites the stamps of the launch before it.  Unset (the
 // default) a stamp site costs one load of the pointer.
-constexpr int kTraceKernels = 5;   // 0 scorer, 1 selection, 2 LRU update, 3 attention (single launch or phase 1), 4 phase 2
+constexpr int kTraceKernels = 6;   // 0 scorer, 1 selection, 2 LRU update, 3 attention (single launch or phase 1), 4 phase 2,
+                                   // 5 gather of the head shards (events: 0 on the SM, 2 rows ready, 3 sent, 1 all there and copied)
+constexpr int kTraceGather = 5;
 constexpr int kTraceCtas = 1024;   // CTA index modulo this
 constexpr int kTraceEvents = 4;
 static __device__ unsigned long long *g_trace_buf;   // one copy per kernel file, all set together
@@ -127,6 +129,7 @@ cudaError_t trace_set_topk(void *buffer);
 cudaError_t trace_set_lru(void *buffer);
 cudaError_t trace_set_attn(void *buffer);
 cudaError_t trace_set_attn_mma(void *buffer);
+cudaError_t trace_set_gather(void *buffer);
 
 // ---- programmatic dependent launch ---------------------------------------------
 // The kernels of a generate step form a chain (scores -> page list -> tables -> attention).  A

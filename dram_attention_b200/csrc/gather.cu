@@ -1,22 +1,27 @@
 // All-gather of the per-KV-head-shard attention outputs over NVLink peer memory, for
 // KV-head sharding on the GPUs of one node.  One launch of one CTA per rank per step:
 //
-//   push   the rank's own rows go into slot (seq & 1) of EVERY rank's gather buffer
-//          (plain 128-bit stores to peer pointers), a system-scope fence, then one flag
-//          per peer is set to seq + 1;
-//   wait   the CTA polls its OWN flags (one per source rank) until all carry seq + 1 -
-//          bounded by the GPU's nanosecond timer: after `timeout_us` it sets
-//          DA_STATUS_WAIT_TIMEOUT and goes on;
-//   copy   the assembled (world, rows) block is copied to the caller's output tensor (the rows
-//          of a rank whose flag never came are filled with 0xFF bytes, a NaN in every
-//          floating-point format, so that a timed-out gather cannot pass for a result) and the
-//          step counter is advanced.
+//   push   the rank's own rows go into slot (seq & 1) of EVERY rank's gather buffer as 8-byte
+//          words {4 bytes of payload, the step's tag seq + 1}: one naturally aligned 8-byte store
+//          per word, which arrives whole, so the tag travels with the data it vouches for and
+//          no fence, flag or second round over the link is needed;
+//   wait   every thread polls the words of its OWN buffer that it will copy until they carry
+//          the step's tag - bounded by the GPU's nanosecond timer: after `timeout_us` the block
+//          sets DA_STATUS_WAIT_TIMEOUT and goes on;
+//   copy   the payload halves go to the caller's output tensor (words whose tag never came are
+//          written as 0xFFFFFFFF, a NaN in every floating-point format, so that a timed-out
+//          gather cannot pass for a result) and the step counter is advanced.
 //
 // Two slots suffice: a rank can start step s + 2 (which reuses slot s & 1) only after its
-// wait of step s + 1 saw every peer's flag of step s + 1, and a peer sets that flag after
-// (in stream order) its own copy of step s.  No multimem, no multicast loads: ordinary
-// peer stores and local loads.  The payload is a few KiB, so the step is latency-bound:
-// one NVLink store round instead of the several a library ring/tree takes.
+// wait of step s + 1 saw every peer's words of step s + 1, and a peer sends those after
+// (in stream order) its own copy of step s.  A tag is used once per slot (it grows by one per
+// step), and the buffers start out zero.  No multimem, no multicast loads: ordinary peer stores
+// and local loads.  The payload is a few KiB, so the step is latency-bound: one NVLink store
+// round instead of the several a library ring/tree takes.
+//
+// The kernel is launched as a programmatic dependent of the kernel before it in the stream
+// (the attention kernel, which releases its dependents early): its block is on an SM, with
+// its arguments and the step counter read, when the rows it sends are ready.
 
 #include "da_common.cuh"
 
@@ -32,77 +37,77 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     return t;
 }
 
-__device__ __forceinline__ void st_release_sys(int32_t *p, int32_t v) {
-    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_word_sys(uint2 *p, uint32_t payload, uint32_t tag) {
+    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(payload), "r"(tag) : "memory");
 }
 
-__device__ __forceinline__ int32_t ld_acquire_sys(const int32_t *p) {
-    int32_t v;
-    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ uint2 ld_word_sys(const uint2 *p) {
+    uint2 v;
+    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
     return v;
 }
 
-// Layout of every rank's symmetric buffer: [2 slots][world][bytes_per_rank] payload, then at
-// flag_offset [2 slots][world] int32 flags.
+// Layout of every rank's symmetric buffer: [2 slots][world][bytes_per_rank / 4] words of 8 bytes.
 __global__ void __launch_bounds__(kGatherThreads)
-gather_heads_kernel(const unsigned char *__restrict__ local, int bytes_per_rank, unsigned char *const *peer_bufs,
-                    long long flag_offset, int32_t *seq, int rank, int world, unsigned char *out,
-                    unsigned int timeout_us, int32_t *status) {
+gather_heads_kernel(const uint32_t *__restrict__ local, int words_per_rank, uint2 *const *peer_bufs,
+                    int32_t *seq, int rank, int world, uint32_t *out, unsigned int timeout_us, int32_t *status) {
     __shared__ int sh_timeout;
-    __shared__ int sh_missing[kGatherMaxWorld];
     const int tid = threadIdx.x;
+    if (tid == 0) trace_stamp(kTraceGather, 0, 0);
+    // the step counter was last written by this stream's previous gather, which is long complete
     const int s = *reinterpret_cast<volatile int32_t *>(seq);
     const int slot = s & 1;
-    const int tag = s + 1;
-    const size_t slot_bytes = (size_t)world * bytes_per_rank;
+    const uint32_t tag = (uint32_t)(s + 1);
+    const int total = words_per_rank * world;
+    const size_t slot_words = (size_t)total;
     if (tid == 0) sh_timeout = 0;
-    if (tid < kGatherMaxWorld) sh_missing[tid] = 0;
+    uint2 *dst0 = nullptr;
+    if (tid < total) dst0 = peer_bufs[tid / words_per_rank];   // first target of this thread, read early
+    __syncthreads();
+    griddep_wait();   // the rows come from the kernel before this one
+    if (tid == 0) trace_stamp(kTraceGather, 0, 2);
 
     // ---- push ---------------------------------------------------------------------------
-    const int vecs = bytes_per_rank / 16;
-    for (int i = tid; i < vecs * world; i += kGatherThreads) {
-        const int g = i / vecs, v = i % vecs;
-        const uint4 val = reinterpret_cast<const uint4 *>(local)[v];
-        uint4 *dst = reinterpret_cast<uint4 *>(peer_bufs[g] + slot * slot_bytes + (size_t)rank * bytes_per_rank);
-        dst[v] = val;
+    for (int i = tid; i < total; i += kGatherThreads) {
+        const int g = i / words_per_rank, w = i % words_per_rank;
+        uint2 *dst = (i == tid ? dst0 : peer_bufs[g]) + slot * slot_words + (size_t)rank * words_per_rank + w;
+        st_word_sys(dst, local[w], tag);
     }
-    __threadfence_system();
-    __syncthreads();
-    if (tid < world) {
-        int32_t *flags = reinterpret_cast<int32_t *>(peer_bufs[tid] + flag_offset);
-        st_release_sys(flags + slot * world + rank, tag);
-    }
+    if (tid == 0) trace_stamp(kTraceGather, 0, 3);
 
-    // ---- wait (bounded) -----------------------------------------------------------------
-    if (tid < world) {
-        const int32_t *mine = reinterpret_cast<const int32_t *>(peer_bufs[rank] + flag_offset) + slot * world + tid;
-        const unsigned long long deadline = global_timer_ns() + (unsigned long long)timeout_us * 1000ull;
-        while (ld_acquire_sys(mine) < tag) {
-            if (global_timer_ns() > deadline) {
-                sh_timeout = 1;
-                sh_missing[tid] = 1;
+    // ---- wait (bounded) and copy out ------------------------------------------------------
+    const uint2 *mine = peer_bufs[rank] + slot * slot_words;
+    const unsigned long long deadline = global_timer_ns() + (unsigned long long)timeout_us * 1000ull;
+    bool late = false;
+    for (int i = tid; i < total; i += kGatherThreads) {
+        uint2 v = ld_word_sys(mine + i);
+        while (v.y != tag) {
+            if (late || global_timer_ns() > deadline) {   // once late, the thread's other words get one look each
+                late = true;
+                v.x = ~0u;
                 break;
             }
-            __nanosleep(40);
+            __nanosleep(20);
+            v = ld_word_sys(mine + i);
         }
+        out[i] = v.x;
     }
+    if (late) sh_timeout = 1;
     __syncthreads();
-    if (sh_timeout && tid == 0) atomicOr(status, DA_STATUS_WAIT_TIMEOUT);
-
-    // ---- copy out (L2 loads: the rows were written by other GPUs) ----------------------------
-    const uint4 *src = reinterpret_cast<const uint4 *>(peer_bufs[rank] + slot * slot_bytes);
-    for (int i = tid; i < vecs * world; i += kGatherThreads) {
-        const uint4 v = sh_missing[i / vecs] ? make_uint4(~0u, ~0u, ~0u, ~0u) : __ldcg(src + i);
-        reinterpret_cast<uint4 *>(out)[i] = v;
+    if (tid == 0) {
+        if (sh_timeout) atomicOr(status, DA_STATUS_WAIT_TIMEOUT);
+        *seq = (int32_t)tag;
+        trace_stamp(kTraceGather, 0, 1);
     }
-    if (tid == 0) *seq = tag;
 }
 
 }  // namespace da
 
+DA_DEFINE_TRACE_SETTER(trace_set_gather)
+
 extern "C" size_t da_gather_heads_buffer_bytes(int bytes_per_rank, int world) {
     if (bytes_per_rank < 16 || world < 1 || world > da::kGatherMaxWorld) return 0;
-    return (size_t)2 * world * bytes_per_rank + (size_t)2 * world * sizeof(int32_t);
+    return (size_t)2 * world * 2 * bytes_per_rank;
 }
 
 extern "C" int da_gather_heads(const void *local, int bytes_per_rank, void *const *peer_buffers, int32_t *seq,
@@ -112,11 +117,11 @@ extern "C" int da_gather_heads(const void *local, int bytes_per_rank, void *cons
     if (world < 1 || world > da::kGatherMaxWorld || rank < 0 || rank >= world) return DA_ERR_SHAPE;
     if (bytes_per_rank < 16 || bytes_per_rank % 16 != 0 || timeout_us < 0) return DA_ERR_SHAPE;
     if ((reinterpret_cast<uintptr_t>(local) | reinterpret_cast<uintptr_t>(out)) & 15) return DA_ERR_ALIGN;
-    const long long flag_offset = (long long)2 * world * bytes_per_rank;
-    da::gather_heads_kernel<<<1, da::kGatherThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const unsigned char *>(local), bytes_per_rank,
-        reinterpret_cast<unsigned char *const *>(peer_buffers), flag_offset, seq, rank, world,
-        static_cast<unsigned char *>(out),
+    const cudaError_t e = da::launch_dependent(
+        da::gather_heads_kernel, dim3(1), dim3(da::kGatherThreads), (size_t)0, static_cast<cudaStream_t>(stream),
+        static_cast<const uint32_t *>(local), bytes_per_rank / 4, reinterpret_cast<uint2 *const *>(peer_buffers), seq,
+        rank, world, static_cast<uint32_t *>(out),
         timeout_us > 0 ? (unsigned int)timeout_us : da::kGatherDefaultTimeoutUs, status);
+    if (e != cudaSuccess) return (int)e;
     return (int)cudaGetLastError();
 }

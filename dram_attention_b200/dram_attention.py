@@ -4,6 +4,8 @@ hand-written sm_100a kernels."""
 
 from __future__ import annotations
 
+from typing import Optional
+
 import torch
 
 from . import _native
@@ -124,14 +126,23 @@ class DRAMAttention(torch.nn.Module):
         self._overlap_ok = {}
 
     # ---- forward ------------------------------------------------------------------
-    def forward(self, xq: torch.Tensor, xk: torch.Tensor, xv: torch.Tensor, *, start_pos, stage: str):
+    def forward(self, xq: torch.Tensor, xk: torch.Tensor, xv: torch.Tensor, *, start_pos, stage: str,
+                freqs_cis: Optional[torch.Tensor] = None):
         """xq (1, s, Hq, D), xk/xv (1, s, Hk, D).  `stage` is "prefill" (dense causal
         attention, then init_cache) or "generate" (one new token; start_pos is its
         absolute position, a Python int or an int32 CUDA tensor of shape (1,)).  Generate also
         takes s > 1 tokens (appended at start_pos .. start_pos + s - 1), as the reference does for
-        the unaligned tail of a prompt."""
+        the unaligned tail of a prompt.
+
+        `freqs_cis` (not in the reference's signature): when given, xq and xk are the caller's
+        projections BEFORE the rotary embedding and the operator applies it itself, in one launch
+        chained to the scorer (rotate_), instead of the caller's apply_rotary_emb
+        (evaluation/dram-attention/model.py:201).  Shape (s, D / 2) complex64, or (s, D / 2, 2)
+        float32 (cos, sin), on the device: the rows of the call's positions."""
         bsz, seqlen, H, D = xq.shape
         assert bsz == 1, "Only support batch size 1"
+        if freqs_cis is not None:
+            xq, xk = self.rotate_(xq, xk, freqs_cis)
         if stage == "prefill":
             output = self._prefill_attention(xq, xk, xv)
             self.init_cache(xk, xv)
@@ -140,6 +151,26 @@ class DRAMAttention(torch.nn.Module):
             return self._generate(xq, xk, xv, start_pos)
         else:
             raise RuntimeError(f"Unsupported stage: {stage}")
+
+    def rotate_(self, xq: torch.Tensor, xk: torch.Tensor, freqs_cis: torch.Tensor):
+        """Enqueue the rotary embedding of xq (1, s, Hq, D) and xk (1, s, Hk, D) with freqs_cis
+        (s, D / 2) and return the rotated pair (new tensors).  Same arithmetic as the reference
+        caller's apply_rotary_emb (evaluation/dram-attention/model.py:125-135)."""
+        _native.require_cuda(xq, "xq")
+        bsz, seqlen, n_q_heads, D = xq.shape
+        assert xk.shape[:2] == xq.shape[:2] and xk.shape[3] == D and xk.dtype == xq.dtype and D % 2 == 0
+        f = torch.view_as_real(freqs_cis) if freqs_cis.is_complex() else freqs_cis
+        assert f.dtype == torch.float32 and tuple(f.shape) == (seqlen, D // 2, 2), \
+            f"freqs_cis must be ({seqlen}, {D // 2}) complex64, got {tuple(freqs_cis.shape)} {freqs_cis.dtype}"
+        f = f if f.is_contiguous() else f.contiguous()
+        xq = xq if xq.is_contiguous() else xq.contiguous()
+        xk = xk if xk.is_contiguous() else xk.contiguous()
+        with torch.cuda.device(xq.device):
+            q_out, k_out = torch.empty_like(xq), torch.empty_like(xk)
+            _native.check(_native.lib().da_rope_qk(
+                xq.data_ptr(), xk.data_ptr(), f.data_ptr(), q_out.data_ptr(), k_out.data_ptr(), bsz * seqlen,
+                n_q_heads, xk.shape[2], D, _native.dtype_code(xq.dtype), _native.stream_ptr()), "da_rope_qk")
+        return q_out, k_out
 
     def _prefill_attention(self, xq, xk, xv):
         """Dense causal attention of the prompt (the reference calls a third-party library

@@ -124,9 +124,10 @@ class KVHeadShardedDRAMAttention(torch.nn.Module):
     def init_cache(self, k_cache: torch.Tensor, v_cache: torch.Tensor):
         self.inner.init_cache(self._kv(k_cache), self._kv(v_cache))
 
-    def forward(self, xq, xk, xv, *, start_pos, stage: str):
+    def forward(self, xq, xk, xv, *, start_pos, stage: str, freqs_cis=None):
+        extra = {} if freqs_cis is None else {"freqs_cis": freqs_cis}   # rotary embedding inside the call
         local = self.inner(self._q(xq).contiguous(), self._kv(xk).contiguous(), self._kv(xv).contiguous(),
-                           start_pos=start_pos, stage=stage)
+                           start_pos=start_pos, stage=stage, **extra)
         return self.all_gather_heads(local)
 
     def all_gather_heads(self, local: torch.Tensor) -> torch.Tensor:

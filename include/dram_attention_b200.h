@@ -71,11 +71,12 @@ DA_API const char *da_error_string(int code);
  * Profiling switch (no counterpart in the reference).  While a buffer of da_trace_bytes() bytes
  * of device memory is set, thread 0 of every CTA of every kernel of this library writes the
  * GPU's global nanosecond timer into it at a few points: the buffer is
- * [5 kernels][1024 CTAs (index modulo)][4 events] of uint64, kernels 0 = page scorer,
- * 1 = selection, 2 = LRU update, 3 = attention (single launch or phase 1), 4 = attention phase 2;
- * events 0 = the CTA is on its SM, 1 = it is done, and for selection and LRU update 2 = the
- * kernel before it in the stream has finished (they are launched early and wait), for the
- * attention 2 = its warps are through their units, 3 = its ticket is taken.  A launch overwrites
+ * [6 kernels][1024 CTAs (index modulo)][4 events] of uint64, kernels 0 = page scorer,
+ * 1 = selection, 2 = LRU update, 3 = attention (single launch or phase 1), 4 = attention phase 2,
+ * 5 = gather of the head shards; events 0 = the CTA is on its SM, 1 = it is done, and for
+ * selection, LRU update and gather 2 = the kernel before it in the stream has finished (they
+ * are launched early and wait), for the attention 2 = its warps are through their units, 3 = its
+ * ticket is taken, for the gather 3 = its rows are sent.  A launch overwrites
  * the stamps of the launch before it, so after a step the buffer holds that step's time line,
  * including the kernels that ran side by side on different streams.  da_trace_set(NULL)
  * switches it off (the default).  Applies to the current device; call it outside stream capture.
@@ -432,6 +433,25 @@ DA_API int da_build_pages(const void *k, const void *v,
                    int dtype, da_stream_t stream);
 
 /*
+ * Rotary position embedding of the new queries and keys: the caller-side step in front of the
+ * operator call, apply_rotary_emb (evaluation/dram-attention/model.py:125-135, called at :201;
+ * freqs_cis as precompute_freqs_cis :105-114 makes it and Transformer.forward slices it to the
+ * call's positions).  Adjacent channels (2i, 2i+1) of every head are one complex number that
+ * is multiplied by freqs_cis[token][i]; fp32 arithmetic with each product and the sum rounded
+ * once, as a complex64 multiply, then rounding to the tensors' type.  One launch for q and k
+ * of all tokens of the call, chained to the launch after it (the page scorer) by a programmatic
+ * dependent launch.
+ *
+ * q, q_out     (n_tokens, n_q_heads, head_dim) contiguous
+ * k, k_out     (n_tokens, n_kv_heads, head_dim) contiguous (q_out may be q, k_out may be k)
+ * freqs_cis    (n_tokens, head_dim / 2) pairs of float32 (cos, sin) = complex64
+ * All pointers 8-byte aligned, head_dim even.
+ */
+DA_API int da_rope_qk(const void *q, const void *k, const void *freqs_cis, void *q_out, void *k_out,
+                      int n_tokens, int n_q_heads, int n_kv_heads, int head_dim, int dtype,
+                      da_stream_t stream);
+
+/*
  * Dense causal attention of the prompt: replaces the flash_attn_func call of the prefill
  * stage (dram_attention/dram_attention.py:136) for 16-bit element types and head_dim 128.
  * tcgen05 tensor-core kernel (operands by TMA into shared memory, accumulators in tensor
@@ -457,13 +477,16 @@ DA_API int da_prefill_attention(const void *q, const void *k, const void *v, voi
  * sharding on the GPUs of one node (no counterpart in the reference, which runs on one
  * GPU; it replaces the library all-gather that would otherwise follow the attention
  * launch).  One launch of one CTA: the rank's rows are stored into every rank's gather
- * buffer, one flag per peer is released, the CTA waits until every source rank's flag for
- * this step is set in its own buffer, copies the assembled block to `out` and advances *seq.
+ * buffer as 8-byte words {4 bytes of payload, tag = *seq + 1} (one aligned store each, so a
+ * word that carries the tag carries its payload; no fence or flag round follows), the CTA
+ * waits until every word of its own buffer carries this step's tag, copies the payload to
+ * `out` and advances *seq.  The kernel is launched as a programmatic dependent of the kernel
+ * before it in the stream and waits for it on the device before it reads `local`.
  * The wait is bounded by the GPU's timer: after timeout_us microseconds (0 = the default,
- * 200 000) the kernel sets DA_STATUS_WAIT_TIMEOUT in *status, fills the rows of every rank
- * whose flag did not come with 0xFF bytes (NaN in every floating-point format) and returns:
- * nothing hangs, and a gather that timed out cannot be mistaken for a result.  The caller
- * has to look at *status (between steps; it is sticky).
+ * 200 000) the kernel sets DA_STATUS_WAIT_TIMEOUT in *status, writes 0xFF bytes (NaN in every
+ * floating-point format) for what did not come and returns: nothing hangs, and a gather that
+ * timed out cannot be mistaken for a result.  The caller has to look at *status (between
+ * steps; it is sticky).
  *
  * local         bytes_per_rank bytes, device memory, 16-byte aligned (this rank's rows)
  * peer_buffers  DEVICE array of `world` pointers; entry g = rank g's gather buffer of

@@ -34,6 +34,26 @@ import torch
 # Page summaries and the Quest upper-bound page score
 # --------------------------------------------------------------------------
 
+def rope_qk(xq: torch.Tensor, xk: torch.Tensor, freqs_cis: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The caller's rotary embedding in front of the operator call
+    (evaluation/dram-attention/model.py:125-135): channels (2i, 2i+1) of every head as a
+    complex number times freqs_cis[token, i], in float32, rounded to the input type.
+    xq (1, s, Hq, D), xk (1, s, Hk, D), freqs_cis (s, D/2) complex64.  Written out on the real
+    and imaginary parts with numpy float32 arrays, so every product and the sum round once."""
+    f = torch.view_as_real(freqs_cis).numpy().astype(np.float32)      # (s, D/2, 2)
+    c, sn = f[None, :, None, :, 0], f[None, :, None, :, 1]
+
+    def rot(x: torch.Tensor) -> torch.Tensor:
+        a = x.float().numpy().reshape(*x.shape[:-1], -1, 2)
+        x0, x1 = a[..., 0], a[..., 1]
+        re = (x0 * c).astype(np.float32) - (x1 * sn).astype(np.float32)
+        im = (x0 * sn).astype(np.float32) + (x1 * c).astype(np.float32)
+        out = np.stack([re, im], axis=-1).reshape(x.shape).astype(np.float32)
+        return torch.from_numpy(out).to(x.dtype)
+
+    return rot(xq), rot(xk)
+
+
 def page_minmax(k_cache: torch.Tensor, num_pages: int) -> torch.Tensor:
     """Per-page, per-channel min and max of the keys.
 

@@ -21,6 +21,9 @@ Outputs (all small .npz files, committed):
                       head layouts, the ones the reference's selector accepts with more than
                       one token (its `view` after `swapaxes`, topk_selector.py:52-55, needs
                       one KV head or a GQA group of one; anything else raises there).
+  rope_values.npz     the rotary embedding of the reference's caller
+                      (evaluation/dram-attention/model.py: precompute_freqs_cis, apply_rotary_emb)
+                      on float32 and bfloat16 queries and keys at scattered positions.
 """
 
 from __future__ import annotations
@@ -222,8 +225,36 @@ def multi_traj(ref, hq, hk):
     print("multi-token trajectory: out", res["out"].shape, "lists", [l.shape for l in lists])
 
 
+def rope_values(ref):
+    """apply_rotary_emb of the reference's model file, float32 and bfloat16."""
+    import importlib.util
+    from oracle.ref_harness import REFERENCE_ROOT
+    spec = importlib.util.spec_from_file_location(
+        "ref_caller_model", os.path.join(REFERENCE_ROOT, "evaluation", "dram-attention", "model.py"))
+    model = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(model)
+    g = torch.Generator().manual_seed(7)
+    hq, hk, d, s = 8, 2, 128, 5
+    freqs_all = model.precompute_freqs_cis(d, 200000, 500000.0)
+    pos = torch.tensor([0, 1, 4097, 131071, 199999])
+    freqs = freqs_all[pos]
+    res = dict(pos=pos.numpy(), freqs=torch.view_as_real(freqs).numpy())
+    for name, dt in (("f32", torch.float32), ("bf16", torch.bfloat16)):
+        xq = torch.randn(1, s, hq, d, generator=g).to(dt)
+        xk = (torch.randn(1, s, hk, d, generator=g) * 3).to(dt)
+        oq, ok = model.apply_rotary_emb(xq, xk, freqs_cis=freqs)
+        assert oq.dtype == dt and ok.dtype == dt
+        as_np = (lambda t: t.numpy()) if dt == torch.float32 else (lambda t: t.view(torch.int16).numpy())
+        res.update({f"xq_{name}": as_np(xq), f"xk_{name}": as_np(xk), f"oq_{name}": as_np(oq), f"ok_{name}": as_np(ok)})
+    np.savez_compressed(os.path.join(HERE, "rope_values.npz"), **res)
+    print("rope values:", {k: v.shape for k, v in res.items()})
+
+
 if __name__ == "__main__":
     with reference_on_cpu() as ref:
+        if "--only-rope" in sys.argv:
+            rope_values(ref)
+            sys.exit(0)
         if "--only-multi" in sys.argv:
             multi_traj(ref, 4, 1)
             multi_traj(ref, 2, 2)
@@ -234,6 +265,7 @@ if __name__ == "__main__":
         plumbing_traj(ref)
         multi_traj(ref, 4, 1)
         multi_traj(ref, 2, 2)
+        rope_values(ref)
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")

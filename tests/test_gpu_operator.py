@@ -434,6 +434,45 @@ def test_multi_token_generate_against_oracle(da, dtype, counts):
     m.check_status()
 
 
+def test_rotary_embedding_inside_the_call(da, fused):
+    """`freqs_cis=` makes the operator apply the caller's rotary embedding itself: the outputs,
+    the appended keys and the tables equal those of a twin that is handed the rotated tensors (the
+    oracle's rotation), eagerly and with the steps captured in a graph."""
+    dtype = torch.bfloat16
+    n = 6
+    w = llama_layer_workload(seed=9, steps=n, dram_tokens=8192, n_kv_heads=2, lru=4096, local=256,
+                             top_k=256, needles=2, dtype=dtype)
+    ms = [da.DRAMAttention(device=DEV, dtype=dtype, **w.ctor_kwargs()) for _ in range(2)]
+    for m in ms:
+        m.init_cache(w.k.to(DEV), w.v.to(DEV))
+    S = w.k.shape[1]
+    d = w.xq.shape[-1]
+    inv = 1.0 / (500000.0 ** (torch.arange(0, d, 2).float() / d))
+    freqs = [torch.polar(torch.ones(1, d // 2), (float(S + i) * inv)[None]) for i in range(n)]
+    dq, dk, dv = w.xq.to(DEV), w.xk.to(DEV), w.xv.to(DEV)
+    fdev = [f.to(DEV) for f in freqs]
+    rot = [orc.rope_qk(w.xq[i], w.xk[i], freqs[i]) for i in range(n)]
+    outs = []
+    for i in range(3):
+        a = ms[0](dq[i], dk[i], dv[i], start_pos=S + i, stage="generate", freqs_cis=fdev[i])
+        b = ms[1](rot[i][0].to(DEV), rot[i][1].to(DEV), dv[i], start_pos=S + i, stage="generate")
+        assert torch.equal(a, b), i
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        outs = [ms[0](dq[i], dk[i], dv[i], start_pos=S + i, stage="generate", freqs_cis=fdev[i]) for i in range(3, n)]
+    g.replay()
+    torch.cuda.synchronize()
+    for j, i in enumerate(range(3, n)):
+        b = ms[1](rot[i][0].to(DEV), rot[i][1].to(DEV), dv[i], start_pos=S + i, stage="generate")
+        assert torch.equal(outs[j], b), i
+    t = S + n - ms[0].dram_kv_cache_size
+    assert torch.equal(ms[0].cache_k[0, :t], ms[1].cache_k[0, :t])
+    assert torch.equal(ms[0].lru_cache.hbm_page_to_dram_page_mapping, ms[1].lru_cache.hbm_page_to_dram_page_mapping)
+    for m in ms:
+        m.check_status()
+
+
 # ---- the reference's operator API tests (dram_attention/dram_attention_test.py) ----
 
 @pytest.fixture

@@ -548,19 +548,59 @@ def test_decode_attention_bad_position_is_reported(da):
     assert float(lk.abs().sum()) == 0  # nothing appended outside the window
 
 
+# -------------------------------------------------------------------- rope ----
+
+@pytest.mark.parametrize("name", ["f32", "bf16"])
+def test_rope_kernel_matches_reference_caller(da, golden_dir, name):
+    """da_rope_qk against the outputs of the reference caller's apply_rotary_emb (fixture made by
+    running it), bit for bit, out of place and in place."""
+    from dram_attention_b200 import _native
+    from tests.test_oracle_golden import _rope_case, _load
+    xq, xk, freqs, want_q, want_k = _rope_case(_load(golden_dir, "rope_values.npz"), name)
+    lib = _native.lib()
+    q, k = xq.to(DEV).contiguous(), xk.to(DEV).contiguous()
+    f = torch.view_as_real(freqs).contiguous().to(DEV)
+    oq, ok = torch.zeros_like(q), torch.zeros_like(k)
+    s, hq, hk, d = q.shape[1], q.shape[2], k.shape[2], q.shape[3]
+    code = _native.dtype_code(q.dtype)
+    _native.check(lib.da_rope_qk(q.data_ptr(), k.data_ptr(), f.data_ptr(), oq.data_ptr(), ok.data_ptr(), s, hq, hk, d,
+                                 code, _native.stream_ptr()))
+    torch.cuda.synchronize()
+    assert torch.equal(oq.cpu(), want_q) and torch.equal(ok.cpu(), want_k)
+    _native.check(lib.da_rope_qk(q.data_ptr(), k.data_ptr(), f.data_ptr(), q.data_ptr(), k.data_ptr(), s, hq, hk, d,
+                                 code, _native.stream_ptr()))
+    torch.cuda.synchronize()
+    assert torch.equal(q.cpu(), want_q) and torch.equal(k.cpu(), want_k)
+    # the oracle's statement at a shape of its own (odd head counts, 1 token, fp16)
+    g = _g(5)
+    xq2, xk2 = torch.randn(1, 1, 3, 64, generator=g).half(), torch.randn(1, 1, 1, 64, generator=g).half()
+    ang = torch.rand(1, 32, generator=g) * 6.0
+    fr = torch.polar(torch.ones_like(ang), ang)
+    wq, wk = orc.rope_qk(xq2, xk2, fr)
+    q2, k2 = xq2.to(DEV), xk2.to(DEV)
+    f2 = torch.view_as_real(fr).contiguous().to(DEV)
+    _native.check(lib.da_rope_qk(q2.data_ptr(), k2.data_ptr(), f2.data_ptr(), q2.data_ptr(), k2.data_ptr(), 1, 3, 1, 64,
+                                 _native.dtype_code(torch.float16), _native.stream_ptr()))
+    torch.cuda.synchronize()
+    assert torch.equal(q2.cpu(), wq) and torch.equal(k2.cpu(), wk)
+    assert lib.da_rope_qk(q2.data_ptr(), k2.data_ptr(), f2.data_ptr(), q2.data_ptr(), k2.data_ptr(), 1, 3, 1, 63,
+                          _native.dtype_code(torch.float16), _native.stream_ptr()) == -2
+
+
 # ------------------------------------------------------------------ gather ----
 
 def test_gather_wait_runs_out_and_is_reported(da):
     """The all-gather kernel of the KV-head sharding with a peer that never shows up (rank 0 of 2
-    on one GPU, nothing sets rank 1's flag): the kernel returns after its time budget, reports
+    on one GPU, nothing writes rank 1's words): the kernel returns after its time budget, reports
     DA_STATUS_WAIT_TIMEOUT, marks the missing rank's rows with NaN, and the context stays usable;
-    when the peer's rows and flag are there (written by hand, as its stores would) the next call
+    when the peer's words are there (written by hand, as its stores would) the next call
     succeeds."""
     from dram_attention_b200 import _native
     lib = _native.lib()
     world, nbytes = 2, 4 * 128 * 2
+    words = nbytes // 4
     total = lib.da_gather_heads_buffer_bytes(nbytes, world)
-    assert total == 2 * world * nbytes + 2 * world * 4
+    assert total == 2 * world * 2 * nbytes
     bufs = [torch.zeros(total, dtype=torch.uint8, device=DEV) for _ in range(world)]
     ptrs = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device=DEV)
     seq = torch.zeros(1, dtype=torch.int32, device=DEV)
@@ -579,16 +619,16 @@ def test_gather_wait_runs_out_and_is_reported(da):
     assert torch.equal(out[:4], local)
     assert bool(torch.isnan(out[4:].float()).all())     # nobody can take these rows for a result
     assert int(seq) == 1
-    # rank 0's own rows went into both buffers, its flag (step 1 -> tag 1, slot 0) into both
-    flags1 = bufs[1][2 * world * nbytes:].view(torch.int32)
-    assert int(flags1[0 * world + 0]) == 1
-    assert torch.equal(bufs[1][:nbytes].view(torch.bfloat16).view(4, 128), local)
+    # rank 0's own rows went into both buffers as {payload, tag 1} words of slot 0, rank 0's place
+    sent = bufs[1].view(torch.int32).view(2, world, words, 2)
+    assert bool((sent[0, 0, :, 1] == 1).all()) and bool((sent[0, 1] == 0).all()) and bool((sent[1] == 0).all())
+    assert torch.equal(sent[0, 0, :, 0].contiguous().view(torch.bfloat16).view(4, 128), local)
     # the peer shows up for the next step (seq 1 -> slot 1, tag 2)
     status.zero_()
     peer_rows = torch.randn(4, 128, generator=g).bfloat16().to(DEV)
-    slot_bytes = world * nbytes
-    bufs[0][1 * slot_bytes + 1 * nbytes:1 * slot_bytes + 2 * nbytes] = peer_rows.view(torch.uint8).view(-1)
-    bufs[0][2 * world * nbytes:].view(torch.int32)[1 * world + 1] = 2
+    mine = bufs[0].view(torch.int32).view(2, world, words, 2)
+    mine[1, 1, :, 0] = peer_rows.view(torch.int32).view(-1)
+    mine[1, 1, :, 1] = 2
     local2 = torch.randn(4, 128, generator=g).bfloat16().to(DEV)
     _native.check(lib.da_gather_heads(local2.data_ptr(), nbytes, ptrs.data_ptr(), seq.data_ptr(), 0, world,
                                       out.data_ptr(), 2000, status.data_ptr(), _native.stream_ptr()))

@@ -213,3 +213,23 @@ def test_multi_token_generate_matches_reference(golden_dir, heads):
         a += c
     assert np.array_equal(m.lru_cache.d2h, g["d2h_final"])
     assert np.array_equal(m.cache_k.numpy(), g["cache_k"])
+
+
+def _rope_case(g, name):
+    """(xq, xk, freqs, want_q, want_k) of the rope fixture in its own dtype."""
+    freqs = torch.view_as_complex(torch.from_numpy(g["freqs"]).contiguous())
+    if name == "f32":
+        conv = lambda a: torch.from_numpy(a)
+    else:
+        conv = lambda a: torch.from_numpy(a).view(torch.bfloat16)
+    return (conv(g[f"xq_{name}"]), conv(g[f"xk_{name}"]), freqs, conv(g[f"oq_{name}"]), conv(g[f"ok_{name}"]))
+
+
+@pytest.mark.parametrize("name", ["f32", "bf16"])
+def test_rope_matches_reference_caller(golden_dir, name):
+    """The rotary embedding in front of the operator call, as the reference's model file applies
+    it (precompute_freqs_cis rows at scattered positions up to 199 999): bit for bit."""
+    xq, xk, freqs, want_q, want_k = _rope_case(_load(golden_dir, "rope_values.npz"), name)
+    got_q, got_k = orc.rope_qk(xq, xk, freqs)
+    assert got_q.dtype == xq.dtype
+    assert torch.equal(got_q, want_q) and torch.equal(got_k, want_k)
