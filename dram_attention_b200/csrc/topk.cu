@@ -1,7 +1,8 @@
 // Per-query-head top-k page selection: radix select on order-preserving 32-bit
 // keys, exact lowest-index tie-break, then the k survivors are ranked by
-// (score descending, page id ascending).  One CTA per (token, query head) row;
-// the result is written straight into the per-KV-head page list.
+// (score descending, page id ascending).  One CTA per (token, query head) row, or a cluster of
+// four CTAs for rows of more than 16 384 pages; the result is written straight into the
+// per-KV-head page list.
 
 #include "da_common.cuh"
 
@@ -115,21 +116,52 @@ __device__ __forceinline__ void descending_crossing(const int *hist, int need, i
     }
 }
 
-template <int IPT>
-__global__ void __launch_bounds__(kTopkThreads)
-topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_list, int n_kv_heads, int rep,
-                  int n_pages, int k) {
-    if (threadIdx.x == 0) trace_stamp(1, blockIdx.x, 0);
-    // on whichever path the kernel leaves: thread 0's end stamp
-    struct EndStamp {
-        __device__ ~EndStamp() {
-            if (threadIdx.x == 0) trace_stamp(1, blockIdx.x, 1);
+// Orders m candidates (composite keys: ~score key in the high word, page id in the low word, so that
+// ascending composite order is score descending, page id ascending): rank = number of smaller
+// composite keys; the first k leave.  The candidate array is read two entries per 128-bit load; with
+// m odd the pad entry is the largest possible key and counts for nobody.  `rank` is scratch of m ints.
+__device__ __forceinline__ void rank_candidates(unsigned long long *cand, int *rank, int m, int k,
+                                                int32_t *__restrict__ dst, int tid) {
+    for (int e = tid; e < m; e += kTopkThreads) rank[e] = 0;
+    if (tid == 0 && (m & 1)) cand[m] = ~0ull;
+    __syncthreads();
+    {
+        // with m < 1024 the comparisons of one element are split over several threads
+        const int n_pairs = (m + 1) >> 1;
+        int segs = kTopkThreads / m;
+        if (segs < 1) segs = 1;
+        const int per_sweep = kTopkThreads / segs;
+        const int seg_pairs = (n_pairs + segs - 1) / segs;
+        const ulonglong2 *pairs = reinterpret_cast<const ulonglong2 *>(cand);
+        for (int e0 = 0; e0 < m; e0 += per_sweep) {
+            const int e = e0 + tid % per_sweep;
+            const int seg = tid / per_sweep;
+            if (e < m && seg < segs) {
+                const unsigned long long v = cand[e];
+                const int j0 = seg * seg_pairs;
+                const int j1 = min(n_pairs, j0 + seg_pairs);
+                int c = 0;
+#pragma unroll 4
+                for (int j = j0; j < j1; ++j) {
+                    const ulonglong2 w = pairs[j];
+                    c += (w.x < v) + (w.y < v);
+                }
+                if (c) atomicAdd(&rank[e], c);
+            }
         }
-    } end_stamp;
-    griddep_wait();                // the scores come from the kernel before this one
-    if (threadIdx.x == 0) trace_stamp(1, blockIdx.x, 2);
-    griddep_launch_dependents();   // the LRU update may move onto the SMs and wait there
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    }
+    __syncthreads();
+    for (int e = tid; e < m; e += kTopkThreads) {
+        const int rk = rank[e];
+        if (rk < k) dst[rk] = (int32_t)(cand[e] & 0xffffffffu);
+    }
+}
+
+// One row, one CTA: the whole selection.  `dst` receives the k page ids in (score descending,
+// page id ascending) order.
+template <int IPT>
+__device__ __forceinline__ void topk_row(const float *__restrict__ srow, int n_pages, int k, int32_t *__restrict__ dst,
+                                         unsigned char *smem_raw) {
     const int cap = topk_candidate_capacity(k);
     unsigned long long *cand = reinterpret_cast<unsigned long long *>(smem_raw);  // [cap + 2]
     int *rank = reinterpret_cast<int *>(cand + cap + 2);                          // [cap]
@@ -139,11 +171,6 @@ topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_l
     __shared__ uint32_t sh_kmin, sh_kmax;
     __shared__ int above_of[256];   // linear level 1: candidates in higher buckets, per bucket
 
-    const int row = blockIdx.x;  // (token * n_kv_heads + hk) * rep + r
-    const int r = row % rep;
-    const int hk = (row / rep) % n_kv_heads;
-    const int tok = row / (rep * n_kv_heads);
-    const float *srow = scores + (size_t)row * n_pages;
     const int tid = threadIdx.x;
     const int lane = tid & 31;
     const int warp = tid >> 5;
@@ -281,9 +308,6 @@ topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_l
     }
     // Without the early exit: prefix = key of the k-th largest; `need` of the `count_eq` keys equal
     // to it are taken.  With it: every key whose masked bits are >= prefix is a candidate.
-    const int n_tokens = gridDim.x / (n_kv_heads * rep);
-    int32_t *dst = page_list + (size_t)hk * n_tokens * rep * k + (size_t)(tok * rep + r) * k;
-
     if (lin_levels == 1) {
         // ---- candidates sorted by bucket as they are gathered, then ranked inside their bucket ----
         // Bucket b's candidates go to cand[above_of[b] ...] (a counter per bucket hands out the
@@ -382,44 +406,246 @@ topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_l
     }
     __syncthreads();
 
-    // ---- order the m candidates: rank = number of smaller composite keys; the first k leave ----
-    // The candidate array is read two entries per 128-bit load; with m odd the pad entry is
-    // the largest possible key and counts for nobody.
-    for (int e = tid; e < m; e += kTopkThreads) rank[e] = 0;
-    if (tid == 0 && (m & 1)) cand[m] = ~0ull;
-    __syncthreads();
-    {
-        // with m < 1024 the comparisons of one element are split over several threads
-        const int n_pairs = (m + 1) >> 1;
-        int segs = kTopkThreads / m;
-        if (segs < 1) segs = 1;
-        const int per_sweep = kTopkThreads / segs;
-        const int seg_pairs = (n_pairs + segs - 1) / segs;
-        const ulonglong2 *pairs = reinterpret_cast<const ulonglong2 *>(cand);
-        for (int e0 = 0; e0 < m; e0 += per_sweep) {
-            const int e = e0 + tid % per_sweep;
-            const int seg = tid / per_sweep;
-            if (e < m && seg < segs) {
-                const unsigned long long v = cand[e];
-                const int j0 = seg * seg_pairs;
-                const int j1 = min(n_pairs, j0 + seg_pairs);
-                int c = 0;
-#pragma unroll 4
-                for (int j = j0; j < j1; ++j) {
-                    const ulonglong2 w = pairs[j];
-                    c += (w.x < v) + (w.y < v);
-                }
-                if (c) atomicAdd(&rank[e], c);
-            }
-        }
-    }
-    __syncthreads();
-    for (int e = tid; e < m; e += kTopkThreads) {
-        const int rk = rank[e];
-        if (rk < k) dst[rk] = (int32_t)(cand[e] & 0xffffffffu);
-    }
+    rank_candidates(cand, rank, m, k, dst, tid);
 }
 
+// Where row `row` of the launch ((token * n_kv_heads + hk) * rep + r) goes in the per-KV-head page list.
+__device__ __forceinline__ int32_t *row_destination(int32_t *page_list, int row, int rows, int n_kv_heads, int rep, int k) {
+    const int r = row % rep;
+    const int hk = (row / rep) % n_kv_heads;
+    const int tok = row / (rep * n_kv_heads);
+    const int n_tokens = rows / (n_kv_heads * rep);
+    return page_list + (size_t)hk * n_tokens * rep * k + (size_t)(tok * rep + r) * k;
+}
+
+template <int IPT>
+__global__ void __launch_bounds__(kTopkThreads)
+topk_pages_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_list, int n_kv_heads, int rep,
+                  int n_pages, int k) {
+    if (threadIdx.x == 0) trace_stamp(1, blockIdx.x, 0);
+    // on whichever path the kernel leaves: thread 0's end stamp
+    struct EndStamp {
+        __device__ ~EndStamp() {
+            if (threadIdx.x == 0) trace_stamp(1, blockIdx.x, 1);
+        }
+    } end_stamp;
+    griddep_wait();                // the scores come from the kernel before this one
+    if (threadIdx.x == 0) trace_stamp(1, blockIdx.x, 2);
+    griddep_launch_dependents();   // the LRU update may move onto the SMs and wait there
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int row = blockIdx.x;
+    topk_row<IPT>(scores + (size_t)row * n_pages, n_pages, k,
+                  row_destination(page_list, row, gridDim.x, n_kv_heads, rep, k), smem_raw);
+}
+
+// ---- long rows: one row per cluster of kTopkCluster CTAs ---------------------------------------
+// A single CTA spends its time walking the row (64 keys per thread at 65 536 pages, several
+// sweeps).  Here every CTA of a cluster keeps a quarter of the row in registers (16 keys per
+// thread); the row's value range and the bucket counts are summed over the cluster through
+// distributed shared memory, every CTA finds the same threshold bucket, and the candidates of
+// all CTAs meet in CTA 0's shared memory (remote atomics hand out the places), where they are
+// ranked as in the one-CTA kernel.  Rows that the two linear levels cannot resolve (extreme
+// outliers, massive ties, a constant row) fall back to the one-CTA selection, run by CTA 0.
+constexpr int kTopkCluster = 4;
+constexpr int kTopkClusterIpt = 16;
+constexpr int kTopkClusterMaxPages = kTopkCluster * kTopkClusterIpt * kTopkThreads;   // 65 536
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// address of the same shared-memory variable in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t dsmem_addr(const void *local, uint32_t rank) {
+    uint32_t a = smem_addr(local), r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ int dsmem_ld_s32(uint32_t addr) {
+    int v;
+    asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ int dsmem_atomic_add_s32(uint32_t addr, int v) {
+    int old;
+    asm volatile("atom.shared::cluster.add.s32 %0, [%1], %2;" : "=r"(old) : "r"(addr), "r"(v) : "memory");
+    return old;
+}
+__device__ __forceinline__ void dsmem_st_u64(uint32_t addr, unsigned long long v) {
+    asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(addr), "l"(v) : "memory");
+}
+
+__global__ void __launch_bounds__(kTopkThreads)
+topk_pages_cluster_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_list, int n_kv_heads, int rep,
+                          int n_pages, int k) {
+    if (threadIdx.x == 0) trace_stamp(1, blockIdx.x, 0);
+    struct EndStamp {
+        __device__ ~EndStamp() {
+            if (threadIdx.x == 0) trace_stamp(1, blockIdx.x, 1);
+        }
+    } end_stamp;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int cap = topk_candidate_capacity(k);
+    unsigned long long *cand = reinterpret_cast<unsigned long long *>(smem_raw);  // [cap + 2], used in CTA 0
+    int *rank = reinterpret_cast<int *>(cand + cap + 2);                          // [cap]
+    __shared__ int hist[2][256];      // this CTA's bucket counts of level 1 and level 2
+    __shared__ int total[256];        // the cluster's counts of the level at hand
+    __shared__ int above_of[256];     // level 1: candidates in higher buckets, per bucket
+    __shared__ int fill[256];         // CTA 0: places handed out per bucket (level 1) / in all ([0], level 2)
+    __shared__ uint32_t sh_kmin, sh_kmax;
+    __shared__ int sh_digit, sh_above, sh_count;
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const uint32_t crank = cluster_ctarank();
+    const int row = blockIdx.x / kTopkCluster;
+    const int rows = gridDim.x / kTopkCluster;
+    const float *srow = scores + (size_t)row * n_pages;
+    int32_t *dst = row_destination(page_list, row, rows, n_kv_heads, rep, k);
+    // this CTA's part of the row: `per` pages from `base` (a multiple of 4 pages, so that every part starts aligned)
+    const int per = (((n_pages + kTopkCluster - 1) / kTopkCluster) + 3) & ~3;
+    const int base = min((int)crank * per, n_pages);
+    const int n_mine = min(per, n_pages - base);
+
+    if (tid < 256) {
+        hist[0][tid] = 0;
+        hist[1][tid] = 0;
+        fill[tid] = 0;
+    }
+    if (tid == 0) {
+        sh_kmin = 0xffffffffu;
+        sh_kmax = 0u;
+    }
+    griddep_wait();                // the scores come from the kernel before this one
+    if (tid == 0) trace_stamp(1, blockIdx.x, 2);
+    griddep_launch_dependents();   // the LRU update may move onto the SMs and wait there
+    RowKeys<kTopkClusterIpt> keys;
+    keys.load(srow + base, n_mine, tid);
+    __syncthreads();
+
+    // ---- the row's value range ------------------------------------------------------------------
+    {
+        uint32_t kmn = 0xffffffffu, kmx = 0u;
+        keys.for_each(srow + base, n_mine, tid, [&](int, uint32_t key, bool valid) {
+            if (valid) {
+                kmn = min(kmn, key);
+                kmx = max(kmx, key);
+            }
+        });
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            kmn = min(kmn, __shfl_xor_sync(DA_FULL_MASK, kmn, off));
+            kmx = max(kmx, __shfl_xor_sync(DA_FULL_MASK, kmx, off));
+        }
+        if (lane == 0) {
+            atomicMin(&sh_kmin, kmn);
+            atomicMax(&sh_kmax, kmx);
+        }
+    }
+    cluster_sync_all();   // every CTA's range (and its cleared counters) can be read
+    uint32_t gmin = 0xffffffffu, gmax = 0u;
+#pragma unroll
+    for (uint32_t c = 0; c < kTopkCluster; ++c) {
+        gmin = min(gmin, (uint32_t)dsmem_ld_s32(dsmem_addr(&sh_kmin, c)));
+        gmax = max(gmax, (uint32_t)dsmem_ld_s32(dsmem_addr(&sh_kmax, c)));
+    }
+    const float lo = key_score(gmin), hi = key_score(gmax);
+    const float width = hi - lo;
+    int lin_levels = 0, lin_b = 0, lin_b2 = 0, lin_m = 0;
+    const float lin_lo = lo, lin_scale = 256.f / width;
+    float lin_lo2 = 0.f, lin_scale2 = 0.f;
+    if (width > 0.f && width < 3.0e38f) {   // also false for NaN; uniform over the cluster
+        int need_lin = k, above_total = 0;
+        for (int level = 1; level <= 2; ++level) {
+            int *h = hist[level - 1];
+            keys.for_each(srow + base, n_mine, tid, [&](int, uint32_t key, bool valid) {
+                if (!valid) return;
+                const float x = key_score(key);
+                const int b1 = linear_bucket(x, lin_lo, lin_scale);
+                if (level == 1) atomicAdd(&h[b1], 1);
+                else if (b1 == lin_b) atomicAdd(&h[linear_bucket(x, lin_lo2, lin_scale2)], 1);
+            });
+            cluster_sync_all();
+            if (tid < 256) {
+                int t = 0;
+#pragma unroll
+                for (uint32_t c = 0; c < kTopkCluster; ++c) t += dsmem_ld_s32(dsmem_addr(&h[tid], c));
+                total[tid] = t;
+            }
+            __syncthreads();
+            if (warp == 0)
+                descending_crossing(total, need_lin, lane, &sh_digit, &sh_above, &sh_count,
+                                    level == 1 ? above_of : nullptr);
+            __syncthreads();
+            const int b = sh_digit, above = sh_above, cnt = sh_count;
+            if (level == 1) {
+                lin_b = b;
+                lin_lo2 = lin_lo + (float)b / lin_scale;
+                lin_scale2 = lin_scale * 256.f;
+            } else {
+                lin_b2 = b;
+            }
+            above_total += above;
+            need_lin -= above;
+            if (above_total + cnt <= cap) {
+                lin_levels = level;
+                lin_m = above_total + cnt;
+                break;
+            }
+            __syncthreads();   // sh_* and total are rewritten by the next level
+        }
+    }
+    if (lin_levels == 0) {
+        // the one-CTA selection over the whole row, by CTA 0 (nobody reads anybody's shared memory from here on)
+        cluster_sync_all();
+        if (crank == 0) topk_row<0>(srow, n_pages, k, dst, smem_raw);
+        return;
+    }
+
+    // ---- the candidates meet in CTA 0 -------------------------------------------------------------
+    // Level 1: bucket b's candidates go to cand[above_of[b] ...], so that a candidate's final rank is
+    // above_of[b] plus its rank among the few keys of its own bucket.  Level 2: places in arrival order.
+    const uint32_t cand0 = dsmem_addr(cand, 0);
+    keys.for_each(srow + base, n_mine, tid, [&](int i, uint32_t key, bool valid) {
+        if (!valid) return;
+        const float x = key_score(key);
+        const int b1 = linear_bucket(x, lin_lo, lin_scale);
+        bool take;
+        int counter, first;
+        if (lin_levels == 1) {
+            take = b1 >= lin_b;
+            counter = b1;
+            first = above_of[b1];
+        } else {
+            take = b1 > lin_b || (b1 == lin_b && linear_bucket(x, lin_lo2, lin_scale2) >= lin_b2);
+            counter = 0;
+            first = 0;
+        }
+        if (take) {
+            const int at = first + dsmem_atomic_add_s32(dsmem_addr(&fill[counter], 0), 1);
+            dsmem_st_u64(cand0 + (uint32_t)at * 8u, ((unsigned long long)(~key) << 32) | (uint32_t)(base + i));
+        }
+    });
+    cluster_sync_all();   // all candidates are in place; the other CTAs are done
+    if (crank != 0) return;
+    if (lin_levels == 1) {
+        for (int e = tid; e < lin_m; e += kTopkThreads) {
+            const unsigned long long v = cand[e];
+            const int b = linear_bucket(key_score(~(uint32_t)(v >> 32)), lin_lo, lin_scale);
+            const int first = above_of[b];
+            const int last = first + total[b];
+            int c = first;
+            for (int j = first; j < last; ++j) c += cand[j] < v;
+            if (c < k) dst[c] = (int32_t)(v & 0xffffffffu);
+        }
+        return;
+    }
+    rank_candidates(cand, rank, lin_m, k, dst, tid);
+}
 template <int IPT>
 static cudaError_t launch_topk(const float *scores, int32_t *page_list, int rows, int n_kv_heads, int rep,
                                int n_pages, int k, cudaStream_t stream) {
@@ -443,21 +669,65 @@ static cudaError_t launch_topk(const float *scores, int32_t *page_list, int rows
     return cudaGetLastError();
 }
 
+static cudaError_t launch_topk_cluster(const float *scores, int32_t *page_list, int rows, int n_kv_heads, int rep,
+                                       int n_pages, int k, cudaStream_t stream) {
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!attr_set[dev]) {
+        e = cudaFuncSetAttribute(topk_pages_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 topk_candidate_capacity(kTopkMaxK) * 12 + 16);
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    const int cap = topk_candidate_capacity(k);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(rows * kTopkCluster);
+    cfg.blockDim = dim3(kTopkThreads);
+    cfg.dynamicSmemBytes = (size_t)(cap + 2) * sizeof(unsigned long long) + (size_t)cap * sizeof(int);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = kTopkCluster;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    e = cudaLaunchKernelEx(&cfg, topk_pages_cluster_kernel, scores, page_list, n_kv_heads, rep, n_pages, k);
+    if (e != cudaSuccess) return e;
+    return cudaGetLastError();
+}
+
 }  // namespace da
 
-extern "C" int da_topk_pages(const float *scores, int32_t *page_list, int n_tokens, int n_kv_heads, int rep,
-                             int n_pages, int k, da_stream_t stream) {
+extern "C" int da_topk_pages_wide(const float *scores, int32_t *page_list, int n_tokens, int n_kv_heads, int rep,
+                                  int n_pages, int k, int sm_budget, da_stream_t stream) {
     if (!scores || !page_list) return DA_ERR_NULL;
-    if (n_tokens < 1 || n_kv_heads < 1 || rep < 1 || n_pages < 1 || k < 1 || k > n_pages) return DA_ERR_SHAPE;
+    if (n_tokens < 1 || n_kv_heads < 1 || rep < 1 || n_pages < 1 || k < 1 || k > n_pages || sm_budget < 0)
+        return DA_ERR_SHAPE;
     if (k > da::kTopkMaxK) return DA_ERR_UNSUPPORTED;
     const int rows = n_tokens * n_kv_heads * rep;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     cudaError_t e;
-    if (n_pages <= 4 * da::kTopkThreads) e = da::launch_topk<4>(scores, page_list, rows, n_kv_heads, rep, n_pages, k, s);
+    if (sm_budget == 0) sm_budget = 148;
+    // long rows are split over a cluster when all clusters find an SM per CTA at once; otherwise the
+    // clusters would run in turns and one CTA per row is as fast
+    if (n_pages > 16 * da::kTopkThreads && n_pages <= da::kTopkClusterMaxPages && rows * da::kTopkCluster <= sm_budget)
+        e = da::launch_topk_cluster(scores, page_list, rows, n_kv_heads, rep, n_pages, k, s);
+    else if (n_pages <= 4 * da::kTopkThreads) e = da::launch_topk<4>(scores, page_list, rows, n_kv_heads, rep, n_pages, k, s);
     else if (n_pages <= 8 * da::kTopkThreads) e = da::launch_topk<8>(scores, page_list, rows, n_kv_heads, rep, n_pages, k, s);
     else if (n_pages <= 16 * da::kTopkThreads) e = da::launch_topk<16>(scores, page_list, rows, n_kv_heads, rep, n_pages, k, s);
     else e = da::launch_topk<0>(scores, page_list, rows, n_kv_heads, rep, n_pages, k, s);
     return (int)e;
+}
+
+extern "C" int da_topk_pages(const float *scores, int32_t *page_list, int n_tokens, int n_kv_heads, int rep,
+                             int n_pages, int k, da_stream_t stream) {
+    return da_topk_pages_wide(scores, page_list, n_tokens, n_kv_heads, rep, n_pages, k, 0, stream);
 }
 
 DA_DEFINE_TRACE_SETTER(trace_set_topk)

@@ -76,6 +76,8 @@ class DRAMAttention(torch.nn.Module):
     # CTAs per KV head of the two launches (0: the library's defaults)
     phase1_ctas = 0
     phase2_ctas = 0
+    selection_sm_budget = 0    # SMs the selection may count on beside the first attention launch of the
+                               # two-launch step; 0 = 148 minus that launch's CTAs (one SM each)
 
     # ---- cache construction ---------------------------------------------------
     def init_cache(self, k_cache: torch.Tensor, v_cache: torch.Tensor):
@@ -264,19 +266,21 @@ class DRAMAttention(torch.nn.Module):
         # Only inside a graph capture: a graph dispatches the scorer's CTAs ahead of phase 1's (node
         # order), whereas two eager launches that become ready together (a backlogged GPU) may be
         # dispatched either way round, and phase 1 first would starve the scorer of SMs.
+        budget = self.selection_sm_budget or max(
+            1, 148 - self.n_kv_heads * (self.phase1_ctas or min(20, max(1, 116 // self.n_kv_heads))))
         early = self.fork_before_score and torch.cuda.is_current_stream_capturing()
         if early:
             self._fork.record(main)
         sel.score_(xq, lc.top_k)
         if not early:
             self._fork.record(main)
-            page_list = sel.select_(1, rep, lc.top_k)     # ahead of phase 1, so that its CTAs find SMs free
+            page_list = sel.select_(1, rep, lc.top_k, sm_budget=budget)     # ahead of phase 1, so that its CTAs find SMs free
         self._side.wait_event(self._fork)
         with torch.cuda.stream(self._side):
             self.attend_(xq, xk, xv, start_pos, out, phase=1)
             self._join.record(self._side)
         if early:
-            page_list = sel.select_(1, rep, lc.top_k)
+            page_list = sel.select_(1, rep, lc.top_k, sm_budget=budget)
         lc.update_tables_(page_list, advance_split=False, inline_fetch=True)
         # phase 2 needs the update, not phase 1: whichever of the two launches finishes last merges
         self.attend_(xq, xk, xv, start_pos, out, phase=2)

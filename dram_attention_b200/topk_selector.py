@@ -73,14 +73,15 @@ class IPUpperboundTopKSelector:
         score_pages_(qc, self.chunk_min_max, scores, seq_len, self.num_kv_heads, rep, ordered=True)
         return scores
 
-    def select_(self, seq_len: int, rep: int, k: int):
+    def select_(self, seq_len: int, rep: int, k: int, sm_budget: int = 0):
         """Enqueue the top-k selection on the scores of the last score_ call with the
-        same (seq_len, rep, k); returns the int32 page list (Hk, S*rep*k)."""
+        same (seq_len, rep, k); returns the int32 page list (Hk, S*rep*k).  `sm_budget`: SMs the
+        selection may count on (0 = all), see da_topk_pages_wide."""
         k = min(k, self.num_pages)
         scores, page_list = self._workspace(seq_len, rep, k)
-        _native.check(_native.lib().da_topk_pages(
+        _native.check(_native.lib().da_topk_pages_wide(
             scores.data_ptr(), page_list.data_ptr(), seq_len, self.num_kv_heads, rep, self.num_pages, k,
-            _native.stream_ptr()), "da_topk_pages")
+            int(sm_budget), _native.stream_ptr()), "da_topk_pages_wide")
         return page_list
 
     def page_list_(self, q: torch.Tensor, k: int):

@@ -125,6 +125,19 @@ DA_API int da_topk_pages(const float *scores, int32_t *page_list,
                   da_stream_t stream);
 
 /*
+ * The same selection with a hint on how many SMs it may count on.  Rows of more than 16 384 pages
+ * (up to 65 536) are split over a thread-block cluster of four CTAs (partial histograms summed
+ * through distributed shared memory, candidates collected in one CTA) when all clusters of the
+ * launch find an SM per CTA at once: n_tokens * n_kv_heads * rep * 4 <= sm_budget.  A caller
+ * that runs another launch beside the selection (the first attention launch of the two-launch
+ * step keeps all but 32 SMs) passes what is left; 0 means the whole GPU, which is what
+ * da_topk_pages passes.  The result does not depend on sm_budget.
+ */
+DA_API int da_topk_pages_wide(const float *scores, int32_t *page_list,
+                       int n_tokens, int n_kv_heads, int rep, int n_pages, int k,
+                       int sm_budget, da_stream_t stream);
+
+/*
  * LRU slot-table update, one call for all KV heads.  Replaces load_lru_cache_()
  * without its payload copy: _update_page_access_time_
  * (dram_attention/lru_triton_kernel.py:110-137), the stable argsort of the

@@ -121,6 +121,10 @@ def _topk_oracle(scores, hk, rep, k):
     (300, 300, 2, 1, 1, "normal"), (4096, 4096, 1, 1, 1, "normal"), (1, 1, 2, 2, 1, "normal"),
     (8192, 256, 2, 4, 1, "quantised"), (3000, 500, 2, 2, 1, "quantised"), (2048, 64, 2, 2, 1, "constant"),
     (4096, 100, 2, 2, 1, "zeros"), (1500, 200, 2, 2, 1, "bf16like"), (2000, 128, 2, 2, 1, "negative"),
+    # rows of more than 16384 pages: a cluster of four CTAs per row (uneven parts, ties, the fall-back)
+    (20000, 300, 1, 2, 1, "normal"), (16385, 64, 1, 1, 2, "bf16like"), (65536, 4096, 1, 1, 1, "normal"),
+    (65536, 256, 1, 2, 1, "quantised"), (30000, 128, 1, 2, 1, "constant"), (40000, 200, 1, 2, 1, "zeros"),
+    (50000, 100, 1, 2, 1, "negative"), (65536, 256, 1, 2, 1, "outlier"), (65534, 512, 2, 4, 1, "normal"),
 ])
 def test_topk_bit_exact(da, pages, k, hk, rep, s, kind):
     g = _g(pages * 7 + k)
@@ -136,6 +140,9 @@ def test_topk_bit_exact(da, pages, k, hk, rep, s, kind):
         sc = sc.to(torch.bfloat16).float()  # the reference's own score resolution
     elif kind == "negative":
         sc = -sc.abs() - 1
+    elif kind == "outlier":
+        sc[..., 5] = 1e30                   # the row's range is useless for equal-width buckets
+        sc[..., 77] = -1e30
     got = _topk(da, sc, hk, rep, k)
     want = _topk_oracle(sc, hk, rep, k)
     assert torch.equal(got, want)
