@@ -28,8 +28,9 @@ timeline_us  where the time of a step goes: start and end of every kernel of the
 cpu_baseline  the CPU oracle (a port of the reference's pure-PyTorch path, float32) timed on a
          bounded sample of the same workload on this box's host cores.
 
-Extras in the same line (skipped with --no-extras): fetch_report (miss fetch against the host
-link), scorer_sweep (config 3), prefill, and the two other multi-GPU configurations:
+Extras in the same line (skipped with --no-extras): rope_in_call (the step with the caller's
+rotary embedding done by the operator), fetch_report (miss fetch against the host link),
+scorer_sweep (config 3), prefill, and the two other multi-GPU configurations:
 cfg4     8 independent 64K-token sequences, 128 steps with a query re-draw every 32 steps,
          sequences dealt round-robin to the N GPUs (no collective).
 cfg5     a 32-layer stack at a 1,048,576-token prefix per layer, KV heads sharded N-way with the
@@ -86,6 +87,9 @@ def parse_args():
     ap.add_argument("--prefill-tokens", type=int, default=32768, help="prompt length of the prefill report")
     ap.add_argument("--only-prefill", action="store_true",
                     help="time just the prefill kernel at --prefill-tokens (a small launch to profile) and exit")
+    ap.add_argument("--only-sweep", action="store_true",
+                    help="run just the page scorer and the selection at 8 KV heads x 65536 pages (config 3's largest "
+                         "case) three times and exit: a small job to profile")
     ap.add_argument("--settle-steps", type=int, default=0,
                     help="cfg2: untimed decode steps before the warm-up (0: the timed windows start right after "
                          "the warm-up, inside the 64 steps the configuration names)")
@@ -438,7 +442,7 @@ def bench_cfg2(args, ctx):
     K, W = args.steps, max(args.warmup, 3)
     NW = max(1, args.windows)
     settle = max(0, args.settle_steps)
-    total = settle + W + (NW + 1) * K + (W + K) + K + 8 + (W + 2 * K + 4 if args.reference_gpu else 0)
+    total = settle + W + (NW + 1) * K + (W + K) + 3 * K + 8 + (W + 2 * K + 4 if args.reference_gpu else 0)
     by_seq = world > 1 and args.shard == "sequence"
     n_seq = world if by_seq else 1
     w = llama_layer_workload(seed=(rank if by_seq else 0), steps=total, dram_tokens=args.dram_tokens, max_out=total)
@@ -651,6 +655,33 @@ def cfg2_extras(args, ctx, r):
     launch_us = r["launch_us"]
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     out = {}
+
+    # ---------------- the caller's rotary embedding inside the call (freqs_cis=) ----------------------
+    t_a = time.perf_counter()
+    inv = 1.0 / (500000.0 ** (torch.arange(0, D, 2, device=dev).float() / D))
+    rope_us = {}
+    for name in ("without", "with_freqs_cis"):
+        first_r = step
+        fr = [torch.polar(torch.ones(1, D // 2, device=dev), (float(S + first_r + i) * inv)[None]) for i in range(K)]
+        torch.cuda.synchronize()
+        g_r = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g_r):
+            outs_r = [op(dq[first_r + i], dk[first_r + i], dv[first_r + i], start_pos=S + first_r + i, stage="generate",
+                         **({"freqs_cis": fr[i]} if name == "with_freqs_cis" else {})) for i in range(K)]
+        upload_graph(g_r, torch)
+        torch.cuda.synchronize()
+        ev0.record()
+        g_r.replay()
+        ev1.record()
+        torch.cuda.synchronize()
+        rope_us[name] = ev0.elapsed_time(ev1) / K * 1e3
+        step += K
+        del outs_r, g_r
+    inner.check_status()
+    out["rope_in_call"] = {"what": "K captured steps with the operator applying the caller's rotary embedding itself "
+                                   "(da_rope_qk, one launch in front of the scorer) and K steps without, us per step",
+                           "us_per_step": rope_us}
+    ctx.windows.append((t_a, time.perf_counter()))
 
     # ---------------- miss fetch: a steady step without misses, and a cold step against the host link ----
     t_a = time.perf_counter()
@@ -1170,6 +1201,32 @@ def run_b200(args):
     ctx = Ctx(args)
     torch, dist = ctx.torch, ctx.dist
     world, rank, dev = ctx.world, ctx.rank, ctx.dev
+
+    if args.only_sweep:
+        from dram_attention_b200.topk_selector import IPUpperboundTopKSelector
+        gs = torch.Generator(device=dev).manual_seed(0)
+        s_hk, s_rep, s_pg, n_pages, D = 8, 4, 16, 65536, 128
+        mm = torch.empty(s_hk, n_pages, 2, D, dtype=torch.bfloat16, device=dev)
+        for h in range(s_hk):
+            keys = torch.randn(n_pages, s_pg, D, generator=gs, device=dev).to(torch.bfloat16)
+            mm[h, :, 0], mm[h, :, 1] = torch.aminmax(keys, dim=1)
+            del keys
+        q_s = torch.randn(1, 1, s_hk * s_rep, D, generator=gs, device=dev).to(torch.bfloat16)
+        sel = IPUpperboundTopKSelector(torch.empty(s_hk, n_pages * s_pg, D, dtype=torch.bfloat16, device="meta"), n_pages,
+                                       device=dev, _summaries=mm)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        res = []
+        for _ in range(3):
+            ev[0].record()
+            sel.score_(q_s, 256)
+            ev[1].record()
+            pl = sel.select_(1, s_rep, 256)
+            ev[2].record()
+            torch.cuda.synchronize()
+            res.append((ev[0].elapsed_time(ev[1]) * 1e3, ev[1].elapsed_time(ev[2]) * 1e3))
+        print(json.dumps({"pages": n_pages, "score_us": [r[0] for r in res], "topk_us": [r[1] for r in res],
+                          "first_pages_of_head_0": pl[0, :4].tolist()}), file=RESULT_OUT, flush=True)
+        return
 
     if args.only_prefill:
         import dram_attention_b200 as da

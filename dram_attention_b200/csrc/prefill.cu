@@ -2,30 +2,41 @@
 // head_dim 128, on the 5th-generation tensor cores: tcgen05.mma with both operands in shared
 // memory (filled by TMA tensor copies, 128-byte swizzle) and the accumulators in tensor memory.
 //
-// One CTA per (128 query rows, query head): four softmax warps and one issuing warp.  Softmax
-// thread t owns query row t, which is lane t of tensor memory, so the softmax needs no
-// shuffles: a row's 128 logits come back with tcgen05.ld as plain registers of its thread.
-// One lane of the fifth warp issues every TMA copy and every MMA; the two roles meet only at
-// mbarriers (S ready, P ready, product complete), never at a CTA-wide barrier, so a softmax
-// warp is never held up by another warp's pace.  Per 128-key tile:
+// One CTA per (128 query rows, query head), TWO CTAs per SM: four softmax warps and one issuing
+// warp each.  Softmax thread t owns query row t, which is lane t of tensor memory, so the
+// softmax needs no shuffles: a row's logits come back with tcgen05.ld as plain registers of
+// its thread.  One lane of the fifth warp issues every MMA, one lane of the sixth every TMA
+// copy; the roles meet only at mbarriers (tile arrived, S ready, P ready, product complete),
+// never at a CTA-wide barrier.  The MMA lane's instruction stream sets the pace of the CTA
+// (measured with time stamps: 1.4 us per tile when it also issued the copies and rebuilt its
+// operand descriptors per MMA), hence a warp of its own and descriptors made before the loop.
+// A CTA alone leaves the tensor core idle most of the time: its softmax is a chain of phases
+// (read S, maximum, exponentials on the special-function unit, sum, conversion, write P) that
+// the same four warps walk tile after tile.  Two CTAs on an SM walk it out of step, so one's
+// exponentials overlap the other's loads, conversions and hand-offs, and both feed the tensor
+// core.  To fit twice, a CTA takes 64-key tiles (97 KB of shared memory) and 256 columns of
+// tensor memory.  Per 64-key tile:
 //
-//   S = Q K^T      8 MMAs (M128 N128 K16), Q and the key tile K-major      -> TMEM columns 0..127 / 128..255
+//   S = Q K^T      8 MMAs (M128 N64 K16), Q and the key tile K-major          -> TMEM columns 0..63 / 64..127
 //   softmax        row max / exp2 / row sum in registers (log2 domain, online rescale);
-//                  P is written as 16-bit values into shared memory in the swizzled K-major
-//                  layout an A operand has
-//   O += P V       8 MMAs, the value tile as an MN-major B operand, accumulating over all
-//                  tiles                                                    -> TMEM columns 256..383
+//                  P goes back into tensor memory as packed 16-bit pairs, over the first 32
+//                  columns of the S buffer it was computed from (tcgen05.st: a thread writes
+//                  its own lane, no shared-memory traffic)
+//   O += P V       4 MMAs (M128 N128 K16) with P as the A operand from tensor memory and the
+//                  value tile as an MN-major B operand from shared memory, accumulating over
+//                  all tiles                                                   -> TMEM columns 128..255
 //
 // O never leaves tensor memory until the end: the exponentials of a row are taken against a
 // reference that follows the row maximum lazily, and O is rescaled in place (tcgen05.ld / st)
 // only when a tile's maximum outgrows the reference by more than 2^8 - after the first tiles,
 // hardly ever.  The loop is software-pipelined so that the tensor core is not waited on in
-// line: S of tile j+1 is issued (into a second S buffer) before the softmax of tile j starts,
-// and the product of tile j runs during the softmax of tile j+1.  Key and value tiles are
-// double-buffered (a key stage is refilled as soon as its S is complete, a value stage once
-// its product is).  Every wait on an mbarrier is bounded: a
-// wait that runs out sets DA_STATUS_WAIT_TIMEOUT and a flag that makes both roles leave their
-// loops; the CTA then frees its tensor memory and returns.
+// line: S of tile j+1 is issued (into the second S buffer) before the softmax of tile j starts,
+// and the product of tile j runs during the softmax of tile j+1.  The tensor core executes in
+// issue order, so S of tile j+2, which overwrites the buffer P of tile j lies in, runs after
+// the product that reads it.  Key and value tiles are double-buffered (a key stage is refilled
+// as soon as its S is complete, a value stage once its product is).  Every wait on an
+// mbarrier is bounded: a wait that runs out sets DA_STATUS_WAIT_TIMEOUT and a flag that makes
+// both roles leave their loops; the CTA then frees its tensor memory and returns.
 //
 // GQA: query head hq reads KV head hq / rep.  Causal: key tiles above the diagonal are
 // skipped, the diagonal tile is masked per element.  Rows past the end of the prompt are
@@ -38,13 +49,15 @@
 namespace da {
 
 constexpr int kPfRows = 128;    // query rows per CTA (= softmax threads, = TMEM lanes)
-constexpr int kPfThreads = kPfRows + 32;   // plus the warp that issues copies and MMAs
-constexpr int kPfKeys = 128;    // keys per tile
+constexpr int kPfThreads = kPfRows + 64;   // plus the warp that issues the MMAs and the warp that issues the copies
+constexpr int kPfKeys = 64;     // keys per tile
 constexpr int kPfDim = 128;     // head_dim
-constexpr int kPfBoxBytes = kPfRows * 128;            // one TMA box: 128 rows x 64 elements
-constexpr int kPfTileBytes = 2 * kPfBoxBytes;         // 128 x 128 elements
-constexpr int kPfSmemBytes = 7 * kPfTileBytes + 1024; // Q, K x2, V x2, P x2, alignment slack
-constexpr uint32_t kPfTmemCols = 512;            // 384 used (two S buffers, one product); a power of two
+constexpr int kPfQBoxBytes = kPfRows * 128;           // one TMA box of Q: 128 rows x 64 elements
+constexpr int kPfQTileBytes = 2 * kPfQBoxBytes;       // 128 x 128 elements
+constexpr int kPfBoxBytes = kPfKeys * 128;            // one TMA box of K or V: 64 rows x 64 elements
+constexpr int kPfTileBytes = 2 * kPfBoxBytes;         // 64 x 128 elements
+constexpr int kPfSmemBytes = kPfQTileBytes + 4 * kPfTileBytes + 1024;   // Q, K x2, V x2, alignment slack
+constexpr uint32_t kPfTmemCols = 256;            // two S buffers of 64 columns (P over them), the product
 
 struct PrefillParams {
     void *out;              // (S, Hq, D)
@@ -95,6 +108,37 @@ __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+
+// D[tmem] (+)= A[tmem] * B[smem]: A is 128 lanes x 8 columns of packed 16-bit pairs (K16)
+__device__ __forceinline__ void tc_mma_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                              uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+
+// The same two with the accumulate flag known at compile time (no predicate to set up per MMA).
+template <bool ACC>
+__device__ __forceinline__ void tc_mma_c(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "n"(ACC ? 1 : 0), "r"(0u)
+        : "memory");
+}
+template <bool ACC>
+__device__ __forceinline__ void tc_mma_a_tmem_c(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "n"(ACC ? 1 : 0), "r"(0u)
         : "memory");
 }
 
@@ -171,9 +215,9 @@ __device__ __forceinline__ uint64_t desc_mn_major(uint32_t saddr) {
            ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
 
-__device__ __forceinline__ uint32_t instr_desc(bool bf16, bool b_mn_major) {
+__device__ __forceinline__ uint32_t instr_desc(bool bf16, bool b_mn_major, int n) {
     const uint32_t fmt = bf16 ? 1u : 0u;
-    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(kPfKeys >> 3) << 17) |
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
            ((uint32_t)(kPfRows >> 4) << 24);
 }
 
@@ -188,16 +232,15 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
 }
 
 template <bool BF16>
-__global__ void __launch_bounds__(kPfThreads, 1)
+__global__ void __launch_bounds__(kPfThreads, 2)
 prefill_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const PrefillParams p) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                             ~(uintptr_t)1023);
     unsigned char *sQ = smem;
-    unsigned char *sK = sQ + kPfTileBytes;            // two stages
+    unsigned char *sK = sQ + kPfQTileBytes;           // two stages
     unsigned char *sV = sK + 2 * kPfTileBytes;        // two stages
-    unsigned char *sP = sV + 2 * kPfTileBytes;        // two buffers
     __shared__ __align__(8) uint64_t bar_q, bar_k[2], bar_v[2], bar_s[2], bar_p[2], bar_pv;
     __shared__ uint32_t tmem_holder;
     __shared__ int sh_abort;
@@ -230,7 +273,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_holder;
-    // columns: S of even tiles 0..127, S of odd tiles 128..255, O 256..383
+    // columns: S of even tiles 0..63, S of odd tiles 64..127 (P over the first 32 of each), O 128..255
     const uint32_t tmem_o = 2 * kPfKeys;
 
     // keys 0 .. q0 + 127 are visible to this tile's rows
@@ -243,44 +286,69 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         *abort_flag = 1;
     };
 
-    if (warp == kPfRows / 32) {
-        // =================== the issuing warp: all TMA copies and all MMAs, by one lane ===================
+    if (warp == kPfRows / 32 + 1) {
+        // =================== the copy warp: every TMA copy, by one lane ===================================
+        // Key tile j+2 goes into the stage of tile j once S(j) is complete, value tile j+2 into the stage
+        // of tile j once the product of tile j is.
         if ((tid & 31) == 0) {
             auto load_tile = [&](unsigned char *dst, const CUtensorMap *map, int j, uint64_t *bar) {
                 mbar_arrive_expect_tx(bar, kPfTileBytes);
                 tma_load_3d(dst, map, 0, hk, j * kPfKeys, bar);
                 tma_load_3d(dst + kPfBoxBytes, map, 64, hk, j * kPfKeys, bar);
             };
-            const uint32_t idesc_s = instr_desc(bf16, false), idesc_o = instr_desc(bf16, true);
-            // S(j) = Q K(j)^T into the S buffer of j's parity; K(j) has arrived when this is called
+            mbar_arrive_expect_tx(&bar_q, kPfQTileBytes);
+            tma_load_3d(sQ, &map_q, 0, hq, q0, &bar_q);
+            tma_load_3d(sQ + kPfQBoxBytes, &map_q, 64, hq, q0, &bar_q);
+            load_tile(sK, &map_k, 0, &bar_k[0]);
+            load_tile(sV, &map_v, 0, &bar_v[0]);
+            if (n_tiles > 1) {
+                load_tile(sK + kPfTileBytes, &map_k, 1, &bar_k[1]);
+                load_tile(sV + kPfTileBytes, &map_v, 1, &bar_v[1]);
+            }
+            bool ok = true;
+            for (int j = 0; ok && j + 2 < n_tiles; ++j) {
+                const int b = j & 1;
+                if (*abort_flag) break;
+                ok = mbar_wait_bounded(&bar_s[b], (uint32_t)((j >> 1) & 1));
+                if (!ok) break;
+                load_tile(sK + b * kPfTileBytes, &map_k, j + 2, &bar_k[b]);
+                ok = mbar_wait_bounded(&bar_pv, (uint32_t)(j & 1));
+                if (!ok) break;
+                load_tile(sV + b * kPfTileBytes, &map_v, j + 2, &bar_v[b]);
+            }
+            if (!ok) give_up();
+        }
+    } else if (warp == kPfRows / 32) {
+        // =================== the issuing warp: every MMA, by one lane =====================================
+        // Its instruction stream is the pace of the whole CTA, so everything that can be is computed
+        // before the loop: the operand descriptors of both stages (an MMA's own is a 64-bit add away).
+        if ((tid & 31) == 0) {
+            const uint32_t idesc_s = instr_desc(bf16, false, kPfKeys), idesc_o = instr_desc(bf16, true, kPfDim);
+            const uint64_t dq = desc_k_major(smem_addr(sQ));
+            const uint64_t dk0 = desc_k_major(smem_addr(sK)), dk1 = desc_k_major(smem_addr(sK + kPfTileBytes));
+            const uint64_t dv0 = desc_mn_major(smem_addr(sV)), dv1 = desc_mn_major(smem_addr(sV + kPfTileBytes));
+            // S(j) = Q K(j)^T into the S buffer of j's parity; K(j) has arrived when this is called.  That
+            // buffer's last readers were the softmax of tile j-2 (done: its P was waited for before the
+            // product of tile j-2 was issued) and that product (issued earlier: the tensor core runs in order).
             auto issue_s = [&](int j) {
                 tc_fence_after();
-                const uint32_t a0 = smem_addr(sQ), b0 = smem_addr(sK + (j & 1) * kPfTileBytes);
+                const uint64_t kb = (j & 1) ? dk1 : dk0;
+                const uint32_t d = tmem + (j & 1) * kPfKeys;
 #pragma unroll
                 for (int ks = 0; ks < kPfDim / 16; ++ks) {
-                    const uint32_t off = (ks >> 2) * kPfBoxBytes + (ks & 3) * 32;
-                    tc_mma(tmem + (j & 1) * kPfKeys, desc_k_major(a0 + off), desc_k_major(b0 + off), idesc_s, ks > 0);
+                    const uint32_t a_off = ((ks >> 2) * kPfQBoxBytes + (ks & 3) * 32) >> 4;
+                    const uint32_t b_off = ((ks >> 2) * kPfBoxBytes + (ks & 3) * 32) >> 4;
+                    if (ks == 0) tc_mma_c<false>(d, dq + a_off, kb + b_off, idesc_s);
+                    else tc_mma_c<true>(d, dq + a_off, kb + b_off, idesc_s);
                 }
                 tc_commit(&bar_s[j & 1]);
             };
-            mbar_arrive_expect_tx(&bar_q, kPfTileBytes);
-            tma_load_3d(sQ, &map_q, 0, hq, q0, &bar_q);
-            tma_load_3d(sQ + kPfBoxBytes, &map_q, 64, hq, q0, &bar_q);
-            load_tile(sK, &map_k, 0, &bar_k[0]);
-            if (n_tiles > 1) load_tile(sK + kPfTileBytes, &map_k, 1, &bar_k[1]);
-            load_tile(sV, &map_v, 0, &bar_v[0]);
             bool ok = mbar_wait_bounded(&bar_q, 0) && mbar_wait_bounded(&bar_k[0], 0);
             if (ok) issue_s(0);
             for (int j = 0; ok && j < n_tiles; ++j) {
                 const int b = j & 1;
                 const uint32_t use = (uint32_t)((j >> 1) & 1);     // parity of this use of a two-deep buffer
                 if (*abort_flag) break;
-                // S(j) complete: its key stage can take tile j+2
-                ok = mbar_wait_bounded(&bar_s[b], use);
-                if (!ok) break;
-                if (j + 2 < n_tiles) load_tile(sK + b * kPfTileBytes, &map_k, j + 2, &bar_k[b]);
-                // S(j+1) goes into the other S buffer, whose last reader was the softmax of tile j-1:
-                // done, or its P would not have been ready for the product issued one round ago
                 if (j + 1 < n_tiles) {
                     ok = mbar_wait_bounded(&bar_k[b ^ 1], (uint32_t)(((j + 1) >> 1) & 1));
                     if (!ok) break;
@@ -288,21 +356,16 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 }
                 // O += P(j) V(j) once every softmax thread has written its row of P (and has
                 // rescaled its row of O if it had to)
-                ok = mbar_wait_bounded(&bar_p[b], use);
-                if (ok && j > 0) ok = mbar_wait_bounded(&bar_pv, (uint32_t)((j - 1) & 1));   // frees V's other stage
-                if (!ok) break;
-                if (j + 1 < n_tiles) load_tile(sV + (b ^ 1) * kPfTileBytes, &map_v, j + 1, &bar_v[b ^ 1]);
-                ok = mbar_wait_bounded(&bar_v[b], use);
+                ok = mbar_wait_bounded(&bar_p[b], use) && mbar_wait_bounded(&bar_v[b], use);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t a0 = smem_addr(sP + b * kPfTileBytes), b0 = smem_addr(sV + b * kPfTileBytes);
+                const uint32_t a0 = tmem + (uint32_t)b * kPfKeys;
+                const uint64_t vb = b ? dv1 : dv0;
+                if (j == 0) tc_mma_a_tmem_c<false>(tmem + tmem_o, a0, vb, idesc_o);
+                else tc_mma_a_tmem_c<true>(tmem + tmem_o, a0, vb, idesc_o);
 #pragma unroll
-                for (int ks = 0; ks < kPfKeys / 16; ++ks) {
-                    const uint32_t a_off = (ks >> 2) * kPfBoxBytes + (ks & 3) * 32;
-                    const uint32_t b_off = ks * 16 * 128;               // 16 keys further down the tile
-                    tc_mma(tmem + tmem_o, desc_k_major(a0 + a_off), desc_mn_major(b0 + b_off), idesc_o,
-                           (j > 0 || ks > 0) ? 1u : 0u);
-                }
+                for (int ks = 1; ks < kPfKeys / 16; ++ks)      // 16 keys further down the tile per step
+                    tc_mma_a_tmem_c<true>(tmem + tmem_o, a0 + ks * 8, vb + ((ks * 16 * 128) >> 4), idesc_o);
                 tc_commit(&bar_pv);
             }
             if (!ok) give_up();
@@ -341,15 +404,11 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             const int key0 = j * kPfKeys;
             const bool diagonal = key0 + kPfKeys - 1 > q0;      // some key of the tile is masked for some row
             const int n_vis = diagonal ? min(max(qpos - key0 + 1, 0), kPfKeys) : kPfKeys;   // keys this row sees
-            uint32_t s0[32], s1[32], s2[32], s3[32];
+            uint32_t s0[32], s1[32];
             tmem_issue32(tmem_row + tmem_s, s0);
             tmem_issue32(tmem_row + tmem_s + 32, s1);
-            tmem_issue32(tmem_row + tmem_s + 64, s2);
-            tmem_issue32(tmem_row + tmem_s + 96, s3);
             tmem_wait32(s0);
             tmem_wait32(s1);
-            tmem_wait32(s2);
-            tmem_wait32(s3);
             float mx = -INFINITY;
             auto chunk_max = [&](int c, const uint32_t (&s)[32]) {
                 if (!diagonal) {
@@ -363,8 +422,6 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             };
             chunk_max(0, s0);
             chunk_max(1, s1);
-            chunk_max(2, s2);
-            chunk_max(3, s3);
             const float m_tile = mx * p.scale_log2;
 
             // ---- move the reference if this tile outgrows it (whole warp together: the tensor-memory
@@ -397,11 +454,11 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             }
             const float m_ref = (m_used == -INFINITY) ? 0.f : m_used;
 
-            // ---- P = exp2(S * scale - reference) as 16-bit values into shared memory ----------------
+            // ---- P = exp2(S * scale - reference) as packed 16-bit pairs into tensor memory, over this
+            //      row's own (already read) S --------------------------------------------------------------
             float row_sum = 0.f;
-            unsigned char *sPb = sP + b * kPfTileBytes;
+            uint32_t packed[32];
             auto chunk_p = [&](int c, const uint32_t (&s)[32]) {
-                uint32_t packed[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
                     float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), p.scale_log2, -m_ref));
@@ -411,25 +468,15 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                         if (c * 32 + i + 1 >= n_vis) p1 = 0.f;
                     }
                     row_sum += p0 + p1;
-                    packed[i >> 1] = pack16<BF16>(p0, p1);
-                }
-                // row `tid` of P, keys 32c .. 32c+31 = 64 bytes = four 16-byte chunks of the row's box
-                unsigned char *row = sPb + (c >> 1) * kPfBoxBytes + tid * 128;
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int chunk = (c & 1) * 4 + q;                     // chunk inside the 128-byte row
-                    const int phys = chunk ^ (tid & 7);                    // 128-byte swizzle
-                    *reinterpret_cast<uint4 *>(row + phys * 16) =
-                        make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                    packed[c * 16 + (i >> 1)] = pack16<BF16>(p0, p1);
                 }
             };
             chunk_p(0, s0);
             chunk_p(1, s1);
-            chunk_p(2, s2);
-            chunk_p(3, s3);
+            tmem_store32(tmem_row + tmem_s, packed);
+            tmem_wait_store();
             l_run += row_sum;
-            proxy_fence_async_smem();     // P must be visible to the tensor core's reads of shared memory
-            tc_fence_before();            // ... and this thread's tensor-memory accesses ordered before the arrival
+            tc_fence_before();            // this thread's tensor-memory accesses are ordered before the arrival
             mbar_arrive(&bar_p[b]);
         }
 
@@ -483,14 +530,14 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// (S, H, D) tensor with unit channel stride -> map with boxes of 64 channels x 1 head x 128 rows
+// (S, H, D) tensor with unit channel stride -> map with boxes of 64 channels x 1 head x box_rows rows
 static bool make_map(CUtensorMap *map, const void *base, int seq_len, int heads, long long row_stride_elems,
-                     long long head_stride_elems, bool bf16) {
+                     long long head_stride_elems, bool bf16, int box_rows) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
     const cuuint64_t dims[3] = {(cuuint64_t)kPfDim, (cuuint64_t)heads, (cuuint64_t)seq_len};
     const cuuint64_t strides[2] = {(cuuint64_t)head_stride_elems * 2, (cuuint64_t)row_stride_elems * 2};
-    const cuuint32_t box[3] = {64, 1, (cuuint32_t)kPfRows};
+    const cuuint32_t box[3] = {64, 1, (cuuint32_t)box_rows};
     const cuuint32_t elem_strides[3] = {1, 1, 1};
     return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
               const_cast<void *>(base), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -516,9 +563,9 @@ extern "C" int da_prefill_attention(const void *q, const void *k, const void *v,
     if ((q_row_stride * 2) % 16 != 0 || (kv_row_stride * 2) % 16 != 0) return DA_ERR_ALIGN;
     const bool bf16 = dtype == DA_BF16;
     CUtensorMap mq, mk, mv;
-    if (!da::make_map(&mq, q, seq_len, n_q_heads, q_row_stride, head_dim, bf16) ||
-        !da::make_map(&mk, k, seq_len, n_kv_heads, kv_row_stride, head_dim, bf16) ||
-        !da::make_map(&mv, v, seq_len, n_kv_heads, kv_row_stride, head_dim, bf16))
+    if (!da::make_map(&mq, q, seq_len, n_q_heads, q_row_stride, head_dim, bf16, da::kPfRows) ||
+        !da::make_map(&mk, k, seq_len, n_kv_heads, kv_row_stride, head_dim, bf16, da::kPfKeys) ||
+        !da::make_map(&mv, v, seq_len, n_kv_heads, kv_row_stride, head_dim, bf16, da::kPfKeys))
         return DA_ERR_UNSUPPORTED;
     static bool attr_set[64] = {};
     int dev = 0;
