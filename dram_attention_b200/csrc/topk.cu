@@ -478,6 +478,13 @@ __device__ __forceinline__ void dsmem_st_u64(uint32_t addr, unsigned long long v
     asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(addr), "l"(v) : "memory");
 }
 
+// The fall-back of the cluster kernel, kept out of line so that the common path stays small in the
+// instruction cache.
+__device__ __noinline__ void topk_row_fallback(const float *__restrict__ srow, int n_pages, int k,
+                                               int32_t *__restrict__ dst, unsigned char *smem_raw) {
+    topk_row<0>(srow, n_pages, k, dst, smem_raw);
+}
+
 __global__ void __launch_bounds__(kTopkThreads)
 topk_pages_cluster_kernel(const float *__restrict__ scores, int32_t *__restrict__ page_list, int n_kv_heads, int rep,
                           int n_pages, int k) {
@@ -602,7 +609,7 @@ topk_pages_cluster_kernel(const float *__restrict__ scores, int32_t *__restrict_
     if (lin_levels == 0) {
         // the one-CTA selection over the whole row, by CTA 0 (nobody reads anybody's shared memory from here on)
         cluster_sync_all();
-        if (crank == 0) topk_row<0>(srow, n_pages, k, dst, smem_raw);
+        if (crank == 0) topk_row_fallback(srow, n_pages, k, dst, smem_raw);
         return;
     }
 
