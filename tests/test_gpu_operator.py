@@ -586,6 +586,13 @@ def test_full_size_layer_invariants(da, fused):
     _check_layer_invariants(da, llama_layer_workload(seed=0, steps=4), 4)
 
 
+def test_full_size_layer_with_a_query_redraw(da, fused):
+    """The same at the benchmark's size with the query re-drawn every other step (thousands of
+    misses in one step: the eviction front is overrun, the second attention launch covers whole
+    heads and reads the marked slots from DRAM), in every step layout."""
+    _check_layer_invariants(da, llama_layer_workload(seed=1, steps=5, redraw_every=2), 5)
+
+
 def test_batched_sequences_are_independent(da):
     """Batched decode = one operator per sequence (the reference asserts batch 1,
     dram_attention/dram_attention.py:133): three 64K-token sequences stepped round-robin,
