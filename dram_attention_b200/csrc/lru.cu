@@ -518,6 +518,24 @@ lru_queue_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *d
         }
     }
 
+    // Few misses: the update copies the pages itself.  The pages are known now (not yet the slots they go
+    // to), so the loads from DRAM go out here and are stored at the very end: the host-link latency
+    // hides behind the rest of the update.
+    const bool may_copy = dram_pages != nullptr && n_miss <= inline_max;
+    const int vec_per_page = (int)(page_bytes / 16);
+    const unsigned char *src_h = dram_pages + (size_t)h * n_dram_pages * page_bytes;
+    unsigned char *dst_h = slots + (size_t)h * n_slots * page_bytes;
+    uint4 first[kLruInlineBatch];
+    if (may_copy && n_miss > 0) {
+        __syncthreads();   // mpage is complete
+        const int n_first = n_miss * vec_per_page;
+#pragma unroll
+        for (int b = 0; b < kLruInlineBatch; ++b) {
+            const int i = b * kLruThreads + tid;
+            if (i < n_first) first[b] = ld_stream_16(src_h + (size_t)mpage[i / vec_per_page] * page_bytes + (size_t)(i % vec_per_page) * 16);
+        }
+    }
+
     // ---- 3. victims = the first n_miss slots of the queue that no hit touched ------------------
     int urank[SR];        // rank of this queue position among the untouched ones, or -1
     int n_untouched = 0;
@@ -530,19 +548,8 @@ lru_queue_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *d
         for (int r = 0; r < SR; ++r)
             if (!flag[r]) urank[r] = -1;
     }
-    // Few misses: the update copies the pages itself.  The pages are known now, so the loads from
-    // DRAM go out here and are stored at the very end: the host-link latency hides behind the rest.
-    const bool copy_here = dram_pages != nullptr && n_miss <= inline_max && n_miss <= n_untouched;
-    const int vec_per_page = (int)(page_bytes / 16);
+    const bool copy_here = may_copy && n_miss <= n_untouched;   // (what was loaded for nothing is dropped)
     const int n_vec = copy_here ? n_miss * vec_per_page : 0;
-    const unsigned char *src_h = dram_pages + (size_t)h * n_dram_pages * page_bytes;
-    unsigned char *dst_h = slots + (size_t)h * n_slots * page_bytes;
-    uint4 first[kLruInlineBatch];
-#pragma unroll
-    for (int b = 0; b < kLruInlineBatch; ++b) {
-        const int i = b * kLruThreads + tid;
-        if (i < n_vec) first[b] = ld_stream_16(src_h + (size_t)mpage[i / vec_per_page] * page_bytes + (size_t)(i % vec_per_page) * 16);
-    }
     if (n_miss > n_untouched) {
         // more distinct non-resident pages than slots this call may evict: tables stay as after the hits
         if (tid == 0) atomicOr(status, DA_STATUS_LRU_OVERFLOW);
