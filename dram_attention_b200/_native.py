@@ -41,6 +41,7 @@ _SIGNATURES = {
                                      c_longlong, c_longlong, c_int, c_void_p, c_void_p]),
     "da_rope_qk": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                            c_void_p]),
+    "da_decode_attention_push_next": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int]),
     "da_gather_heads_buffer_bytes": (c_size_t, [c_int, c_int]),
     "da_gather_heads": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,
                                 c_void_p]),

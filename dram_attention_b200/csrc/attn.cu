@@ -268,6 +268,14 @@ struct AttnCall {
     da_stream_t stream = nullptr;
 };
 
+// What da_decode_attention_push_next() left for the next attention call of this host thread.
+struct PeerPush {
+    void *const *bufs = nullptr;
+    const int32_t *seq = nullptr;
+    int rank = 0, world = 0, bytes_per_rank = 0;
+};
+static thread_local PeerPush g_next_push;
+
 static int max_rows_of(int dtype) { return dtype == DA_F32 ? kSimtMaxRows : kAttnMaxRows; }
 
 static size_t partial_bytes(int n_kv_heads, int part_rows, int rows, int head_dim) {
@@ -275,6 +283,8 @@ static size_t partial_bytes(int n_kv_heads, int part_rows, int rows, int head_di
 }
 
 static int run_attention(const AttnCall &c) {
+    const PeerPush push = g_next_push;   // consumed by this call, whatever becomes of it
+    g_next_push = PeerPush();
     if (!c.q || !c.prefix_kv || !c.local_k || !c.local_v || !c.new_k || !c.new_v || !c.out || !c.workspace ||
         !c.status)
         return DA_ERR_NULL;
@@ -294,6 +304,9 @@ static int run_attention(const AttnCall &c) {
         return DA_ERR_ALIGN;
     if (c.phase < 0 || c.phase > 2) return DA_ERR_SHAPE;
     if (c.phase != 0 && c.n_q_tokens != 1) return DA_ERR_UNSUPPORTED;
+    if (push.bufs != nullptr &&
+        (c.n_q_tokens != 1 || (size_t)push.bytes_per_rank != (size_t)c.n_kv_heads * c.rep * c.head_dim * esz))
+        return DA_ERR_SHAPE;
 
     const int tokens_per_launch = max_rows_of(c.dtype) / c.rep;
     const int rows_max = (c.n_q_tokens < tokens_per_launch ? c.n_q_tokens : tokens_per_launch) * c.rep;
@@ -303,6 +316,11 @@ static int run_attention(const AttnCall &c) {
         return DA_ERR_WORKSPACE;
 
     AttnParams p{};
+    p.peer_bufs = reinterpret_cast<uint2 *const *>(push.bufs);
+    p.peer_seq = push.seq;
+    p.peer_rank = push.rank;
+    p.peer_world = push.world;
+    p.peer_words = push.bytes_per_rank / 4;
     p.q = static_cast<const unsigned char *>(c.q);
     p.prefix = static_cast<const unsigned char *>(c.prefix_kv);
     p.prefix_head_stride = c.prefix_head_stride;
@@ -528,6 +546,19 @@ extern "C" int da_decode_attention_phased(int phase, const int32_t *order, const
     c.splits1 = phase_splits(n_kv_heads, phase1_ctas, 1);
     c.splits2 = phase_splits(n_kv_heads, phase2_ctas, 2);
     return da::run_attention(c);
+}
+
+extern "C" int da_decode_attention_push_next(void *const *peer_buffers, const int32_t *seq, int rank, int world,
+                                             int bytes_per_rank) {
+    if (!peer_buffers || !seq) return DA_ERR_NULL;
+    if (world < 1 || world > 16 || rank < 0 || rank >= world || bytes_per_rank < 16 || bytes_per_rank % 16 != 0)
+        return DA_ERR_SHAPE;
+    da::g_next_push.bufs = peer_buffers;
+    da::g_next_push.seq = seq;
+    da::g_next_push.rank = rank;
+    da::g_next_push.world = world;
+    da::g_next_push.bytes_per_rank = bytes_per_rank;
+    return 0;
 }
 
 DA_DEFINE_TRACE_SETTER(trace_set_attn)

@@ -51,6 +51,11 @@ __host__ __device__ inline int attn_splits_phase2(int n_kv_heads) {
 }
 
 struct AttnParams {
+    // KV-head sharding: the CTA that merges a head also sends the head's output rows to every rank's gather
+    // buffer (see gather.cu for the layout and the tag); null when the caller gathers itself
+    uint2 *const *peer_bufs;
+    const int32_t *peer_seq;
+    int peer_rank, peer_world, peer_words;   // words (4 bytes of payload each) per rank
     const unsigned char *q;        // (s_total, n_kv_heads * rep, D)
     const unsigned char *prefix;
     long long prefix_head_stride;  // elements
@@ -323,11 +328,38 @@ __device__ __forceinline__ void merge_splits(const AttnParams &p, int h, int spl
             const int tok = p.q_tok0 + r / p.rep;
             const size_t orow = (size_t)tok * p.n_kv_heads * p.rep + (size_t)h * p.rep + r % p.rep;
             T *dst = reinterpret_cast<T *>(p.out) + orow * D + 4 * c4;
-            dst[0] = from_float<T>(a[k].x * inv);
-            dst[1] = from_float<T>(a[k].y * inv);
-            dst[2] = from_float<T>(a[k].z * inv);
-            dst[3] = from_float<T>(a[k].w * inv);
+            const T v0 = from_float<T>(a[k].x * inv), v1 = from_float<T>(a[k].y * inv),
+                    v2 = from_float<T>(a[k].z * inv), v3 = from_float<T>(a[k].w * inv);
+            dst[0] = v0;
+            dst[1] = v1;
+            dst[2] = v2;
+            dst[3] = v3;
             if (c4 == 0 && p.lse_out) p.lse_out[orow] = (sh_m[r] + log2f(ll)) * 0.6931471805599453f;
+            if (p.peer_bufs != nullptr) {
+                // these four values as payload words {payload, tag} into slot (seq & 1) of every rank's buffer,
+                // at this rank's place (one query token per call: orow is the head row)
+                const int32_t sq = __ldcg(p.peer_seq);
+                const uint32_t tag = (uint32_t)(sq + 1);
+                constexpr int NW = (int)(4 * sizeof(T) / 4);
+                uint32_t w[NW];
+                if constexpr (sizeof(T) == 4) {
+                    w[0] = __float_as_uint((float)v0);
+                    w[1] = __float_as_uint((float)v1);
+                    w[NW - 2] = __float_as_uint((float)v2);
+                    w[NW - 1] = __float_as_uint((float)v3);
+                } else {
+                    auto bits = [](T v) -> uint32_t { return (uint32_t)(*reinterpret_cast<const unsigned short *>(&v)); };
+                    w[0] = bits(v0) | (bits(v1) << 16);
+                    w[NW - 1] = bits(v2) | (bits(v3) << 16);
+                }
+                const size_t word0 = (size_t)(sq & 1) * p.peer_world * p.peer_words + (size_t)p.peer_rank * p.peer_words +
+                                     (orow * D + 4 * c4) * sizeof(T) / 4;
+                for (int g = 0; g < p.peer_world; ++g) {
+                    uint2 *pd = p.peer_bufs[g] + word0;
+#pragma unroll
+                    for (int i = 0; i < NW; ++i) st_word_sys(pd + i, w[i], tag);
+                }
+            }
         }
     }
 }

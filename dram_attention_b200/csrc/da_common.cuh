@@ -157,6 +157,13 @@ static inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, 
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// ---- peer gather words ---------------------------------------------------------------
+// The all-gather of the head shards moves 8-byte words {4 bytes of payload, the step's tag}: one naturally
+// aligned 8-byte store per word arrives whole, so a word that carries the tag carries its payload.
+__device__ __forceinline__ void st_word_sys(uint2 *p, uint32_t payload, uint32_t tag) {
+    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(payload), "r"(tag) : "memory");
+}
+
 // ---- small math ------------------------------------------------------------
 
 __device__ __forceinline__ float fast_exp2(float x) {

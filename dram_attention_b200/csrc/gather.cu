@@ -37,10 +37,6 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     return t;
 }
 
-__device__ __forceinline__ void st_word_sys(uint2 *p, uint32_t payload, uint32_t tag) {
-    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(payload), "r"(tag) : "memory");
-}
-
 __device__ __forceinline__ uint2 ld_word_sys(const uint2 *p) {
     uint2 v;
     asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
@@ -67,8 +63,8 @@ gather_heads_kernel(const uint32_t *__restrict__ local, int words_per_rank, uint
     griddep_wait();   // the rows come from the kernel before this one
     if (tid == 0) trace_stamp(kTraceGather, 0, 2);
 
-    // ---- push ---------------------------------------------------------------------------
-    for (int i = tid; i < total; i += kGatherThreads) {
+    // ---- push (not when the attention kernel has sent the rows itself: local == nullptr) ------------
+    for (int i = tid; local != nullptr && i < total; i += kGatherThreads) {
         const int g = i / words_per_rank, w = i % words_per_rank;
         uint2 *dst = (i == tid ? dst0 : peer_bufs[g]) + slot * slot_words + (size_t)rank * words_per_rank + w;
         st_word_sys(dst, local[w], tag);
@@ -113,7 +109,7 @@ extern "C" size_t da_gather_heads_buffer_bytes(int bytes_per_rank, int world) {
 extern "C" int da_gather_heads(const void *local, int bytes_per_rank, void *const *peer_buffers, int32_t *seq,
                                int rank, int world, void *out, int timeout_us, int32_t *status,
                                da_stream_t stream) {
-    if (!local || !peer_buffers || !seq || !out || !status) return DA_ERR_NULL;
+    if (!peer_buffers || !seq || !out || !status) return DA_ERR_NULL;   // local may be NULL: see the header
     if (world < 1 || world > da::kGatherMaxWorld || rank < 0 || rank >= world) return DA_ERR_SHAPE;
     if (bytes_per_rank < 16 || bytes_per_rank % 16 != 0 || timeout_us < 0) return DA_ERR_SHAPE;
     if ((reinterpret_cast<uintptr_t>(local) | reinterpret_cast<uintptr_t>(out)) & 15) return DA_ERR_ALIGN;

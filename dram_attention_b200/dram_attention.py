@@ -76,6 +76,9 @@ class DRAMAttention(torch.nn.Module):
     # CTAs per KV head of the two launches (0: the library's defaults)
     phase1_ctas = 0
     phase2_ctas = 0
+    # KV-head sharding (set by KVHeadShardedDRAMAttention): (peer buffer array, step counter, rank, world, bytes
+    # per rank) of the peer gather; the attention launches of a one-token step then send the output rows
+    peer_push = None
     selection_sm_budget = 0    # SMs the selection may count on beside the first attention launch of the
                                # two-launch step; 0 = 148 minus that launch's CTAs (one SM each)
 
@@ -306,6 +309,8 @@ class DRAMAttention(torch.nn.Module):
             pos_dev, pos_host = 0, int(start_pos)
         lib = _native.lib()
         lse_ptr = 0 if lse is None else lse.data_ptr()
+        if self.peer_push is not None and seqlen == 1:
+            _native.check(lib.da_decode_attention_push_next(*self.peer_push), "da_decode_attention_push_next")
         if phase:
             lc = self.lru_cache
             _native.check(lib.da_decode_attention_phased(

@@ -48,6 +48,7 @@ class KVHeadShardedDRAMAttention(torch.nn.Module):
     synchronises): call it between steps, or at the latest before the outputs are trusted."""
 
     gather_timeout_us = 0   # 0: the library's default (0.2 s)
+    push_from_attention = True   # one-token steps: the CTA that merges a head sends its rows to the peers itself
 
     def __init__(self, *, n_kv_heads: int, rank: Optional[int] = None, world_size: Optional[int] = None,
                  process_group=None, operator_factory: Optional[Callable] = None, presliced: bool = False,
@@ -89,7 +90,9 @@ class KVHeadShardedDRAMAttention(torch.nn.Module):
         status = torch.zeros(1, dtype=torch.int32, device=local.device)
         return handle, buf, seq, status, nbytes
 
-    def _peer_gather(self, local: torch.Tensor) -> torch.Tensor:
+    def _peer_gather(self, local: torch.Tensor, pushed: bool = False) -> torch.Tensor:
+        """`pushed`: the attention launches of this step have sent the rows already (the operator was given
+        the gather's buffers, see DRAMAttention.peer_push); the kernel then only waits and copies."""
         from . import _native
         handle, buf, seq, status, nbytes = self._peer
         b, s, h, d = local.shape
@@ -98,7 +101,7 @@ class KVHeadShardedDRAMAttention(torch.nn.Module):
         src = local if local.is_contiguous() else local.contiguous()
         with torch.cuda.device(local.device):
             _native.check(_native.lib().da_gather_heads(
-                src.data_ptr(), nbytes, handle.buffer_ptrs_dev, seq.data_ptr(), self.rank, self.world_size,
+                0 if pushed else src.data_ptr(), nbytes, handle.buffer_ptrs_dev, seq.data_ptr(), self.rank, self.world_size,
                 out.data_ptr(), int(self.gather_timeout_us), status.data_ptr(), _native.stream_ptr()),
                 "da_gather_heads")
         return out
@@ -126,11 +129,14 @@ class KVHeadShardedDRAMAttention(torch.nn.Module):
 
     def forward(self, xq, xk, xv, *, start_pos, stage: str, freqs_cis=None):
         extra = {} if freqs_cis is None else {"freqs_cis": freqs_cis}   # rotary embedding inside the call
+        # once the peer gather is set up, a one-token generate step sends its rows from the attention launches
+        pushed = (stage == "generate" and xq.shape[1] == 1 and self._peer is not None
+                  and getattr(self.inner, "peer_push", None) is not None)
         local = self.inner(self._q(xq).contiguous(), self._kv(xk).contiguous(), self._kv(xv).contiguous(),
                            start_pos=start_pos, stage=stage, **extra)
-        return self.all_gather_heads(local)
+        return self.all_gather_heads(local, pushed=pushed)
 
-    def all_gather_heads(self, local: torch.Tensor) -> torch.Tensor:
+    def all_gather_heads(self, local: torch.Tensor, pushed: bool = False) -> torch.Tensor:
         """(1, s, Hq/G, D) on every rank -> (1, s, Hq, D) on every rank."""
         if self.world_size == 1:
             return local
@@ -148,7 +154,10 @@ class KVHeadShardedDRAMAttention(torch.nn.Module):
                     self._peer = None
                     self._peer_failed = self._peer_failed or "another rank could not set up its gather buffer"
             if self._peer is not None:
-                return self._peer_gather(local)
+                if self.push_from_attention and hasattr(self.inner, "peer_push") and self.inner.peer_push is None:
+                    handle, _buf, seq, _status, nbytes = self._peer
+                    self.inner.peer_push = (handle.buffer_ptrs_dev, seq.data_ptr(), self.rank, self.world_size, nbytes)
+                return self._peer_gather(local, pushed)
         if s == 1:
             # rank-major concatenation is the head order; a tensor of its own per call, like the
             # single-GPU operator's result

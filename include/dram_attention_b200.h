@@ -501,7 +501,9 @@ DA_API int da_prefill_attention(const void *q, const void *k, const void *v, voi
  * timed out cannot be mistaken for a result.  The caller has to look at *status (between
  * steps; it is sticky).
  *
- * local         bytes_per_rank bytes, device memory, 16-byte aligned (this rank's rows)
+ * local         bytes_per_rank bytes, device memory, 16-byte aligned (this rank's rows); NULL when the
+ *               attention launch before it has sent them itself (da_decode_attention_push_next): the
+ *               kernel then only waits and copies
  * peer_buffers  DEVICE array of `world` pointers; entry g = rank g's gather buffer of
  *               da_gather_heads_buffer_bytes(bytes_per_rank, world) bytes, mapped into
  *               this process (symmetric / IPC memory), zero before the first call
@@ -510,6 +512,18 @@ DA_API int da_prefill_attention(const void *q, const void *k, const void *v, voi
  * out           world * bytes_per_rank bytes: rank-major concatenation
  * Every rank of the group must make the call for a step; ranks run on different GPUs.
  */
+/*
+ * Makes the NEXT attention call of this host thread (da_decode_attention, _tokens with one token, _fetch,
+ * _phased: both launches of a step need it) send its output rows to the gather buffers of all ranks
+ * straight from the CTA that merges a head, in the word format above, with tag *seq + 1 into slot *seq & 1:
+ * the rows are on their way while the other heads are still being merged, and da_gather_heads(local =
+ * NULL) after the launch only waits and copies.  The setting is consumed by that one call.
+ * bytes_per_rank must equal n_kv_heads * rep * head_dim * element size of the call; the arrays must stay
+ * valid until the launch has run.
+ */
+DA_API int da_decode_attention_push_next(void *const *peer_buffers, const int32_t *seq, int rank, int world,
+                                  int bytes_per_rank);
+
 DA_API size_t da_gather_heads_buffer_bytes(int bytes_per_rank, int world);
 DA_API int da_gather_heads(const void *local, int bytes_per_rank, void *const *peer_buffers,
                     int32_t *seq, int rank, int world, void *out, int timeout_us, int32_t *status,

@@ -555,6 +555,79 @@ def test_decode_attention_bad_position_is_reported(da):
     assert float(lk.abs().sum()) == 0  # nothing appended outside the window
 
 
+@pytest.mark.parametrize("dtype,d,hk,rep", [(torch.bfloat16, 128, 2, 4), (torch.float32, 64, 3, 2)])
+def test_attention_sends_its_rows_to_the_gather_buffers(da, dtype, d, hk, rep):
+    """da_decode_attention_push_next: the CTA that merges a head stores the head's output rows as
+    {payload, tag} words into every rank's gather buffer (two local buffers stand in for two ranks,
+    this launch is rank 1), and da_gather_heads with local = NULL only waits and copies: rank 1's rows
+    of its output are the attention's output, rank 0's are what was put into the buffer by hand.  The
+    setting is used up by one call."""
+    from dram_attention_b200 import _native
+    lib = _native.lib()
+    g = _g(hk * 10 + rep)
+    hq, n_prefix, cap, t0, dram_tokens = hk * rep, 700, 64, 9, 4096
+    prefix = torch.randn(hk, n_prefix, 2, d, generator=g).to(dtype).to(DEV)
+    local_k = torch.randn(cap, hk, d, generator=g).to(dtype).to(DEV)
+    local_v = torch.randn(cap, hk, d, generator=g).to(dtype).to(DEV)
+    q = torch.randn(1, hq, d, generator=g).to(dtype).to(DEV)
+    nk = torch.randn(1, hk, d, generator=g).to(dtype).to(DEV)
+    nv = torch.randn(1, hk, d, generator=g).to(dtype).to(DEV)
+    ws_bytes = lib.da_decode_attention_tokens_workspace_bytes(hk, rep, d, 1)
+    ws = torch.zeros(ws_bytes, dtype=torch.uint8, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    world, rank = 2, 1
+    nbytes = hq * d * q.element_size()
+    words = nbytes // 4
+    total = lib.da_gather_heads_buffer_bytes(nbytes, world)
+    bufs = [torch.zeros(total, dtype=torch.uint8, device=DEV) for _ in range(world)]
+    ptrs = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device=DEV)
+    seq = torch.full((1,), 4, dtype=torch.int32, device=DEV)      # step 4: slot 0, tag 5
+
+    def attend(out):
+        _native.check(lib.da_decode_attention_tokens(
+            q.data_ptr(), 1, prefix.data_ptr(), prefix.stride(0), n_prefix, local_k.data_ptr(), local_v.data_ptr(),
+            local_k.stride(0), local_k.stride(1), cap, nk.data_ptr(), nv.data_ptr(), 0, dram_tokens + t0, dram_tokens,
+            out.data_ptr(), 0, ws.data_ptr(), ws_bytes, status.data_ptr(), hk, rep, d, _native.dtype_code(dtype),
+            _native.stream_ptr()))
+
+    out = torch.empty(1, hq, d, dtype=dtype, device=DEV)
+    _native.check(lib.da_decode_attention_push_next(ptrs.data_ptr(), seq.data_ptr(), rank, world, nbytes))
+    attend(out)
+    torch.cuda.synchronize()
+    assert int(status) == 0
+    for b in bufs:      # both "ranks" got rank 1's rows: slot 0, place 1, every word tagged 5
+        wv = b.view(torch.int32).view(2, world, words, 2)
+        assert bool((wv[0, rank, :, 1] == 5).all()) and bool((wv[0, 1 - rank] == 0).all()) and bool((wv[1] == 0).all())
+        assert torch.equal(wv[0, rank, :, 0].contiguous().view(dtype).view(1, hq, d), out)
+    # rank 0's rows by hand, then the gather that only waits and copies
+    other = torch.randn(1, hq, d, generator=g).to(dtype).to(DEV)
+    mine = bufs[rank].view(torch.int32).view(2, world, words, 2)
+    mine[0, 0, :, 0] = other.view(torch.int32).view(-1)
+    mine[0, 0, :, 1] = 5
+    gathered = torch.zeros(world, hq, d, dtype=dtype, device=DEV)
+    _native.check(lib.da_gather_heads(0, nbytes, ptrs.data_ptr(), seq.data_ptr(), rank, world, gathered.data_ptr(), 2000,
+                                      status.data_ptr(), _native.stream_ptr()))
+    torch.cuda.synchronize()
+    assert int(status) == 0 and int(seq) == 5
+    assert torch.equal(gathered[1:2], out) and torch.equal(gathered[0:1], other)
+    # the setting was used up: a second launch sends nothing
+    for b in bufs:
+        b.zero_()
+    out2 = torch.empty_like(out)
+    attend(out2)
+    torch.cuda.synchronize()
+    assert torch.equal(out2, out) and all(int(b.count_nonzero()) == 0 for b in bufs)
+    # a size that does not match the call is refused (and uses the setting up)
+    _native.check(lib.da_decode_attention_push_next(ptrs.data_ptr(), seq.data_ptr(), rank, world, nbytes + 16))
+    rc = lib.da_decode_attention_tokens(
+        q.data_ptr(), 1, prefix.data_ptr(), prefix.stride(0), n_prefix, local_k.data_ptr(), local_v.data_ptr(),
+        local_k.stride(0), local_k.stride(1), cap, nk.data_ptr(), nv.data_ptr(), 0, dram_tokens + t0, dram_tokens,
+        out2.data_ptr(), 0, ws.data_ptr(), ws_bytes, status.data_ptr(), hk, rep, d, _native.dtype_code(dtype),
+        _native.stream_ptr())
+    assert rc == -2
+    assert lib.da_decode_attention_push_next(ptrs.data_ptr(), seq.data_ptr(), 2, world, nbytes) == -2
+
+
 # -------------------------------------------------------------------- rope ----
 
 @pytest.mark.parametrize("name", ["f32", "bf16"])
