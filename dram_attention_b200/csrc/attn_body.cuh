@@ -245,8 +245,11 @@ __device__ __forceinline__ void decode_attention_body(const AttnParams &p, unsig
     }
     __syncthreads();
     if (tid == 0) {
-        __threadfence();   // the CTA's rows (ordered before this thread by the barrier) before its ticket
-        const unsigned int ticket = atomicAdd(&p.counters[h], 1u);
+        // The ticket releases this CTA's rows (ordered before this thread by the barrier) and acquires the rows
+        // of every CTA that took a ticket before: one acq_rel read-modify-write at GPU scope instead of a fence
+        // on either side.  The barrier below carries the acquire to the other threads of the CTA.
+        unsigned int ticket;
+        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(ticket) : "l"(p.counters + h) : "memory");
         sh_last = (ticket == (unsigned int)(p.ticket_target - 1));
     }
     __syncthreads();
@@ -257,12 +260,11 @@ __device__ __forceinline__ void decode_attention_body(const AttnParams &p, unsig
     if (!sh_last) return;
 
     // ---- the CTA of this head that finished last (of both launches, when there are two) --------
-    __threadfence();   // the other CTAs fenced their rows before their tickets: pair that here
     // a head that phase 2 redid: phase 1's rows (the first in the workspace) are left out
     merge_splits<T, D, THREADS>(p, h, p.part_rows, rows, p.phase != 0 ? p.redo + h : nullptr, p.splits1, smem,
                                 WARPS * STAGES * STAGEB);
     // every CTA of this head is done with the eviction front: the one the LRU update left becomes current
-    if (p.phase != 0 && tid == 0) p.flip[h] ^= 1;
+    if (p.phase != 0 && tid == 0) atomicXor(p.flip + h, 1);   // (no result wanted: the CTA does not wait for it)
     if (tid == 0) p.counters[h] = 0u;
     if (tid == 0) trace_stamp(trace_kernel, trace_cta, 1);
 }
