@@ -461,7 +461,9 @@ lru_queue_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *d
         qs[r] = r * kLruThreads + tid < n_slots ? min(max(v, 0), n_slots - 1) : -1;
     }
     // the page held by the slots at the head of the queue, where the victims come from
-    const int sd0 = qs[0] >= 0 ? s2d[qs[0]] : -1;
+    int sd[SR];
+#pragma unroll
+    for (int r = 0; r < SR; ++r) sd[r] = qs[r] >= 0 ? s2d[qs[r]] : -1;
 
     // slot_source is rewritten by every call: -1 everywhere, then (after several barriers) the
     // marks of this call's misses
@@ -564,7 +566,7 @@ lru_queue_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *d
                 const int j = urank[r];
                 const int v = qs[r];
                 const int p = mpage[j];
-                const int old = r == 0 ? sd0 : s2d[v];
+                const int old = sd[r];
                 if (old >= 0 && old < n_dram_pages) d2s[old] = -1;
                 s2d[v] = p;
                 d2s[p] = v;
@@ -625,8 +627,9 @@ lru_queue_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *d
         const int cap = split_cap > 0 ? min(split_cap, n_slots) : n_slots;
         n_front_io[(size_t)(1 - cur) * gridDim.x + h] = cap;
         split_redo[h] = sh_redo;     // (the barrier after round 4 orders its writes before this read)
-        split_redo[gridDim.x + h] += n_miss;        // running totals, for whoever wants to watch the cache
-        split_redo[2 * gridDim.x + h] += sh_redo;
+        // running totals, for whoever wants to watch the cache (posted: the CTA does not wait for the old values)
+        if (n_miss) atomicAdd(split_redo + gridDim.x + h, n_miss);
+        if (sh_redo) atomicAdd(split_redo + 2 * gridDim.x + h, sh_redo);
         if (split_advance) split_flip[h] = 1 - cur;
     }
     if (g_trace_buf != nullptr) {
