@@ -122,9 +122,12 @@ __device__ __forceinline__ LaunchUnits launch_units(const AttnParams &p, int h, 
     if (p.phase == 0) {
         lu.units_slots = (p.n_prefix_tokens + kUnitTokens - 1) / kUnitTokens;
     } else {
+        // (the front sizes of both queue copies are read beside the flip word, not after it: one round trip less
+        // before the first copy of a launch can be issued)
+        const int nf0 = p.n_evictable[h], nf1 = p.n_evictable[p.n_kv_heads + h];
         const int cur = p.flip[h] & 1;
         const int32_t *order = p.order + ((size_t)cur * p.n_kv_heads + h) * p.n_slots;
-        const int n_ev = min(max(p.n_evictable[cur * p.n_kv_heads + h], 0), p.n_slots);
+        const int n_ev = min(max(cur ? nf1 : nf0, 0), p.n_slots);
         if (p.phase == 1) {
             lu.units_slots = (p.n_slots - n_ev) * lu.ups;
             lu.order = order;
