@@ -379,17 +379,6 @@ lru_update_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *
 }
 
 
-// 16-byte load that bypasses L1 (page payloads in pinned host memory are read once)
-__device__ __forceinline__ uint4 ld_stream_16(const void *p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
-}
-
-constexpr int kLruInlineBatch = 4;   // 16-byte loads a thread keeps in flight while it copies pages
-
 // With the eviction queue.  SR = slots per thread (n_slots <= SR * 1024), LR = list entries per thread.
 //   queue      [2][n_kv_heads][n_slots]: copy flip[h] is read (slots in eviction order), the other written
 //   n_front    [2][n_kv_heads]: how many slots at the head of the queue the attention leaves to its
@@ -402,7 +391,7 @@ lru_queue_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *d
                  int32_t *__restrict__ n_miss_out, int32_t *slot_source, int32_t *queue, int32_t *n_front_io,
                  int32_t *split_flip, int32_t *split_redo, int split_cap, int split_advance,
                  const unsigned char *dram_pages, unsigned char *slots, unsigned long long page_bytes,
-                 int inline_max, int32_t *status) {
+                 int inline_max, unsigned int stage_off, int32_t *status) {
     if (threadIdx.x == 0) trace_stamp(2, blockIdx.x, 0);
     griddep_wait();   // the page list comes from the kernel before this one
     if (threadIdx.x == 0) trace_stamp(2, blockIdx.x, 2);
@@ -413,8 +402,11 @@ lru_queue_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *d
     int *mpage = tval + table;           // [list_len] miss pages in list order
     int *vslot = mpage + list_len;       // [list_len] victims in queue order
     unsigned char *touched = reinterpret_cast<unsigned char *>(vslot + list_len);   // [n_slots] hit or victim
+    // [inline_max pages] where the missed pages wait between their asynchronous copy from DRAM and their slots
+    uint4 *stage = reinterpret_cast<uint4 *>(reinterpret_cast<unsigned char *>(smem_i) + stage_off);
     __shared__ int wsum[kLruWarps];
     __shared__ int sh_redo;
+    __shared__ __align__(8) uint64_t stage_bar;   // completion of the page copies into the staging area
 
     const int h = blockIdx.x;
     const int tid = threadIdx.x;
@@ -424,6 +416,10 @@ lru_queue_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *d
     int32_t *tim = access_time + (size_t)h * n_slots;
     int32_t *mp_out = miss_pages + (size_t)h * list_len;
     int32_t *ms_out = miss_slots + (size_t)h * list_len;
+    if (tid == 0) {
+        mbar_init(&stage_bar, 1);
+        mbar_fence_init();
+    }
 
     // ---- all independent global reads first (both copies of the queue, so that nothing waits for
     // the flip word) --------------------------------------------------------------------------
@@ -521,20 +517,21 @@ lru_queue_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *d
     }
 
     // Few misses: the update copies the pages itself.  The pages are known now (not yet the slots they go
-    // to), so the loads from DRAM go out here and are stored at the very end: the host-link latency
-    // hides behind the rest of the update.
+    // to), so they set out from DRAM here, one bulk copy (TMA) per page into shared memory (no thread holds
+    // or waits for them), and are moved on to their slots at the very end: the host-link latency of up to
+    // inline_max pages hides behind the rest of the update.
     const bool may_copy = dram_pages != nullptr && n_miss <= inline_max;
     const int vec_per_page = (int)(page_bytes / 16);
     const unsigned char *src_h = dram_pages + (size_t)h * n_dram_pages * page_bytes;
     unsigned char *dst_h = slots + (size_t)h * n_slots * page_bytes;
-    uint4 first[kLruInlineBatch];
-    if (may_copy && n_miss > 0) {
+    const bool in_flight = may_copy && n_miss > 0;
+    if (in_flight) {
         __syncthreads();   // mpage is complete
-        const int n_first = n_miss * vec_per_page;
-#pragma unroll
-        for (int b = 0; b < kLruInlineBatch; ++b) {
-            const int i = b * kLruThreads + tid;
-            if (i < n_first) first[b] = ld_stream_16(src_h + (size_t)mpage[i / vec_per_page] * page_bytes + (size_t)(i % vec_per_page) * 16);
+        if (tid == 0) {
+            mbar_arrive_expect_tx(&stage_bar, (uint32_t)(n_miss * page_bytes));
+            for (int j = 0; j < n_miss; ++j)
+                bulk_copy_g2s(reinterpret_cast<unsigned char *>(stage) + (size_t)j * page_bytes,
+                              src_h + (size_t)mpage[j] * page_bytes, (uint32_t)page_bytes, &stage_bar);
         }
     }
 
@@ -598,27 +595,14 @@ lru_queue_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *d
             if (flag[r]) q_out[n_untouched - n_miss + pos[r]] = r * kLruThreads + tid;
     }
 
-    // ---- 6. store the copied pages --------------------------------------------------------------
-    if (n_miss > 0) {   // (not after an overflow)
-#pragma unroll
-        for (int b = 0; b < kLruInlineBatch; ++b) {
-            const int i = b * kLruThreads + tid;
-            if (i < n_vec)
-                *reinterpret_cast<uint4 *>(dst_h + (size_t)vslot[i / vec_per_page] * page_bytes + (size_t)(i % vec_per_page) * 16) = first[b];
-        }
-        for (int i0 = kLruInlineBatch * kLruThreads; i0 < n_vec; i0 += kLruInlineBatch * kLruThreads) {
-            uint4 v[kLruInlineBatch];
-#pragma unroll
-            for (int b = 0; b < kLruInlineBatch; ++b) {
-                const int i = i0 + b * kLruThreads + tid;
-                if (i < n_vec) v[b] = ld_stream_16(src_h + (size_t)mpage[i / vec_per_page] * page_bytes + (size_t)(i % vec_per_page) * 16);
-            }
-#pragma unroll
-            for (int b = 0; b < kLruInlineBatch; ++b) {
-                const int i = i0 + b * kLruThreads + tid;
-                if (i < n_vec)
-                    *reinterpret_cast<uint4 *>(dst_h + (size_t)vslot[i / vec_per_page] * page_bytes + (size_t)(i % vec_per_page) * 16) = v[b];
-            }
+    // ---- 6. the copied pages go from shared memory to their slots --------------------------------
+    if (in_flight) {
+        // (waited for also when the pages are dropped: nothing may land in shared memory after the CTA has gone)
+        const bool landed = mbar_wait_bounded(&stage_bar, 0);
+        if (!landed && tid == 0) atomicOr(status, DA_STATUS_WAIT_TIMEOUT);
+        if (landed && n_miss > 0) {   // (not after an overflow)
+            for (int i = tid; i < n_vec; i += kLruThreads)
+                *reinterpret_cast<uint4 *>(dst_h + (size_t)vslot[i / vec_per_page] * page_bytes + (size_t)(i % vec_per_page) * 16) = stage[i];
         }
     }
     if (tid == 0) {
@@ -644,7 +628,7 @@ static size_t lru_smem_bytes(int n_slots, int list_len) {
 
 static size_t lru_queue_smem_bytes(int n_slots, int list_len) {
     return ((size_t)2 * lru_table_size(list_len) + 2 * (size_t)list_len) * sizeof(int) +
-           (((size_t)n_slots + 15) & ~(size_t)15);
+           (((size_t)n_slots + 15) & ~(size_t)15);   // a multiple of 16: the page staging area follows
 }
 
 constexpr size_t kLruMaxSmem = 227 * 1024 - 4096;
@@ -674,12 +658,13 @@ static cudaError_t launch_lru(const LruArgs &a, cudaStream_t stream) {
         attr_set[dev] = true;
     }
     if (a.queue) {
+        const size_t tables = lru_queue_smem_bytes(a.n_slots, a.list_len);
         return launch_dependent(lru_queue_kernel<SR, LR>, dim3(a.n_kv_heads), dim3(kLruThreads),
-                                lru_queue_smem_bytes(a.n_slots, a.list_len), stream, a.page_list, a.list_len,
+                                tables + (size_t)a.inline_max * a.page_bytes, stream, a.page_list, a.list_len,
                                 a.dram_to_slot, a.n_dram_pages, a.slot_to_dram, a.access_time, a.n_slots, a.step,
                                 a.miss_pages, a.miss_slots, a.n_miss, a.slot_source, a.queue, a.n_front,
                                 a.split_flip, a.split_redo, a.split_cap, a.split_advance, a.dram_pages, a.slots,
-                                a.page_bytes, a.inline_max, a.status);
+                                a.page_bytes, a.inline_max, (unsigned int)tables, a.status);
     }
     return launch_dependent(lru_update_kernel<SR, LR>, dim3(a.n_kv_heads), dim3(kLruThreads),
                             lru_smem_bytes(a.n_slots, a.list_len), stream, a.page_list, a.list_len,
@@ -711,12 +696,17 @@ extern "C" int da_lru_update(const int32_t *page_list, int list_len, int32_t *dr
     // pages are copied by the update itself only with a queue, 16-byte granularity and both ends given
     const bool can_copy = evict_queue && dram_pages && slots && inline_fetch_max > 0 && page_bytes >= 16 &&
                           page_bytes % 16 == 0 && (((uintptr_t)dram_pages | (uintptr_t)slots) & 15) == 0;
+    // the pages it copies wait in shared memory beside the tables: as many as fit
+    if (can_copy) {
+        const size_t room = (da::kLruMaxSmem - smem) / page_bytes;
+        if ((size_t)inline_fetch_max > room) inline_fetch_max = (int)room;
+    }
     da::LruArgs a{page_list, list_len, dram_to_slot, n_dram_pages, slot_to_dram, access_time, n_slots, step,
                   n_kv_heads, miss_pages, miss_slots, n_miss, slot_source, evict_queue, front_count, split_flip,
                   split_redo, split_cap, split_advance,
                   can_copy ? static_cast<const unsigned char *>(dram_pages) : nullptr,
                   can_copy ? static_cast<unsigned char *>(slots) : nullptr, (unsigned long long)page_bytes,
-                  can_copy ? inline_fetch_max : 0, status};
+                  can_copy && inline_fetch_max > 0 ? inline_fetch_max : 0, status};
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     cudaError_t e;
     if (n_slots <= 2048 && list_len <= 1024) e = da::launch_lru<2, 1>(a, s);

@@ -189,10 +189,13 @@ DA_API int da_topk_pages_wide(const float *scores, int32_t *page_list,
  * dram_pages, slots, page_bytes, inline_fetch_max  optional (queue only): when a head misses at
  *             most inline_fetch_max pages, the call copies them from dram_pages (n_kv_heads,
  *             n_dram_pages, page_bytes; pinned, device-mapped host memory) into slots
- *             (n_kv_heads, n_slots, page_bytes) itself -- the loads overlap the rest of the update
- *             -- and leaves their slot_source entries at -1.  page_bytes a multiple of 16, both
- *             bases 16-byte aligned.  NULL / 0: the pages are left to da_fetch_pages or to the
- *             attention kernel.
+ *             (n_kv_heads, n_slots, page_bytes) itself -- one bulk copy (TMA) per page into
+ *             shared memory as soon as the missed pages are known, moved on to the slots at the
+ *             end, so that the host-link latency overlaps the rest of the update; the wait is
+ *             bounded (DA_STATUS_WAIT_TIMEOUT) -- and leaves their slot_source entries at -1.
+ *             inline_fetch_max is lowered to what fits into shared memory beside the tables.
+ *             page_bytes a multiple of 16, both bases 16-byte aligned.  NULL / 0: the pages are
+ *             left to da_fetch_pages or to the attention kernel.
  * status      (1) int32, bits or-ed in
  * Requires n_slots <= 8192, list_len <= 8192 and the shared-memory plan to fit 222 KiB: with a
  * queue 2*T + 2*list_len ints + n_slots bytes, without 2*T + 2*n_slots + 3*list_len ints
