@@ -270,9 +270,9 @@ struct AttnCall {
 
 // What da_decode_attention_push_next() left for the next attention call of this host thread.
 struct PeerPush {
-    void *const *bufs = nullptr;
+    void *bufs[kAttnMaxPeers] = {};
     const int32_t *seq = nullptr;
-    int rank = 0, world = 0, bytes_per_rank = 0;
+    int rank = 0, world = 0, bytes_per_rank = 0;   // world == 0: nothing set
 };
 static thread_local PeerPush g_next_push;
 
@@ -304,7 +304,7 @@ static int run_attention(const AttnCall &c) {
         return DA_ERR_ALIGN;
     if (c.phase < 0 || c.phase > 2) return DA_ERR_SHAPE;
     if (c.phase != 0 && c.n_q_tokens != 1) return DA_ERR_UNSUPPORTED;
-    if (push.bufs != nullptr &&
+    if (push.world > 0 &&
         (c.n_q_tokens != 1 || (size_t)push.bytes_per_rank != (size_t)c.n_kv_heads * c.rep * c.head_dim * esz))
         return DA_ERR_SHAPE;
 
@@ -316,7 +316,7 @@ static int run_attention(const AttnCall &c) {
         return DA_ERR_WORKSPACE;
 
     AttnParams p{};
-    p.peer_bufs = reinterpret_cast<uint2 *const *>(push.bufs);
+    for (int g = 0; g < kAttnMaxPeers; ++g) p.peer_buf[g] = static_cast<uint2 *>(push.bufs[g]);
     p.peer_seq = push.seq;
     p.peer_rank = push.rank;
     p.peer_world = push.world;
@@ -551,9 +551,13 @@ extern "C" int da_decode_attention_phased(int phase, const int32_t *order, const
 extern "C" int da_decode_attention_push_next(void *const *peer_buffers, const int32_t *seq, int rank, int world,
                                              int bytes_per_rank) {
     if (!peer_buffers || !seq) return DA_ERR_NULL;
-    if (world < 1 || world > 16 || rank < 0 || rank >= world || bytes_per_rank < 16 || bytes_per_rank % 16 != 0)
+    if (world < 1 || world > da::kAttnMaxPeers || rank < 0 || rank >= world || bytes_per_rank < 16 ||
+        bytes_per_rank % 16 != 0)
         return DA_ERR_SHAPE;
-    da::g_next_push.bufs = peer_buffers;
+    for (int g = 0; g < world; ++g) {
+        if (!peer_buffers[g]) return DA_ERR_NULL;
+        da::g_next_push.bufs[g] = peer_buffers[g];
+    }
     da::g_next_push.seq = seq;
     da::g_next_push.rank = rank;
     da::g_next_push.world = world;

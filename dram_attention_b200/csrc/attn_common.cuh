@@ -50,10 +50,14 @@ __host__ __device__ inline int attn_splits_phase2(int n_kv_heads) {
     return s;
 }
 
+constexpr int kAttnMaxPeers = 16;
+
 struct AttnParams {
     // KV-head sharding: the CTA that merges a head also sends the head's output rows to every rank's gather
     // buffer (see gather.cu for the layout and the tag); null when the caller gathers itself
-    uint2 *const *peer_bufs;
+    // (the pointers travel in the kernel's parameters, so that the store loop at the end of a merge has no
+    // dependent load in it; peer_world == 0: nothing is sent)
+    uint2 *peer_buf[kAttnMaxPeers];
     const int32_t *peer_seq;
     int peer_rank, peer_world, peer_words;   // words (4 bytes of payload each) per rank
     const unsigned char *q;        // (s_total, n_kv_heads * rep, D)
@@ -240,6 +244,7 @@ __device__ __forceinline__ void merge_splits(const AttnParams &p, int h, int spl
     constexpr int MAXE = (kAttnMaxRows * VPR + THREADS - 1) / THREADS;   // output float4 per thread
     __shared__ float sh_m[kAttnMaxRows], sh_l[kAttnMaxRows];
     const int tid = threadIdx.x;
+    const int32_t peer_step = p.peer_world > 0 ? __ldcg(p.peer_seq) : 0;   // (needed at the very end: read now)
     const float *hp = p.partials + ((size_t)h * p.part_rows * rows) * PW;
     const int n = splits * rows;
     float *wgt = reinterpret_cast<float *>(smem);   // [n] max, then weight
@@ -338,10 +343,10 @@ __device__ __forceinline__ void merge_splits(const AttnParams &p, int h, int spl
             dst[2] = v2;
             dst[3] = v3;
             if (c4 == 0 && p.lse_out) p.lse_out[orow] = (sh_m[r] + log2f(ll)) * 0.6931471805599453f;
-            if (p.peer_bufs != nullptr) {
+            if (p.peer_world > 0) {
                 // these four values as payload words {payload, tag} into slot (seq & 1) of every rank's buffer,
                 // at this rank's place (one query token per call: orow is the head row)
-                const int32_t sq = __ldcg(p.peer_seq);
+                const int32_t sq = peer_step;
                 const uint32_t tag = (uint32_t)(sq + 1);
                 constexpr int NW = (int)(4 * sizeof(T) / 4);
                 uint32_t w[NW];
@@ -357,10 +362,13 @@ __device__ __forceinline__ void merge_splits(const AttnParams &p, int h, int spl
                 }
                 const size_t word0 = (size_t)(sq & 1) * p.peer_world * p.peer_words + (size_t)p.peer_rank * p.peer_words +
                                      (orow * D + 4 * c4) * sizeof(T) / 4;
-                for (int g = 0; g < p.peer_world; ++g) {
-                    uint2 *pd = p.peer_bufs[g] + word0;
 #pragma unroll
-                    for (int i = 0; i < NW; ++i) st_word_sys(pd + i, w[i], tag);
+                for (int g = 0; g < kAttnMaxPeers; ++g) {
+                    if (g < p.peer_world) {
+                        uint2 *pd = p.peer_buf[g] + word0;
+#pragma unroll
+                        for (int i = 0; i < NW; ++i) st_word_sys(pd + i, w[i], tag);
+                    }
                 }
             }
         }

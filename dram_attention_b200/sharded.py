@@ -155,8 +155,11 @@ class KVHeadShardedDRAMAttention(torch.nn.Module):
                     self._peer_failed = self._peer_failed or "another rank could not set up its gather buffer"
             if self._peer is not None:
                 if self.push_from_attention and hasattr(self.inner, "peer_push") and self.inner.peer_push is None:
+                    import ctypes
                     handle, _buf, seq, _status, nbytes = self._peer
-                    self.inner.peer_push = (handle.buffer_ptrs_dev, seq.data_ptr(), self.rank, self.world_size, nbytes)
+                    self._peer_host_ptrs = (ctypes.c_void_p * self.world_size)(*[int(x) for x in handle.buffer_ptrs])
+                    self.inner.peer_push = (ctypes.cast(self._peer_host_ptrs, ctypes.c_void_p), seq.data_ptr(),
+                                            self.rank, self.world_size, nbytes)
                 return self._peer_gather(local, pushed)
         if s == 1:
             # rank-major concatenation is the head order; a tensor of its own per call, like the

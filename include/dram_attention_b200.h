@@ -521,8 +521,9 @@ DA_API int da_prefill_attention(const void *q, const void *k, const void *v, voi
  * straight from the CTA that merges a head, in the word format above, with tag *seq + 1 into slot *seq & 1:
  * the rows are on their way while the other heads are still being merged, and da_gather_heads(local =
  * NULL) after the launch only waits and copies.  The setting is consumed by that one call.
- * bytes_per_rank must equal n_kv_heads * rep * head_dim * element size of the call; the arrays must stay
- * valid until the launch has run.
+ * peer_buffers is a HOST array of `world` device pointers (the same buffers da_gather_heads is given as a
+ * device array; they are copied into the launch's parameters), seq device memory.  bytes_per_rank must equal
+ * n_kv_heads * rep * head_dim * element size of the call.
  */
 DA_API int da_decode_attention_push_next(void *const *peer_buffers, const int32_t *seq, int rank, int world,
                                   int bytes_per_rank);

@@ -580,7 +580,10 @@ def test_attention_sends_its_rows_to_the_gather_buffers(da, dtype, d, hk, rep):
     words = nbytes // 4
     total = lib.da_gather_heads_buffer_bytes(nbytes, world)
     bufs = [torch.zeros(total, dtype=torch.uint8, device=DEV) for _ in range(world)]
-    ptrs = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device=DEV)
+    ptrs = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device=DEV)     # for the gather kernel
+    import ctypes
+    host_ptrs = (ctypes.c_void_p * world)(*[b.data_ptr() for b in bufs])                # for the attention launch
+    host_ptrs_p = ctypes.cast(host_ptrs, ctypes.c_void_p)
     seq = torch.full((1,), 4, dtype=torch.int32, device=DEV)      # step 4: slot 0, tag 5
 
     def attend(out):
@@ -591,7 +594,7 @@ def test_attention_sends_its_rows_to_the_gather_buffers(da, dtype, d, hk, rep):
             _native.stream_ptr()))
 
     out = torch.empty(1, hq, d, dtype=dtype, device=DEV)
-    _native.check(lib.da_decode_attention_push_next(ptrs.data_ptr(), seq.data_ptr(), rank, world, nbytes))
+    _native.check(lib.da_decode_attention_push_next(host_ptrs_p, seq.data_ptr(), rank, world, nbytes))
     attend(out)
     torch.cuda.synchronize()
     assert int(status) == 0
@@ -618,14 +621,14 @@ def test_attention_sends_its_rows_to_the_gather_buffers(da, dtype, d, hk, rep):
     torch.cuda.synchronize()
     assert torch.equal(out2, out) and all(int(b.count_nonzero()) == 0 for b in bufs)
     # a size that does not match the call is refused (and uses the setting up)
-    _native.check(lib.da_decode_attention_push_next(ptrs.data_ptr(), seq.data_ptr(), rank, world, nbytes + 16))
+    _native.check(lib.da_decode_attention_push_next(host_ptrs_p, seq.data_ptr(), rank, world, nbytes + 16))
     rc = lib.da_decode_attention_tokens(
         q.data_ptr(), 1, prefix.data_ptr(), prefix.stride(0), n_prefix, local_k.data_ptr(), local_v.data_ptr(),
         local_k.stride(0), local_k.stride(1), cap, nk.data_ptr(), nv.data_ptr(), 0, dram_tokens + t0, dram_tokens,
         out2.data_ptr(), 0, ws.data_ptr(), ws_bytes, status.data_ptr(), hk, rep, d, _native.dtype_code(dtype),
         _native.stream_ptr())
     assert rc == -2
-    assert lib.da_decode_attention_push_next(ptrs.data_ptr(), seq.data_ptr(), 2, world, nbytes) == -2
+    assert lib.da_decode_attention_push_next(host_ptrs_p, seq.data_ptr(), 2, world, nbytes) == -2
 
 
 # -------------------------------------------------------------------- rope ----
