@@ -60,7 +60,10 @@ gather_heads_kernel(const uint32_t *__restrict__ local, int words_per_rank, uint
     uint2 *dst0 = nullptr;
     if (tid < total) dst0 = peer_bufs[tid / words_per_rank];   // first target of this thread, read early
     __syncthreads();
-    griddep_wait();   // the rows come from the kernel before this one
+    // With rows of its own to send, the kernel needs the launch before it complete first.  Without (the
+    // attention launch has sent them, every word vouched for by its tag), that wait moves to the end, behind
+    // the wait for the other ranks.
+    if (local != nullptr) griddep_wait();
     if (tid == 0) trace_stamp(kTraceGather, 0, 2);
 
     // ---- push (not when the attention kernel has sent the rows itself: local == nullptr) ------------
@@ -89,6 +92,7 @@ gather_heads_kernel(const uint32_t *__restrict__ local, int words_per_rank, uint
         out[i] = v.x;
     }
     if (late) sh_timeout = 1;
+    if (local == nullptr) griddep_wait();   // nothing after this kernel starts before the launch before it is complete
     __syncthreads();
     if (tid == 0) {
         if (sh_timeout) atomicOr(status, DA_STATUS_WAIT_TIMEOUT);
