@@ -188,6 +188,30 @@ score_pages_mma_kernel(const T *__restrict__ q, const T *__restrict__ summaries,
     const int row = lane >> 2;   // query row (A, C) and page inside the n-tile (B)
     const int qd = lane & 3;
 
+    const uint4 *base = reinterpret_cast<const uint4 *>(summaries + (size_t)hk * n_pages * 2 * D);
+    float *out = scores + ((size_t)(tok * n_kv_heads + hk) * REP) * n_pages;
+    const int n_tiles = (n_pages + 7) >> 3;
+    const int workers = gridDim.x * kScoreWarps;
+    // warp-major worker ids: the warps that get one tile more are spread over all CTAs
+    const int worker = warp * gridDim.x + blockIdx.x;
+
+    // two page tiles in flight per warp; the first two set out before anything waits for the query
+    uint4 b[2][NI];
+    int page0[2];
+    auto load_tiles = [&](int t0) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int tile = t0 + u * workers;
+            page0[u] = tile < n_tiles ? tile * 8 : -1;
+            int pg = (page0[u] < 0 ? 0 : page0[u]) + row;
+            if (pg >= n_pages) pg = n_pages - 1;
+            const uint4 *src = base + (size_t)pg * CHUNKS + qd;
+#pragma unroll
+            for (int i = 0; i < NI; ++i) b[u][i] = __ldcs(src + 4 * i);
+        }
+    };
+    if (worker < n_tiles) load_tiles(worker);
+
     // A fragments: [min(q,0) | max(q,0)] of query row `row`, chunk permutation as for B
     uint32_t a0[2 * NI], a2[2 * NI];
     {
@@ -210,26 +234,7 @@ score_pages_mma_kernel(const T *__restrict__ q, const T *__restrict__ summaries,
         }
     }
 
-    const uint4 *base = reinterpret_cast<const uint4 *>(summaries + (size_t)hk * n_pages * 2 * D);
-    float *out = scores + ((size_t)(tok * n_kv_heads + hk) * REP) * n_pages;
-    const int n_tiles = (n_pages + 7) >> 3;
-    const int workers = gridDim.x * kScoreWarps;
-    // warp-major worker ids: the warps that get one tile more are spread over all CTAs
-    const int worker = warp * gridDim.x + blockIdx.x;
-
-    for (int t0 = worker; t0 < n_tiles; t0 += 2 * workers) {
-        uint4 b[2][NI];
-        int page0[2];
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            const int tile = t0 + u * workers;
-            page0[u] = tile < n_tiles ? tile * 8 : -1;
-            int pg = (page0[u] < 0 ? 0 : page0[u]) + row;
-            if (pg >= n_pages) pg = n_pages - 1;
-            const uint4 *src = base + (size_t)pg * CHUNKS + qd;
-#pragma unroll
-            for (int i = 0; i < NI; ++i) b[u][i] = __ldcs(src + 4 * i);
-        }
+    for (int t0 = worker; t0 < n_tiles;) {
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
             if (page0[u] < 0) continue;  // warp-uniform
@@ -245,6 +250,8 @@ score_pages_mma_kernel(const T *__restrict__ q, const T *__restrict__ summaries,
                 if (pg + 1 < n_pages) out[(size_t)row * n_pages + pg + 1] = c[1];
             }
         }
+        t0 += 2 * workers;
+        if (t0 < n_tiles) load_tiles(t0);
     }
     if (g_trace_buf != nullptr) {
         __syncthreads();
