@@ -65,8 +65,15 @@ __device__ __forceinline__ void decode_attention_body(const AttnParams &p, unsig
         griddep_launch_dependents();   // a dependent launch after this one (the gather of the head shards) may move in
     }
 
-    // ---- position and unit range ------------------------------------------------
+    // ---- everything the CTA has to read before it can plan sets out together: the position, the state of the
+    //      eviction queue, the query rows (the first instruction that needs any of them is in Math::init);
+    //      one round trip to memory instead of one after the other ------------------------------------
     const int pos = p.start_pos_dev ? *p.start_pos_dev : p.start_pos_host;
+    const FrontWords fw = load_front(p, h);
+    typename Math::State st;
+    Math::init(st, p, h, lane, rows);
+
+    // ---- position and unit range ------------------------------------------------
     int t0 = pos - p.dram_tokens;   // index of the first new token in the local window
     bool pos_ok = true;
     if (t0 < 0 || t0 + p.s_total > p.local_capacity) {
@@ -78,7 +85,7 @@ __device__ __forceinline__ void decode_attention_body(const AttnParams &p, unsig
     const int n_prefix = p.n_prefix_tokens;
     const int n_workers = splits * WARPS;
     const int worker = x * WARPS + warp;
-    LaunchUnits lu = launch_units(p, h, n_local, false);
+    LaunchUnits lu = launch_units(p, h, n_local, false, fw);
     int units = lu.units_slots + lu.units_local;
     int total_my = units > worker ? (units - worker + n_workers - 1) / n_workers : 0;
 
@@ -101,9 +108,6 @@ __device__ __forceinline__ void decode_attention_body(const AttnParams &p, unsig
         }
     }
 
-    typename Math::State st;
-    Math::init(st, p, h, lane, rows);
-
     const uint64_t stream_policy = l2_policy_evict_first();   // the KV stream is read once per step
     bool dead = false;
 
@@ -113,7 +117,7 @@ __device__ __forceinline__ void decode_attention_body(const AttnParams &p, unsig
         griddep_launch_dependents();
         if (p.redo[h] != 0) {
             // it evicted beyond the front: this launch covers the whole head
-            lu = launch_units(p, h, n_local, true);
+            lu = launch_units(p, h, n_local, true, fw);
             units = lu.units_slots + lu.units_local;
             total_my = units > worker ? (units - worker + n_workers - 1) / n_workers : 0;
             base0 = plan_base(p, lu, worker, n_workers, lane, 0, total_my);

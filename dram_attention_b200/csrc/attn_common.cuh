@@ -116,8 +116,23 @@ struct LaunchUnits {
     int ups;              // units per slot page
 };
 
+// The words of the eviction queue's state a launch plans from: read together, early (see the kernel body).
+struct FrontWords {
+    int flip, nf0, nf1;
+};
+__device__ __forceinline__ FrontWords load_front(const AttnParams &p, int h) {
+    FrontWords f = {0, 0, 0};
+    if (p.phase != 0) {
+        f.nf0 = p.n_evictable[h];
+        f.nf1 = p.n_evictable[p.n_kv_heads + h];
+        f.flip = p.flip[h];
+    }
+    return f;
+}
+
 // `redo`: the LRU update had to evict beyond the front (second launch only).
-__device__ __forceinline__ LaunchUnits launch_units(const AttnParams &p, int h, int n_local, bool redo) {
+__device__ __forceinline__ LaunchUnits launch_units(const AttnParams &p, int h, int n_local, bool redo,
+                                                    const FrontWords &fw) {
     LaunchUnits lu;
     lu.order = nullptr;
     lu.order_off = 0;
@@ -126,12 +141,10 @@ __device__ __forceinline__ LaunchUnits launch_units(const AttnParams &p, int h, 
     if (p.phase == 0) {
         lu.units_slots = (p.n_prefix_tokens + kUnitTokens - 1) / kUnitTokens;
     } else {
-        // (the front sizes of both queue copies are read beside the flip word, not after it: one round trip less
-        // before the first copy of a launch can be issued)
-        const int nf0 = p.n_evictable[h], nf1 = p.n_evictable[p.n_kv_heads + h];
-        const int cur = p.flip[h] & 1;
+        // (the front sizes of both queue copies were read beside the flip word, not after it)
+        const int cur = fw.flip & 1;
         const int32_t *order = p.order + ((size_t)cur * p.n_kv_heads + h) * p.n_slots;
-        const int n_ev = min(max(cur ? nf1 : nf0, 0), p.n_slots);
+        const int n_ev = min(max(cur ? fw.nf1 : fw.nf0, 0), p.n_slots);
         if (p.phase == 1) {
             lu.units_slots = (p.n_slots - n_ev) * lu.ups;
             lu.order = order;
