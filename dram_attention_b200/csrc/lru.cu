@@ -393,8 +393,9 @@ lru_queue_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *d
                  const unsigned char *dram_pages, unsigned char *slots, unsigned long long page_bytes,
                  int inline_max, unsigned int stage_off, int32_t *status) {
     if (threadIdx.x == 0) trace_stamp(2, blockIdx.x, 0);
-    griddep_wait();   // the page list comes from the kernel before this one
-    if (threadIdx.x == 0) trace_stamp(2, blockIdx.x, 2);
+    // The CTA is on its SM while the kernel before it still runs (programmatic dependent launch).  All it
+    // needs from that kernel is the page list: its own tables, both copies of the queue, the pages of the
+    // queue's slots and the cleared work areas are ready when the list is.
     extern __shared__ __align__(16) int smem_i[];
     const int table = lru_table_size(list_len);
     int *tkey = smem_i;                  // [table] page id or -1
@@ -434,20 +435,7 @@ lru_queue_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *d
     }
     const int nf_a = n_front_io[h], nf_b = n_front_io[(size_t)gridDim.x + h];
     const int cur = split_flip[h] & 1;
-    int pg[LR], sl[LR];
-    int bad = 0;
-#pragma unroll
-    for (int r = 0; r < LR; ++r) {
-        const int i = r * kLruThreads + tid;
-        pg[r] = -1;
-        if (i < list_len) {
-            const int p = list[i];
-            if (p < 0 || p >= n_dram_pages) bad = 1; else pg[r] = p;
-        }
-    }
     const int step = step_counters[h] + 1;
-#pragma unroll
-    for (int r = 0; r < LR; ++r) sl[r] = pg[r] >= 0 ? d2s[pg[r]] : 0;
     int32_t *q_out = queue + ((size_t)(1 - cur) * gridDim.x + h) * n_slots;
     const int n_front = min(max(cur ? nf_b : nf_a, 0), n_slots);
     int qs[SR];
@@ -473,6 +461,22 @@ lru_queue_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *d
     }
     for (int x = tid; x < n_slots; x += kLruThreads) touched[x] = 0;
     if (tid == 0) sh_redo = 0;
+
+    griddep_wait();   // the page list comes from the kernel before this one
+    if (threadIdx.x == 0) trace_stamp(2, blockIdx.x, 2);
+    int pg[LR], sl[LR];
+    int bad = 0;
+#pragma unroll
+    for (int r = 0; r < LR; ++r) {
+        const int i = r * kLruThreads + tid;
+        pg[r] = -1;
+        if (i < list_len) {
+            const int p = list[i];
+            if (p < 0 || p >= n_dram_pages) bad = 1; else pg[r] = p;
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < LR; ++r) sl[r] = pg[r] >= 0 ? d2s[pg[r]] : 0;
     if (bad) atomicOr(status, DA_STATUS_BAD_PAGE_ID);
     __syncthreads();
     griddep_launch_dependents();   // the kernel after this one may move onto the SMs and wait there
