@@ -393,9 +393,14 @@ lru_queue_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *d
                  const unsigned char *dram_pages, unsigned char *slots, unsigned long long page_bytes,
                  int inline_max, unsigned int stage_off, int32_t *status) {
     if (threadIdx.x == 0) trace_stamp(2, blockIdx.x, 0);
-    // The CTA is on its SM while the kernel before it still runs (programmatic dependent launch).  All it
-    // needs from that kernel is the page list: its own tables, both copies of the queue, the pages of the
-    // queue's slots and the cleared work areas are ready when the list is.
+    // The CTA is on its SM while the kernel before it still runs (programmatic dependent launch).  When the
+    // caller vouches that that kernel is the selection (split_advance bit 1: it writes nothing but the page
+    // list, and it has itself waited for everything before it), all this kernel needs from it is the list:
+    // its own tables, both copies of the queue, the pages of the queue's slots and the cleared work areas are
+    // then ready when the list is.  Otherwise the kernel before it may still be writing any of those (another
+    // update, an attention launch flipping the queue) and the wait comes first.
+    const bool list_only = (split_advance & 2) != 0;
+    if (!list_only) griddep_wait();
     extern __shared__ __align__(16) int smem_i[];
     const int table = lru_table_size(list_len);
     int *tkey = smem_i;                  // [table] page id or -1
@@ -462,7 +467,7 @@ lru_queue_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *d
     for (int x = tid; x < n_slots; x += kLruThreads) touched[x] = 0;
     if (tid == 0) sh_redo = 0;
 
-    griddep_wait();   // the page list comes from the kernel before this one
+    if (list_only) griddep_wait();   // the page list comes from the kernel before this one
     if (threadIdx.x == 0) trace_stamp(2, blockIdx.x, 2);
     int pg[LR], sl[LR];
     int bad = 0;
@@ -618,7 +623,7 @@ lru_queue_kernel(const int32_t *__restrict__ page_list, int list_len, int32_t *d
         // running totals, for whoever wants to watch the cache (posted: the CTA does not wait for the old values)
         if (n_miss) atomicAdd(split_redo + gridDim.x + h, n_miss);
         if (sh_redo) atomicAdd(split_redo + 2 * gridDim.x + h, sh_redo);
-        if (split_advance) split_flip[h] = 1 - cur;
+        if (split_advance & 1) split_flip[h] = 1 - cur;
     }
     if (g_trace_buf != nullptr) {
         __syncthreads();

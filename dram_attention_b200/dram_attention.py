@@ -237,7 +237,7 @@ class DRAMAttention(torch.nn.Module):
                 # score -> select -> LRU update -> attention that also brings in the misses
                 lc = self.lru_cache
                 _, page_list = lc.top_k_selector.page_list_(xq, lc.top_k)
-                lc.update_tables_(page_list, inline_fetch=True)
+                lc.update_tables_(page_list, inline_fetch=True, after_selection=True)
                 self.attend_(xq, xk, xv, start_pos, out, fetch=True)
             else:
                 # score -> select -> LRU update -> fetch (no-ops for a fully resident prefix)
@@ -284,7 +284,7 @@ class DRAMAttention(torch.nn.Module):
             self._join.record(self._side)
         if early:
             page_list = sel.select_(1, rep, lc.top_k, sm_budget=budget)
-        lc.update_tables_(page_list, advance_split=False, inline_fetch=True)
+        lc.update_tables_(page_list, advance_split=False, inline_fetch=True, after_selection=True)
         # phase 2 needs the update, not phase 1: whichever of the two launches finishes last merges
         self.attend_(xq, xk, xv, start_pos, out, phase=2)
         main.wait_event(self._join)

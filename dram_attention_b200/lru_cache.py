@@ -188,7 +188,7 @@ class LRUCache(torch.nn.Module):
         return bufs
 
     def update_tables_(self, page_list: torch.Tensor, advance_split: bool = True,
-                       inline_fetch: bool = False) -> None:
+                       inline_fetch: bool = False, after_selection: bool = False) -> None:
         """Enqueue the LRU table update for an int32 page list (Hk, list_len): step
         counters, hit stamps, victim choice, both maps, the device-side miss list, and the
         eviction front for the following step (written into the copy of evict_order /
@@ -196,7 +196,10 @@ class LRUCache(torch.nn.Module):
         attention follows: its second launch makes the new front current when both are done;
         otherwise the update does it itself.  With `inline_fetch` the kernel also copies the
         pages of heads that miss only a few (at most `inline_fetch_max`) into their slots; the
-        others are marked in slot_source for the attention kernel that fetches on the fly."""
+        others are marked in slot_source for the attention kernel that fetches on the fly.
+        `after_selection`: the launch before this one in the stream is the selection kernel that wrote
+        `page_list` (the generate step's chain); the update then reads its tables while that launch still
+        runs.  Leave it False after anything else (another update, an attention launch)."""
         list_len = page_list.shape[1]
         miss_pages, miss_slots, n_miss = self._miss_buffers(list_len)
         _native.check(_native.lib().da_lru_update(
@@ -206,7 +209,7 @@ class LRUCache(torch.nn.Module):
             self.num_kv_heads, miss_pages.data_ptr(), miss_slots.data_ptr(), n_miss.data_ptr(),
             self.slot_source.data_ptr(), self.evict_order.data_ptr(), self.n_evictable.data_ptr(),
             self.evict_flip.data_ptr(), self.evict_redo.data_ptr(), int(self.split_cap),
-            1 if advance_split else 0,
+            (1 if advance_split else 0) | (2 if after_selection else 0),
             self.dram_kv_cache.data_ptr() if inline_fetch else 0,
             self.hbm_kv_cache.data_ptr() if inline_fetch else 0,
             self.dram_kv_cache.shape[2] * self.dram_kv_cache.element_size(),

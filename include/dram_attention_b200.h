@@ -181,8 +181,13 @@ DA_API int da_topk_pages_wide(const float *scores, int32_t *page_list,
  *               - writes the other copy: the untouched slots in their old order, then the slots
  *                 this call touched in slot order, with front_count = split_cap (n_slots when
  *                 split_cap <= 0);
- *               - with split_advance != 0 makes that copy current itself (callers that run no
- *                 phased attention after the update); otherwise phase 2 of the attention does.
+ *               - with bit 0 of split_advance set makes that copy current itself (callers that run
+ *                 no phased attention after the update); otherwise phase 2 of the attention does.
+ *             Bit 1 of split_advance is a promise about the launch before this one in the stream: it
+ *             is da_topk_pages (or anything else that writes none of this call's tables and has
+ *             itself waited for its predecessors).  The kernel is launched as a programmatic
+ *             dependent; with the promise it reads its tables and both queue copies while that
+ *             launch still runs and waits only for the page list, without it it waits first.
  *             Before the first call: both copies = the slots sorted by (access_time, slot) (the
  *             identity when every time is zero), split_flip = 0, front_count at most n_slots.
  *             Without a queue the victims are found by a radix select on access_time.
