@@ -84,7 +84,9 @@ __device__ __forceinline__ void decode_attention_body(const AttnParams &p, unsig
     const int n_local = t0 + p.s_total;
     const int n_prefix = p.n_prefix_tokens;
     const int n_workers = splits * WARPS;
-    const int worker = x * WARPS + warp;
+    // warp-major worker ids: the workers that get one unit more than the others are spread over all CTAs of
+    // the head (one or two per SM), not packed into the first CTAs (twelve on the same SM)
+    const int worker = warp * splits + x;
     LaunchUnits lu = launch_units(p, h, n_local, false, fw);
     int units = lu.units_slots + lu.units_local;
     int total_my = units > worker ? (units - worker + n_workers - 1) / n_workers : 0;
