@@ -434,6 +434,63 @@ def test_multi_token_generate_against_oracle(da, dtype, counts):
     m.check_status()
 
 
+def test_long_run_of_captured_steps_agrees_with_the_plain_layout(da):
+    """150 steps with a query re-draw every 13 (slot churn, overrun eviction fronts, in-kernel page copies and
+    pages marked for the attention in the same run): the default two-launch layout, replayed as CUDA graphs of
+    10 steps, against the gather-copy + single-launch layout run eagerly.  Page lists are the same up to near
+    ties, so the twin is fed the first operator's lists; tables and slot payloads bit-exact after every graph,
+    outputs within the suite's tolerance."""
+    dtype = torch.bfloat16
+    n, k_graph = 150, 10
+    w = llama_layer_workload(seed=11, steps=n, dram_tokens=16384, n_kv_heads=2, lru=4096, local=512,
+                             top_k=512, needles=4, redraw_every=13, dtype=dtype)
+    a = da.DRAMAttention(device=DEV, dtype=dtype, **w.ctor_kwargs())
+    b = da.DRAMAttention(device=DEV, dtype=dtype, **w.ctor_kwargs())
+    b.fused_fetch, b.overlap = False, False
+    for m in (a, b):
+        m.init_cache(w.k.to(DEV), w.v.to(DEV))
+    S = w.k.shape[1]
+    dq, dk, dv = w.xq.to(DEV), w.xk.to(DEV), w.xv.to(DEV)
+    a(dq[0], dk[0], dv[0], start_pos=S, stage="generate")        # workspaces, side stream
+    b(dq[0], dk[0], dv[0], start_pos=S, stage="generate")
+    rep = w.n_q_heads // w.n_kv_heads
+    for first in range(1, n - k_graph + 1, k_graph):
+        lists = []
+        orig = a.lru_cache.update_tables_
+
+        def spy(page_list, **kw):
+            lists.append(page_list.clone())
+            return orig(page_list, **kw)
+
+        a.lru_cache.update_tables_ = spy
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            outs = [a(dq[i], dk[i], dv[i], start_pos=S + i, stage="generate") for i in range(first, first + k_graph)]
+        a.lru_cache.update_tables_ = orig
+        g.replay()
+        torch.cuda.synchronize()
+        for j, i in enumerate(range(first, first + k_graph)):
+            # the twin takes this step's list instead of selecting itself (near ties may differ)
+            lc = b.lru_cache
+            lc.update_tables_(lists[j])
+            lc.fetch_(lists[j].shape[1])
+            ob = torch.empty_like(dq[i])
+            b.attend_(dq[i], dk[i], dv[i], S + i, ob)
+            assert_out_close(outs[j][0, 0].float().cpu(), ob[0, 0].float().cpu(), dtype, i)
+        torch.cuda.synchronize()
+        la, lb = a.lru_cache, b.lru_cache
+        assert torch.equal(la.hbm_page_to_dram_page_mapping, lb.hbm_page_to_dram_page_mapping), first
+        assert torch.equal(la.dram_page_to_hbm_page_mapping, lb.dram_page_to_hbm_page_mapping), first
+        assert torch.equal(la.hbm_kv_cache, lb.hbm_kv_cache), first
+        del g, outs
+    t = S + first + k_graph - a.dram_kv_cache_size          # tokens in the local window after the last step run
+    assert torch.equal(a.cache_k[0, :t], b.cache_k[0, :t]) and torch.equal(a.cache_v[0, :t], b.cache_v[0, :t])
+    assert float(a.lru_cache.evict_redo[2].sum()) > 0       # the run did overrun fronts
+    for m in (a, b):
+        m.check_status()
+
+
 def test_rotary_embedding_inside_the_call(da, fused):
     """`freqs_cis=` makes the operator apply the caller's rotary embedding itself: the outputs,
     the appended keys and the tables equal those of a twin that is handed the rotated tensors (the
