@@ -32,7 +32,8 @@ Extras in the same line (skipped with --no-extras): rope_in_call (the step with 
 rotary embedding done by the operator), fetch_report (miss fetch against the host link),
 scorer_sweep (config 3), prefill, and the two other multi-GPU configurations:
 cfg4     8 independent 64K-token sequences, 128 steps with a query re-draw every 32 steps,
-         sequences dealt round-robin to the N GPUs (no collective).
+         sequences dealt round-robin to the N GPUs (no collective) and, on a GPU, to up to four
+         streams (they are independent); the one-stream figure is in the object as well.
 cfg5     a 32-layer stack at a 1,048,576-token prefix per layer, KV heads sharded N-way with the
          per-head outputs all-gathered by a peer-memory kernel over NVLink; the whole token step
          (all layers) in one CUDA graph.
@@ -101,6 +102,10 @@ def parse_args():
     ap.add_argument("--cfg4-sequences", type=int, default=8)
     ap.add_argument("--cfg4-steps", type=int, default=128)
     ap.add_argument("--cfg4-redraw", type=int, default=32)
+    ap.add_argument("--cfg4-streams", type=int, default=4,
+                    help="the sequences of a GPU are dealt to this many streams (they are independent: one "
+                         "sequence's selection chain then overlaps another's attention); the one-stream figure is "
+                         "measured as well, on the steps that follow")
     ap.add_argument("--cfg5-layers", type=int, default=32)
     ap.add_argument("--cfg5-steps", type=int, default=32)
     ap.add_argument("--cfg5-prefixes", type=int, default=4,
@@ -972,7 +977,8 @@ def bench_cfg4(args, ctx):
     redraw = args.cfg4_redraw
     mine = list(range(rank, n_seq, world))
     hk, rep, D, page, lru, local, top_k, dram = 8, 4, 128, 16, 32768, 4096, 4096, 65536
-    steps = W + K4
+    n_streams = max(1, min(args.cfg4_streams, max(len(range(r, n_seq, world)) for r in range(world))))
+    steps = W + (2 * K4 if n_streams > 1 else K4)
     ops, inputs = [], []
     for sidx in mine:
         k, v, xq, xk, xv, _u, _ch = device_layer_inputs(dev, 1000 + sidx, steps, dram, n_kv_heads=hk, rep=rep,
@@ -990,28 +996,58 @@ def bench_cfg4(args, ctx):
     torch.cuda.synchronize()
     miss0 = sum(total_misses(op.lru_cache) for op in ops)
     redo0 = sum(op.lru_cache.evict_redo[2].sum().item() for op in ops)
+    streams = [torch.cuda.Stream(device=dev) for _ in range(n_streams)] if n_streams > 1 else []
 
-    def capture():
+    def capture(first, last, use_streams):
+        """Steps first .. last-1 of every sequence of this GPU, step by step; with streams, sequence j's steps go
+        to stream j % n (the sequences are independent of each other)."""
         outs = []
-        for i in range(W, W + K4):
-            for op, (xq, xk, xv) in zip(ops, inputs):
-                outs.append(op(xq[i], xk[i], xv[i], start_pos=S + i, stage="generate"))
+        if use_streams and streams:
+            main = torch.cuda.current_stream()
+            fork = torch.cuda.Event()
+            fork.record(main)
+            for st in streams:
+                st.wait_event(fork)
+        for i in range(first, last):
+            for j, (op, (xq, xk, xv)) in enumerate(zip(ops, inputs)):
+                if use_streams and streams:
+                    with torch.cuda.stream(streams[j % n_streams]):
+                        outs.append(op(xq[i], xk[i], xv[i], start_pos=S + i, stage="generate"))
+                else:
+                    outs.append(op(xq[i], xk[i], xv[i], start_pos=S + i, stage="generate"))
+        if use_streams and streams:
+            for st in streams:
+                done = torch.cuda.Event()
+                done.record(st)
+                main.wait_event(done)
         return outs
 
-    if mine:
-        ms, outs, up, _w, _g = time_graph(ctx, capture)
-        assert all(bool(torch.isfinite(o.float()).all()) for o in outs[-len(ops):])
-        del outs, _g
-    else:   # more GPUs than sequences: this rank only takes part in the barriers
-        ctx.barrier()
-        ctx.barrier()
-        ms = 0.0
-    (ms,) = ctx.max_over_ranks([ms])
+    # the configuration's 128 steps over the streams; the same number of steps after them (as many re-draws)
+    # on one stream, for comparison
+    order = [(f"sequences_over_{n_streams}_streams" if n_streams > 1 else "sequences_on_one_stream", True, W, W + K4)]
+    if n_streams > 1:
+        order.append(("sequences_on_one_stream", False, W + K4, W + 2 * K4))
+    by_schedule = {}
+    misses_first = redos_first = 0.0
+    for name, use_streams, a, b in order:
+        if mine:
+            ms, outs, up, _w, _g = time_graph(ctx, lambda: capture(a, b, use_streams))
+            assert all(bool(torch.isfinite(o.float()).all()) for o in outs[-len(ops):])
+            del outs, _g
+        else:   # more GPUs than sequences: this rank only takes part in the barriers
+            ctx.barrier()
+            ctx.barrier()
+            ms = 0.0
+        (ms,) = ctx.max_over_ranks([ms])
+        by_schedule[name] = ms
+        if name == order[0][0]:
+            misses_first = sum(total_misses(op.lru_cache) for op in ops) - miss0
+            redos_first = sum(op.lru_cache.evict_redo[2].sum().item() for op in ops) - redo0
+    best_name = order[0][0]          # the headline is the configuration's own 128 steps
+    ms = by_schedule[best_name]
     for op in ops:
         op.check_status()
-    misses = sum(total_misses(op.lru_cache) for op in ops) - miss0
-    redos = sum(op.lru_cache.evict_redo[2].sum().item() for op in ops) - redo0
-    misses, redos = ctx.sum_over_ranks([misses, redos])
+    misses, redos = ctx.sum_over_ranks([misses_first, redos_first])
     t_local = local - page + W + K4 // 2
     b_score, b_attn = layer_bytes(hk, rep, D, dram // page, lru // page, page, t_local)
     per_gpu_steps = max(len(range(r, n_seq, world)) for r in range(world)) * K4
@@ -1026,14 +1062,17 @@ def bench_cfg4(args, ctx):
                     f"a re-draw from N(0,1) every {redraw} steps (steps {redraw_steps} of the timed region re-draw)",
         "metric": "decode tok/s, all sequences", "value": n_seq * K4 / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
         "scaling": "strong (fixed batch)", "parallelism": f"sequences dealt round-robin to {world} GPU(s), no collective",
-        "ms_total": ms, "us_per_sequence_step": us_per_seq_step,
+        "ms_total": ms, "us_per_sequence_step": us_per_seq_step, "schedule": best_name,
+        "ms_total_by_schedule": by_schedule,
         "roofline_step": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
                           "frac_of_nominal_8tbs": ach / NOMINAL_HBM_GBS, "peak_kind": kind + " HBM copy bandwidth",
                           "algorithmic_bytes_per_sequence_step": b_score + b_attn,
                           "note": "includes the re-draw steps, which are bound by the host link, not by HBM"},
         "misses_per_sequence_step": misses / (n_seq * K4), "miss_bytes_total": misses * page_bytes,
         "steps_that_took_the_redo_path": redos,
-        "timed_region": "one CUDA graph per rank holding every step of its sequences (interleaved), uploaded, one replay",
+        "timed_region": "one CUDA graph per rank holding every step of its sequences (step by step, the sequences dealt "
+                        "to the streams of the schedule), uploaded, one replay; the one-stream schedule is timed on the "
+                        "128 steps that follow (as many re-draws)",
         "data": "synthetic, generated on the device",
     }
 
